@@ -1,0 +1,305 @@
+/*
+ * rg_b200.h — C ABI of the B200 (sm_100a) kernel library for the RefactorGraph decoder hot path.
+ *
+ * The reference has no C ABI: its boundary is C++ virtual dispatch
+ * (InfoCollector::filter -> Kernel::lower(Resources&) -> RoutineWorkspace,
+ *  src/04kernel/include/kernel/collector.h:10-20, kernel.h:12-23) and a routine of type
+ *   void(Resources&, void* workspace, void const* const* inputs, void* const* outputs)
+ * (src/03runtime/include/runtime/stream.h:10).  Every entry point below keeps that calling shape:
+ * a POD parameter struct that is filled once at lower() time from the tensor shapes, then
+ *   int rg_b200_X(const params*, void* workspace, const void* const* inputs, void* const* outputs, void* stream)
+ * with raw DEVICE pointers in operator-input order, and
+ *   size_t rg_b200_X_workspace(const params*)
+ * for the byte count a kernel returns in RoutineWorkspace.  No torch types, no exceptions, no exit():
+ * the return value is an rg_status and the C++ adapters turn non-zero into RUNTIME_ERROR.
+ *
+ * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream, which is what the
+ * reference launches on).  All launches are asynchronous; nothing here allocates device memory
+ * except rg_b200_comm_create.
+ */
+#ifndef RG_B200_H
+#define RG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes. */
+typedef enum rg_status {
+    RG_OK = 0,
+    RG_ERR_NULL = 1,        /* a required pointer is NULL */
+    RG_ERR_SHAPE = 2,       /* shape outside what the kernel supports */
+    RG_ERR_DTYPE = 3,       /* data type not supported by this kernel */
+    RG_ERR_ALIGN = 4,       /* pointer or leading dimension not aligned as required */
+    RG_ERR_CUDA = 5,        /* a CUDA runtime call or launch failed */
+    RG_ERR_TIMEOUT = 6,     /* a bounded device-side or rendezvous wait ran out */
+    RG_ERR_UNSUPPORTED = 7, /* valid request that this build has no kernel for */
+    RG_ERR_LIMIT = 8        /* size beyond a stated fixed maximum */
+} rg_status;
+
+/* Data type codes = the reference's DataType enum (src/00common/include/common/data_type.h:14-35). */
+typedef enum rg_dtype {
+    RG_F32 = 1, RG_U8 = 2, RG_I8 = 3, RG_I32 = 6, RG_I64 = 7, RG_BOOL = 9,
+    RG_FP16 = 10, RG_F64 = 11, RG_U32 = 12, RG_BF16 = 16
+} rg_dtype;
+
+const char *rg_b200_status_string(int status);
+/* Library ABI version (bumped on any struct change). */
+int rg_b200_version(void);
+/* Number of kernels this library has launched in the calling process since load (all entry points). */
+uint64_t rg_b200_launch_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * RmsNormalization.  Replaces RmsNormalizationCuda
+ * (src/04kernel/src/kernels/rms_normalization/cuda_kernel.cc:24-131; CPU semantics cpu_kernel.cc:41-66):
+ *   y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * w[:]
+ * inputs {x[rows,dim], w[dim]}, outputs {y[rows,dim]}.  Sum of squares is accumulated in fp32.
+ * With add_residual != 0: inputs {x, w, r[rows,dim]}, outputs {y, s}; s = x + r (stored in dtype) and
+ * the norm is taken of s — the residual-add + norm pair of a decoder layer in one pass. */
+typedef struct rg_rms_norm_params {
+    int32_t dtype; /* RG_F32, RG_FP16, RG_BF16 */
+    uint32_t rows, dim;
+    float epsilon;
+    int32_t add_residual;
+} rg_rms_norm_params;
+size_t rg_b200_rms_norm_workspace(const rg_rms_norm_params *);
+int rg_b200_rms_norm(const rg_rms_norm_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Softmax over the middle axis of [pre, mid, post].  Replaces SoftmaxCudnn / SoftmaxCuda
+ * (src/04kernel/src/collectors/softmax.cc:22-29, src/04kernel/src/kernels/softmax/cuda_kernel.cu:21-105;
+ * SoftmaxInfo src/04kernel/src/attributes/softmax_info.cc:6-13).  A true softmax (what the reference's
+ * CUDA and cuDNN kernels compute), max/sum in fp32.  inputs {x}, outputs {y}. */
+typedef struct rg_softmax_params {
+    int32_t dtype; /* RG_F32, RG_FP16, RG_BF16 */
+    uint32_t pre, mid, post;
+} rg_softmax_params;
+size_t rg_b200_softmax_workspace(const rg_softmax_params *);
+int rg_b200_softmax(const rg_softmax_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * TopK (no reference counterpart: the reference has no TopK operator or kernel).
+ * Per row of x[rows,n]: the k largest values in descending order, ties broken by the lower index,
+ * NaN treated as smaller than every number.  inputs {x}, outputs {values[rows,k] (dtype of x, or fp32
+ * probabilities when softmax != 0), indices[rows,k] int64}.  With softmax != 0 the values are
+ * softmax(x)[idx] over the WHOLE row (max and sum of exp over all n, fp32).  k <= 64. */
+typedef struct rg_topk_params {
+    int32_t dtype;
+    uint32_t rows, n, k;
+    int32_t softmax;
+} rg_topk_params;
+size_t rg_b200_topk_workspace(const rg_topk_params *);
+int rg_b200_topk(const rg_topk_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Top-k sampling (no reference counterpart).  Draws one token per row from softmax(x/temperature)
+ * restricted to the row's top-k set.  The uniform number for (seed, step, row) is a Philox-4x32-10
+ * draw with key (seed lo, seed hi) and counter (row, 0, step lo, step hi); the token is the first entry
+ * of the descending top-k list whose cumulative probability exceeds u.
+ * inputs {x[rows,n], step (device uint64[1])}, outputs {token[rows] int64}. */
+typedef struct rg_topk_sample_params {
+    int32_t dtype;
+    uint32_t rows, n, k;
+    float temperature;
+    uint64_t seed;
+} rg_topk_sample_params;
+size_t rg_b200_topk_sample_workspace(const rg_topk_sample_params *);
+int rg_b200_topk_sample(const rg_topk_sample_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Gather along one axis (embedding lookup).  Replaces GatherCuda
+ * (src/04kernel/src/kernels/gather/cuda_kernel.cc:32-56, src/04kernel/cuda/src/gather.cu:7-29) with
+ * GatherInfo's fields (src/04kernel/src/attributes/gather_info.cc:19-27): out[p, i, :] = data[p, idx[i], :],
+ * negative indices wrap by mid_in; byte-exact.  inputs {data, indices}, outputs {out}. */
+typedef struct rg_gather_params {
+    uint32_t prefix, mid_in, mid_out;
+    uint64_t postfix_bytes;
+    int32_t idx_dtype; /* RG_I32 or RG_I64 */
+} rg_gather_params;
+size_t rg_b200_gather_workspace(const rg_gather_params *);
+int rg_b200_gather(const rg_gather_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Element-wise binary with multidirectional broadcast, rank <= 4.  Replaces BinaryCudnn / BinaryCuda
+ * (src/04kernel/src/kernels/simple_binary/cuda_kernel.cc:42-136).  op uses the reference's
+ * SimpleBinaryType values (src/04kernel/include/kernel/collectors/simple_binary.h:8-19): 0 Add, 1 Sub,
+ * 2 Mul, 3 Div.  Strides are in elements, 0 on a broadcast axis.  inputs {a, b}, outputs {y}. */
+typedef struct rg_binary_params {
+    int32_t op, dtype;
+    uint32_t shape[4];
+    uint32_t a_stride[4], b_stride[4];
+} rg_binary_params;
+size_t rg_b200_binary_workspace(const rg_binary_params *);
+int rg_b200_binary(const rg_binary_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Element-wise unary.  Replaces ActivationCudnn / SimpleUnaryCuda
+ * (src/04kernel/src/kernels/simple_unary/cuda_kernel.cc:96-175).  op uses SimpleUnaryType values
+ * (src/04kernel/include/kernel/collectors/simple_unary.h:8-30): 12 Tanh, 13 Relu, 14 Sqrt, 15 Sigmoid,
+ * 17 Neg, 20 Exp; 100 = SiLU (x*sigmoid(x), the fused pair the decoder uses).  inputs {x}, outputs {y}. */
+typedef struct rg_unary_params {
+    int32_t op, dtype;
+    uint64_t n;
+} rg_unary_params;
+size_t rg_b200_unary_workspace(const rg_unary_params *);
+int rg_b200_unary(const rg_unary_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Where (select): y = cond ? a : b with rank <= 4 broadcast.  Replaces WhereCuda
+ * (src/04kernel/cuda/src/where.cu:7-36).  inputs {cond (bool/u8), a, b}, outputs {y}. */
+typedef struct rg_where_params {
+    int32_t dtype;
+    uint32_t shape[4];
+    uint32_t c_stride[4], a_stride[4], b_stride[4];
+} rg_where_params;
+size_t rg_b200_where_workspace(const rg_where_params *);
+int rg_b200_where(const rg_where_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Transpose (permuted copy), rank <= 4, byte-exact.  Replaces TransposeCuda
+ * (src/04kernel/cuda/src/transpose.cu:7-28).  out has shape[i] = in_shape[perm[i]].  inputs {x}, outputs {y}. */
+typedef struct rg_transpose_params {
+    uint32_t elem_bytes; /* 1, 2, 4 or 8 */
+    uint32_t rank;
+    uint32_t in_shape[4];
+    uint32_t perm[4];
+} rg_transpose_params;
+size_t rg_b200_transpose_workspace(const rg_transpose_params *);
+int rg_b200_transpose(const rg_transpose_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * RotaryPositionEmbedding (no reference counterpart).  x[tokens, heads, head_dim], rotate-half pairing
+ * (i, i + head_dim/2), angle = pos * theta^(-2i/head_dim) evaluated in fp32; pos = positions[token]
+ * (device int64[tokens]).  inputs {x, positions}, outputs {y}. */
+typedef struct rg_rope_params {
+    int32_t dtype;
+    uint32_t tokens, heads, head_dim;
+    float theta; /* 10000 */
+} rg_rope_params;
+size_t rg_b200_rope_workspace(const rg_rope_params *);
+int rg_b200_rope(const rg_rope_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * MatMul: Y[b] = alpha * op(A[b]) * op(B[b]) + beta * C (C broadcast to [m,n]).  Replaces MatMulCublas
+ * (src/04kernel/src/kernels/mat_mul/cublas_kernel.cu:9-100) with MatMulInfo's fields
+ * (src/04kernel/src/attributes/mat_mul_info.cc:27-42).  Row-major.  Batch strides are in elements and are 0
+ * for an operand that is broadcast over the batch (the reference's Broadcaster over the leading dims is
+ * flattened by the adapter into `batch` strided launches).  fp32 accumulation for every type.
+ * inputs {A, B, C or NULL}, outputs {Y}.
+ * Kernel selection (all hand-written, no vendor GEMM):
+ *   - fp16/bf16, transA=0, transB=1, m <= 4: HBM-streaming GEMV (bulk-copy smem ring),
+ *   - fp16/bf16, transA=0, transB=1, aligned, m*n large: tcgen05/TMEM tensor-core GEMM fed by TMA,
+ *   - anything else: shared-memory tiled SIMT GEMM. */
+typedef struct rg_mat_mul_params {
+    int32_t dtype; /* RG_F32, RG_FP16, RG_BF16 */
+    uint32_t m, n, k;
+    int32_t trans_a, trans_b;
+    float alpha, beta;
+    uint32_t batch;
+    uint64_t stride_a, stride_b, stride_y; /* per-batch element strides (0 = broadcast) */
+    int32_t has_bias;
+    uint32_t bias_row_stride, bias_col_stride; /* element strides of C over (m, n); 0 = broadcast */
+    uint64_t stride_c;
+    int32_t force_kernel; /* 0 auto, 1 SIMT tile, 2 streaming GEMV, 3 tcgen05 */
+} rg_mat_mul_params;
+size_t rg_b200_mat_mul_workspace(const rg_mat_mul_params *);
+int rg_b200_mat_mul(const rg_mat_mul_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * KV-cache addressing shared by the fused linear layer and attention.
+ * Contiguous (the reference Attention operator's cache edge, src/08-01llm/src/operators/attention.cc:53-66):
+ *   cache[b, kv_head, t, d], t < max_seq.
+ * Paged (block_table != NULL at call time): cache[block, kv_head, t % page, d] with
+ *   block = block_table[b * max_blocks_per_seq + t / page]. */
+typedef struct rg_kv_layout {
+    uint32_t n_kv_heads, head_dim;
+    uint32_t max_seq;            /* contiguous: tokens per (b, head) */
+    uint32_t page_size;          /* paged: tokens per block (16) ; 0 = contiguous */
+    uint32_t max_blocks_per_seq; /* paged: row length of the block table */
+} rg_kv_layout;
+
+/* Fused decode linear layer  Y = epilogue( prologue(X) * W^T ),  W[n,k] row-major (the reference MatMul with
+ * transB = 1), X[m,k], m <= 4.  One launch replaces RmsNormalization + MatMul + (Add | Sigmoid,Mul,Mul |
+ * RoPE + cache append) of the reference graph.
+ *   prologue: 0 none; 1 RMSNorm with weight g[k] and epsilon (fp32 statistics).
+ *   epilogue: 0 none                      outputs {Y[m,n]}
+ *             1 residual add              inputs + {R[m,n]}; Y = R + X*W^T
+ *             2 SiLU gate                 W = [gate rows 0..n/2) ; up rows n/2..n); Y[m,n/2] = silu(g)*u
+ *             3 QKV split + RoPE + append W = [q heads | k heads | v heads]; q -> Y[m, n_heads*head_dim] rotated,
+ *                                         k rotated and v stored into the caches at positions[m]
+ * inputs  {X, W, g or NULL, R or NULL, positions (int64[m]) or NULL, block_table (int32) or NULL}
+ * outputs {Y, k_cache or NULL, v_cache or NULL}. */
+typedef struct rg_linear_params {
+    int32_t dtype; /* RG_FP16, RG_BF16 */
+    uint32_t m, n, k;
+    int32_t prologue, epilogue;
+    float epsilon;
+    uint32_t n_heads; /* epilogue 3: query heads; n = (n_heads + 2*kv.n_kv_heads) * kv.head_dim */
+    float theta;
+    rg_kv_layout kv;
+} rg_linear_params;
+size_t rg_b200_linear_workspace(const rg_linear_params *);
+int rg_b200_linear(const rg_linear_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Attention.  Completes AttentionCuda, which the reference declares without a definition
+ * (src/04kernel/src/kernels/attention/cuda_kernel.hh:10-25); semantics follow the operator spec
+ * src/08-01llm/README.md:29-63 and shape rules src/08-01llm/src/operators/attention.cc:37-128:
+ * causal multi-head self-attention, q head h uses kv head h / (n_heads / n_kv_heads),
+ * scores = q.k / sqrt(head_dim), query row i (absolute position past + i) sees keys j <= past + i,
+ * softmax and accumulation in fp32.
+ *
+ * rg_b200_attention (reference tensor layout):
+ *   inputs {q[N,n_heads,S,D], k[N,n_kv,S,D], v[N,n_kv,S,D], past_seq_len (device int64[1]) or NULL,
+ *           k_cache[N,n_kv,max_seq,D] or NULL, v_cache or NULL}
+ *   outputs {o[N,n_heads,S,D], k_cache_out or NULL, v_cache_out or NULL}
+ * With caches: k, v are first written at [past, past+S) of the cache (in place when k_cache_out == k_cache,
+ * else the whole live prefix is copied), then attention runs over [0, past+S). */
+typedef struct rg_attention_params {
+    int32_t dtype;
+    uint32_t batch, n_heads, n_kv_heads, seq_len, head_dim, max_seq;
+    int32_t has_cache;
+} rg_attention_params;
+size_t rg_b200_attention_workspace(const rg_attention_params *);
+int rg_b200_attention(const rg_attention_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Split-K flash-decoding over a (paged or contiguous) KV cache, one new token per sequence.
+ *   inputs {q[batch, n_heads, D], k_cache, v_cache, seq_lens (device int64[batch]; keys [0, len) are attended,
+ *           the new token's k/v already appended), block_table (int32) or NULL}
+ *   outputs {o[batch, n_heads, D]}
+ * Workspace holds the per-split partial (max, sum, acc) records and one arrival counter per (sequence, head);
+ * the counters must be zero on first use (rg_b200_attn_decode_workspace bytes, zero-filled once) and are
+ * left zero by every call. */
+typedef struct rg_attn_decode_params {
+    int32_t dtype;
+    uint32_t batch, n_heads;
+    uint32_t max_len; /* upper bound of seq_lens, sizes the split count */
+    rg_kv_layout kv;
+} rg_attn_decode_params;
+size_t rg_b200_attn_decode_workspace(const rg_attn_decode_params *);
+int rg_b200_attn_decode(const rg_attn_decode_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * AllReduce across the GPUs of one box.  Replaces AllReduceNccl + NcclCommunicator
+ * (src/04kernel/src/kernels/all_reduce/nccl_kernel.cu:9-19, src/04kernel/src/utilities/cuda/nccl_communicator.cu:11-44).
+ * One process per GPU.  rg_b200_comm_create allocates this rank's symmetric buffer and returns an opaque
+ * 64-byte IPC handle; the caller exchanges handles out of band (any host transport) and calls
+ * rg_b200_comm_connect with all ranks' handles.  The reduction is a one-shot pull over NVLink peer memory
+ * with plain loads, summed in fp32 in rank order (bit-identical on every rank).  Device-side waits on peer
+ * flags are bounded; on expiry the status word is set and the call that observes it returns RG_ERR_TIMEOUT.
+ * op uses AllReduceType (src/04kernel/include/kernel/attributes/communication.h:5-11): 0 Sum, 1 Avg, 2 Min, 3 Max, 4 Prod.
+ * inputs {x}, outputs {y}; bytes <= the capacity given at create. */
+typedef struct rg_comm rg_comm;
+int rg_b200_comm_create(int world, int rank, size_t capacity_bytes, rg_comm **out, void *handle64);
+int rg_b200_comm_connect(rg_comm *, const void *all_handles /* world * 64 bytes */);
+int rg_b200_comm_status(rg_comm *); /* RG_OK or RG_ERR_TIMEOUT seen by a kernel; synchronises the stream last used */
+int rg_b200_comm_destroy(rg_comm *);
+typedef struct rg_all_reduce_params {
+    int32_t dtype, op;
+    uint64_t count;
+} rg_all_reduce_params;
+int rg_b200_all_reduce(rg_comm *, const rg_all_reduce_params *, const void *const *in, void *const *out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RG_B200_H */

@@ -1,0 +1,164 @@
+"""ctypes view of the C ABI declared in include/rg_b200.h (struct layouts mirror the header one to one).
+
+The library must be present: there is no CPU or eager fallback.  `load()` raises if librg_b200.so is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librg_b200.so")
+
+# rg_status
+OK, ERR_NULL, ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_LIMIT = range(9)
+# rg_dtype (= the reference's DataType codes)
+F32, U8, I8, I32, I64, BOOL, FP16, F64, U32, BF16 = 1, 2, 3, 6, 7, 9, 10, 11, 12, 16
+
+
+class RmsNormParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("rows", C.c_uint32), ("dim", C.c_uint32), ("epsilon", C.c_float),
+                ("add_residual", C.c_int32)]
+
+
+class SoftmaxParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("pre", C.c_uint32), ("mid", C.c_uint32), ("post", C.c_uint32)]
+
+
+class TopkParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("rows", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
+                ("softmax", C.c_int32)]
+
+
+class TopkSampleParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("rows", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
+                ("temperature", C.c_float), ("seed", C.c_uint64)]
+
+
+class GatherParams(C.Structure):
+    _fields_ = [("prefix", C.c_uint32), ("mid_in", C.c_uint32), ("mid_out", C.c_uint32),
+                ("postfix_bytes", C.c_uint64), ("idx_dtype", C.c_int32)]
+
+
+class BinaryParams(C.Structure):
+    _fields_ = [("op", C.c_int32), ("dtype", C.c_int32), ("shape", C.c_uint32 * 4),
+                ("a_stride", C.c_uint32 * 4), ("b_stride", C.c_uint32 * 4)]
+
+
+class UnaryParams(C.Structure):
+    _fields_ = [("op", C.c_int32), ("dtype", C.c_int32), ("n", C.c_uint64)]
+
+
+class WhereParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("shape", C.c_uint32 * 4), ("c_stride", C.c_uint32 * 4),
+                ("a_stride", C.c_uint32 * 4), ("b_stride", C.c_uint32 * 4)]
+
+
+class TransposeParams(C.Structure):
+    _fields_ = [("elem_bytes", C.c_uint32), ("rank", C.c_uint32), ("in_shape", C.c_uint32 * 4),
+                ("perm", C.c_uint32 * 4)]
+
+
+class RopeParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("tokens", C.c_uint32), ("heads", C.c_uint32), ("head_dim", C.c_uint32),
+                ("theta", C.c_float)]
+
+
+class MatMulParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
+                ("trans_a", C.c_int32), ("trans_b", C.c_int32), ("alpha", C.c_float), ("beta", C.c_float),
+                ("batch", C.c_uint32), ("stride_a", C.c_uint64), ("stride_b", C.c_uint64), ("stride_y", C.c_uint64),
+                ("has_bias", C.c_int32), ("bias_row_stride", C.c_uint32), ("bias_col_stride", C.c_uint32),
+                ("stride_c", C.c_uint64), ("force_kernel", C.c_int32)]
+
+
+class KvLayout(C.Structure):
+    _fields_ = [("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("max_seq", C.c_uint32),
+                ("page_size", C.c_uint32), ("max_blocks_per_seq", C.c_uint32)]
+
+
+class LinearParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
+                ("prologue", C.c_int32), ("epilogue", C.c_int32), ("epsilon", C.c_float), ("n_heads", C.c_uint32),
+                ("theta", C.c_float), ("kv", KvLayout)]
+
+
+class AttentionParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint32), ("n_heads", C.c_uint32), ("n_kv_heads", C.c_uint32),
+                ("seq_len", C.c_uint32), ("head_dim", C.c_uint32), ("max_seq", C.c_uint32), ("has_cache", C.c_int32)]
+
+
+class AttnDecodeParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint32), ("n_heads", C.c_uint32), ("max_len", C.c_uint32),
+                ("kv", KvLayout)]
+
+
+class AllReduceParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("op", C.c_int32), ("count", C.c_uint64)]
+
+
+# name -> params struct, for every op with the (params, ws, in, out, stream) calling shape
+OPS = {
+    "rms_norm": RmsNormParams, "softmax": SoftmaxParams, "topk": TopkParams, "topk_sample": TopkSampleParams,
+    "gather": GatherParams, "binary": BinaryParams, "unary": UnaryParams, "where": WhereParams,
+    "transpose": TransposeParams, "rope": RopeParams, "mat_mul": MatMulParams, "linear": LinearParams,
+    "attention": AttentionParams, "attn_decode": AttnDecodeParams,
+}
+# every symbol include/rg_b200.h declares
+SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_comm_create",
+            "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]
+           + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load librg_b200.so (built by __graft_entry__.build() / make -C refactorgraph_b200/csrc)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()'). "
+                               "There is no fallback path.")
+        lib = C.CDLL(LIB_PATH)
+        lib.rg_b200_status_string.restype = C.c_char_p
+        lib.rg_b200_launch_count.restype = C.c_uint64
+        for name, ptype in OPS.items():
+            fn = getattr(lib, f"rg_b200_{name}")
+            fn.restype = C.c_int
+            fn.argtypes = [C.POINTER(ptype), C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p]
+            ws = getattr(lib, f"rg_b200_{name}_workspace")
+            ws.restype = C.c_size_t
+            ws.argtypes = [C.POINTER(ptype)]
+        lib.rg_b200_comm_create.argtypes = [C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
+        lib.rg_b200_comm_connect.argtypes = [C.c_void_p, C.c_void_p]
+        lib.rg_b200_comm_status.argtypes = [C.c_void_p]
+        lib.rg_b200_comm_destroy.argtypes = [C.c_void_p]
+        lib.rg_b200_all_reduce.argtypes = [C.c_void_p, C.POINTER(AllReduceParams), C.POINTER(C.c_void_p),
+                                           C.POINTER(C.c_void_p), C.c_void_p]
+        _lib = lib
+    return _lib
+
+
+class RgError(RuntimeError):
+    def __init__(self, op: str, status: int):
+        self.status = status
+        super().__init__(f"rg_b200_{op}: {load().rg_b200_status_string(status).decode()} (status {status})")
+
+
+def _ptrs(ptrs):
+    arr = (C.c_void_p * max(1, len(ptrs)))()
+    for i, p in enumerate(ptrs):
+        arr[i] = p if p else None
+    return arr
+
+
+def workspace(op: str, params) -> int:
+    return int(getattr(load(), f"rg_b200_{op}_workspace")(C.byref(params)))
+
+
+def call(op: str, params, inputs, outputs, ws: int = 0, stream: int = 0, check: bool = True) -> int:
+    """Invoke rg_b200_<op> with raw device addresses (ints; 0/None = NULL)."""
+    rc = getattr(load(), f"rg_b200_{op}")(C.byref(params), ws or None, _ptrs(inputs), _ptrs(outputs), stream or None)
+    if check and rc != OK:
+        raise RgError(op, rc)
+    return rc

@@ -1,0 +1,39 @@
+// Library-wide host helpers of the C ABI: status strings, version, launch counter, SM count cache.
+#include "common.cuh"
+#include <atomic>
+
+namespace rg {
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+}// namespace rg
+
+extern "C" {
+const char *rg_b200_status_string(int s) {
+    switch (s) {
+        case RG_OK: return "ok";
+        case RG_ERR_NULL: return "null pointer";
+        case RG_ERR_SHAPE: return "unsupported shape";
+        case RG_ERR_DTYPE: return "unsupported data type";
+        case RG_ERR_ALIGN: return "misaligned pointer or stride";
+        case RG_ERR_CUDA: return "CUDA error";
+        case RG_ERR_TIMEOUT: return "bounded wait expired";
+        case RG_ERR_UNSUPPORTED: return "no kernel for this request";
+        case RG_ERR_LIMIT: return "size beyond a fixed maximum";
+        default: return "unknown status";
+    }
+}
+int rg_b200_version(void) { return 1; }
+uint64_t rg_b200_launch_count(void) { return rg::g_launches.load(std::memory_order_relaxed); }
+}

@@ -1,0 +1,332 @@
+// Data-movement and element-wise kernels of the decoder path: Gather (embedding), binary/unary/where with
+// broadcast, Transpose, rotary position embedding.  All HBM-bound; the wide paths move 16 bytes per thread
+// and size the grid as a multiple of the SM count.
+#include "common.cuh"
+
+namespace rg {
+
+static unsigned grid_for(size_t work_items, unsigned threads) {
+    const size_t want = (work_items + threads - 1) / threads;
+    const size_t cap = static_cast<size_t>(sm_count()) * 16;
+    return static_cast<unsigned>(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+// ---- Gather ----------------------------------------------------------------------------------
+// out[p, i, :] = data[p, idx[i], :] in units of U bytes (U = 16 when everything is 16-byte aligned).
+template<class U, class I>
+__global__ void gather_kernel(const U *__restrict__ data, const I *__restrict__ idx, U *__restrict__ out,
+                              uint32_t prefix, uint32_t mid_in, uint32_t mid_out, uint64_t units) {
+    const uint64_t total = static_cast<uint64_t>(prefix) * mid_out * units;
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint64_t u = t % units, row = t / units;
+        const uint64_t i = row % mid_out, p = row / mid_out;
+        int64_t k = static_cast<int64_t>(idx[i]);
+        if (k < 0) k += mid_in;
+        out[t] = data[(p * mid_in + static_cast<uint64_t>(k)) * units + u];
+    }
+}
+
+template<class I>
+static int gather_launch(const rg_gather_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+    const uint64_t pb = p->postfix_bytes;
+    const bool v16 = pb % 16 == 0 && aligned16(in[0]) && aligned16(out[0]);
+    const uint64_t rows = static_cast<uint64_t>(p->prefix) * p->mid_out;
+    auto idx = static_cast<const I *>(in[1]);
+#define RG_GATHER(U)                                                                                      \
+    gather_kernel<U, I><<<grid_for(rows * (pb / sizeof(U)), 256), 256, 0, st>>>(                          \
+        static_cast<const U *>(in[0]), idx, static_cast<U *>(out[0]), p->prefix, p->mid_in, p->mid_out,   \
+        pb / sizeof(U))
+    if (v16) RG_GATHER(uint4);
+    else if (pb % 4 == 0 && (reinterpret_cast<uintptr_t>(in[0]) | reinterpret_cast<uintptr_t>(out[0])) % 4 == 0)
+        RG_GATHER(uint32_t);
+    else if (pb % 2 == 0 && (reinterpret_cast<uintptr_t>(in[0]) | reinterpret_cast<uintptr_t>(out[0])) % 2 == 0)
+        RG_GATHER(uint16_t);
+    else
+        RG_GATHER(uint8_t);
+#undef RG_GATHER
+    count_launch();
+    return launch_status();
+}
+
+// ---- Binary / Where with rank-4 broadcast -----------------------------------------------------
+struct Idx4 {
+    uint32_t shape[4];
+    uint32_t sa[4], sb[4], sc[4];
+};
+__device__ __forceinline__ void locate(const Idx4 &ix, uint64_t t, uint64_t &a, uint64_t &b, uint64_t &c) {
+    a = b = c = 0;
+#pragma unroll
+    for (int d = 3; d >= 0; --d) {
+        const uint32_t i = static_cast<uint32_t>(t % ix.shape[d]);
+        t /= ix.shape[d];
+        a += static_cast<uint64_t>(i) * ix.sa[d];
+        b += static_cast<uint64_t>(i) * ix.sb[d];
+        c += static_cast<uint64_t>(i) * ix.sc[d];
+    }
+}
+__device__ __forceinline__ float binary_op(int op, float a, float b) {
+    switch (op) {
+        case 0: return a + b;
+        case 1: return a - b;
+        case 2: return a * b;
+        default: return a / b;
+    }
+}
+template<class T>
+__global__ void binary_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ y, Idx4 ix, int op,
+                              uint64_t total) {
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        uint64_t ia, ib, ic;
+        locate(ix, t, ia, ib, ic);
+        y[t] = Num<T>::from_f(binary_op(op, Num<T>::to_f(a[ia]), Num<T>::to_f(b[ib])));
+    }
+}
+// same shape, contiguous, 16-byte aligned
+template<class T>
+__global__ void binary_vec_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ y, int op,
+                                  uint64_t chunks) {
+    constexpr int N = Vec16<T>::N;
+    for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks;
+         c += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        Vec16<T> va, vb;
+        float fa[N], fb[N];
+        va.load(a + c * N);
+        vb.load(b + c * N);
+        va.unpack(fa);
+        vb.unpack(fb);
+#pragma unroll
+        for (int j = 0; j < N; ++j) fa[j] = binary_op(op, fa[j], fb[j]);
+        va.pack(fa);
+        va.store(y + c * N);
+    }
+}
+template<class T>
+__global__ void where_kernel(const uint8_t *__restrict__ c, const T *__restrict__ a, const T *__restrict__ b,
+                             T *__restrict__ y, Idx4 ix, uint64_t total) {
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        uint64_t ia, ib, ic;
+        locate(ix, t, ia, ib, ic);
+        y[t] = c[ic] ? a[ia] : b[ib];
+    }
+}
+
+template<class T>
+static int binary_launch(const rg_binary_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+    constexpr int N = Vec16<T>::N;
+    uint64_t total = 1;
+    bool same = true;
+    uint32_t expect = 1;
+    for (int d = 3; d >= 0; --d) {
+        total *= p->shape[d];
+        if (p->shape[d] > 1 && (p->a_stride[d] != expect || p->b_stride[d] != expect)) same = false;
+        expect *= p->shape[d];
+    }
+    if (total == 0) return RG_OK;
+    auto a = static_cast<const T *>(in[0]);
+    auto b = static_cast<const T *>(in[1]);
+    auto y = static_cast<T *>(out[0]);
+    if (same && total % N == 0 && aligned16(a) && aligned16(b) && aligned16(y)) {
+        binary_vec_kernel<T><<<grid_for(total / N, 256), 256, 0, st>>>(a, b, y, p->op, total / N);
+    } else {
+        Idx4 ix;
+        for (int d = 0; d < 4; ++d) ix.shape[d] = p->shape[d], ix.sa[d] = p->a_stride[d], ix.sb[d] = p->b_stride[d], ix.sc[d] = 0;
+        binary_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(a, b, y, ix, p->op, total);
+    }
+    count_launch();
+    return launch_status();
+}
+
+// ---- Unary ------------------------------------------------------------------------------------
+__device__ __forceinline__ float unary_op(int op, float x) {
+    switch (op) {
+        case 12: return tanhf(x);
+        case 13: return x > 0.f ? x : 0.f;
+        case 14: return sqrtf(x);
+        case 15: return 1.f / (1.f + expf(-x));
+        case 17: return -x;
+        case 20: return expf(x);
+        default: return x / (1.f + expf(-x));// 100: SiLU
+    }
+}
+template<class T>
+__global__ void unary_kernel(const T *__restrict__ x, T *__restrict__ y, int op, uint64_t n) {
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < n;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x)
+        y[t] = Num<T>::from_f(unary_op(op, Num<T>::to_f(x[t])));
+}
+
+// ---- Transpose ----------------------------------------------------------------------------------
+template<class U>
+__global__ void transpose_kernel(const U *__restrict__ x, U *__restrict__ y, Idx4 ix, uint64_t total) {
+    // ix.shape = output shape, ix.sa = input stride of each output axis
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        uint64_t ia, ib, ic;
+        locate(ix, t, ia, ib, ic);
+        y[t] = x[ia];
+    }
+}
+
+// ---- RoPE -------------------------------------------------------------------------------------
+// One thread per (token, head, i < D/2): rotates the pair (i, i + D/2).
+template<class T>
+__global__ void rope_kernel(const T *__restrict__ x, const int64_t *__restrict__ pos, T *__restrict__ y,
+                            uint32_t tokens, uint32_t heads, uint32_t dim, float log2_theta) {
+    const uint32_t half = dim / 2;
+    const uint64_t total = static_cast<uint64_t>(tokens) * heads * half;
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t i = static_cast<uint32_t>(t % half);
+        const uint64_t th = t / half;// token*heads + head
+        const uint64_t tok = th / heads;
+        const float inv_freq = exp2f(-log2_theta * (2.0f * static_cast<float>(i) / static_cast<float>(dim)));
+        const float ang = static_cast<float>(pos[tok]) * inv_freq;
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        const uint64_t base = th * dim;
+        const float a = Num<T>::to_f(x[base + i]), b = Num<T>::to_f(x[base + i + half]);
+        y[base + i] = Num<T>::from_f(a * cs - b * sn);
+        y[base + i + half] = Num<T>::from_f(b * cs + a * sn);
+    }
+}
+
+}// namespace rg
+
+using namespace rg;
+
+extern "C" {
+
+size_t rg_b200_gather_workspace(const rg_gather_params *) { return 0; }
+int rg_b200_gather(const rg_gather_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
+    if (p->mid_in == 0) return RG_ERR_SHAPE;
+    if (p->prefix == 0 || p->mid_out == 0 || p->postfix_bytes == 0) return RG_OK;
+    auto st = static_cast<cudaStream_t>(stream);
+    switch (p->idx_dtype) {
+        case RG_I32: return gather_launch<int32_t>(p, in, out, st);
+        case RG_I64: return gather_launch<int64_t>(p, in, out, st);
+        default: return RG_ERR_DTYPE;
+    }
+}
+
+size_t rg_b200_binary_workspace(const rg_binary_params *) { return 0; }
+int rg_b200_binary(const rg_binary_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
+    if (p->op < 0 || p->op > 3) return RG_ERR_UNSUPPORTED;
+    auto st = static_cast<cudaStream_t>(stream);
+    switch (p->dtype) {
+        case RG_F32: return binary_launch<float>(p, in, out, st);
+        case RG_FP16: return binary_launch<__half>(p, in, out, st);
+        case RG_BF16: return binary_launch<__nv_bfloat16>(p, in, out, st);
+        default: return RG_ERR_DTYPE;
+    }
+}
+
+size_t rg_b200_unary_workspace(const rg_unary_params *) { return 0; }
+int rg_b200_unary(const rg_unary_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+    switch (p->op) {
+        case 12: case 13: case 14: case 15: case 17: case 20: case 100: break;
+        default: return RG_ERR_UNSUPPORTED;
+    }
+    if (p->n == 0) return RG_OK;
+    auto st = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(p->n, 256);
+    switch (p->dtype) {
+        case RG_F32: unary_kernel<float><<<g, 256, 0, st>>>(static_cast<const float *>(in[0]), static_cast<float *>(out[0]), p->op, p->n); break;
+        case RG_FP16: unary_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half *>(in[0]), static_cast<__half *>(out[0]), p->op, p->n); break;
+        case RG_BF16: unary_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(in[0]), static_cast<__nv_bfloat16 *>(out[0]), p->op, p->n); break;
+        default: return RG_ERR_DTYPE;
+    }
+    count_launch();
+    return launch_status();
+}
+
+size_t rg_b200_where_workspace(const rg_where_params *) { return 0; }
+int rg_b200_where(const rg_where_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !in[1] || !in[2] || !out[0]) return RG_ERR_NULL;
+    Idx4 ix;
+    uint64_t total = 1;
+    for (int d = 0; d < 4; ++d) {
+        ix.shape[d] = p->shape[d], ix.sa[d] = p->a_stride[d], ix.sb[d] = p->b_stride[d], ix.sc[d] = p->c_stride[d];
+        total *= p->shape[d];
+    }
+    if (total == 0) return RG_OK;
+    auto st = static_cast<cudaStream_t>(stream);
+    auto c = static_cast<const uint8_t *>(in[0]);
+    const unsigned g = grid_for(total, 256);
+    switch (p->dtype) {
+        case RG_F32: case RG_I32: case RG_U32:
+            where_kernel<uint32_t><<<g, 256, 0, st>>>(c, static_cast<const uint32_t *>(in[1]), static_cast<const uint32_t *>(in[2]), static_cast<uint32_t *>(out[0]), ix, total);
+            break;
+        case RG_FP16: case RG_BF16:
+            where_kernel<uint16_t><<<g, 256, 0, st>>>(c, static_cast<const uint16_t *>(in[1]), static_cast<const uint16_t *>(in[2]), static_cast<uint16_t *>(out[0]), ix, total);
+            break;
+        case RG_I64: case RG_F64:
+            where_kernel<uint64_t><<<g, 256, 0, st>>>(c, static_cast<const uint64_t *>(in[1]), static_cast<const uint64_t *>(in[2]), static_cast<uint64_t *>(out[0]), ix, total);
+            break;
+        case RG_U8: case RG_I8: case RG_BOOL:
+            where_kernel<uint8_t><<<g, 256, 0, st>>>(c, static_cast<const uint8_t *>(in[1]), static_cast<const uint8_t *>(in[2]), static_cast<uint8_t *>(out[0]), ix, total);
+            break;
+        default: return RG_ERR_DTYPE;
+    }
+    count_launch();
+    return launch_status();
+}
+
+size_t rg_b200_transpose_workspace(const rg_transpose_params *) { return 0; }
+int rg_b200_transpose(const rg_transpose_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+    if (p->rank == 0 || p->rank > 4) return RG_ERR_SHAPE;
+    uint32_t in_stride[4], stride = 1;
+    for (int d = static_cast<int>(p->rank) - 1; d >= 0; --d) {
+        in_stride[d] = stride;
+        stride *= p->in_shape[d];
+    }
+    Idx4 ix;
+    uint64_t total = 1;
+    const int pad = 4 - static_cast<int>(p->rank);
+    for (int d = 0; d < 4; ++d) ix.shape[d] = 1, ix.sa[d] = ix.sb[d] = ix.sc[d] = 0;
+    for (uint32_t d = 0; d < p->rank; ++d) {
+        if (p->perm[d] >= p->rank) return RG_ERR_SHAPE;
+        ix.shape[pad + d] = p->in_shape[p->perm[d]];
+        ix.sa[pad + d] = in_stride[p->perm[d]];
+        total *= ix.shape[pad + d];
+    }
+    if (total == 0) return RG_OK;
+    auto st = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(total, 256);
+    switch (p->elem_bytes) {
+        case 1: transpose_kernel<uint8_t><<<g, 256, 0, st>>>(static_cast<const uint8_t *>(in[0]), static_cast<uint8_t *>(out[0]), ix, total); break;
+        case 2: transpose_kernel<uint16_t><<<g, 256, 0, st>>>(static_cast<const uint16_t *>(in[0]), static_cast<uint16_t *>(out[0]), ix, total); break;
+        case 4: transpose_kernel<uint32_t><<<g, 256, 0, st>>>(static_cast<const uint32_t *>(in[0]), static_cast<uint32_t *>(out[0]), ix, total); break;
+        case 8: transpose_kernel<uint64_t><<<g, 256, 0, st>>>(static_cast<const uint64_t *>(in[0]), static_cast<uint64_t *>(out[0]), ix, total); break;
+        default: return RG_ERR_DTYPE;
+    }
+    count_launch();
+    return launch_status();
+}
+
+size_t rg_b200_rope_workspace(const rg_rope_params *) { return 0; }
+int rg_b200_rope(const rg_rope_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
+    if (p->head_dim == 0 || p->head_dim % 2 != 0 || !(p->theta > 0.f)) return RG_ERR_SHAPE;
+    const uint64_t total = static_cast<uint64_t>(p->tokens) * p->heads * (p->head_dim / 2);
+    if (total == 0) return RG_OK;
+    auto st = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(total, 256);
+    const float l2t = log2f(p->theta);
+    auto pos = static_cast<const int64_t *>(in[1]);
+    switch (p->dtype) {
+        case RG_F32: rope_kernel<float><<<g, 256, 0, st>>>(static_cast<const float *>(in[0]), pos, static_cast<float *>(out[0]), p->tokens, p->heads, p->head_dim, l2t); break;
+        case RG_FP16: rope_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half *>(in[0]), pos, static_cast<__half *>(out[0]), p->tokens, p->heads, p->head_dim, l2t); break;
+        case RG_BF16: rope_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(in[0]), pos, static_cast<__nv_bfloat16 *>(out[0]), p->tokens, p->heads, p->head_dim, l2t); break;
+        default: return RG_ERR_DTYPE;
+    }
+    count_launch();
+    return launch_status();
+}
+}

@@ -1,0 +1,13 @@
+// Internal entry points behind rg_b200_mat_mul / rg_b200_linear.
+#pragma once
+#include "common.cuh"
+namespace rg {
+int gemm_simt(const rg_mat_mul_params *p, const void *const *in, void *const *out, cudaStream_t st);
+int linear_stream(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
+// tcgen05/TMEM GEMM: Y[m,n] = alpha * A[m,k] * B[n,k]^T (+ beta*C), fp16/bf16, fp32 accumulation in TMEM.
+int gemm_tc(const rg_mat_mul_params *p, const void *const *in, void *const *out, cudaStream_t st);
+bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *const *out);
+int linear_error_word();
+int attn_error_word();
+int gemm_tc_error_word();
+}// namespace rg
