@@ -201,9 +201,10 @@ extern "C" {
 
 size_t rg_b200_gather_workspace(const rg_gather_params *) { return 0; }
 int rg_b200_gather(const rg_gather_params *p, void *, const void *const *in, void *const *out, void *stream) {
-    if (!p || !in || !out || !in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
+    if (!p || !in || !out) return RG_ERR_NULL;
+    if (p->prefix == 0 || p->mid_out == 0 || p->postfix_bytes == 0) return RG_OK;// empty index list / rows
+    if (!in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
     if (p->mid_in == 0) return RG_ERR_SHAPE;
-    if (p->prefix == 0 || p->mid_out == 0 || p->postfix_bytes == 0) return RG_OK;
     auto st = static_cast<cudaStream_t>(stream);
     switch (p->idx_dtype) {
         case RG_I32: return gather_launch<int32_t>(p, in, out, st);
