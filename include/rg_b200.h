@@ -178,6 +178,17 @@ typedef struct rg_rope_params {
 size_t rg_b200_rope_workspace(const rg_rope_params *);
 int rg_b200_rope(const rg_rope_params *, void *ws, const void *const *in, void *const *out, void *stream);
 
+/* State update for device-resident generation loops (no reference counterpart: the reference feeds every step
+ * from the host).  state[i] = (src ? src[i] : state[i]) + delta, int64, in place.  Lets a captured decode step
+ * carry the sampled token and the position to the next replay without a host round trip.
+ * inputs {src or NULL}, outputs {state}. */
+typedef struct rg_state_update_params {
+    uint32_t n;
+    int64_t delta;
+} rg_state_update_params;
+size_t rg_b200_state_update_workspace(const rg_state_update_params *);
+int rg_b200_state_update(const rg_state_update_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * MatMul: Y[b] = alpha * op(A[b]) * op(B[b]) + beta * C (C broadcast to [m,n]).  Replaces MatMulCublas
  * (src/04kernel/src/kernels/mat_mul/cublas_kernel.cu:9-100) with MatMulInfo's fields

@@ -64,6 +64,10 @@ class RopeParams(C.Structure):
                 ("theta", C.c_float)]
 
 
+class StateUpdateParams(C.Structure):
+    _fields_ = [("n", C.c_uint32), ("delta", C.c_int64)]
+
+
 class MatMulParams(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
                 ("trans_a", C.c_int32), ("trans_b", C.c_int32), ("alpha", C.c_float), ("beta", C.c_float),
@@ -101,7 +105,7 @@ class AllReduceParams(C.Structure):
 OPS = {
     "rms_norm": RmsNormParams, "softmax": SoftmaxParams, "topk": TopkParams, "topk_sample": TopkSampleParams,
     "gather": GatherParams, "binary": BinaryParams, "unary": UnaryParams, "where": WhereParams,
-    "transpose": TransposeParams, "rope": RopeParams, "mat_mul": MatMulParams, "linear": LinearParams,
+    "transpose": TransposeParams, "rope": RopeParams, "state_update": StateUpdateParams, "mat_mul": MatMulParams, "linear": LinearParams,
     "attention": AttentionParams, "attn_decode": AttnDecodeParams,
 }
 # every symbol include/rg_b200.h declares

@@ -193,6 +193,12 @@ __global__ void rope_kernel(const T *__restrict__ x, const int64_t *__restrict__
     }
 }
 
+__global__ void state_update_kernel(const int64_t *__restrict__ src, int64_t *__restrict__ state, uint32_t n,
+                                    int64_t delta) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) state[i] = (src ? src[i] : state[i]) + delta;
+}
+
 }// namespace rg
 
 using namespace rg;
@@ -327,6 +333,16 @@ int rg_b200_rope(const rg_rope_params *p, void *, const void *const *in, void *c
         case RG_BF16: rope_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(in[0]), pos, static_cast<__nv_bfloat16 *>(out[0]), p->tokens, p->heads, p->head_dim, l2t); break;
         default: return RG_ERR_DTYPE;
     }
+    count_launch();
+    return launch_status();
+}
+
+size_t rg_b200_state_update_workspace(const rg_state_update_params *) { return 0; }
+int rg_b200_state_update(const rg_state_update_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !out[0]) return RG_ERR_NULL;
+    if (p->n == 0) return RG_OK;
+    state_update_kernel<<<(p->n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const int64_t *>(in[0]), static_cast<int64_t *>(out[0]), p->n, p->delta);
     count_launch();
     return launch_status();
 }

@@ -74,9 +74,9 @@ namespace refactor::kernel {
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
     // Fused decode linear layer (rg_b200_linear): prologue 0|1 (RMSNorm), epilogue 0 none | 1 residual | 2 SiLU gate |
-    // 3 QKV split + RoPE + cache append.  Inputs in rg_b200_linear order; absent ones are omitted from the list by
-    // giving them zero-rank placeholders is NOT needed: the operator passes exactly
-    //   {X, W, [G], [R], [positions, (block_table)]} and outputs {Y, [k_cache, v_cache]}.
+    // 3 QKV split + RoPE + cache append.  The operator passes exactly
+    //   {X, W, [G], [R], [positions, (block_table), k_cache, v_cache]} and outputs {Y};
+    // the caches are state edges that the kernel appends to in place.
     struct FusedLinearCollector final : public InfoCollector {
         int prologue, epilogue;
         float epsilon, theta;
@@ -94,6 +94,9 @@ namespace refactor::kernel {
             : InfoCollector(target), maxLen(maxLen_), pageSize(pageSize_) {}
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
+    // In-place int64 state update: inputs {state, [src]}; state = (src ? src : state) + delta.  The routine writes
+    // through inputs[0] (a state edge of the graph); it has no outputs.
+    RG_COLLECTOR(StateUpdateCollector, int64_t, delta);
 #undef RG_COLLECTOR
 
 }// namespace refactor::kernel

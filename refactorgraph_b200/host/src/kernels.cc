@@ -68,6 +68,21 @@ namespace refactor::kernel {
     RG_SIMPLE_KERNEL(TopKSampleB200, rg_topk_sample_params, rg_b200_topk_sample, "Top-k sampling on B200 (radix select + Philox)");
     RG_SIMPLE_KERNEL(AttentionB200, rg_attention_params, rg_b200_attention, "Causal attention with KV cache on B200");
 
+    struct StateUpdateB200 final : public Kernel {
+        rg_state_update_params info;
+        bool hasSrc;
+        StateUpdateB200(rg_state_update_params p, bool hasSrc_) noexcept : info(p), hasSrc(hasSrc_) {}
+        RG_KERNEL_IDS(StateUpdateB200, "In-place int64 state update on B200")
+        RoutineWorkspace lower(Resources &res) const final {
+            auto st = res.fetchOrStore<CudaStream>();
+            return RoutineWorkspace([info = info, hasSrc = hasSrc, st](Resources &, void *ws, void const *const *in, void *const *) {
+                void const *in_[1] = {hasSrc ? in[1] : nullptr};
+                void *out_[1] = {const_cast<void *>(in[0])};
+                check(rg_b200_state_update(&info, ws, in_, out_, st->stream), "rg_b200_state_update");
+            });
+        }
+    };
+
     // ---- RmsNormalization ---------------------------------------------------------------------------------------
     std::vector<KernelBox> RmsNormalizationCollector::filter(TensorRefs inputs, TensorRefs) const {
         std::vector<KernelBox> ans;
@@ -388,16 +403,19 @@ namespace refactor::kernel {
             auto st = res.fetchOrStore<CudaStream>();
             return RoutineWorkspace(
                 [info = info, paged = paged, st](Resources &, void *ws, void const *const *in, void *const *out) {
-                    // operator order {X, W, [G], [R], [positions, (block_table)]} -> C ABI order
+                    // operator order {X, W, [G], [R], [positions, (block_table), k_cache, v_cache]} -> C ABI order.
+                    // The caches are state edges of the graph: listed as inputs, appended to in place.
                     int i = 2;
                     void const *in_[6] = {in[0], in[1], nullptr, nullptr, nullptr, nullptr};
+                    void *out_[3] = {out[0], nullptr, nullptr};
                     if (info.prologue == 1) in_[2] = in[i++];
                     if (info.epilogue == 1) in_[3] = in[i++];
                     if (info.epilogue == 3) {
                         in_[4] = in[i++];
                         if (paged) in_[5] = in[i++];
+                        out_[1] = const_cast<void *>(in[i++]);
+                        out_[2] = const_cast<void *>(in[i++]);
                     }
-                    void *out_[3] = {out[0], info.epilogue == 3 ? out[1] : nullptr, info.epilogue == 3 ? out[2] : nullptr};
                     check(rg_b200_linear(&info, ws, in_, out_, st->stream), "rg_b200_linear");
                 },
                 rg_b200_linear_workspace(&info));
@@ -417,9 +435,17 @@ namespace refactor::kernel {
         p.kv.n_kv_heads = nKVHeads, p.kv.head_dim = headDim, p.kv.max_seq = maxSeq, p.kv.page_size = pageSize;
         bool paged = false;
         if (epilogue == 3) {
-            const size_t expect = 2 + (prologue == 1) + 1;
+            const size_t expect = 2 + (prologue == 1) + 1 + 2;
+            if (inputs.size() != expect && inputs.size() != expect + 1) return ans;
             paged = inputs.size() == expect + 1;
-            if (paged) p.kv.max_blocks_per_seq = inputs.back().get().shape.back();
+            auto const &kc = inputs[inputs.size() - 2].get();
+            if (kc.shape.size() != 4) return ans;
+            if (paged) {
+                p.kv.max_blocks_per_seq = inputs[inputs.size() - 3].get().shape.back();
+                if (!p.kv.page_size) p.kv.page_size = kc.shape[2];
+            } else if (!p.kv.max_seq) {
+                p.kv.max_seq = kc.shape[2];
+            }
         }
         ans.emplace_back(std::make_unique<FusedLinearB200>(p, paged));
         return ans;
@@ -461,6 +487,19 @@ namespace refactor::kernel {
             p.kv.max_seq = kc.shape[2];
         }
         ans.emplace_back(std::make_unique<AttentionDecodeB200>(p, paged));
+        return ans;
+    }
+
+    // state (outputs[0] aliases inputs[0] in the graph) = (src ? src : state) + delta
+    std::vector<KernelBox> StateUpdateCollector::filter(TensorRefs inputs, TensorRefs) const {
+        std::vector<KernelBox> ans;
+        auto const &s = inputs[0].get();
+        if (_target != Target::Nvidia || s.dataType != DataType::I64) return ans;
+        if (inputs.size() > 1 && (inputs[1].get().dataType != DataType::I64 || inputs[1].get().elementsSize() < s.elementsSize())) return ans;
+        rg_state_update_params p{};
+        p.n = static_cast<uint32_t>(s.elementsSize());
+        p.delta = delta;
+        ans.emplace_back(std::make_unique<StateUpdateB200>(p, inputs.size() > 1));
         return ans;
     }
 
