@@ -1,0 +1,487 @@
+#!/usr/bin/env python
+"""Benchmark of the decoder hot path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload 7b|tiny]
+
+Workload at N = 1 (BASELINE.json configs[1]): Llama-7B-shaped fp16 batch-1 greedy decode (32 layers, hidden 4096,
+32 heads x 128, FFN 11008, vocab 32000), KV cache prefilled to 2048 tokens with N(0,1), random weights N(0,0.02);
+one "step" = one generated token through executor.run().  Prints ONE JSON line (rank 0).
+
+value  : tokens/s with token / position / cache state resident on the device (CUDA-graph replays only).
+e2e    : tokens/s when every step's input token comes from pinned host memory (H2D inside the timed region)
+         and the sampled token is read back (D2H + synchronise) through the executor API.
+roofline: the weight-streaming linear kernel, timed live with CUDA events over one pass of every linear launch
+         of a step on the real weights (13.2 GB, far larger than L2), against the measured HBM copy peak.
+cpu_baseline / --impl reference: the reference's own CPU kernels (oracle/_ref, else the C port) on the host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="7b", choices=["7b", "tiny"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "topk"],
+                    help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
+    ap.add_argument("--launches", type=int, default=6)
+    return ap.parse_args()
+
+
+def workload_config(name):
+    from refactorgraph_b200.llama import LlamaConfig
+    if name == "tiny":  # for quick functional runs only; never the reported configuration
+        return LlamaConfig(layers=2, hidden=512, heads=4, kv_heads=4, head_dim=128, ffn=1024, vocab=2000, max_seq=512), 256
+    return LlamaConfig(max_seq=2048 + 512), 2048
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's CPU kernels for one decoder layer (+ LM head) of one token, fp32, 1 core.
+class CpuLayer:
+    def __init__(self, cfg, kv_len):
+        import oracle
+        self.oracle = oracle
+        self.kind = "reference" if oracle.load_ref() is not None else "port"
+        rng = np.random.default_rng(0)
+        H, D, nH, F = cfg.hidden, cfg.head_dim, cfg.heads, cfg.ffn
+        self.cfg, self.L = cfg, kv_len
+        f32 = lambda *s: (0.02 * rng.standard_normal(s, dtype=np.float32))
+        self.x = rng.standard_normal((1, H), dtype=np.float32)
+        self.g = np.ones(H, np.float32)
+        self.wqkv, self.wo = f32(3 * nH * D, H), f32(H, nH * D)
+        self.wg, self.wu, self.wd = f32(F, H), f32(F, H), f32(H, F)
+        self.kc = rng.standard_normal((nH, kv_len, D), dtype=np.float32)
+        self.vc = rng.standard_normal((nH, kv_len, D), dtype=np.float32)
+        self.lm = None
+
+    def _mm(self, a, b, trans_b=True):
+        if self.kind == "reference":
+            return self.oracle.ref_mat_mul(a, b, trans_b=trans_b)
+        if a.ndim == 2:
+            return self.oracle.port_mat_mul(a, b, trans_b=trans_b)
+        return np.stack([self.oracle.port_mat_mul(a[i], b[i], trans_b=trans_b) for i in range(a.shape[0])])
+
+    def layer(self):
+        o, c = self.oracle, self.cfg
+        ref = self.kind == "reference"
+        rms = (lambda x: o.ref_rms_norm(x, self.g, c.eps)) if ref else (lambda x: o.port_rms_norm(x, self.g, c.eps))
+        sm = (lambda s: o.ref_softmax(s, 2)) if ref else (lambda s: o.port_softmax_asbuilt(s, 2))
+        n1 = rms(self.x)
+        qkv = self._mm(n1, self.wqkv)                                        # weights stored [out, in]: transB
+        q = np.ascontiguousarray(qkv[:, : c.heads * c.head_dim].reshape(c.heads, 1, c.head_dim))
+        s = self._mm(q, self.kc)                                             # [nH, 1, L]
+        p = sm(np.ascontiguousarray(s * np.float32(1.0 / np.sqrt(c.head_dim))))
+        a = self._mm(p, self.vc, trans_b=False).reshape(1, c.heads * c.head_dim)
+        h = self.x + self._mm(a, self.wo)
+        n2 = rms(h)
+        gt, up = self._mm(n2, self.wg), self._mm(n2, self.wu)
+        act = gt * (1.0 / (1.0 + np.exp(-gt))) * up
+        return h + self._mm(np.ascontiguousarray(act, dtype=np.float32), self.wd)
+
+    def lm_head(self):
+        if self.lm is None:
+            self.lm = (0.02 * np.random.default_rng(1).standard_normal((self.cfg.vocab, self.cfg.hidden), dtype=np.float32))
+        return self._mm(self.x, self.lm)
+
+
+def cpu_baseline(cfg, kv_len, layer_reps=2):
+    cl = CpuLayer(cfg, kv_len)
+    cl.layer()  # warm caches / page in
+    t0 = time.perf_counter()
+    for _ in range(layer_reps):
+        cl.layer()
+    t_layer = (time.perf_counter() - t0) / layer_reps
+    t0 = time.perf_counter()
+    cl.lm_head()
+    t_head = time.perf_counter() - t0
+    tok_s = 1.0 / (cfg.layers * t_layer + t_head)
+    return {"value": tok_s, "unit": "tokens/s", "cores": 1, "kind": cl.kind,
+            "sample": f"{layer_reps} x one decoder layer for one token at KV {kv_len} ({t_layer:.3f} s each) + LM head once "
+                      f"({t_head:.3f} s), fp32, weights stored [out,in] (transB); token time extrapolated x{cfg.layers} layers"}
+
+
+def run_reference(args):
+    """--impl reference: the reference's own CPU kernels on the host cores; each step = one decoder layer of one
+    token (a bounded sample), tokens/s extrapolated over the layer count."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg, kv_len = workload_config(args.workload)
+    cl = CpuLayer(cfg, kv_len)
+    t0 = time.perf_counter()
+    cl.lm_head()
+    t_head = time.perf_counter() - t0
+    for _ in range(max(1, min(args.warmup, 2))):
+        cl.layer()
+    steps = max(1, args.steps)
+    budget_s = 150.0
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        cl.layer()
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    t_layer = (time.perf_counter() - t0) / done
+    tok_s = 1.0 / (cfg.layers * t_layer + t_head)
+    sample = (f"{done} timed steps, each one decoder layer of one token at KV {kv_len} ({t_layer:.3f} s) ; LM head timed once "
+              f"({t_head:.3f} s); fp32; token time = {cfg.layers} x layer + head")
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / tok_s, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(args.workload), "timed_steps_done": done},
+            "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": 1, "kind": cl.kind, "sample": sample},
+            "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(w):
+    if w == "tiny":
+        return "tiny functional decoder (not a reported configuration)"
+    return "Llama-7B-shaped fp16 batch-1 greedy decode, KV cache prefilled to 2048 tokens, one token per step"
+
+
+# ----------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi sampling during the timed region (read-only)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc, self.index = None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.strip().splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_executor(cfg, kv_len, torch):
+    from refactorgraph_b200.llama import decode_step_graph, weight_inputs
+    g, index = decode_step_graph(cfg)
+    ex = g.compiler().compile("cuda", "flat", [])
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    dt = torch.float16
+    for name, shape in weight_inputs(cfg):
+        w = torch.empty(shape, dtype=torch.float32, device="cuda").normal_(0.0, 0.02, generator=gen)
+        if "norm" in name:
+            w += 1.0
+        w = w.to(dt)
+        ex.set_input_blob(index[name], w.data_ptr(), w.numel() * 2)
+        del w
+    for l in range(cfg.layers):
+        for nm in ("k_cache", "v_cache"):
+            c = torch.empty((cfg.batch, cfg.kv_heads, cfg.max_seq, cfg.head_dim), dtype=torch.float32, device="cuda").normal_(0.0, 1.0, generator=gen).to(dt)
+            ex.set_input_blob(index[f"l{l}.{nm}"], c.data_ptr(), c.numel() * 2)
+            del c
+    torch.cuda.empty_cache()
+    return ex, index
+
+
+def reset_state(ex, index, cfg, kv_len, token0):
+    ex.set_input(index["token"], token0)
+    ex.set_input(index["pos"], np.full(cfg.batch, kv_len, np.int64))
+    ex.set_input(index["lens"], np.full(cfg.batch, kv_len + 1, np.int64))
+
+
+def time_linear_kernel(ex, index, cfg, torch, stream, reps=3):
+    """One pass over every linear launch of a step (real weights, eager launches on the executor's stream),
+    bracketed by CUDA events: average launch duration and algorithmic bytes of the weight-streaming kernel."""
+    from refactorgraph_b200 import capi
+    B, H, D = cfg.batch, cfg.hidden, cfg.head_dim
+    dt = torch.float16
+    x = torch.randn(B, H, device="cuda").to(dt)
+    act = torch.randn(B, cfg.ffn, device="cuda").to(dt)
+    y = torch.empty(B, max(cfg.vocab, 2 * cfg.ffn), dtype=dt, device="cuda")
+    gnorm = torch.ones(H, dtype=dt, device="cuda")
+    calls, bytes_total = [], 0
+    for l in range(cfg.layers):
+        for name, n, k, src in ((f"l{l}.wqkv", (cfg.heads + 2 * cfg.kv_heads) * D, H, x), (f"l{l}.wo", H, cfg.heads * D, x),
+                                (f"l{l}.wgu", 2 * cfg.ffn, H, x), (f"l{l}.wd", H, cfg.ffn, act)):
+            p = capi.LinearParams()
+            p.dtype, p.m, p.n, p.k = capi.FP16, B, n, k
+            p.prologue, p.epilogue, p.epsilon = (1 if k == H and n != H else 0), (2 if "wgu" in name else 0), cfg.eps
+            calls.append((p, [src.data_ptr(), ex.input_address(index[name]), gnorm.data_ptr() if p.prologue else 0, 0, 0, 0]))
+            bytes_total += n * k * 2
+    p = capi.LinearParams()
+    p.dtype, p.m, p.n, p.k, p.prologue, p.epsilon = capi.FP16, B, cfg.vocab, H, 1, cfg.eps
+    calls.append((p, [x.data_ptr(), ex.input_address(index["lm_head"]), gnorm.data_ptr(), 0, 0, 0]))
+    bytes_total += cfg.vocab * H * 2
+    sid = stream.cuda_stream
+    outs = [y.data_ptr(), 0, 0]
+
+    def one_pass():
+        for p, ins in calls:
+            capi.call("linear", p, ins, outs, stream=sid)
+    one_pass()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        one_pass()
+    e1.record(stream)
+    stream.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return {"launches": len(calls), "ms_per_pass": ms, "bytes_per_pass": bytes_total,
+            "avg_launch_us": 1000.0 * ms / len(calls), "gbs": bytes_total / (ms * 1e-3) / 1e9}
+
+
+def run_case(args):
+    """One kernel alone at its Llama-7B decode shape, inputs rotated over buffers larger than L2 in total."""
+    import torch
+    from refactorgraph_b200 import capi
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    torch.cuda.set_device(0)
+    capi.load()
+    dt, dev = torch.float16, "cuda"
+    H, nH, D, F, V = 4096, 32, 128, 11008, 32000
+    st = torch.cuda.current_stream()
+    sid = st.cuda_stream
+    nbuf = 4
+    if args.case.startswith("linear"):
+        n, k, pro, epi = {"linear_gate_up": (2 * F, H, 1, 2), "linear_down": (H, F, 0, 1), "linear_qkv": (3 * H, H, 1, 3)}[args.case]
+        ws = [(0.02 * torch.randn(n, k, device=dev)).to(dt) for _ in range(nbuf)]
+        x = torch.randn(1, k, device=dev).to(dt)
+        g = torch.ones(k, dtype=dt, device=dev)
+        r = torch.randn(1, n, device=dev).to(dt)
+        y = torch.empty(1, n, dtype=dt, device=dev)
+        kc = torch.zeros(1, nH, 256, D, dtype=dt, device=dev)
+        vc = torch.zeros_like(kc)
+        pos = torch.tensor([100], device=dev)
+        p = capi.LinearParams()
+        p.dtype, p.m, p.n, p.k, p.prologue, p.epilogue, p.epsilon, p.n_heads, p.theta = capi.FP16, 1, n, k, pro, epi, 1e-6, nH, 10000.0
+        p.kv = capi.KvLayout(nH, D, 256, 0, 0)
+        bytes_per = n * k * 2
+
+        def launch(i):
+            capi.call("linear", p, [x.data_ptr(), ws[i % nbuf].data_ptr(), g.data_ptr() if pro else 0, r.data_ptr() if epi == 1 else 0,
+                                    pos.data_ptr() if epi == 3 else 0, 0], [y.data_ptr(), kc.data_ptr() if epi == 3 else 0, vc.data_ptr() if epi == 3 else 0], stream=sid)
+    elif args.case == "attn_decode":
+        L, MS = 2112, 2560
+        q = torch.randn(1, nH, D, device=dev).to(dt)
+        caches = [(torch.randn(1, nH, MS, D, device=dev).to(dt), torch.randn(1, nH, MS, D, device=dev).to(dt)) for _ in range(nbuf * 2)]
+        lens = torch.tensor([L], device=dev)
+        o = torch.empty_like(q)
+        p = capi.AttnDecodeParams(capi.FP16, 1, nH, MS, capi.KvLayout(nH, D, MS, 0, 0))
+        wsb = torch.zeros(capi.workspace("attn_decode", p), dtype=torch.uint8, device=dev)
+        bytes_per = 2 * nH * L * D * 2
+
+        def launch(i):
+            kc, vc = caches[i % len(caches)]
+            capi.call("attn_decode", p, [q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), 0], [o.data_ptr()], ws=wsb.data_ptr(), stream=sid)
+    else:
+        xs = [torch.randn(1, V, device=dev).to(dt) for _ in range(nbuf)]
+        vals = torch.empty(1, 1, dtype=torch.float32, device=dev)
+        idx = torch.empty(1, 1, dtype=torch.int64, device=dev)
+        p = capi.TopkParams(capi.FP16, 1, V, 1, 1)
+        bytes_per = V * 2
+
+        def launch(i):
+            capi.call("topk", p, [xs[i % nbuf].data_ptr()], [vals.data_ptr(), idx.data_ptr()], stream=sid)
+    for i in range(3):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.launches):
+        launch(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = 1000.0 * e0.elapsed_time(e1) / args.launches
+    print(json.dumps({"case": args.case, "launches": args.launches, "us_per_launch": us, "algorithmic_bytes_per_launch": bytes_per,
+                      "gbs": bytes_per / us / 1e3}), flush=True)
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from refactorgraph_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernel library has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = capi.load()
+    cfg, kv_len = workload_config(args.workload)
+    ex, index = build_executor(cfg, kv_len, torch)
+    stream = torch.cuda.ExternalStream(ex.cuda_stream())
+    token0 = np.random.default_rng(rank).integers(0, cfg.vocab, (cfg.batch,)).astype(np.int64)
+    K, W = args.steps, max(args.warmup, 3)
+    assert kv_len + W + K + 1 <= cfg.max_seq, "steps exceed the KV cache capacity of this benchmark configuration"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # launches per step, counted on the eager first pass
+    reset_state(ex, index, cfg, kv_len, token0)
+    l0 = lib.rg_b200_launch_count()
+    ex.run()
+    ex.sync()
+    launches_per_step = int(lib.rg_b200_launch_count() - l0)
+
+    # ---- device-resident loop ----
+    reset_state(ex, index, cfg, kv_len, token0)
+    for _ in range(W):
+        ex.run()
+    ex.sync()
+    reset_state(ex, index, cfg, kv_len, token0)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(K):
+        ex.run()
+    e1.record(stream)
+    stream.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    last_tokens = ex.get_output(index["next"]).ravel().tolist()
+    logits_finite = bool(np.isfinite(ex.get_output(index["logits"]).astype(np.float32)).all())
+    if not logits_finite:
+        raise SystemExit("bench.py: non-finite logits after the timed loop; the number would be meaningless")
+
+    # ---- end-to-end loop: token from pinned host memory each step, sampled token read back ----
+    reset_state(ex, index, cfg, kv_len, token0)
+    pin_in = torch.from_numpy(token0.copy()).pin_memory()
+    pin_out = torch.zeros(cfg.batch, 1, dtype=torch.int64).pin_memory()
+    nbytes = cfg.batch * 8
+    for _ in range(3):
+        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes)
+        ex.run()
+        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes)
+        pin_in.copy_(pin_out.view(-1))
+    reset_state(ex, index, cfg, kv_len, token0)
+    pin_in.copy_(torch.from_numpy(token0))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes)
+        ex.run()
+        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes)   # synchronises
+        pin_in.copy_(pin_out.view(-1))
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+
+    # max over ranks
+    if world > 1:
+        t = torch.tensor([ms, e2e_s * 1000.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    else:
+        e2e_ms = e2e_s * 1000.0
+    lin = time_linear_kernel(ex, index, cfg, torch, stream) if rank == 0 else None
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        tokens = K * cfg.batch * world
+        value = tokens / (ms * 1e-3)
+        kv_mean = kv_len + 1 + (K - 1) / 2.0
+        step_bytes = cfg.weight_bytes_per_step + cfg.kv_bytes_per_token * kv_mean * cfg.batch
+        line = {
+            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(args.workload), "layers": cfg.layers, "hidden": cfg.hidden, "batch": cfg.batch,
+                       "logits_finite": logits_finite,
+                       "kv_len_start": kv_len, "l2": "inputs larger than L2 (13.2 GB of weights streamed per step)",
+                       "parallelism": "one independent replica per GPU" if world > 1 else "single GPU",
+                       "last_tokens": last_tokens},
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
+            "gpu_launches": launches_per_step * K,
+            "launches_per_step": launches_per_step,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
+                         "traffic": None, "kernel": "linear_stream_kernel", "peak_source": peak_kind + " HBM copy bandwidth",
+                         "avg_launch_us": lin["avg_launch_us"], "launches_timed": lin["launches"],
+                         "algorithmic_bytes_per_launch": lin["bytes_per_pass"] / lin["launches"]},
+            "roofline_step": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
+                              "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak,
+                              "frac_of_nominal_8tbs": step_bytes / (ms / K * 1e-3) / 1e9 / 8000.0},
+        }
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(cfg, kv_len)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

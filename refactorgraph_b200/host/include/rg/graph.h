@@ -66,6 +66,7 @@ namespace refactor::runtime {
         void *outputAddress(count_t i) const;
         void run();                                                  // one pass; CUDA-graph replay after the first
         void sync() const;
+        void deviceSync() const;
         std::vector<std::chrono::nanoseconds> bench(bool sync);
         void trace(std::function<void(count_t, void const *const *, void const *const *)>);
         void setGraphMode(bool on) { _useGraph = on; }
@@ -107,6 +108,9 @@ namespace refactor::kernel {
         std::vector<Node> nodes;// topological order
         std::vector<Edge> edges;
         std::vector<size_t> globalInputs, globalOutputs;
+        // descriptors of the global outputs as the graph's author sees them (an output behind an identity
+        // operator shares the storage of the edge it aliases but keeps its own shape)
+        std::vector<Arc<Tensor>> outputTensors;
 
         // allocator: "flat" gives every edge its own region (state edges persist across run()); anything else
         // reuses regions of dead edges, like reusableAllocate (src/04kernel/src/allocators/reusable_allocator.cpp).

@@ -361,7 +361,10 @@ namespace refactor::computation {
             g.nodes.push_back(std::move(kn));
         }
         if (!missing.empty()) RUNTIME_ERROR("No kernel selected for " + missing);
-        for (auto &e : g.globalOutputs) e = alias[e];
+        for (auto &e : g.globalOutputs) {
+            g.outputTensors.push_back(edges[e].tensor);
+            e = alias[e];
+        }
         return g;
     }
 }// namespace refactor::computation

@@ -133,6 +133,10 @@ namespace refactor::runtime {
         if (cudaStreamSynchronize(streamOf(const_cast<Resources &>(_resources))) != cudaSuccess) RUNTIME_ERROR("stream synchronize failed");
     }
 
+    void Stream::deviceSync() const {
+        if (cudaDeviceSynchronize() != cudaSuccess) RUNTIME_ERROR("device synchronize failed");
+    }
+
     void Stream::runEager() {
         std::vector<void const *> in;
         std::vector<void *> out;

@@ -73,6 +73,9 @@ namespace {
         // src/09python_ffi/src/executor.cc setInputBlob: the data already lives on the device
         void setInputBlob(count_t i, uintptr_t devicePtr, size_t bytes) {
             ASSERT(i < _inputs.size(), "input index out of range");
+            // the producer of the blob may have run on any stream (this executor's stream does not synchronise
+            // with the legacy default stream), so wait for the whole device before copying
+            _stream->deviceSync();
             _stream->setDataDevice(i, reinterpret_cast<void const *>(devicePtr), bytes);
             _stream->sync();
         }
@@ -143,7 +146,7 @@ namespace {
             auto kg = _g.lower(t);
             std::vector<Arc<Tensor>> in, out;
             for (auto e : kg.globalInputs) in.push_back(kg.edges[e].tensor);
-            for (auto e : kg.globalOutputs) out.push_back(kg.edges[e].tensor);
+            out = kg.outputTensors;
             auto stream = kg.lower(allocator);
             // constants are on the device now; drop the host copies (a 7B model is 13 GB of them)
             for (auto &e : _g.edges)
