@@ -289,6 +289,24 @@ typedef struct rg_attn_decode_params {
 size_t rg_b200_attn_decode_workspace(const rg_attn_decode_params *);
 int rg_b200_attn_decode(const rg_attn_decode_params *, void *ws, const void *const *in, void *const *out, void *stream);
 
+/* Flash-decoding without caller-provided scratch.  No counterpart in the reference.
+ * Same inputs, outputs and results as rg_b200_attn_decode, but the split-K scratch (arrival counters and partial
+ * records) sits in a fixed array inside this library's device image, so the call needs no workspace pointer and
+ * performs no device allocation of any kind.  It is meant for hosts that cannot hand a kernel fresh device
+ * memory at the point of the call: a runtime whose pool already owns the GPU's free memory (the reference's
+ * Nvidia device takes 90 % of it at start-up, src/02hardware/src/devices/nvidia/device.cc:24-35), a latency-bound
+ * serving loop that must not hit the synchronisation cudaMalloc implies, or a plugin that is only given input
+ * and output buffers.
+ *   - Limit: rg_b200_attn_decode_workspace(p) must not exceed rg_b200_attn_decode_static_capacity() (8 MiB);
+ *     larger requests return RG_ERR_LIMIT and launch nothing.  Every GPU that loads the library holds the array
+ *     until the process exits.
+ *   - The first call on each device looks up the array's device address (one-time set-up, with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Calls that may overlap on the GPU (different streams, or
+ *     graph branches) race on it; serialise them.  The counters are cleared at the start of every call. */
+size_t rg_b200_attn_decode_static_capacity(void);
+int rg_b200_attn_decode_static(const rg_attn_decode_params *, const void *const *in, void *const *out, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * AllReduce across the GPUs of one box.  Replaces AllReduceNccl + NcclCommunicator
  * (src/04kernel/src/kernels/all_reduce/nccl_kernel.cu:9-19, src/04kernel/src/utilities/cuda/nccl_communicator.cu:11-44).

@@ -109,7 +109,8 @@ OPS = {
     "attention": AttentionParams, "attn_decode": AttnDecodeParams,
 }
 # every symbol include/rg_b200.h declares
-SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_comm_create",
+SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_attn_decode_static",
+            "rg_b200_attn_decode_static_capacity", "rg_b200_comm_create",
             "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]
            + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])
 
@@ -133,6 +134,9 @@ def load() -> C.CDLL:
             ws = getattr(lib, f"rg_b200_{name}_workspace")
             ws.restype = C.c_size_t
             ws.argtypes = [C.POINTER(ptype)]
+        lib.rg_b200_attn_decode_static_capacity.restype = C.c_size_t
+        lib.rg_b200_attn_decode_static.restype = C.c_int
+        lib.rg_b200_attn_decode_static.argtypes = [C.POINTER(AttnDecodeParams), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p]
         lib.rg_b200_comm_create.argtypes = [C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
         lib.rg_b200_comm_connect.argtypes = [C.c_void_p, C.c_void_p]
         lib.rg_b200_comm_status.argtypes = [C.c_void_p]
@@ -165,4 +169,12 @@ def call(op: str, params, inputs, outputs, ws: int = 0, stream: int = 0, check: 
     rc = getattr(load(), f"rg_b200_{op}")(C.byref(params), ws or None, _ptrs(inputs), _ptrs(outputs), stream or None)
     if check and rc != OK:
         raise RgError(op, rc)
+    return rc
+
+
+def attn_decode_static(params, inputs, outputs, stream: int = 0, check: bool = True) -> int:
+    """rg_b200_attn_decode_static: flash-decoding with library-owned scratch (no workspace argument)."""
+    rc = load().rg_b200_attn_decode_static(C.byref(params), _ptrs(inputs), _ptrs(outputs), stream or None)
+    if check and rc != OK:
+        raise RgError("attn_decode_static", rc)
     return rc

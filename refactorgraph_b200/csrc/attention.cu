@@ -457,4 +457,35 @@ int rg_b200_attn_decode(const rg_attn_decode_params *p, void *ws, const void *co
     }
     return RG_ERR_DTYPE;
 }
+
+// ---- allocation-free variant ---------------------------------------------------------------------------------
+// Scratch for rg_b200_attn_decode_static: arrival counters followed by the per-split partial records, held in
+// device memory that belongs to this library image instead of to the caller.  Every GPU that loads the library
+// carries these 8 MiB until the process exits.
+#define RG_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char s_decode_scratch[RG_DECODE_STATIC_SCRATCH_BYTES];
+
+size_t rg_b200_attn_decode_static_capacity(void) { return RG_DECODE_STATIC_SCRATCH_BYTES; }
+
+int rg_b200_attn_decode_static(const rg_attn_decode_params *p, const void *const *in, void *const *out, void *stream) {
+    if (!p) return RG_ERR_NULL;
+    const DecodePlan pl = decode_plan(p);
+    if (pl.cnt_bytes + pl.part_bytes > RG_DECODE_STATIC_SCRATCH_BYTES) return RG_ERR_LIMIT;
+    // In host code `s_decode_scratch` names a host-side shadow of the symbol, not device memory, so the device
+    // address is looked up once per device (with that device current) and remembered.
+    static void *scratch_of_device[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RG_ERR_CUDA;
+    if (!scratch_of_device[dev]) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, s_decode_scratch) != cudaSuccess || !ptr) return RG_ERR_CUDA;
+        scratch_of_device[dev] = ptr;
+    }
+    void *ws = scratch_of_device[dev];
+    auto st = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the previous call left: the arrival counters have to start at zero
+    if (cudaMemsetAsync(ws, 0, pl.cnt_bytes, st) != cudaSuccess) return RG_ERR_CUDA;
+    return rg_b200_attn_decode(p, ws, in, out, stream);
 }
+}
+
