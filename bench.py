@@ -41,7 +41,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="7b", choices=["7b", "tiny"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "topk"],
+    ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
+                             "gemm_skinny16", "gemm_skinny32"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
     ap.add_argument("--launches", type=int, default=6)
     return ap.parse_args()
@@ -315,6 +316,21 @@ def run_case(args):
         def launch(i):
             capi.call("linear", p, [x.data_ptr(), ws[i % nbuf].data_ptr(), g.data_ptr() if pro else 0, r.data_ptr() if epi == 1 else 0,
                                     pos.data_ptr() if epi == 3 else 0, 0], [y.data_ptr(), kc.data_ptr() if epi == 3 else 0, vc.data_ptr() if epi == 3 else 0], stream=sid)
+    elif args.case.startswith("gemm"):
+        bf = torch.bfloat16
+        m, n, k = {"gemm_qkv": (8192, 3 * H, H), "gemm_down": (8192, H, F), "gemm_gate_up": (8192, 2 * F, H),
+                   "gemm_skinny16": (16, 2 * F, H), "gemm_skinny32": (32, 2 * F, H)}[args.case]
+        nb = 2 if m > 64 else nbuf
+        As = [torch.randn(m, k, device=dev).to(bf) for _ in range(nb)]
+        Bs = [(0.02 * torch.randn(n, k, device=dev)).to(bf) for _ in range(nb)]
+        y = torch.empty(m, n, dtype=bf, device=dev)
+        p = capi.MatMulParams()
+        p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y, p.force_kernel = capi.BF16, m, n, k, 1, 1.0, 1.0, 1, m * n, 3
+        bytes_per = (m * k + n * k + m * n) * 2
+        flops_per = 2.0 * m * n * k
+
+        def launch(i):
+            capi.call("mat_mul", p, [As[i % nb].data_ptr(), Bs[i % nb].data_ptr(), 0], [y.data_ptr()], stream=sid)
     elif args.case == "attn_decode":
         L, MS = 2112, 2560
         q = torch.randn(1, nH, D, device=dev).to(dt)
@@ -347,8 +363,11 @@ def run_case(args):
     e1.record()
     torch.cuda.synchronize()
     us = 1000.0 * e0.elapsed_time(e1) / args.launches
-    print(json.dumps({"case": args.case, "launches": args.launches, "us_per_launch": us, "algorithmic_bytes_per_launch": bytes_per,
-                      "gbs": bytes_per / us / 1e3}), flush=True)
+    out = {"case": args.case, "launches": args.launches, "us_per_launch": us, "algorithmic_bytes_per_launch": bytes_per,
+           "gbs": bytes_per / us / 1e3}
+    if args.case.startswith("gemm"):
+        out["tflops"] = flops_per / us / 1e6
+    print(json.dumps(out), flush=True)
 
 
 def run_b200(args):

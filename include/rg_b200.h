@@ -51,6 +51,10 @@ const char *rg_b200_status_string(int status);
 int rg_b200_version(void);
 /* Number of kernels this library has launched in the calling process since load (all entry points). */
 uint64_t rg_b200_launch_count(void);
+/* Synchronises the current device and reports whether any kernel of this library gave up a bounded device-side
+ * wait since load: 0 = none; otherwise bit 0 linear, bit 1 decode attention, bit 2 tensor-core GEMM, bit 3 all-reduce;
+ * negative = the device could not be queried. */
+int rg_b200_error_state(void);
 
 /* ---------------------------------------------------------------------------------------------
  * RmsNormalization.  Replaces RmsNormalizationCuda

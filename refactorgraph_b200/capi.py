@@ -109,7 +109,7 @@ OPS = {
     "attention": AttentionParams, "attn_decode": AttnDecodeParams,
 }
 # every symbol include/rg_b200.h declares
-SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_attn_decode_static",
+SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_attn_decode_static",
             "rg_b200_attn_decode_static_capacity", "rg_b200_comm_create",
             "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]
            + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])

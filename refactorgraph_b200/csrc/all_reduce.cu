@@ -1,5 +1,8 @@
 // placeholder until the peer-memory all-reduce lands
-#include "common.cuh"
+#include "gemm_dispatch.cuh"
+namespace rg {
+int all_reduce_error_word() { return 0; }
+}// namespace rg
 extern "C" {
 int rg_b200_comm_create(int, int, size_t, rg_comm **, void *) { return RG_ERR_UNSUPPORTED; }
 int rg_b200_comm_connect(rg_comm *, const void *) { return RG_ERR_UNSUPPORTED; }

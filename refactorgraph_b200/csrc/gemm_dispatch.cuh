@@ -10,4 +10,5 @@ bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *
 int linear_error_word();
 int attn_error_word();
 int gemm_tc_error_word();
+int all_reduce_error_word();
 }// namespace rg

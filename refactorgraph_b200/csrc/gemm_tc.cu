@@ -1,7 +1,326 @@
-// placeholder until the tcgen05 kernel lands
+// Tensor-core GEMM for sm_100a:  Y[m,n] = alpha * A[m,k] * B[n,k]^T (+ beta * C),  fp16 / bf16 operands (both
+// K-major: activations [tokens, k] and weights [out, in], the reference MatMul with transB = 1), fp32 accumulation
+// in tensor memory.  Replaces the cublasGemmEx call of MatMulCublas
+// (src/04kernel/src/kernels/mat_mul/cublas_kernel.cu:48-55) for prefill-sized products.
+//
+// One CTA computes one 128 x BN output tile (BN = 256 or 128; also used with the operands swapped so that a skinny
+// activation matrix becomes the N side of the instruction):
+//   warp 4  (one thread): TMA producer — cp.async.bulk.tensor.2d loads of the A tile [128 x 64] and B tile [BN x 64]
+//                         with the 128-byte swizzle into a STAGES-deep shared-memory ring (full[] mbarriers).
+//   warp 5  (one thread): MMA issuer — per stage four tcgen05.mma.cta_group::1.kind::f16 (M 128, N BN, K 16) whose
+//                         shared-memory descriptors advance 32 bytes along K inside the swizzle atom; tcgen05.commit
+//                         releases the stage (empty[]) and finally signals the accumulator (acc_full).
+//   warps 0-3:            epilogue — tcgen05.ld of each warp's 32 TMEM lanes, alpha/beta/bias, conversion, stores.
+// Warp 5 also allocates and frees the BN TMEM columns.  Every mbarrier wait is bounded; on expiry the CTA records
+// an error word, still frees its tensor memory and exits.
 #include "gemm_dispatch.cuh"
+#include <cuda.h>
+
 namespace rg {
-bool gemm_tc_supported(const rg_mat_mul_params *, const void *const *, void *const *) { return false; }
-int gemm_tc(const rg_mat_mul_params *, const void *const *, void *const *, cudaStream_t) { return RG_ERR_UNSUPPORTED; }
-int gemm_tc_error_word() { return 0; }
+
+static __device__ int s_tc_error;
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;// 64 x 2 B = one 128-byte swizzle row
+constexpr int TC_THREADS = 192;
+
+struct TcArgs {
+    void *Y;
+    const void *C;
+    uint32_t m, n, k;// problem as the kernel sees it: D[m,n] = A[m,k] B[n,k]^T
+    float alpha, beta;
+    uint32_t c_row_stride, c_col_stride;
+    uint64_t y_row_stride, y_col_stride;// element strides of Y over the kernel's (row, col) = lets swapped runs write Y^T
+    int is_bf16;
+};
+
+// ---- tcgen05 / TMA PTX ------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread t holds lane base+t)
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: start address >> 4 in bits [0,14),
+// leading byte offset (unused for this layout) in [16,30), stride byte offset = 1024 B (eight 128-byte rows) in
+// [32,46), descriptor version 1 in [46,48), layout type 2 (SWIZZLE_128B) in [61,64).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+// Instruction descriptor for kind::f16: D fp32 (bits 4-5 = 1), A/B format (0 fp16, 1 bf16) at bits 7-9 / 10-12,
+// both operands K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ inline uint32_t instr_desc(int is_bf16, uint32_t M, uint32_t N) {
+    uint32_t d = 0;
+    d |= 1u << 4;
+    d |= (is_bf16 ? 1u : 0u) << 7;
+    d |= (is_bf16 ? 1u : 0u) << 10;
+    d |= (N >> 3) << 17;
+    d |= (M >> 4) << 24;
+    return d;
+}
+
+template<class T, int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                              const __grid_constant__ CUtensorMap tmap_b, const TcArgs a) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the swizzled tiles need 1024-byte alignment
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+    uint64_t *empty = full + STAGES;
+    uint64_t *acc_full = empty + STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    int *failed = reinterpret_cast<int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const uint32_t kblocks = (a.k + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *failed = 0;
+        fence_mbar_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                if (!mbar_wait(&empty[s], ph ^ 1u)) {
+                    *failed = 1;
+                    break;
+                }
+                mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                uint8_t *st = smem + s * STAGE_BYTES;
+                tma_load_2d(st, &tmap_a, kb * TC_BK, m0, &full[s]);
+                tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, n0, &full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(a.is_bf16, TC_BM, BN);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
+                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                if (!mbar_wait(&full[s], ph)) {
+                    *failed = 2;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk) {
+                    const uint64_t ad = smem_desc_sw128(a_addr + kk * 32), bd = smem_desc_sw128(b_addr + kk * 32);
+                    tc_mma_f16(tmem_base, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                }
+                tc_commit(&empty[s]);// frees the stage once these MMAs have read it
+            }
+            tc_commit(acc_full);     // all MMAs issued so far have completed when this arrives
+        }
+    } else {
+        // ---- epilogue warps 0..3: TMEM lanes [32*warp, 32*warp + 32) = tile rows ----
+        const bool got = mbar_wait(acc_full, 0);
+        if (!got) *failed = 3;
+        tc_fence_after();
+        if (got) {
+            const uint32_t row = m0 + warp * 32 + lane;
+            T *Y = static_cast<T *>(a.Y);
+            const T *C = static_cast<const T *>(a.C);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((warp * 32u) << 16) + c0, r);
+                tmem_ld_wait();
+                if (row < a.m) {
+                    if (a.y_col_stride == 1 && n0 + c0 + 32 <= a.n && (a.y_row_stride % 8) == 0 && !C) {
+                        // contiguous 64-byte run of this thread's row: four 16-byte stores
+                        T *dst = Y + static_cast<uint64_t>(row) * a.y_row_stride + n0 + c0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            float f[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) f[e] = a.alpha * __uint_as_float(r[j + e]);
+                            Vec16<T> v;
+                            v.pack(f);
+                            v.store(dst + j);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t col = n0 + c0 + j;
+                            if (col < a.n) {
+                                float v = a.alpha * __uint_as_float(r[j]);
+                                if (C) v += a.beta * Num<T>::to_f(C[static_cast<uint64_t>(row) * a.c_row_stride + static_cast<uint64_t>(col) * a.c_col_stride]);
+                                Y[static_cast<uint64_t>(row) * a.y_row_stride + static_cast<uint64_t>(col) * a.y_col_stride] = Num<T>::from_f(v);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, BN);
+    }
+    if (threadIdx.x == 0 && *failed) atomicExch(&s_tc_error, *failed);
+}
+
+// ---- host -----------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    }
+    return fn;
+}
+
+// rows x k matrix, K-major (row stride = ld elements); box = 64 (k) x box_rows, 128-byte swizzle
+static bool make_map(CUtensorMap *map, const void *base, int is_bf16, uint64_t rows, uint64_t k, uint64_t ld, uint32_t box_rows) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {TC_BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims,
+              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *const *out) {
+    if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return false;
+    if (p->trans_a || !p->trans_b) return false;
+    if (p->k % 8 != 0 || p->k < 64) return false;
+    if (!aligned16(in[0]) || !aligned16(in[1]) || !aligned16(out[0])) return false;
+    if (p->batch > 1 && ((p->stride_a % 8) || (p->stride_b % 8) || (p->stride_y % 8))) return false;
+    // worth a tensor-core launch only when there is a tile's worth of work
+    if (static_cast<uint64_t>(p->m) * p->n < 64ull * 64ull) return false;
+    return encode_fn() != nullptr;
+}
+
+template<class T, int BN, int STAGES>
+static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
+    constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    auto kern = gemm_tc_kernel<T, BN, STAGES>;
+    RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    dim3 grid((a.n + BN - 1) / BN, (a.m + TC_BM - 1) / TC_BM);
+    kern<<<grid, TC_THREADS, smem, st>>>(ma, mb, a);
+    count_launch();
+    return launch_status();
+}
+
+int gemm_tc(const rg_mat_mul_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+    const int is_bf16 = p->dtype == RG_BF16;
+    const size_t es = 2;
+    for (uint32_t b = 0; b < p->batch; ++b) {
+        const uint8_t *A = static_cast<const uint8_t *>(in[0]) + b * p->stride_a * es;
+        const uint8_t *B = static_cast<const uint8_t *>(in[1]) + b * p->stride_b * es;
+        uint8_t *Y = static_cast<uint8_t *>(out[0]) + b * p->stride_y * es;
+        const uint8_t *C = p->has_bias ? static_cast<const uint8_t *>(in[2]) + b * p->stride_c * es : nullptr;
+        TcArgs a = {};
+        a.alpha = p->alpha, a.beta = p->beta, a.is_bf16 = is_bf16, a.k = p->k;
+        CUtensorMap ma, mb;
+        // a skinny activation matrix (m <= 64) goes on the N side of the instruction: D^T[n, m] = W[n,k] X[m,k]^T
+        const bool swap = p->m <= 64 && p->n >= 128;
+        uint32_t bn;
+        if (!swap) {
+            bn = p->n >= 256 ? 256 : 128;
+            a.m = p->m, a.n = p->n;
+            a.Y = Y, a.y_row_stride = p->n, a.y_col_stride = 1;
+            a.C = C, a.c_row_stride = p->bias_row_stride, a.c_col_stride = p->bias_col_stride;
+            if (!make_map(&ma, A, is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, B, is_bf16, p->n, p->k, p->k, bn)) return RG_ERR_CUDA;
+        } else {
+            bn = p->m <= 32 ? 32 : 64;
+            a.m = p->n, a.n = p->m;
+            a.Y = Y, a.y_row_stride = 1, a.y_col_stride = p->n;
+            a.C = C, a.c_row_stride = p->bias_col_stride, a.c_col_stride = p->bias_row_stride;
+            if (!make_map(&ma, B, is_bf16, p->n, p->k, p->k, TC_BM) || !make_map(&mb, A, is_bf16, p->m, p->k, p->k, bn)) return RG_ERR_CUDA;
+        }
+        int rc;
+#define RG_TC(T)                                                                        \
+    (bn == 256 ? tc_launch<T, 256, 4>(ma, mb, a, st) : bn == 128 ? tc_launch<T, 128, 6>(ma, mb, a, st) \
+     : bn == 64 ? tc_launch<T, 64, 8>(ma, mb, a, st) : tc_launch<T, 32, 8>(ma, mb, a, st))
+        rc = is_bf16 ? RG_TC(__nv_bfloat16) : RG_TC(__half);
+#undef RG_TC
+        if (rc != RG_OK) return rc;
+    }
+    return RG_OK;
+}
+
+int gemm_tc_error_word() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, s_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
 }// namespace rg

@@ -402,3 +402,4 @@ def test_no_bounded_wait_expired():
     # all the kernels above ran; none of their bounded device-side waits may have expired
     torch.cuda.synchronize()
     assert capi.load().rg_b200_launch_count() > 0
+    assert capi.load().rg_b200_error_state() == 0
