@@ -232,6 +232,29 @@ typedef struct rg_kv_layout {
     uint32_t max_blocks_per_seq; /* paged: row length of the block table */
 } rg_kv_layout;
 
+/* QKV split + RoPE + cache append for batched decode (no reference counterpart; what the m <= 4 linear kernel does in
+ * its epilogue, as a separate launch behind a tensor-core GEMM).  qkv[tokens, (n_heads + 2 n_kv_heads) * D]: q heads
+ * are rotated to q[tokens, n_heads * D]; k heads are rotated and v heads copied into the caches at positions[token].
+ * inputs {qkv, positions (int64[tokens]), block_table (int32) or NULL}, outputs {q, k_cache, v_cache}. */
+typedef struct rg_qkv_rope_append_params {
+    int32_t dtype;
+    uint32_t tokens, n_heads;
+    float theta;
+    rg_kv_layout kv;
+} rg_qkv_rope_append_params;
+size_t rg_b200_qkv_rope_append_workspace(const rg_qkv_rope_append_params *);
+int rg_b200_qkv_rope_append(const rg_qkv_rope_append_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* SiLU gate: y[r, j] = silu(x[r, j]) * x[r, f + j] for x[rows, 2f] — the Sigmoid, Mul, Mul triple of the reference
+ * graph (src/04kernel/src/kernels/simple_unary/cuda_kernel.cc:96-175, simple_binary/cuda_kernel.cc:42-136) in one pass.
+ * inputs {x}, outputs {y[rows, f]}. */
+typedef struct rg_swiglu_params {
+    int32_t dtype;
+    uint32_t rows, f;
+} rg_swiglu_params;
+size_t rg_b200_swiglu_workspace(const rg_swiglu_params *);
+int rg_b200_swiglu(const rg_swiglu_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
 /* Fused decode linear layer  Y = epilogue( prologue(X) * W^T ),  W[n,k] row-major (the reference MatMul with
  * transB = 1), X[m,k], m <= 4.  One launch replaces RmsNormalization + MatMul + (Add | Sigmoid,Mul,Mul |
  * RoPE + cache append) of the reference graph.
@@ -320,11 +343,17 @@ int rg_b200_attn_decode_static(const rg_attn_decode_params *, const void *const 
  * with plain loads, summed in fp32 in rank order (bit-identical on every rank).  Device-side waits on peer
  * flags are bounded; on expiry the status word is set and the call that observes it returns RG_ERR_TIMEOUT.
  * op uses AllReduceType (src/04kernel/include/kernel/attributes/communication.h:5-11): 0 Sum, 1 Avg, 2 Min, 3 Max, 4 Prod.
- * inputs {x}, outputs {y}; bytes <= the capacity given at create. */
+ * inputs {x, residual or NULL}, outputs {y}; y = reduce(x) (+ residual, added after the reduced value has been rounded
+ * to the storage type); bytes <= the capacity given at create.  Every rank must issue the same sequence of calls. */
 typedef struct rg_comm rg_comm;
 int rg_b200_comm_create(int world, int rank, size_t capacity_bytes, rg_comm **out, void *handle64);
 int rg_b200_comm_connect(rg_comm *, const void *all_handles /* world * 64 bytes */);
-int rg_b200_comm_status(rg_comm *); /* RG_OK or RG_ERR_TIMEOUT seen by a kernel; synchronises the stream last used */
+/* Same-process wiring: bases[r] = rg_b200_comm_base of rank r's communicator (peer access already enabled). */
+void *rg_b200_comm_base(rg_comm *);
+int rg_b200_comm_connect_ptrs(rg_comm *, const void *const *bases);
+/* Bound of the device-side wait for a peer, in nanoseconds (default 2 s). */
+int rg_b200_comm_set_wait_ns(rg_comm *, uint64_t ns);
+int rg_b200_comm_status(rg_comm *); /* RG_OK, or RG_ERR_TIMEOUT once a kernel gave up waiting for a peer; synchronises the device */
 int rg_b200_comm_destroy(rg_comm *);
 typedef struct rg_all_reduce_params {
     int32_t dtype, op;

@@ -87,6 +87,14 @@ class LinearParams(C.Structure):
                 ("theta", C.c_float), ("kv", KvLayout)]
 
 
+class QkvRopeAppendParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("tokens", C.c_uint32), ("n_heads", C.c_uint32), ("theta", C.c_float), ("kv", KvLayout)]
+
+
+class SwigluParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("rows", C.c_uint32), ("f", C.c_uint32)]
+
+
 class AttentionParams(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint32), ("n_heads", C.c_uint32), ("n_kv_heads", C.c_uint32),
                 ("seq_len", C.c_uint32), ("head_dim", C.c_uint32), ("max_seq", C.c_uint32), ("has_cache", C.c_int32)]
@@ -106,11 +114,13 @@ OPS = {
     "rms_norm": RmsNormParams, "softmax": SoftmaxParams, "topk": TopkParams, "topk_sample": TopkSampleParams,
     "gather": GatherParams, "binary": BinaryParams, "unary": UnaryParams, "where": WhereParams,
     "transpose": TransposeParams, "rope": RopeParams, "state_update": StateUpdateParams, "mat_mul": MatMulParams, "linear": LinearParams,
-    "attention": AttentionParams, "attn_decode": AttnDecodeParams,
+    "attention": AttentionParams, "attn_decode": AttnDecodeParams, "qkv_rope_append": QkvRopeAppendParams,
+    "swiglu": SwigluParams,
 }
 # every symbol include/rg_b200.h declares
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_attn_decode_static",
-            "rg_b200_attn_decode_static_capacity", "rg_b200_comm_create",
+            "rg_b200_attn_decode_static_capacity", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_connect_ptrs",
+            "rg_b200_comm_set_wait_ns",
             "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]
            + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])
 
@@ -140,6 +150,10 @@ def load() -> C.CDLL:
         lib.rg_b200_comm_create.argtypes = [C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
         lib.rg_b200_comm_connect.argtypes = [C.c_void_p, C.c_void_p]
         lib.rg_b200_comm_status.argtypes = [C.c_void_p]
+        lib.rg_b200_comm_base.restype = C.c_void_p
+        lib.rg_b200_comm_base.argtypes = [C.c_void_p]
+        lib.rg_b200_comm_connect_ptrs.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        lib.rg_b200_comm_set_wait_ns.argtypes = [C.c_void_p, C.c_uint64]
         lib.rg_b200_comm_destroy.argtypes = [C.c_void_p]
         lib.rg_b200_all_reduce.argtypes = [C.c_void_p, C.POINTER(AllReduceParams), C.POINTER(C.c_void_p),
                                            C.POINTER(C.c_void_p), C.c_void_p]
@@ -178,3 +192,54 @@ def attn_decode_static(params, inputs, outputs, stream: int = 0, check: bool = T
     if check and rc != OK:
         raise RgError("attn_decode_static", rc)
     return rc
+
+
+class Comm:
+    """One rank's NVLink peer-memory communicator (rg_b200_comm_*).  `exchange(handle: bytes) -> list[bytes]` is any
+    host transport that returns every rank's 64-byte handle in rank order (e.g. torch.distributed.all_gather_object)."""
+
+    def __init__(self, world: int, rank: int, capacity_bytes: int, exchange=None):
+        lib = load()
+        self.world, self.rank = world, rank
+        self._ptr = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        rc = lib.rg_b200_comm_create(world, rank, capacity_bytes, C.byref(self._ptr), handle)
+        if rc != OK:
+            raise RgError("comm_create", rc)
+        if world > 1 and exchange is not None:
+            handles = exchange(bytes(handle))
+            blob = (C.c_ubyte * (64 * world)).from_buffer_copy(b"".join(handles))
+            rc = lib.rg_b200_comm_connect(self._ptr, blob)
+            if rc != OK:
+                raise RgError("comm_connect", rc)
+
+    @property
+    def address(self) -> int:
+        return self._ptr.value
+
+    def connect_ptrs(self, bases):
+        arr = (C.c_void_p * self.world)(*bases)
+        rc = load().rg_b200_comm_connect_ptrs(self._ptr, arr)
+        if rc != OK:
+            raise RgError("comm_connect_ptrs", rc)
+
+    def base(self) -> int:
+        return load().rg_b200_comm_base(self._ptr)
+
+    def set_wait_ns(self, ns: int):
+        load().rg_b200_comm_set_wait_ns(self._ptr, ns)
+
+    def all_reduce(self, dtype: int, op: int, count: int, x: int, y: int, residual: int = 0, stream: int = 0, check: bool = True) -> int:
+        p = AllReduceParams(dtype, op, count)
+        rc = load().rg_b200_all_reduce(self._ptr, C.byref(p), _ptrs([x, residual]), _ptrs([y]), stream or None)
+        if check and rc != OK:
+            raise RgError("all_reduce", rc)
+        return rc
+
+    def status(self) -> int:
+        return load().rg_b200_comm_status(self._ptr)
+
+    def destroy(self):
+        if self._ptr:
+            load().rg_b200_comm_destroy(self._ptr)
+            self._ptr = C.c_void_p()

@@ -193,6 +193,63 @@ __global__ void rope_kernel(const T *__restrict__ x, const int64_t *__restrict__
     }
 }
 
+// ---- QKV split + RoPE + cache append (batched decode; the m <= 4 path fuses this into the linear kernel) -----
+// One thread per (token, head, i < D/2) of the fused projection qkv[m, (nH + 2 nKV) * D].
+template<class T>
+__global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t *__restrict__ pos,
+                                       const int32_t *__restrict__ table, T *__restrict__ q, T *__restrict__ kc,
+                                       T *__restrict__ vc, uint32_t tokens, uint32_t nq, rg_kv_layout kv, float log2_theta) {
+    const uint32_t D = kv.head_dim, half = D / 2, nkv = kv.n_kv_heads, heads = nq + 2 * nkv;
+    const uint64_t total = static_cast<uint64_t>(tokens) * heads * half;
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t i = static_cast<uint32_t>(t % half);
+        const uint32_t h = static_cast<uint32_t>((t / half) % heads);
+        const uint32_t m = static_cast<uint32_t>(t / half / heads);
+        const T *src = qkv + (static_cast<uint64_t>(m) * heads + h) * D;
+        float lo = Num<T>::to_f(src[i]), hi = Num<T>::to_f(src[i + half]);
+        const int64_t p = pos[m];
+        if (h < nq + nkv) {
+            const float inv_freq = exp2f(-log2_theta * (2.0f * static_cast<float>(i) / static_cast<float>(D)));
+            float sn, cs;
+            sincosf(static_cast<float>(p) * inv_freq, &sn, &cs);
+            const float a0 = lo * cs - hi * sn, b0 = hi * cs + lo * sn;
+            lo = a0, hi = b0;
+        }
+        if (h < nq) {
+            T *dst = q + (static_cast<uint64_t>(m) * nq + h) * D;
+            dst[i] = Num<T>::from_f(lo);
+            dst[i + half] = Num<T>::from_f(hi);
+        } else {
+            const bool is_k = h < nq + nkv;
+            const uint32_t kvh = is_k ? h - nq : h - nq - nkv;
+            T *cache = is_k ? kc : vc;
+            uint64_t base;
+            if (table) {
+                const uint32_t page = kv.page_size;
+                const int32_t blk = table[static_cast<uint64_t>(m) * kv.max_blocks_per_seq + static_cast<uint32_t>(p) / page];
+                base = ((static_cast<uint64_t>(blk) * nkv + kvh) * page + static_cast<uint32_t>(p) % page) * D;
+            } else {
+                base = ((static_cast<uint64_t>(m) * nkv + kvh) * kv.max_seq + static_cast<uint64_t>(p)) * D;
+            }
+            cache[base + i] = Num<T>::from_f(lo);
+            cache[base + i + half] = Num<T>::from_f(hi);
+        }
+    }
+}
+
+// y[r, j] = silu(x[r, j]) * x[r, f + j]
+template<class T>
+__global__ void swiglu_kernel(const T *__restrict__ x, T *__restrict__ y, uint32_t rows, uint32_t f) {
+    const uint64_t total = static_cast<uint64_t>(rows) * f;
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint64_t r = t / f, j = t % f;
+        const float g = Num<T>::to_f(x[r * 2 * f + j]), u = Num<T>::to_f(x[r * 2 * f + f + j]);
+        y[t] = Num<T>::from_f(g / (1.f + expf(-g)) * u);
+    }
+}
+
 __global__ void state_update_kernel(const int64_t *__restrict__ src, int64_t *__restrict__ state, uint32_t n,
                                     int64_t delta) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -343,6 +400,48 @@ int rg_b200_state_update(const rg_state_update_params *p, void *, const void *co
     if (p->n == 0) return RG_OK;
     state_update_kernel<<<(p->n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int64_t *>(in[0]), static_cast<int64_t *>(out[0]), p->n, p->delta);
+    count_launch();
+    return launch_status();
+}
+
+size_t rg_b200_qkv_rope_append_workspace(const rg_qkv_rope_append_params *) { return 0; }
+int rg_b200_qkv_rope_append(const rg_qkv_rope_append_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !in[1] || !out[0] || !out[1] || !out[2]) return RG_ERR_NULL;
+    const uint32_t D = p->kv.head_dim;
+    if (D == 0 || D % 2 != 0 || p->kv.n_kv_heads == 0 || !(p->theta > 0.f)) return RG_ERR_SHAPE;
+    if (in[2] && p->kv.page_size == 0) return RG_ERR_SHAPE;
+    const uint64_t total = static_cast<uint64_t>(p->tokens) * (p->n_heads + 2 * p->kv.n_kv_heads) * (D / 2);
+    if (total == 0) return RG_OK;
+    auto st = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(total, 256);
+    const float l2t = log2f(p->theta);
+    auto pos = static_cast<const int64_t *>(in[1]);
+    auto tab = static_cast<const int32_t *>(in[2]);
+#define RG_QRA(T) qkv_rope_append_kernel<T><<<g, 256, 0, st>>>(static_cast<const T *>(in[0]), pos, tab, static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t)
+    switch (p->dtype) {
+        case RG_F32: RG_QRA(float); break;
+        case RG_FP16: RG_QRA(__half); break;
+        case RG_BF16: RG_QRA(__nv_bfloat16); break;
+        default: return RG_ERR_DTYPE;
+    }
+#undef RG_QRA
+    count_launch();
+    return launch_status();
+}
+
+size_t rg_b200_swiglu_workspace(const rg_swiglu_params *) { return 0; }
+int rg_b200_swiglu(const rg_swiglu_params *p, void *, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+    const uint64_t total = static_cast<uint64_t>(p->rows) * p->f;
+    if (total == 0) return RG_OK;
+    auto st = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(total, 256);
+    switch (p->dtype) {
+        case RG_F32: swiglu_kernel<float><<<g, 256, 0, st>>>(static_cast<const float *>(in[0]), static_cast<float *>(out[0]), p->rows, p->f); break;
+        case RG_FP16: swiglu_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half *>(in[0]), static_cast<__half *>(out[0]), p->rows, p->f); break;
+        case RG_BF16: swiglu_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(in[0]), static_cast<__nv_bfloat16 *>(out[0]), p->rows, p->f); break;
+        default: return RG_ERR_DTYPE;
+    }
     count_launch();
     return launch_status();
 }

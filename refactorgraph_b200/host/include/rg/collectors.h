@@ -94,6 +94,20 @@ namespace refactor::kernel {
             : InfoCollector(target), maxLen(maxLen_), pageSize(pageSize_) {}
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
+    // qkv[tokens, (nH + 2 nKV) * D] -> q[tokens, nH * D]; k (rotated) and v appended to the cache state edges.
+    // inputs {qkv, positions, [block_table], k_cache, v_cache}, outputs {q}
+    struct QkvRopeAppendCollector final : public InfoCollector {
+        dim_t nHeads, nKVHeads, headDim, pageSize;
+        float theta;
+        QkvRopeAppendCollector(Target target, dim_t nHeads_, dim_t nKVHeads_, dim_t headDim_, dim_t pageSize_, float theta_) noexcept
+            : InfoCollector(target), nHeads(nHeads_), nKVHeads(nKVHeads_), headDim(headDim_), pageSize(pageSize_), theta(theta_) {}
+        std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
+    };
+    // x[rows, 2f] -> silu(x[:, :f]) * x[:, f:]
+    struct SwigluCollector final : public InfoCollector {
+        explicit SwigluCollector(Target target) noexcept : InfoCollector(target) {}
+        std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
+    };
     // In-place int64 state update: inputs {state, [src]}; state = (src ? src : state) + delta.  The routine writes
     // through inputs[0] (a state edge of the graph); it has no outputs.
     RG_COLLECTOR(StateUpdateCollector, int64_t, delta);

@@ -89,6 +89,9 @@ namespace refactor::runtime {
 }// namespace refactor::runtime
 
 namespace refactor::kernel {
+    // wraps an rg_comm* created by the caller (not owned) so that AllReduce routines find it in Resources, the way
+    // the reference's AllReduceNccl fetches its NcclCommunicator (src/04kernel/src/kernels/all_reduce/nccl_kernel.cu:13)
+    runtime::ResourceBox makeCommResource(void *comm);
     // (stack bytes) <- allocator(nodes' workspace sizes -> offsets, edges -> offsets); alignment in bytes.
     struct AllocScheme {
         size_t stackBytes;

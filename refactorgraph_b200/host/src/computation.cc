@@ -257,6 +257,30 @@ namespace refactor::computation {
         CollectorBox candidateKernels(Target t) const final { return std::make_unique<AttentionDecodeCollector>(t, maxLen, pageSize); }
         std::vector<Arc<Tensor>> infer(TensorRefs in) const final { return one(in[0].get().dataType, in[0].get().shape); }
     };
+    struct QkvRopeAppend final : Operator {
+        dim_t nHeads, nKVHeads, headDim, pageSize;
+        float theta;
+        explicit QkvRopeAppend(Attributes const &a)
+            : nHeads(static_cast<dim_t>(getInt(a, "n_heads", 0))), nKVHeads(static_cast<dim_t>(getInt(a, "n_kv_heads", 0))),
+              headDim(static_cast<dim_t>(getInt(a, "head_dim", 0))), pageSize(static_cast<dim_t>(getInt(a, "page_size", 0))),
+              theta(static_cast<float>(getFloat(a, "theta", 10000.0))) {}
+        RG_OP_NAME("QkvRopeAppend")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<QkvRopeAppendCollector>(t, nHeads, nKVHeads, headDim, pageSize, theta); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            ASSERT(in[0].get().shape.size() == 2, "QkvRopeAppend: qkv must be [tokens, (nH + 2 nKV) * D]");
+            return one(in[0].get().dataType, Shape{in[0].get().shape[0], nHeads * headDim});
+        }
+    };
+    struct Swiglu final : Operator {
+        RG_OP_NAME("SwiGLU")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<SwigluCollector>(t); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            Shape o = in[0].get().shape;
+            ASSERT(!o.empty() && o.back() % 2 == 0, "SwiGLU: last dimension must be even");
+            o.back() /= 2;
+            return one(in[0].get().dataType, o);
+        }
+    };
     struct StateUpdate final : Operator {
         int64_t delta;
         explicit StateUpdate(int64_t d) : delta(d) {}
@@ -308,6 +332,8 @@ namespace refactor::computation {
         if (is({"b200::Linear"})) return std::make_unique<FusedLinear>(a);
         if (is({"b200::AttentionDecode"}))
             return std::make_unique<AttentionDecode>(static_cast<dim_t>(getInt(a, "max_len", 0)), static_cast<dim_t>(getInt(a, "page_size", 0)));
+        if (is({"b200::QkvRopeAppend"})) return std::make_unique<QkvRopeAppend>(a);
+        if (is({"b200::SwiGLU"})) return std::make_unique<Swiglu>();
         if (is({"b200::StateUpdate"})) return std::make_unique<StateUpdate>(getInt(a, "delta", 0));
         TODO("Unsupported operator " + type);
     }

@@ -490,6 +490,56 @@ namespace refactor::kernel {
         return ans;
     }
 
+    struct QkvRopeAppendB200 final : public Kernel {
+        rg_qkv_rope_append_params info;
+        bool paged;
+        QkvRopeAppendB200(rg_qkv_rope_append_params p, bool paged_) noexcept : info(p), paged(paged_) {}
+        RG_KERNEL_IDS(QkvRopeAppendB200, "QKV split + RoPE + cache append on B200")
+        RoutineWorkspace lower(Resources &res) const final {
+            auto st = res.fetchOrStore<CudaStream>();
+            return RoutineWorkspace([info = info, paged = paged, st](Resources &, void *ws, void const *const *in, void *const *out) {
+                int i = 2;
+                void const *in_[3] = {in[0], in[1], paged ? in[i++] : nullptr};
+                void *out_[3] = {out[0], const_cast<void *>(in[i]), const_cast<void *>(in[i + 1])};
+                check(rg_b200_qkv_rope_append(&info, ws, in_, out_, st->stream), "rg_b200_qkv_rope_append");
+            });
+        }
+    };
+    std::vector<KernelBox> QkvRopeAppendCollector::filter(TensorRefs inputs, TensorRefs) const {
+        std::vector<KernelBox> ans;
+        auto const &x = inputs[0].get();
+        if (_target != Target::Nvidia || !halfOrFloat(x.dataType) || x.shape.size() != 2) return ans;
+        if (inputs.size() != 4 && inputs.size() != 5) return ans;
+        const bool paged = inputs.size() == 5;
+        auto const &kc = inputs[inputs.size() - 2].get();
+        if (kc.shape.size() != 4 || x.shape[1] != (nHeads + 2 * nKVHeads) * headDim) return ans;
+        rg_qkv_rope_append_params p{};
+        p.dtype = x.dataType;
+        p.tokens = x.shape[0], p.n_heads = nHeads, p.theta = theta;
+        p.kv.n_kv_heads = nKVHeads, p.kv.head_dim = headDim;
+        if (paged) {
+            p.kv.page_size = pageSize ? pageSize : kc.shape[2];
+            p.kv.max_blocks_per_seq = inputs[2].get().shape.back();
+        } else {
+            p.kv.max_seq = kc.shape[2];
+        }
+        ans.emplace_back(std::make_unique<QkvRopeAppendB200>(p, paged));
+        return ans;
+    }
+
+    RG_SIMPLE_KERNEL(SwigluB200, rg_swiglu_params, rg_b200_swiglu, "SiLU gate on B200");
+    std::vector<KernelBox> SwigluCollector::filter(TensorRefs inputs, TensorRefs) const {
+        std::vector<KernelBox> ans;
+        auto const &x = inputs[0].get();
+        if (_target != Target::Nvidia || !halfOrFloat(x.dataType) || x.shape.empty() || x.shape.back() % 2 != 0) return ans;
+        rg_swiglu_params p{};
+        p.dtype = x.dataType;
+        p.f = x.shape.back() / 2;
+        p.rows = static_cast<uint32_t>(x.elementsSize() / x.shape.back());
+        ans.emplace_back(std::make_unique<SwigluB200>(p));
+        return ans;
+    }
+
     // state (outputs[0] aliases inputs[0] in the graph) = (src ? src : state) + delta
     std::vector<KernelBox> StateUpdateCollector::filter(TensorRefs inputs, TensorRefs) const {
         std::vector<KernelBox> ans;
@@ -508,9 +558,10 @@ namespace refactor::kernel {
     // stored there by whoever builds the Stream for this rank (graph.cc, from world/rank).
     struct CommResource final : public runtime::Resource {
         rg_comm *comm;
-        explicit CommResource(rg_comm *c) : comm(c) {}
+        bool owned;
+        explicit CommResource(rg_comm *c, bool owned_ = false) : comm(c), owned(owned_) {}
         ~CommResource() override {
-            if (comm) rg_b200_comm_destroy(comm);
+            if (comm && owned) rg_b200_comm_destroy(comm);
         }
         static size_t typeId() noexcept {
             static uint8_t ID = 1;
@@ -523,14 +574,16 @@ namespace refactor::kernel {
 
     struct AllReduceB200 final : public Kernel {
         rg_all_reduce_params info;
-        explicit AllReduceB200(rg_all_reduce_params p) noexcept : info(p) {}
+        bool hasResidual;
+        AllReduceB200(rg_all_reduce_params p, bool r) noexcept : info(p), hasResidual(r) {}
         RG_KERNEL_IDS(AllReduceB200, "AllReduce over NVLink peer memory on B200 (one-shot pull, fp32 accumulation)")
         RoutineWorkspace lower(Resources &res) const final {
             auto st = res.fetchOrStore<CudaStream>();
-            return RoutineWorkspace([info = info, st](Resources &res, void *, void const *const *in, void *const *out) {
+            return RoutineWorkspace([info = info, r = hasResidual, st](Resources &res, void *, void const *const *in, void *const *out) {
                 auto comm = res.fetch<CommResource>();
                 if (!comm) RUNTIME_ERROR("AllReduce: no communicator in Resources");
-                check(rg_b200_all_reduce(comm->comm, &info, in, out, st->stream), "rg_b200_all_reduce");
+                void const *in_[2] = {in[0], r ? in[1] : nullptr};
+                check(rg_b200_all_reduce(comm->comm, &info, in_, out, st->stream), "rg_b200_all_reduce");
             });
         }
     };
@@ -544,7 +597,7 @@ namespace refactor::kernel {
         p.dtype = x.dataType;
         p.op = static_cast<int>(type);
         p.count = x.elementsSize();
-        ans.emplace_back(std::make_unique<AllReduceB200>(p));
+        ans.emplace_back(std::make_unique<AllReduceB200>(p, inputs.size() > 1));
         return ans;
     }
 

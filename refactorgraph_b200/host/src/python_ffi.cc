@@ -116,6 +116,8 @@ namespace {
         uintptr_t outputAddress(count_t i) const { return reinterpret_cast<uintptr_t>(_stream->outputAddress(i)); }
         uintptr_t cudaStream() { return reinterpret_cast<uintptr_t>(_stream->resources().fetchOrStore<runtime::CudaStream>()->stream); }
         void setGraphMode(bool on) { _stream->setGraphMode(on); }
+        // address of an rg_comm created with rg_b200_comm_create (kept alive by the caller)
+        void setCommunicator(uintptr_t comm) { _stream->resources().fetchOrStore(kernel::makeCommResource(reinterpret_cast<void *>(comm))); }
         size_t nodeCount() const { return _stream->nodeCount(); }
     };
 
@@ -268,5 +270,6 @@ PYBIND11_MODULE(python_ffi, m) {
         .def("output_address", &Executor::outputAddress)
         .def("cuda_stream", &Executor::cudaStream)
         .def("set_graph_mode", &Executor::setGraphMode)
+        .def("set_communicator", &Executor::setCommunicator)
         .def("node_count", &Executor::nodeCount);
 }

@@ -112,6 +112,92 @@ def decode_step_graph(cfg: LlamaConfig, top_k: int = 1, sample: bool = False, te
     return g, index
 
 
+def shard_config(cfg: LlamaConfig, world: int) -> LlamaConfig:
+    """Per-rank shape of a tensor-parallel model: heads, kv heads and FFN columns split `world` ways."""
+    assert cfg.heads % world == 0 and cfg.kv_heads % world == 0 and cfg.ffn % world == 0
+    from dataclasses import replace
+    return replace(cfg, heads=cfg.heads // world, kv_heads=cfg.kv_heads // world, ffn=cfg.ffn // world)
+
+
+def shard_weights(cfg: LlamaConfig, weights: dict, world: int, rank: int) -> dict:
+    """Megatron-style split of full weights for rank `rank` of `world`: column-parallel QKV (whole heads per rank)
+    and gate/up, row-parallel O and down; norms, embedding and LM head replicated."""
+    D, nH, nKV, F = cfg.head_dim, cfg.heads, cfg.kv_heads, cfg.ffn
+    hr, kr, fr = nH // world, nKV // world, F // world
+    out = {}
+    for name, w in weights.items():
+        if name.endswith(".wqkv"):
+            q, k, v = w[: nH * D], w[nH * D: (nH + nKV) * D], w[(nH + nKV) * D:]
+            out[name] = np.concatenate([q[rank * hr * D: (rank + 1) * hr * D], k[rank * kr * D: (rank + 1) * kr * D],
+                                        v[rank * kr * D: (rank + 1) * kr * D]])
+        elif name.endswith(".wo"):
+            out[name] = np.ascontiguousarray(w[:, rank * hr * D: (rank + 1) * hr * D])
+        elif name.endswith(".wgu"):
+            out[name] = np.concatenate([w[rank * fr: (rank + 1) * fr], w[F + rank * fr: F + (rank + 1) * fr]])
+        elif name.endswith(".wd"):
+            out[name] = np.ascontiguousarray(w[:, rank * fr: (rank + 1) * fr])
+        else:
+            out[name] = w
+    return out
+
+
+def decode_step_graph_batched(cfg: LlamaConfig, world: int = 1, paged: bool = False, page: int = 16, max_blocks: int = 0,
+                              n_blocks: int = 0, top_k: int = 1, sample: bool = False, temperature: float = 1.0, seed: int = 0):
+    """Decode step for any batch size, optionally one rank of a tensor-parallel group and/or a paged KV cache.
+    `cfg` holds the PER-RANK shape (see shard_config).  Per layer: RmsNormalization, MatMul (tensor cores for
+    batch > 4), QkvRopeAppend, AttentionDecode, MatMul, AllReduceSum(+residual) or Add, RmsNormalization, MatMul,
+    SwiGLU, MatMul, AllReduceSum(+residual) or Add."""
+    g = GraphBuilder()
+    B, H, D = cfg.batch, cfg.hidden, cfg.head_dim
+    token = g.input("token", I64, (B,))
+    pos = g.input("pos", I64, (B,))
+    lens = g.input("lens", I64, (B,))
+    step = g.input("step", I64, (1,)) if sample else None
+    table = g.input("block_table", I32, (B, max_blocks)) if paged else None
+    for name, shape in weight_inputs(cfg):
+        g.input(name, cfg.dtype, shape)
+    cache_shape = (n_blocks, cfg.kv_heads, page, D) if paged else (B, cfg.kv_heads, cfg.max_seq, D)
+    for l in range(cfg.layers):
+        g.input(f"l{l}.k_cache", cfg.dtype, cache_shape)
+        g.input(f"l{l}.v_cache", cfg.dtype, cache_shape)
+    x = g.op("onnx::Gather", ["embed", token], axis=0)
+    for l in range(cfg.layers):
+        kc, vc = f"l{l}.k_cache", f"l{l}.v_cache"
+        n1 = g.op("llm::RmsNormalization", [x, f"l{l}.norm1"], epsilon=cfg.eps)
+        qkv = g.op("llm::MatMul", [n1, f"l{l}.wqkv"], transB=1)
+        q = g.op("b200::QkvRopeAppend", [qkv, pos] + ([table] if paged else []) + [kc, vc], n_heads=cfg.heads,
+                 n_kv_heads=cfg.kv_heads, head_dim=D, page_size=page if paged else 0, theta=cfg.theta)
+        q3 = g.op("onnx::Reshape", [q], shape=[B, cfg.heads, D])
+        a = g.op("b200::AttentionDecode", [q3, kc, vc, lens] + ([table] if paged else []), max_len=cfg.max_seq, page_size=page if paged else 0)
+        a2 = g.op("onnx::Reshape", [a], shape=[B, cfg.heads * D])
+        o = g.op("llm::MatMul", [a2, f"l{l}.wo"], transB=1)
+        h = g.op("onnx::AllReduceSum", [o, x]) if world > 1 else g.op("onnx::Add", [o, x])
+        n2 = g.op("llm::RmsNormalization", [h, f"l{l}.norm2"], epsilon=cfg.eps)
+        gu = g.op("llm::MatMul", [n2, f"l{l}.wgu"], transB=1)
+        u = g.op("b200::SwiGLU", [gu])
+        d = g.op("llm::MatMul", [u, f"l{l}.wd"], transB=1)
+        x = g.op("onnx::AllReduceSum", [d, h]) if world > 1 else g.op("onnx::Add", [d, h])
+    xf = g.op("llm::RmsNormalization", [x, "norm_f"], epsilon=cfg.eps)
+    logits = g.op("llm::MatMul", [xf, "lm_head"], transB=1)
+    index = {}
+    if sample:
+        nxt = g.op("b200::TopKSample", [logits, step], k=top_k, temperature=temperature, seed=seed)
+        g.op("b200::StateUpdate", [step], n_out=0, delta=1)
+        index["next"] = g.output(nxt)
+    else:
+        probs, idx = g.op("llm::TopK", [logits], n_out=2, k=top_k, softmax=1)
+        nxt = g.op("onnx::Reshape", [idx], shape=[B]) if top_k == 1 else None
+        index["next"] = g.output(idx)
+        index["probs"] = g.output(probs)
+    index["logits"] = g.output(logits)
+    if nxt is not None:
+        g.op("b200::StateUpdate", [token, nxt], n_out=0, delta=0)
+    g.op("b200::StateUpdate", [pos], n_out=0, delta=1)
+    g.op("b200::StateUpdate", [lens], n_out=0, delta=1)
+    index.update({name: i for i, name in enumerate(g.inputs)})
+    return g, index
+
+
 def prefill_graph_reference_ops(cfg: LlamaConfig, weights: dict, seq: int, top_k: int = 5):
     """Causal prefill of `seq` tokens (batch 1) using only operators the reference has kernels for; fp32.
     `weights` maps the names of `weight_inputs` to numpy arrays (wqkv/wgu are split here into the separate

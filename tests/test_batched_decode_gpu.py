@@ -1,0 +1,130 @@
+"""Batched decode path (batch > 4): tensor-core MatMul + QkvRopeAppend + AttentionDecode + SwiGLU, contiguous and
+paged KV cache, against the numpy oracle; and the single-GPU parts of the all-reduce (world 1, bounded wait)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle_np as onp
+from refactorgraph_b200 import capi
+from refactorgraph_b200.graph_builder import FP16
+from refactorgraph_b200.llama import LlamaConfig, decode_step_graph_batched, seeded_weights, weight_inputs
+
+import _ops as ops
+from _decode_oracle import oracle_decode
+
+pytestmark = pytest.mark.gpu
+
+
+def test_qkv_rope_append_and_swiglu_kernels():
+    rng = np.random.default_rng(0)
+    m, nq, nkv, D, page, max_blocks, n_blocks = 5, 8, 2, 128, 16, 8, 64
+    qkv = torch.from_numpy(rng.standard_normal((m, (nq + 2 * nkv) * D)).astype(np.float32)).half()
+    pos = rng.integers(0, page * max_blocks, (m,)).astype(np.int64)
+    table = rng.permutation(n_blocks)[: m * max_blocks].reshape(m, max_blocks).astype(np.int32)
+    kc = torch.zeros(n_blocks, nkv, page, D, dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q = torch.empty(m, nq * D, dtype=torch.float16, device="cuda")
+    p = capi.QkvRopeAppendParams(capi.FP16, m, nq, 10000.0, ops.kv_layout(nkv, D, 0, page, max_blocks))
+    capi.call("qkv_rope_append", p, [qkv.cuda().data_ptr(), ops.dev(pos).data_ptr(), ops.dev(table).data_ptr()],
+              [q.data_ptr(), kc.data_ptr(), vc.data_ptr()])
+    x = qkv.float().numpy()
+    want_q = onp.rope(x[:, : nq * D].reshape(m, nq, D), pos)
+    want_k = onp.rope(x[:, nq * D: (nq + nkv) * D].reshape(m, nkv, D), pos)
+    want_v = x[:, (nq + nkv) * D:].reshape(m, nkv, D)
+    np.testing.assert_allclose(q.float().cpu().numpy().reshape(m, nq, D), want_q, atol=2e-2, rtol=1e-2)
+    k_got = torch.stack([kc[table[i, pos[i] // page], :, pos[i] % page] for i in range(m)]).float().cpu().numpy()
+    v_got = torch.stack([vc[table[i, pos[i] // page], :, pos[i] % page] for i in range(m)]).float().cpu().numpy()
+    np.testing.assert_allclose(k_got, want_k, atol=2e-2, rtol=1e-2)
+    np.testing.assert_array_equal(v_got, want_v)       # v is a plain copy
+    gu = torch.from_numpy(rng.standard_normal((7, 2 * 344)).astype(np.float32)).half()
+    y = torch.empty(7, 344, dtype=torch.float16, device="cuda")
+    capi.call("swiglu", capi.SwigluParams(capi.FP16, 7, 344), [gu.cuda().data_ptr()], [y.data_ptr()])
+    g, u = gu.float().numpy()[:, :344], gu.float().numpy()[:, 344:]
+    np.testing.assert_allclose(y.float().cpu().numpy(), onp.silu(g) * u, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_batched_decode_graph(paged):
+    cfg = LlamaConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=256, batch=16)
+    rng = np.random.default_rng(3)
+    w16 = seeded_weights(cfg, 0, np.float16)
+    w16["lm_head"] = (0.2 * rng.standard_normal(w16["lm_head"].shape)).astype(np.float16)
+    w = {k: v.astype(np.float32) for k, v in w16.items()}
+    B, page = cfg.batch, 16
+    past = rng.integers(1, 200, (B,)).astype(np.int64)
+    kc = [rng.standard_normal((B, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+    vc = [rng.standard_normal((B, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+    token = rng.integers(0, cfg.vocab, (B,)).astype(np.int64)
+    steps = 3
+    want_tok, want_logits = oracle_decode(cfg, w, kc, vc, token, past, steps)
+    max_blocks = cfg.max_seq // page
+    n_blocks = B * max_blocks
+    table = rng.permutation(n_blocks).reshape(B, max_blocks).astype(np.int32)
+    g, index = decode_step_graph_batched(cfg, paged=paged, page=page, max_blocks=max_blocks, n_blocks=n_blocks)
+    ex = g.compiler().compile("cuda", "flat", [])
+    for name, _ in weight_inputs(cfg):
+        ex.set_input(index[name], w16[name])
+    for l in range(cfg.layers):
+        if paged:  # scatter the contiguous caches into their pages
+            for nm, src in (("k_cache", kc[l]), ("v_cache", vc[l])):
+                pages = np.zeros((n_blocks, cfg.kv_heads, page, cfg.head_dim), np.float16)
+                for b in range(B):
+                    for j in range(max_blocks):
+                        pages[table[b, j]] = src[b, :, j * page:(j + 1) * page]
+                ex.set_input(index[f"l{l}.{nm}"], pages)
+        else:
+            ex.set_input(index[f"l{l}.k_cache"], kc[l])
+            ex.set_input(index[f"l{l}.v_cache"], vc[l])
+    if paged:
+        ex.set_input(index["block_table"], table)
+    ex.set_input(index["token"], token)
+    ex.set_input(index["pos"], past)
+    ex.set_input(index["lens"], past + 1)
+    for s in range(steps):
+        ex.run()
+        logits = ex.get_output(index["logits"]).astype(np.float32)
+        np.testing.assert_allclose(logits, want_logits[s], atol=3e-2, rtol=2e-2)
+        tok = ex.get_output(index["next"])[:, 0]
+        # fp16 near-ties may flip an argmax; the token chosen must be (near-)maximal in the oracle's logits
+        gap = want_logits[s].max(axis=1) - want_logits[s][np.arange(B), tok]
+        assert (gap <= 3e-2).all()
+        if not (tok == want_tok[s]).all():
+            break  # trajectories diverged legitimately on a tie
+    assert capi.load().rg_b200_error_state() == 0
+
+
+def test_all_reduce_world_one_and_limits():
+    comm = capi.Comm(1, 0, 1 << 16)
+    x = torch.arange(1000, dtype=torch.float32, device="cuda")
+    r = torch.ones_like(x)
+    y = torch.empty_like(x)
+    comm.all_reduce(capi.F32, 0, x.numel(), x.data_ptr(), y.data_ptr())
+    assert torch.equal(y, x)
+    comm.all_reduce(capi.F32, 1, x.numel(), x.data_ptr(), y.data_ptr(), residual=r.data_ptr())   # Avg of one rank + residual
+    assert torch.equal(y, x + 1)
+    h = torch.randn(4099, device="cuda").half()                                                    # ragged tail (not a multiple of 8)
+    yh = torch.empty_like(h)
+    comm.all_reduce(capi.FP16, 0, h.numel(), h.data_ptr(), yh.data_ptr())
+    assert torch.equal(yh, h)
+    assert comm.all_reduce(capi.F32, 0, 1 << 20, x.data_ptr(), y.data_ptr(), check=False) == capi.ERR_LIMIT
+    assert comm.all_reduce(capi.I64, 0, 8, x.data_ptr(), y.data_ptr(), check=False) == capi.ERR_DTYPE
+    assert comm.status() == capi.OK
+    comm.destroy()
+
+
+def test_all_reduce_missing_peer_reports_timeout_instead_of_hanging():
+    """Failure detection without faulting a GPU: rank 0 of a 2-rank group whose peer never raises its flag (a zeroed
+    buffer stands in for the peer).  The device-side wait is bounded (20 ms here); the kernel returns, the status
+    word says so, and the context stays usable."""
+    comm = capi.Comm(2, 0, 1 << 12)
+    fake_peer = torch.zeros(4096 + 4096 + 2 * 4096, dtype=torch.uint8, device="cuda")
+    comm.connect_ptrs([comm.base(), fake_peer.data_ptr()])
+    comm.set_wait_ns(20_000_000)
+    x = torch.ones(256, device="cuda")
+    y = torch.full_like(x, -1.0)
+    comm.all_reduce(capi.F32, 0, x.numel(), x.data_ptr(), y.data_ptr())
+    assert comm.status() == capi.ERR_TIMEOUT
+    assert torch.equal(y, torch.full_like(x, -1.0))          # output left untouched
+    z = x + 1                                                   # the context is still alive
+    assert float(z.sum()) == 512.0
+    comm.destroy()

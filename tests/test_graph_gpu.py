@@ -9,6 +9,8 @@ from oracle import oracle_np as onp
 from refactorgraph_b200.graph_builder import F32, FP16, I64, GraphBuilder
 from refactorgraph_b200.llama import LlamaConfig, decode_step_graph, prefill_graph_reference_ops, seeded_weights, weight_inputs
 
+from _decode_oracle import oracle_decode as _oracle_decode
+
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 TINY = dict(layers=2, hidden=256, heads=4, kv_heads=4, head_dim=64, ffn=688, vocab=1000, eps=1e-6, max_seq=32, dtype=F32)
@@ -34,34 +36,6 @@ def test_tiny_prefill_matches_the_reference_cpu_kernels():
         np.testing.assert_array_equal(ex.get_output(index["logits"]), logits)
     print("as-built softmax divergence (reported): max |dlogit| =",
           float(np.abs(gold["logits_asbuilt"] - logits).max()))
-
-
-def _oracle_decode(cfg, w, kc, vc, token, pos, steps):
-    """Greedy decode with the numpy oracle on fp16-rounded weights; returns tokens [steps, B] and logits."""
-    r16 = lambda a: a.astype(np.float16).astype(np.float32)
-    B, D, nH, nKV = cfg.batch, cfg.head_dim, cfg.heads, cfg.kv_heads
-    kc = [k.astype(np.float32).copy() for k in kc]
-    vc = [v.astype(np.float32).copy() for v in vc]
-    toks, all_logits = [], []
-    token, pos = token.copy(), pos.copy()
-    for _ in range(steps):
-        x = w["embed"][token].astype(np.float32)
-        for l in range(cfg.layers):
-            q, k, v = onp.linear_fused(x, w[f"l{l}.wqkv"], g=w[f"l{l}.norm1"], eps=cfg.eps, epilogue=3, n_heads=nH, n_kv=nKV,
-                                       head_dim=D, positions=pos, theta=cfg.theta)
-            for b in range(B):
-                kc[l][b, :, pos[b]] = r16(k[b])
-                vc[l][b, :, pos[b]] = r16(v[b])
-            a = r16(onp.attn_decode(r16(q), kc[l], vc[l], pos + 1)).reshape(B, nH * D)
-            h = r16(onp.linear_fused(a, w[f"l{l}.wo"], residual=x, epilogue=1))
-            u = r16(onp.linear_fused(h, w[f"l{l}.wgu"], g=w[f"l{l}.norm2"], eps=cfg.eps, epilogue=2))
-            x = r16(onp.linear_fused(u, w[f"l{l}.wd"], residual=h, epilogue=1))
-        logits = r16(onp.linear_fused(x, w["lm_head"], g=w["norm_f"], eps=cfg.eps))
-        token = onp.topk(logits, 1)[1][:, 0]
-        pos = pos + 1
-        toks.append(token.copy())
-        all_logits.append(logits)
-    return np.stack(toks), np.stack(all_logits)
 
 
 @pytest.mark.parametrize("batch", [1, 2])

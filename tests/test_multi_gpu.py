@@ -1,0 +1,121 @@
+"""Two ranks on two GPUs of one box: the peer-memory all-reduce against the reference's own vector and numpy, and a
+tensor-parallel decode step against the unsharded oracle.  One process per GPU; IPC handles travel over gloo."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _exchange(handle: bytes):
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, handle)
+    return out
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        torch.cuda.set_device(rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from refactorgraph_b200 import capi
+        from refactorgraph_b200.llama import LlamaConfig, decode_step_graph_batched, seeded_weights, shard_config, shard_weights, weight_inputs
+        from _decode_oracle import oracle_decode
+        comm = capi.Comm(world, rank, 1 << 20, exchange=_exchange)
+        res = {}
+        # (1) the reference's all-reduce vector (src/04kernel/test/kernels/all_reduce/test_allreduce_nccl.cpp:44-47)
+        x = torch.tensor([2.0, 3.0] if rank == 0 else [5.0, 6.0], device="cuda")
+        y = torch.empty_like(x)
+        comm.all_reduce(capi.F32, 0, 2, x.data_ptr(), y.data_ptr())
+        torch.cuda.synchronize()
+        res["kat"] = y.cpu().tolist() == [7.0, 9.0]
+        # (2) every op / dtype on seeded data, ragged length, many calls in a row (slot reuse)
+        ok = True
+        for it, (op, dt, n) in enumerate([(0, torch.float32, 100003), (1, torch.float16, 65536), (2, torch.bfloat16, 777),
+                                          (3, torch.float32, 8), (4, torch.float32, 4096), (0, torch.float16, 131072)] * 3):
+            gens = [torch.Generator().manual_seed(100 * it + r) for r in range(world)]
+            parts = [torch.randn(n, generator=g).to(dt) for g in gens]
+            xs = parts[rank].cuda()
+            ys = torch.empty_like(xs)
+            code = {torch.float32: capi.F32, torch.float16: capi.FP16, torch.bfloat16: capi.BF16}[dt]
+            comm.all_reduce(code, op, n, xs.data_ptr(), ys.data_ptr())
+            torch.cuda.synchronize()
+            f = [p.float() for p in parts]
+            want = {0: f[0] + f[1], 1: (f[0] + f[1]) / 2, 2: torch.minimum(f[0], f[1]), 3: torch.maximum(f[0], f[1]), 4: f[0] * f[1]}[op].to(dt)
+            ok = ok and torch.equal(ys.cpu(), want)
+        res["ops"] = ok
+        # (3) tensor-parallel decode step vs the unsharded oracle
+        cfg = LlamaConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=16)
+        rng = np.random.default_rng(3)
+        w16 = seeded_weights(cfg, 0, np.float16)
+        w16["lm_head"] = (0.2 * rng.standard_normal(w16["lm_head"].shape)).astype(np.float16)
+        B = cfg.batch
+        past = rng.integers(1, 100, (B,)).astype(np.int64)
+        kc = [rng.standard_normal((B, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+        vc = [rng.standard_normal((B, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+        token = rng.integers(0, cfg.vocab, (B,)).astype(np.int64)
+        _, want_logits = oracle_decode(cfg, {k: v.astype(np.float32) for k, v in w16.items()}, kc, vc, token, past, 2)
+        sc, kr = shard_config(cfg, world), cfg.kv_heads // world
+        ws = shard_weights(cfg, w16, world, rank)
+        g, index = decode_step_graph_batched(sc, world=world)
+        ex = g.compiler().compile("cuda", "flat", [])
+        ex.set_communicator(comm.address)
+        for name, _ in weight_inputs(sc):
+            ex.set_input(index[name], np.ascontiguousarray(ws[name]))
+        for l in range(cfg.layers):
+            ex.set_input(index[f"l{l}.k_cache"], np.ascontiguousarray(kc[l][:, rank * kr:(rank + 1) * kr]))
+            ex.set_input(index[f"l{l}.v_cache"], np.ascontiguousarray(vc[l][:, rank * kr:(rank + 1) * kr]))
+        ex.set_input(index["token"], token)
+        ex.set_input(index["pos"], past)
+        ex.set_input(index["lens"], past + 1)
+        good = True
+        for s in range(2):
+            dist.barrier()
+            ex.run()          # second run = CUDA-graph replay with the sequence number advancing on the device
+            logits = ex.get_output(index["logits"]).astype(np.float32)
+            if s == 0:
+                good = good and np.allclose(logits, want_logits[0], atol=3e-2, rtol=2e-2)
+            gathered = [None] * world
+            dist.all_gather_object(gathered, logits.tobytes())
+            good = good and gathered[0] == gathered[1]      # bit-identical logits on both ranks
+        res["tp"] = bool(good)
+        res["status"] = comm.status() == capi.OK
+        dist.barrier()
+        del ex
+        comm.destroy()
+        dist.destroy_process_group()
+        q.put((rank, res))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, {"error": traceback.format_exc()}))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs on one box")
+def test_two_ranks_all_reduce_and_tensor_parallel_decode():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=600) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+    for r in range(2):
+        assert "error" not in results[r], results[r].get("error")
+        assert results[r] == {"kat": True, "ops": True, "tp": True, "status": True}, results[r]
