@@ -25,8 +25,10 @@ def test_qkv_rope_append_and_swiglu_kernels():
     vc = torch.zeros_like(kc)
     q = torch.empty(m, nq * D, dtype=torch.float16, device="cuda")
     p = capi.QkvRopeAppendParams(capi.FP16, m, nq, 10000.0, ops.kv_layout(nkv, D, 0, page, max_blocks))
-    capi.call("qkv_rope_append", p, [qkv.cuda().data_ptr(), ops.dev(pos).data_ptr(), ops.dev(table).data_ptr()],
+    qkv_d, pos_d, table_d = qkv.cuda(), ops.dev(pos), ops.dev(table)   # keep the device copies alive across the call
+    capi.call("qkv_rope_append", p, [qkv_d.data_ptr(), pos_d.data_ptr(), table_d.data_ptr()],
               [q.data_ptr(), kc.data_ptr(), vc.data_ptr()])
+    torch.cuda.synchronize()
     x = qkv.float().numpy()
     want_q = onp.rope(x[:, : nq * D].reshape(m, nq, D), pos)
     want_k = onp.rope(x[:, nq * D: (nq + nkv) * D].reshape(m, nkv, D), pos)
@@ -38,7 +40,9 @@ def test_qkv_rope_append_and_swiglu_kernels():
     np.testing.assert_array_equal(v_got, want_v)       # v is a plain copy
     gu = torch.from_numpy(rng.standard_normal((7, 2 * 344)).astype(np.float32)).half()
     y = torch.empty(7, 344, dtype=torch.float16, device="cuda")
-    capi.call("swiglu", capi.SwigluParams(capi.FP16, 7, 344), [gu.cuda().data_ptr()], [y.data_ptr()])
+    gu_d = gu.cuda()
+    capi.call("swiglu", capi.SwigluParams(capi.FP16, 7, 344), [gu_d.data_ptr()], [y.data_ptr()])
+    torch.cuda.synchronize()
     g, u = gu.float().numpy()[:, :344], gu.float().numpy()[:, 344:]
     np.testing.assert_allclose(y.float().cpu().numpy(), onp.silu(g) * u, atol=2e-2, rtol=1e-2)
 
