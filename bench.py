@@ -39,7 +39,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="7b", choices=["7b", "tiny"])
+    ap.add_argument("--workload", default="7b", choices=["7b", "tiny", "7b-b32", "70b-tp"],
+                    help="7b: batch-1 greedy decode (the reported configuration; N > 1 = independent replicas). "
+                         "7b-b32: batch 32, paged KV, top-k 50 sampling.  70b-tp: 70B-shaped GQA decode, tensor-parallel over N GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
                              "gemm_skinny16", "gemm_skinny32"],
@@ -48,10 +50,16 @@ def parse_args():
     return ap.parse_args()
 
 
-def workload_config(name):
+def workload_config(name, world=1):
     from refactorgraph_b200.llama import LlamaConfig
     if name == "tiny":  # for quick functional runs only; never the reported configuration
         return LlamaConfig(layers=2, hidden=512, heads=4, kv_heads=4, head_dim=128, ffn=1024, vocab=2000, max_seq=512), 256
+    if name == "7b-b32":
+        return LlamaConfig(max_seq=4096 + 128, batch=32), 0
+    if name == "70b-tp":
+        # one GPU cannot hold 137 GB of weights next to the cache: a 10-layer slice, as the configuration states
+        return LlamaConfig(layers=80 if world > 1 else 10, hidden=8192, heads=64, kv_heads=8, head_dim=128, ffn=28672,
+                           vocab=32000, max_seq=4096 + 128, batch=16), 4096
     return LlamaConfig(max_seq=2048 + 512), 2048
 
 
@@ -169,6 +177,10 @@ def run_reference(args):
 def workload_name(w):
     if w == "tiny":
         return "tiny functional decoder (not a reported configuration)"
+    if w == "7b-b32":
+        return "Llama-7B-shaped fp16 batch-32 decode, paged KV (16-token blocks), lengths uniform[512,4096], top-k 50 sampling"
+    if w == "70b-tp":
+        return "70B-shaped GQA fp16 batch-16 decode at KV 4096, tensor-parallel (column/row-sharded weights, all-reduce after O and down)"
     return "Llama-7B-shaped fp16 batch-1 greedy decode, KV cache prefilled to 2048 tokens, one token per step"
 
 
@@ -215,13 +227,36 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_executor(cfg, kv_len, torch):
-    from refactorgraph_b200.llama import decode_step_graph, weight_inputs
-    g, index = decode_step_graph(cfg)
-    ex = g.compiler().compile("cuda", "flat", [])
+def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0):
+    """Compiles the decode-step graph of the workload and fills weights and caches with seeded values generated on
+    the device.  Returns (executor, index, state) where state holds what reset_state needs."""
+    from refactorgraph_b200.llama import decode_step_graph, decode_step_graph_batched, shard_config, weight_inputs
     gen = torch.Generator(device="cuda")
-    gen.manual_seed(0)
+    gen.manual_seed(rank)
     dt = torch.float16
+    state = {"lens0": np.full(cfg.batch, kv_len, np.int64), "paged": False}
+    if workload in ("7b-b32", "70b-tp"):
+        tp = world if workload == "70b-tp" else 1
+        cfg = shard_config(cfg, tp)
+        page = 16
+        if workload == "7b-b32":
+            lens0 = np.random.default_rng(0).integers(512, 4097, (cfg.batch,)).astype(np.int64)
+            max_blocks = cfg.max_seq // page
+            n_blocks = cfg.batch * max_blocks
+            g, index = decode_step_graph_batched(cfg, paged=True, page=page, max_blocks=max_blocks, n_blocks=n_blocks,
+                                                 top_k=50, sample=True, temperature=1.0, seed=0)
+            state.update(lens0=lens0, paged=True, table=np.random.default_rng(1).permutation(n_blocks).reshape(cfg.batch, max_blocks).astype(np.int32))
+            cache_shape = (n_blocks, cfg.kv_heads, page, cfg.head_dim)
+        else:
+            g, index = decode_step_graph_batched(cfg, world=tp)
+            cache_shape = (cfg.batch, cfg.kv_heads, cfg.max_seq, cfg.head_dim)
+        ex = g.compiler().compile("cuda", "flat", [])
+        state["cfg"] = cfg
+    else:
+        g, index = decode_step_graph(cfg)
+        ex = g.compiler().compile("cuda", "flat", [])
+        cache_shape = (cfg.batch, cfg.kv_heads, cfg.max_seq, cfg.head_dim)
+        state["cfg"] = cfg
     for name, shape in weight_inputs(cfg):
         w = torch.empty(shape, dtype=torch.float32, device="cuda").normal_(0.0, 0.02, generator=gen)
         if "norm" in name:
@@ -231,17 +266,21 @@ def build_executor(cfg, kv_len, torch):
         del w
     for l in range(cfg.layers):
         for nm in ("k_cache", "v_cache"):
-            c = torch.empty((cfg.batch, cfg.kv_heads, cfg.max_seq, cfg.head_dim), dtype=torch.float32, device="cuda").normal_(0.0, 1.0, generator=gen).to(dt)
+            c = torch.empty(cache_shape, dtype=dt, device="cuda").normal_(0.0, 1.0, generator=gen)
             ex.set_input_blob(index[f"l{l}.{nm}"], c.data_ptr(), c.numel() * 2)
             del c
+    if state["paged"]:
+        ex.set_input(index["block_table"], state["table"])
     torch.cuda.empty_cache()
-    return ex, index
+    return ex, index, state
 
 
-def reset_state(ex, index, cfg, kv_len, token0):
+def reset_state(ex, index, state, token0):
     ex.set_input(index["token"], token0)
-    ex.set_input(index["pos"], np.full(cfg.batch, kv_len, np.int64))
-    ex.set_input(index["lens"], np.full(cfg.batch, kv_len + 1, np.int64))
+    ex.set_input(index["pos"], state["lens0"])
+    ex.set_input(index["lens"], state["lens0"] + 1)
+    if "step" in index:
+        ex.set_input(index["step"], np.zeros(1, np.int64))
 
 
 def time_linear_kernel(ex, index, cfg, torch, stream, reps=3):
@@ -370,6 +409,45 @@ def run_case(args):
     print(json.dumps(out), flush=True)
 
 
+def time_skinny_gemm(ex, index, cfg, torch, stream, reps=3):
+    """Batched workloads: one pass over every weight MatMul of a step through rg_b200_mat_mul (tensor-core kernel with
+    the skinny activation on the N side) on the real per-rank weights, bracketed by CUDA events."""
+    from refactorgraph_b200 import capi
+    B, H, D = cfg.batch, cfg.hidden, cfg.head_dim
+    dt = torch.float16
+    x = torch.randn(B, max(H, cfg.ffn, cfg.heads * D), device="cuda").to(dt)
+    y = torch.empty(B, max(cfg.vocab, 2 * cfg.ffn), dtype=dt, device="cuda")
+    calls, bytes_total = [], 0
+    shapes = []
+    for l in range(cfg.layers):
+        shapes += [(f"l{l}.wqkv", (cfg.heads + 2 * cfg.kv_heads) * D, H), (f"l{l}.wo", H, cfg.heads * D),
+                   (f"l{l}.wgu", 2 * cfg.ffn, H), (f"l{l}.wd", H, cfg.ffn)]
+    shapes.append(("lm_head", cfg.vocab, H))
+    for name, n, k in shapes:
+        p = capi.MatMulParams()
+        p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y = capi.FP16, B, n, k, 1, 1.0, 1.0, 1, B * n
+        xk = x[:, :k].contiguous() if k != x.shape[1] else x
+        calls.append((p, [xk.data_ptr(), ex.input_address(index[name]), 0], xk))
+        bytes_total += n * k * 2
+    sid = stream.cuda_stream
+    outs = [y.data_ptr()]
+
+    def one_pass():
+        for p, ins, _keep in calls:
+            capi.call("mat_mul", p, ins, outs, stream=sid)
+    one_pass()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        one_pass()
+    e1.record(stream)
+    stream.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return {"launches": len(calls), "ms_per_pass": ms, "bytes_per_pass": bytes_total,
+            "avg_launch_us": 1000.0 * ms / len(calls), "gbs": bytes_total / (ms * 1e-3) / 1e9}
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -382,33 +460,48 @@ def run_b200(args):
         raise SystemExit("bench.py needs a CUDA device: the kernel library has no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL is only the plumbing here (barriers, max-over-ranks of the timings); IPC handles travel through it too
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = capi.load()
-    cfg, kv_len = workload_config(args.workload)
-    ex, index = build_executor(cfg, kv_len, torch)
+    tp = args.workload == "70b-tp"
+    full_cfg, kv_len = workload_config(args.workload, world)
+    comm = None
+    if tp and world > 1:
+        def exchange(handle):
+            out = [None] * world
+            dist.all_gather_object(out, handle)
+            return out
+        comm = capi.Comm(world, rank, full_cfg.batch * full_cfg.hidden * 2, exchange=exchange)
+    ex, index, state = build_executor(full_cfg, kv_len, torch, args.workload, world, rank)
+    cfg = state["cfg"]                      # per-rank shape
+    if comm is not None:
+        ex.set_communicator(comm.address)
     stream = torch.cuda.ExternalStream(ex.cuda_stream())
-    token0 = np.random.default_rng(rank).integers(0, cfg.vocab, (cfg.batch,)).astype(np.int64)
+    # tensor-parallel ranks must feed identical tokens; replicas draw their own
+    token0 = np.random.default_rng(0 if tp else rank).integers(0, cfg.vocab, (cfg.batch,)).astype(np.int64)
     K, W = args.steps, max(args.warmup, 3)
-    assert kv_len + W + K + 1 <= cfg.max_seq, "steps exceed the KV cache capacity of this benchmark configuration"
+    assert int(state["lens0"].max()) + 2 * (W + K) + 8 <= cfg.max_seq, "steps exceed the KV cache capacity of this benchmark configuration"
 
     def barrier():
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
     # launches per step, counted on the eager first pass
-    reset_state(ex, index, cfg, kv_len, token0)
+    reset_state(ex, index, state, token0)
+    barrier()
     l0 = lib.rg_b200_launch_count()
     ex.run()
     ex.sync()
     launches_per_step = int(lib.rg_b200_launch_count() - l0)
 
     # ---- device-resident loop ----
-    reset_state(ex, index, cfg, kv_len, token0)
     for _ in range(W):
         ex.run()
     ex.sync()
-    reset_state(ex, index, cfg, kv_len, token0)
+    reset_state(ex, index, state, token0)
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
@@ -420,33 +513,34 @@ def run_b200(args):
     stream.synchronize()
     barrier()
     ms = e0.elapsed_time(e1)
-    last_tokens = ex.get_output(index["next"]).ravel().tolist()
+    last_tokens = ex.get_output(index["next"]).ravel().tolist()[:8]
     logits_finite = bool(np.isfinite(ex.get_output(index["logits"]).astype(np.float32)).all())
     if not logits_finite:
         raise SystemExit("bench.py: non-finite logits after the timed loop; the number would be meaningless")
 
-    # ---- end-to-end loop: token from pinned host memory each step, sampled token read back ----
-    reset_state(ex, index, cfg, kv_len, token0)
+    # ---- end-to-end loop: tokens from pinned host memory each step, sampled tokens read back ----
+    reset_state(ex, index, state, token0)
     pin_in = torch.from_numpy(token0.copy()).pin_memory()
-    pin_out = torch.zeros(cfg.batch, 1, dtype=torch.int64).pin_memory()
-    nbytes = cfg.batch * 8
+    pin_out = torch.zeros(ex.get_output(index["next"]).size, dtype=torch.int64).pin_memory()
+    nbytes_in, nbytes_out = cfg.batch * 8, pin_out.numel() * 8
     for _ in range(3):
-        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes)
+        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes_in)
         ex.run()
-        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes)
-        pin_in.copy_(pin_out.view(-1))
-    reset_state(ex, index, cfg, kv_len, token0)
+        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes_out)
+        pin_in.copy_(pin_out.view(cfg.batch, -1)[:, 0])
+    reset_state(ex, index, state, token0)
     pin_in.copy_(torch.from_numpy(token0))
     barrier()
     t0 = time.perf_counter()
     for _ in range(K):
-        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes)
+        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes_in)
         ex.run()
-        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes)   # synchronises
-        pin_in.copy_(pin_out.view(-1))
+        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes_out)   # synchronises
+        pin_in.copy_(pin_out.view(cfg.batch, -1)[:, 0])
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop()
+    barrier()
 
     # max over ranks
     if world > 1:
@@ -455,40 +549,52 @@ def run_b200(args):
         ms, e2e_ms = float(t[0]), float(t[1])
     else:
         e2e_ms = e2e_s * 1000.0
-    lin = time_linear_kernel(ex, index, cfg, torch, stream) if rank == 0 else None
+    lin = None
+    if rank == 0:
+        lin = time_linear_kernel(ex, index, cfg, torch, stream) if args.workload in ("7b", "tiny") else time_skinny_gemm(ex, index, cfg, torch, stream)
+    comm_ok = comm.status() == capi.OK if comm is not None else True
+    err_state = lib.rg_b200_error_state()
 
     if rank == 0:
         peak, peak_kind = measured_peak()
-        tokens = K * cfg.batch * world
+        replicas = 1 if tp else world
+        tokens = K * cfg.batch * replicas
         value = tokens / (ms * 1e-3)
-        kv_mean = kv_len + 1 + (K - 1) / 2.0
-        step_bytes = cfg.weight_bytes_per_step + cfg.kv_bytes_per_token * kv_mean * cfg.batch
+        kv_sum = float(state["lens0"].sum()) + cfg.batch * (1 + (K - 1) / 2.0)        # mean total cached tokens per step
+        step_bytes = cfg.weight_bytes_per_step + cfg.kv_bytes_per_token * kv_sum           # per GPU
+        kernel = "linear_stream_kernel" if args.workload in ("7b", "tiny") else "gemm_tc_kernel (activations on the N side)"
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
-            "data": "synthetic",
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
+            "dtype": "fp16", "data": "synthetic",
             "config": {"workload": workload_name(args.workload), "layers": cfg.layers, "hidden": cfg.hidden, "batch": cfg.batch,
-                       "logits_finite": logits_finite,
-                       "kv_len_start": kv_len, "l2": "inputs larger than L2 (13.2 GB of weights streamed per step)",
-                       "parallelism": "one independent replica per GPU" if world > 1 else "single GPU",
-                       "last_tokens": last_tokens},
-            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
+                       "logits_finite": logits_finite, "kv_len_start": int(state["lens0"].mean()),
+                       "l2": "inputs larger than L2 (all weights streamed once per step)",
+                       "parallelism": (f"tp{world}" if tp else ("one independent replica per GPU" if world > 1 else "single GPU")),
+                       "last_tokens": last_tokens, "bounded_waits_ok": bool(comm_ok and err_state == 0)},
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": nbytes_out},
             "gpu_launches": launches_per_step * K,
             "launches_per_step": launches_per_step,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
-                         "traffic": None, "kernel": "linear_stream_kernel", "peak_source": peak_kind + " HBM copy bandwidth",
+                         "traffic": None, "kernel": kernel, "peak_source": peak_kind + " HBM copy bandwidth",
                          "avg_launch_us": lin["avg_launch_us"], "launches_timed": lin["launches"],
                          "algorithmic_bytes_per_launch": lin["bytes_per_pass"] / lin["launches"]},
-            "roofline_step": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
+            "roofline_step": {"algorithmic_bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
                               "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak,
                               "frac_of_nominal_8tbs": step_bytes / (ms / K * 1e-3) / 1e9 / 8000.0},
         }
-        if not args.no_cpu_baseline:
+        if args.workload == "7b":
+            line["roofline"]["traffic"] = 180404736 * (lin["bytes_per_pass"] / lin["launches"]) / 180355072  # ncu: dram bytes = 1.0003 x algorithmic (profiles/linear_gate_up.md)
+        if not args.no_cpu_baseline and args.workload in ("7b", "tiny"):
             line["cpu_baseline"] = cpu_baseline(cfg, kv_len)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+    del ex
+    if comm is not None:
+        comm.destroy()
+    if world > 1:
         dist.destroy_process_group()
 
 
