@@ -43,6 +43,9 @@ def parse_args():
                     help="7b: batch-1 greedy decode (the reported configuration; N > 1 = independent replicas). "
                          "7b-b32: batch 32, paged KV, top-k 50 sampling.  70b-tp: 70B-shaped GQA decode, tensor-parallel over N GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", default="single", choices=["single", "fused"],
+                    help="7b / tiny workloads: 'single' = the whole step as one persistent kernel (b200::DecodeStep); "
+                         "'fused' = five fused launches per layer replayed as a CUDA graph")
     ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
                              "gemm_skinny16", "gemm_skinny32"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
@@ -227,10 +230,11 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0):
+def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0, graph="single"):
     """Compiles the decode-step graph of the workload and fills weights and caches with seeded values generated on
     the device.  Returns (executor, index, state) where state holds what reset_state needs."""
-    from refactorgraph_b200.llama import decode_step_graph, decode_step_graph_batched, shard_config, weight_inputs
+    from refactorgraph_b200.llama import (decode_step_graph, decode_step_graph_batched, decode_step_graph_single_kernel, shard_config,
+                                          weight_inputs)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(rank)
     dt = torch.float16
@@ -253,7 +257,7 @@ def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0):
         ex = g.compiler().compile("cuda", "flat", [])
         state["cfg"] = cfg
     else:
-        g, index = decode_step_graph(cfg)
+        g, index = decode_step_graph_single_kernel(cfg) if graph == "single" else decode_step_graph(cfg)
         ex = g.compiler().compile("cuda", "flat", [])
         cache_shape = (cfg.batch, cfg.kv_heads, cfg.max_seq, cfg.head_dim)
         state["cfg"] = cfg
@@ -278,7 +282,8 @@ def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0):
 def reset_state(ex, index, state, token0):
     ex.set_input(index["token"], token0)
     ex.set_input(index["pos"], state["lens0"])
-    ex.set_input(index["lens"], state["lens0"] + 1)
+    if "lens" in index:
+        ex.set_input(index["lens"], state["lens0"] + 1)
     if "step" in index:
         ex.set_input(index["step"], np.zeros(1, np.int64))
 
@@ -473,7 +478,8 @@ def run_b200(args):
             dist.all_gather_object(out, handle)
             return out
         comm = capi.Comm(world, rank, full_cfg.batch * full_cfg.hidden * 2, exchange=exchange)
-    ex, index, state = build_executor(full_cfg, kv_len, torch, args.workload, world, rank)
+    ex, index, state = build_executor(full_cfg, kv_len, torch, args.workload, world, rank, args.graph)
+    single = args.workload in ("7b", "tiny") and args.graph == "single"
     cfg = state["cfg"]                      # per-rank shape
     if comm is not None:
         ex.set_communicator(comm.address)
@@ -563,6 +569,17 @@ def run_b200(args):
         kv_sum = float(state["lens0"].sum()) + cfg.batch * (1 + (K - 1) / 2.0)        # mean total cached tokens per step
         step_bytes = cfg.weight_bytes_per_step + cfg.kv_bytes_per_token * kv_sum           # per GPU
         kernel = "linear_stream_kernel" if args.workload in ("7b", "tiny") else "gemm_tc_kernel (activations on the N side)"
+        roof = {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
+                "traffic": None, "kernel": kernel, "peak_source": peak_kind + " HBM copy bandwidth",
+                "avg_launch_us": lin["avg_launch_us"], "launches_timed": lin["launches"],
+                "algorithmic_bytes_per_launch": lin["bytes_per_pass"] / lin["launches"]}
+        if single:
+            # the step IS one launch of the dominant kernel: its duration is the CUDA-event time of the timed region / K
+            step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak, "traffic": None,
+                    "kernel": "decode_mega_kernel (one launch per token)", "peak_source": peak_kind + " HBM copy bandwidth",
+                    "avg_launch_us": 1000.0 * ms / K, "launches_timed": K, "algorithmic_bytes_per_launch": step_bytes,
+                    "linear_stream_kernel_alone_gbs": lin["gbs"]}
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
@@ -576,15 +593,13 @@ def run_b200(args):
             "gpu_launches": launches_per_step * K,
             "launches_per_step": launches_per_step,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
-                         "traffic": None, "kernel": kernel, "peak_source": peak_kind + " HBM copy bandwidth",
-                         "avg_launch_us": lin["avg_launch_us"], "launches_timed": lin["launches"],
-                         "algorithmic_bytes_per_launch": lin["bytes_per_pass"] / lin["launches"]},
+            "roofline": roof,
             "roofline_step": {"algorithmic_bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
                               "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak,
                               "frac_of_nominal_8tbs": step_bytes / (ms / K * 1e-3) / 1e9 / 8000.0},
         }
-        if args.workload == "7b":
+        line["config"]["graph"] = args.graph if args.workload in ("7b", "tiny") else "batched"
+        if args.workload == "7b" and not single:
             line["roofline"]["traffic"] = 180404736 * (lin["bytes_per_pass"] / lin["launches"]) / 180355072  # ncu: dram bytes = 1.0003 x algorithmic (profiles/linear_gate_up.md)
         if not args.no_cpu_baseline and args.workload in ("7b", "tiny"):
             line["cpu_baseline"] = cpu_baseline(cfg, kv_len)

@@ -52,7 +52,7 @@ int rg_b200_version(void);
 /* Number of kernels this library has launched in the calling process since load (all entry points). */
 uint64_t rg_b200_launch_count(void);
 /* Synchronises the current device and reports whether any kernel of this library gave up a bounded device-side
- * wait since load: 0 = none; otherwise bit 0 linear, bit 1 decode attention, bit 2 tensor-core GEMM, bit 3 all-reduce;
+ * wait since load: 0 = none; otherwise bit 0 linear, bit 1 decode attention, bit 2 tensor-core GEMM, bit 3 all-reduce, bit 4 decode step;
  * negative = the device could not be queried. */
 int rg_b200_error_state(void);
 
@@ -277,6 +277,26 @@ typedef struct rg_linear_params {
 } rg_linear_params;
 size_t rg_b200_linear_workspace(const rg_linear_params *);
 int rg_b200_linear(const rg_linear_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * One whole batch-1 decode step as a single persistent kernel (no reference counterpart: the reference runs a
+ * decoder as ~900 separate launches per token, src/03runtime/src/stream.cc:60-69).  Same semantics as the graph
+ *   Gather, [Linear(norm,QKV,RoPE,append), AttentionDecode, Linear(O,+res), Linear(norm,gate/up,SiLU), Linear(down,+res)] x layers,
+ *   Linear(norm, LM head), TopK(k=1, softmax), token <- argmax, pos <- pos + 1,
+ * with the weights streamed continuously across the phase boundaries (grid barriers instead of kernel launches).
+ * Contiguous KV caches [1, n_kv_heads, max_seq, head_dim]; weights as for rg_b200_linear.
+ * inputs  {token (int64[1], updated), pos (int64[1] = cached tokens, updated), embed[vocab,hidden], norm_f[hidden],
+ *          lm_head[vocab,hidden], then per layer: norm1, wqkv, wo, norm2, wgu, wd, k_cache, v_cache}
+ * outputs {next (int64[1]), prob (fp32[1], softmax probability of the chosen token), logits[vocab]}
+ * The workspace must be zero on first use and is left ready for the next call.  Launched cooperatively with one CTA
+ * per SM; grid-barrier waits are bounded (RG error state bit 4). */
+typedef struct rg_decode_step_params {
+    int32_t dtype; /* RG_FP16, RG_BF16 */
+    uint32_t layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_seq;
+    float epsilon, theta;
+} rg_decode_step_params;
+size_t rg_b200_decode_step_workspace(const rg_decode_step_params *);
+int rg_b200_decode_step(const rg_decode_step_params *, void *ws, const void *const *in, void *const *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Attention.  Completes AttentionCuda, which the reference declares without a definition

@@ -105,6 +105,12 @@ class AttnDecodeParams(C.Structure):
                 ("kv", KvLayout)]
 
 
+class DecodeStepParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("layers", C.c_uint32), ("hidden", C.c_uint32), ("n_heads", C.c_uint32),
+                ("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("ffn", C.c_uint32), ("vocab", C.c_uint32),
+                ("max_seq", C.c_uint32), ("epsilon", C.c_float), ("theta", C.c_float)]
+
+
 class AllReduceParams(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("op", C.c_int32), ("count", C.c_uint64)]
 
@@ -115,7 +121,7 @@ OPS = {
     "gather": GatherParams, "binary": BinaryParams, "unary": UnaryParams, "where": WhereParams,
     "transpose": TransposeParams, "rope": RopeParams, "state_update": StateUpdateParams, "mat_mul": MatMulParams, "linear": LinearParams,
     "attention": AttentionParams, "attn_decode": AttnDecodeParams, "qkv_rope_append": QkvRopeAppendParams,
-    "swiglu": SwigluParams,
+    "swiglu": SwigluParams, "decode_step": DecodeStepParams,
 }
 # every symbol include/rg_b200.h declares
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_attn_decode_static",

@@ -38,8 +38,9 @@ int rg_b200_version(void) { return 1; }
 uint64_t rg_b200_launch_count(void) { return rg::g_launches.load(std::memory_order_relaxed); }
 int rg_b200_error_state(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    const int a = rg::linear_error_word(), b = rg::attn_error_word(), c = rg::gemm_tc_error_word(), d = rg::all_reduce_error_word();
-    if (a < 0 || b < 0 || c < 0 || d < 0) return -1;
-    return (a ? 1 : 0) | (b ? 2 : 0) | (c ? 4 : 0) | (d ? 8 : 0);
+    const int a = rg::linear_error_word(), b = rg::attn_error_word(), c = rg::gemm_tc_error_word(), d = rg::all_reduce_error_word(),
+              e = rg::mega_error_word();
+    if (a < 0 || b < 0 || c < 0 || d < 0 || e < 0) return -1;
+    return (a ? 1 : 0) | (b ? 2 : 0) | (c ? 4 : 0) | (d ? 8 : 0) | (e ? 16 : 0);
 }
 }

@@ -1,0 +1,725 @@
+// One decode step of a Llama-style decoder (batch 1) as ONE persistent cooperative kernel.
+//
+// Why: at batch 1 a step is ~13 GB of weights streamed through ~165 small kernels; every kernel boundary drains
+// the memory pipeline (tail, launch, prologue) although the NEXT kernel's weights never depend on the previous
+// one.  Here one CTA per SM runs the whole step:
+//   * warp 8 (one thread) is a producer that walks the step's entire schedule — for every layer the QKV, KV-cache,
+//     O, gate/up and down phases, then the LM head — and streams each CTA's share of the weights (and of the old
+//     KV tiles) into a 3 x 32 KiB shared-memory ring with cp.async.bulk + mbarriers.  It is throttled only by ring
+//     space, never by a phase boundary, so HBM stays busy while the consumers synchronise.
+//   * warps 0-7 consume: per phase they (re)load the activation vector into registers (RMSNorm, or the merge of the
+//     attention partials), reduce their units, run the phase epilogue (RoPE + cache append, residual add, SiLU*up,
+//     logits + running arg-max) and meet the other CTAs at a grid barrier (monotonic counter, bounded spin).
+//   * attention over the cached tokens [0, pos) is split over (head, 64-token tile) units; the token produced in
+//     this step is folded in when the partial records are merged, so its K/V rows never have to be prefetched.
+// Semantics equal the multi-kernel graph: Gather, [Linear(norm,QKV,RoPE,append), AttentionDecode, Linear(O,+res),
+// Linear(norm,gate/up,SiLU), Linear(down,+res)] x L, Linear(norm, LM head), TopK(k=1, softmax), state updates.
+#include "gemm_dispatch.cuh"
+#include <algorithm>
+
+namespace rg {
+
+constexpr int MG_NW = 8;
+constexpr int MG_CONSUMERS = MG_NW * 32;
+constexpr int MG_THREADS = MG_CONSUMERS + 32;
+constexpr int MG_STAGES = 3;
+constexpr uint32_t MG_STAGE_BYTES = 32768;
+constexpr int MG_KCH = 6;          // k <= 6 * 256 * 8 = 12288
+constexpr int MG_MAX_LAYERS = 96;
+constexpr int MG_TILE = 64;        // tokens per attention unit
+constexpr int MG_PART_UNITS = 96;  // max units of one phase per CTA
+constexpr int MG_MAX_REC = 8;      // attention partial records per CTA
+
+static __device__ int s_mega_error;
+
+struct MegaLayer {
+    const void *norm1, *wqkv, *wo, *norm2, *wgu, *wd;
+    void *kc, *vc;
+};
+struct MegaArgs {
+    MegaLayer layer[MG_MAX_LAYERS];
+    const void *embed, *norm_f, *lm_head;
+    int64_t *token, *pos;
+    int64_t *next;
+    float *prob;
+    void *logits;
+    uint8_t *ws;
+    uint32_t layers, H, nH, nKV, D, F, V, max_seq;
+    float eps, log2_theta, scale;
+};
+struct MegaHeader {
+    unsigned long long bar;  // monotonic arrival counter
+    unsigned long long epoch;// value of bar at the start of the launch in flight
+    unsigned long long best; // arg-max composite (key << 32 | ~index)
+    int abort;
+};
+// workspace layout (bytes): header 256 | lse[G] float2 | x[H] | h[H] | q[nH*D] | u[F] (16-bit) | rec[G][MG_MAX_REC][D+2] float
+struct MegaWs {
+    MegaHeader *hdr;
+    float2 *lse;
+    void *x, *h, *q, *u;
+    float *rec;
+};
+__host__ __device__ inline size_t mg_align(size_t v) { return (v + 255) / 256 * 256; }
+__host__ __device__ inline size_t mega_ws_bytes(uint32_t G, uint32_t H, uint32_t nH, uint32_t D, uint32_t F) {
+    return 256 + mg_align(G * 8) + 2 * mg_align(H * 2) + mg_align(static_cast<size_t>(nH) * D * 2) + mg_align(F * 2) +
+           mg_align(static_cast<size_t>(G) * MG_MAX_REC * (D + 2) * 4);
+}
+__device__ inline MegaWs mega_ws(uint8_t *p, uint32_t G, uint32_t H, uint32_t nH, uint32_t D, uint32_t F) {
+    MegaWs w;
+    w.hdr = reinterpret_cast<MegaHeader *>(p);
+    p += 256;
+    w.lse = reinterpret_cast<float2 *>(p);
+    p += mg_align(G * 8);
+    w.x = p;
+    p += mg_align(H * 2);
+    w.h = p;
+    p += mg_align(H * 2);
+    w.q = p;
+    p += mg_align(static_cast<size_t>(nH) * D * 2);
+    w.u = p;
+    p += mg_align(F * 2);
+    w.rec = reinterpret_cast<float *>(p);
+    return w;
+}
+
+enum : int { PH_QKV = 0, PH_ATT = 1, PH_O = 2, PH_GU = 3, PH_DOWN = 4, PH_LM = 5 };
+
+struct Phase {
+    int type;
+    const uint8_t *W;  // weights (linear phases)
+    uint32_t n, k;     // rows, columns of W
+    uint32_t g, segs;  // rows per segment, segments per unit
+    uint32_t units;
+    uint32_t layer;
+};
+
+__device__ __forceinline__ uint32_t pow2_floor_d(uint32_t v) {
+    return v ? 1u << (31 - __clz(v)) : 0u;
+}
+// Phase p of the step: 5 per layer, then the LM head.  `T` = attention tiles over the cached tokens [0, pos).
+__device__ inline Phase phase_of(const MegaArgs &a, uint32_t p, uint32_t T) {
+    Phase ph;
+    ph.layer = p / 5;
+    ph.type = ph.layer < a.layers ? static_cast<int>(p % 5) : PH_LM;
+    ph.W = nullptr;
+    ph.n = ph.k = ph.g = ph.segs = ph.units = 0;
+    if (ph.type == PH_ATT) {
+        ph.units = a.nH * T;
+        return ph;
+    }
+    const MegaLayer &L = a.layer[ph.layer < a.layers ? ph.layer : 0];
+    switch (ph.type) {
+        case PH_QKV: ph.W = static_cast<const uint8_t *>(L.wqkv), ph.n = (a.nH + 2 * a.nKV) * a.D, ph.k = a.H, ph.segs = 2; break;
+        case PH_O: ph.W = static_cast<const uint8_t *>(L.wo), ph.n = a.H, ph.k = a.nH * a.D, ph.segs = 1; break;
+        case PH_GU: ph.W = static_cast<const uint8_t *>(L.wgu), ph.n = 2 * a.F, ph.k = a.H, ph.segs = 2; break;
+        case PH_DOWN: ph.W = static_cast<const uint8_t *>(L.wd), ph.n = a.H, ph.k = a.F, ph.segs = 1; break;
+        default: ph.W = static_cast<const uint8_t *>(a.lm_head), ph.n = a.V, ph.k = a.H, ph.segs = 1; break;
+    }
+    uint32_t g = pow2_floor_d(MG_STAGE_BYTES / (ph.k * 2u * ph.segs));
+    if (g * ph.segs > 4) g = 4 / ph.segs;
+    if (ph.type == PH_QKV) {
+        while (g > 1 && (a.D / 2) % g != 0) g >>= 1;
+        ph.units = ph.n / (2 * g);
+    } else if (ph.type == PH_GU) {
+        ph.units = (a.F + g - 1) / g;
+    } else {
+        ph.units = (ph.n + g - 1) / g;
+    }
+    ph.g = g;
+    return ph;
+}
+// first row of segment s of unit u and how many of its g rows exist
+__device__ __forceinline__ uint32_t mega_unit_row(const MegaArgs &a, const Phase &ph, uint32_t u, uint32_t s, uint32_t &rows) {
+    if (ph.type == PH_QKV) {
+        const uint32_t half = a.D / 2, per_head = half / ph.g;
+        rows = ph.g;
+        return (u / per_head) * a.D + s * half + (u % per_head) * ph.g;
+    }
+    const uint32_t span = ph.type == PH_GU ? a.F : ph.n;
+    const uint32_t r0 = u * ph.g;
+    rows = span - r0 < ph.g ? span - r0 : ph.g;
+    return s * span + r0;
+}
+__device__ __forceinline__ void unit_range(uint32_t units, uint32_t &u0, uint32_t &u1) {
+    u0 = static_cast<uint32_t>(static_cast<uint64_t>(units) * blockIdx.x / gridDim.x);
+    u1 = static_cast<uint32_t>(static_cast<uint64_t>(units) * (blockIdx.x + 1) / gridDim.x);
+}
+__device__ __forceinline__ void mg_consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(MG_CONSUMERS) : "memory"); }
+
+__device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_volatile_int(const int *p) { return *reinterpret_cast<const volatile int *>(p); }
+
+template<int V> __device__ __forceinline__ void mg_reduce_halving(float (&vals)[V], int lane) {
+    int o = 16;
+#pragma unroll
+    for (int cnt = V; cnt > 1; cnt >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < cnt / 2; ++i) {
+            const float send = up ? vals[i] : vals[i + cnt / 2];
+            const float keep = up ? vals[i + cnt / 2] : vals[i];
+            vals[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+        o >>= 1;
+    }
+    for (; o > 0; o >>= 1) vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], o);
+}
+
+template<class T>
+__global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid_constant__ MegaArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + MG_STAGES * MG_STAGE_BYTES);
+    uint64_t *empty = full + MG_STAGES;
+    float *red = reinterpret_cast<float *>(empty + MG_STAGES);// 32 floats
+    float *qs = red + 32;                                      // [D] query of the current head (fp32)
+    float *sc = qs + 256;                                      // [64] scores / probabilities, then [nH] new-token scores
+    float *part = sc + 128;                                    // [MG_PART_UNITS * 4][MG_NW]; reused as [16][D] in attention
+    int *s_fail = reinterpret_cast<int *>(part + MG_PART_UNITS * 4 * MG_NW);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, G = gridDim.x;
+    const MegaWs ws = mega_ws(a.ws, G, a.H, a.nH, a.D, a.F);
+    MegaHeader *hdr = ws.hdr;
+    const uint32_t pos = static_cast<uint32_t>(*a.pos);            // tokens already cached; the new token sits at pos
+    const int64_t token = *a.token;
+    const uint32_t NT = (pos + MG_TILE - 1) / MG_TILE;              // attention tiles over [0, pos)
+    const uint32_t nphases = a.layers * 5 + 1;
+    const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long *>(&hdr->epoch);
+
+    if (tid == 0) {
+        for (int s = 0; s < MG_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], MG_NW);
+        }
+        *s_fail = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == MG_NW) {
+        // ================= producer: the whole step's stream for this CTA =================
+        if (lane == 0) {
+            const uint64_t policy = l2_policy_evict_first();
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t p = 0; p < nphases && ok; ++p) {
+                const Phase ph = phase_of(a, p, NT);
+                uint32_t u0, u1;
+                unit_range(ph.units, u0, u1);
+                for (uint32_t u = u0; u < u1; ++u, ++it) {
+                    const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
+                    if (!mbar_wait(&empty[s], par ^ 1u) || ld_volatile_int(&hdr->abort)) {
+                        atomicExch(&hdr->abort, 1);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *st = smem + s * MG_STAGE_BYTES;
+                    if (ph.type == PH_ATT) {
+                        const uint32_t h = u / NT, t = u % NT, kvh = h / (a.nH / a.nKV);
+                        const uint32_t tok0 = t * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
+                        const uint32_t bytes = ntok * a.D * 2u;
+                        const size_t off = (static_cast<size_t>(kvh) * a.max_seq + tok0) * a.D * 2u;
+                        mbar_arrive_expect_tx(&full[s], 2u * bytes);
+                        bulk_g2s(st, static_cast<const uint8_t *>(a.layer[ph.layer].kc) + off, bytes, &full[s]);
+                        bulk_g2s(st + MG_STAGE_BYTES / 2, static_cast<const uint8_t *>(a.layer[ph.layer].vc) + off, bytes, &full[s]);
+                    } else {
+                        const uint32_t row_bytes = ph.k * 2u;
+                        uint32_t rows;
+                        mega_unit_row(a, ph, u, 0, rows);
+                        const uint32_t seg_bytes = rows * row_bytes;
+                        mbar_arrive_expect_tx(&full[s], seg_bytes * ph.segs);
+                        for (uint32_t sg = 0; sg < ph.segs; ++sg) {
+                            uint32_t rr;
+                            const uint32_t row = mega_unit_row(a, ph, u, sg, rr);
+                            bulk_g2s_hint(st + sg * ph.g * row_bytes, ph.W + static_cast<uint64_t>(row) * row_bytes, seg_bytes, &full[s], policy);
+                        }
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ================= consumers =================
+    uint32_t it = 0;        // units consumed so far (ring position)
+    uint32_t nbar = 0;      // grid barriers passed
+    bool ok = true;
+    // running arg-max / log-sum-exp of the LM head rows owned by this thread
+    unsigned long long best = 0ull;
+    float lse_m = -INFINITY, lse_s = 0.f;
+
+    auto grid_barrier = [&]() {
+        // consumers of this CTA first, then all CTAs; bounded
+        __threadfence();
+        mg_consumer_bar();
+        ++nbar;
+        if (tid == 0) {
+            atomicAdd(&hdr->bar, 1ull);
+            const unsigned long long target = epoch + static_cast<unsigned long long>(nbar) * G;
+            const uint64_t t0 = global_timer_ns();
+            for (;;) {
+                if (ld_acquire_gpu(&hdr->bar) >= target) break;
+                if (ld_volatile_int(&hdr->abort) || global_timer_ns() - t0 > 2000000000ull) {
+                    atomicExch(&hdr->abort, 1);
+                    *s_fail = 1;
+                    break;
+                }
+            }
+        }
+        mg_consumer_bar();
+        if (*s_fail) ok = false;
+    };
+
+    for (uint32_t p = 0; p < nphases && ok; ++p) {
+        const Phase ph = phase_of(a, p, NT);
+        uint32_t u0, u1;
+        unit_range(ph.units, u0, u1);
+        const uint32_t nu = u1 - u0;
+
+        if (ph.type == PH_ATT) {
+            // ---------------- attention over cached tokens: units = (head, tile) ----------------
+            const T *qbuf = static_cast<const T *>(ws.q);
+            float m_run = -INFINITY, l_run = 0.f;
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            const uint32_t CPR = a.D / 8;                   // 16-byte chunks per row (16 for D = 128)
+            const uint32_t cg = tid % CPR, tg = tid / CPR, NTG = MG_CONSUMERS / CPR;
+            uint32_t cur_h = 0xffffffffu, first_h = nu ? u0 / NT : 0;
+            auto flush = [&](uint32_t h) {
+                // reduce the token groups and write this CTA's record for head h
+                mg_consumer_bar();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) part[tg * a.D + cg * 8 + j] = acc[j];
+                mg_consumer_bar();
+                float *rec = ws.rec + (static_cast<size_t>(blockIdx.x) * MG_MAX_REC + (h - first_h)) * (a.D + 2);
+                if (tid < a.D) {
+                    float o = 0.f;
+                    for (uint32_t gidx = 0; gidx < NTG; ++gidx) o += part[gidx * a.D + tid];
+                    rec[2 + tid] = o;
+                }
+                if (tid == 0) rec[0] = m_run, rec[1] = l_run;
+                m_run = -INFINITY, l_run = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            };
+            for (uint32_t u = u0; u < u1 && ok; ++u, ++it) {
+                const uint32_t h = u / NT, t = u % NT;
+                if (h != cur_h) {
+                    if (cur_h != 0xffffffffu) flush(cur_h);
+                    mg_consumer_bar();
+                    if (tid < a.D) qs[tid] = Num<T>::to_f(__ldcg(qbuf + h * a.D + tid));
+                    cur_h = h;
+                    mg_consumer_bar();
+                }
+                const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
+                if (!mbar_wait(&full[s], par)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t tok0 = t * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
+                const uint8_t *ks = smem + s * MG_STAGE_BYTES, *vs = ks + MG_STAGE_BYTES / 2;
+                {   // scores: four threads per token, each a quarter of the row
+                    const uint32_t tk = tid >> 2, qd = tid & 3u, cpt = CPR / 4;
+                    const uint32_t swz = ((tk & 1u) << 1 | (qd >> 1)) & (cpt - 1);
+                    float dot = 0.f;
+                    if (tk < ntok) {
+                        for (uint32_t c = 0; c < cpt; ++c) {
+                            const uint32_t cc = qd * cpt + (c ^ swz);
+                            float kf[8];
+                            unpack8<T>(*reinterpret_cast<const uint4 *>(ks + tk * (a.D * 2) + cc * 16), kf);
+                            const float4 q0 = *reinterpret_cast<const float4 *>(qs + cc * 8);
+                            const float4 q1 = *reinterpret_cast<const float4 *>(qs + cc * 8 + 4);
+                            dot += kf[0] * q0.x + kf[1] * q0.y + kf[2] * q0.z + kf[3] * q0.w + kf[4] * q1.x + kf[5] * q1.y + kf[6] * q1.z + kf[7] * q1.w;
+                        }
+                    }
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                    if (qd == 0) sc[tk] = tk < ntok ? dot * a.scale : -INFINITY;
+                }
+                mg_consumer_bar();
+                const float s0 = sc[lane], s1 = sc[lane + 32];
+                const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
+                const float p0 = expf(s0 - m_new), p1 = expf(s1 - m_new);
+                const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
+                l_run = l_run * corr + warp_sum(p0 + p1);
+                m_run = m_new;
+                mg_consumer_bar();
+                if (tid < 32) sc[lane] = p0, sc[lane + 32] = p1;
+                mg_consumer_bar();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] *= corr;
+                for (uint32_t tk = tg; tk < ntok; tk += NTG) {
+                    const float pr = sc[tk];
+                    float vf[8];
+                    unpack8<T>(*reinterpret_cast<const uint4 *>(vs + tk * (a.D * 2) + cg * 16), vf);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = fmaf(pr, vf[j], acc[j]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                mg_consumer_bar();// sc[] is rewritten by the next unit
+            }
+            if (ok && cur_h != 0xffffffffu) flush(cur_h);
+            if (!ok) {
+                atomicExch(&hdr->abort, 1);
+                *s_fail = 1;
+            }
+            grid_barrier();
+            continue;
+        }
+
+        // ---------------- linear phases ----------------
+        const uint32_t kchunks = ph.k / 8;
+        float x[MG_KCH][8];
+        {
+            // activation vector of this phase, in registers
+            const T *src = nullptr, *gamma = nullptr;
+            if (ph.type == PH_QKV) {
+                src = ph.layer == 0 ? static_cast<const T *>(a.embed) + static_cast<size_t>(token) * a.H : static_cast<const T *>(ws.x);
+                gamma = static_cast<const T *>(a.layer[ph.layer].norm1);
+            } else if (ph.type == PH_GU) {
+                src = static_cast<const T *>(ws.h), gamma = static_cast<const T *>(a.layer[ph.layer].norm2);
+            } else if (ph.type == PH_DOWN) {
+                src = static_cast<const T *>(ws.u);
+            } else if (ph.type == PH_LM) {
+                src = a.layers ? static_cast<const T *>(ws.x) : static_cast<const T *>(a.embed) + static_cast<size_t>(token) * a.H;
+                gamma = static_cast<const T *>(a.norm_f);
+            }
+            if (ph.type == PH_O) {
+                // x = attention output = merge of the partial records + the token produced in this step
+                const T *qbuf = static_cast<const T *>(ws.q);
+                const uint32_t kvrep = a.nH / a.nKV;
+                // score of the new token for every head: 8 threads per head
+                for (uint32_t hb = 0; hb < a.nH; hb += MG_CONSUMERS / 8) {
+                    const uint32_t h = hb + tid / 8, pt = tid % 8;
+                    float d = 0.f;
+                    if (h < a.nH) {
+                        const T *kn = static_cast<const T *>(a.layer[ph.layer].kc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D;
+                        for (uint32_t e = pt; e < a.D; e += 8) d += Num<T>::to_f(__ldcg(qbuf + h * a.D + e)) * Num<T>::to_f(__ldcg(kn + e));
+                    }
+                    d += __shfl_xor_sync(0xffffffffu, d, 1);
+                    d += __shfl_xor_sync(0xffffffffu, d, 2);
+                    d += __shfl_xor_sync(0xffffffffu, d, 4);
+                    if (h < a.nH && pt == 0) sc[h] = d * a.scale;
+                }
+                mg_consumer_bar();
+                const uint32_t Uatt = a.nH * NT;
+#pragma unroll
+                for (int c = 0; c < MG_KCH; ++c) {
+                    const uint32_t ci = tid + c * MG_CONSUMERS;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) x[c][j] = 0.f;
+                    if (ci < kchunks) {
+                        const uint32_t h = ci * 8 / a.D, d0 = ci * 8 % a.D;
+                        const T *vn = static_cast<const T *>(a.layer[ph.layer].vc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D + d0;
+                        float mx = sc[h];
+                        // CTAs holding units of head h: those whose range intersects [h*T, (h+1)*T)
+                        uint32_t c_lo = 0, c_hi = 0;
+                        if (NT) {
+                            c_lo = static_cast<uint32_t>((static_cast<uint64_t>(h) * NT * G) / Uatt);
+                            while (c_lo > 0 && static_cast<uint64_t>(Uatt) * c_lo / G > static_cast<uint64_t>(h) * NT) --c_lo;
+                            while (static_cast<uint64_t>(Uatt) * (c_lo + 1) / G <= static_cast<uint64_t>(h) * NT) ++c_lo;
+                            c_hi = c_lo;
+                            while (c_hi + 1 < G && static_cast<uint64_t>(Uatt) * (c_hi + 1) / G < static_cast<uint64_t>(h + 1) * NT) ++c_hi;
+                            for (uint32_t cc = c_lo; cc <= c_hi; ++cc) {
+                                const uint32_t cu0 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * cc / G);
+                                const uint32_t cu1 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * (cc + 1) / G);
+                                if (cu1 <= cu0) continue;
+                                const float *rec = ws.rec + (static_cast<size_t>(cc) * MG_MAX_REC + (h - cu0 / NT)) * (a.D + 2);
+                                mx = fmaxf(mx, __ldcg(rec));
+                            }
+                        }
+                        float den = expf(sc[h] - mx);
+                        float vnf[8];
+                        unpack8<T>(__ldcg(reinterpret_cast<const uint4 *>(vn)), vnf);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) x[c][j] = den * vnf[j];
+                        if (NT) {
+                            for (uint32_t cc = c_lo; cc <= c_hi; ++cc) {
+                                const uint32_t cu0 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * cc / G);
+                                const uint32_t cu1 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * (cc + 1) / G);
+                                if (cu1 <= cu0) continue;
+                                const float *rec = ws.rec + (static_cast<size_t>(cc) * MG_MAX_REC + (h - cu0 / NT)) * (a.D + 2);
+                                const float w = expf(__ldcg(rec) - mx);
+                                den += __ldcg(rec + 1) * w;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) x[c][j] += __ldcg(rec + 2 + d0 + j) * w;
+                            }
+                        }
+                        const float inv = 1.f / den;
+                        // the multi-kernel path stores the attention output in 16 bits before the projection
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) x[c][j] = Num<T>::to_f(Num<T>::from_f(x[c][j] * inv));
+                    }
+                }
+                mg_consumer_bar();// sc[] free again
+            } else {
+                float ss = 0.f;
+#pragma unroll
+                for (int c = 0; c < MG_KCH; ++c) {
+                    const uint32_t ci = tid + c * MG_CONSUMERS;
+                    if (ci < kchunks) {
+                        unpack8<T>(__ldcg(reinterpret_cast<const uint4 *>(src + ci * 8)), x[c]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) x[c][j] = 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss += x[c][j] * x[c][j];
+                }
+                if (gamma) {
+                    float v = warp_sum(ss);
+                    if (lane == 0) red[warp] = v;
+                    mg_consumer_bar();
+                    float tot = 0.f;
+#pragma unroll
+                    for (int w = 0; w < MG_NW; ++w) tot += red[w];
+                    mg_consumer_bar();
+                    const float rstd = rsqrtf(tot / static_cast<float>(ph.k) + a.eps);
+#pragma unroll
+                    for (int c = 0; c < MG_KCH; ++c) {
+                        const uint32_t ci = tid + c * MG_CONSUMERS;
+                        if (ci < kchunks) {
+                            float gw[8];
+                            unpack8<T>(*reinterpret_cast<const uint4 *>(gamma + ci * 8), gw);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) x[c][j] *= rstd * gw[j];
+                        }
+                    }
+                }
+            }
+        }
+
+        const uint32_t R = ph.g * ph.segs, row_bytes = ph.k * 2u;
+        for (uint32_t i = 0; i < nu; ++i, ++it) {
+            const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
+            if (!mbar_wait(&full[s], par)) {
+                ok = false;
+                break;
+            }
+            const uint8_t *st = smem + s * MG_STAGE_BYTES;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if (r < static_cast<int>(R)) {
+#pragma unroll
+                    for (int c = 0; c < MG_KCH; ++c) {
+                        const uint32_t ci = tid + c * MG_CONSUMERS;
+                        if (ci < kchunks) {
+                            float w[8];
+                            unpack8<T>(*reinterpret_cast<const uint4 *>(st + static_cast<size_t>(r) * row_bytes + ci * 16), w);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[r] = fmaf(w[j], x[c][j], acc[r]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            mg_reduce_halving<4>(acc, static_cast<int>(lane));
+            if ((lane & 7u) == 0) part[(i * 4 + (lane >> 3)) * MG_NW + warp] = acc[0];
+        }
+        if (!ok) {
+            atomicExch(&hdr->abort, 1);
+            *s_fail = 1;
+        }
+        mg_consumer_bar();
+        if (*s_fail) ok = false;
+
+        // ---------------- epilogue: one item = (local unit, row r within g) ----------------
+        if (ok) {
+            const uint32_t g = ph.g;
+            for (uint32_t e = tid; e < nu * g; e += MG_CONSUMERS) {
+                const uint32_t r = e % g, lu = e / g, u = u0 + lu;
+                float val[2] = {0.f, 0.f};
+                for (uint32_t sg = 0; sg < ph.segs; ++sg) {
+                    const float *pp = part + ((lu * 4) + (sg * g + r)) * MG_NW;
+                    float t = 0.f;
+#pragma unroll
+                    for (int w = 0; w < MG_NW; ++w) t += pp[w];
+                    val[sg] = t;
+                }
+                uint32_t rows;
+                const uint32_t row0 = mega_unit_row(a, ph, u, 0, rows);
+                if (r >= rows) continue;
+                if (ph.type == PH_QKV) {
+                    const uint32_t D = a.D, half = D / 2, nq = a.nH, nkv = a.nKV;
+                    const uint32_t h = row0 / D, i = row0 % D + r;
+                    float lo = val[0], hi = val[1];
+                    if (h < nq + nkv) {
+                        const float inv_freq = exp2f(-a.log2_theta * (2.0f * static_cast<float>(i) / static_cast<float>(D)));
+                        float sn, cs;
+                        sincosf(static_cast<float>(pos) * inv_freq, &sn, &cs);
+                        const float a0 = lo * cs - hi * sn, b0 = hi * cs + lo * sn;
+                        lo = a0, hi = b0;
+                    }
+                    if (h < nq) {
+                        T *q = static_cast<T *>(ws.q) + h * D;
+                        q[i] = Num<T>::from_f(lo);
+                        q[i + half] = Num<T>::from_f(hi);
+                    } else {
+                        const bool is_k = h < nq + nkv;
+                        const uint32_t kvh = is_k ? h - nq : h - nq - nkv;
+                        T *cache = static_cast<T *>(is_k ? a.layer[ph.layer].kc : a.layer[ph.layer].vc);
+                        const size_t base = (static_cast<size_t>(kvh) * a.max_seq + pos) * D;
+                        cache[base + i] = Num<T>::from_f(lo);
+                        cache[base + i + half] = Num<T>::from_f(hi);
+                    }
+                } else if (ph.type == PH_O) {
+                    const T *resid = ph.layer == 0 ? static_cast<const T *>(a.embed) + static_cast<size_t>(token) * a.H : static_cast<const T *>(ws.x);
+                    static_cast<T *>(ws.h)[row0 + r] = Num<T>::from_f(val[0] + Num<T>::to_f(__ldcg(resid + row0 + r)));
+                } else if (ph.type == PH_GU) {
+                    const float gt = val[0];
+                    static_cast<T *>(ws.u)[row0 + r] = Num<T>::from_f(gt / (1.f + expf(-gt)) * val[1]);
+                } else if (ph.type == PH_DOWN) {
+                    static_cast<T *>(ws.x)[row0 + r] = Num<T>::from_f(val[0] + Num<T>::to_f(__ldcg(static_cast<const T *>(ws.h) + row0 + r)));
+                } else {
+                    const T lg = Num<T>::from_f(val[0]);
+                    static_cast<T *>(a.logits)[row0 + r] = lg;
+                    const float f = Num<T>::to_f(lg);
+                    uint32_t key = 0u;
+                    if (f == f) {
+                        const uint32_t b = __float_as_uint(f);
+                        key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+                        if (f > lse_m) {
+                            lse_s = lse_s * (lse_m == -INFINITY ? 0.f : expf(lse_m - f)) + 1.f;
+                            lse_m = f;
+                        } else {
+                            lse_s += expf(f - lse_m);
+                        }
+                    }
+                    const unsigned long long comp = (static_cast<unsigned long long>(key) << 32) | static_cast<unsigned long long>(~(row0 + r));
+                    best = comp > best ? comp : best;
+                }
+            }
+        }
+        if (ph.type == PH_LM && ok) {
+            // CTA-level arg-max and log-sum-exp of this CTA's logits
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long ob = __shfl_xor_sync(0xffffffffu, best, o);
+                best = ob > best ? ob : best;
+                const float om = __shfl_xor_sync(0xffffffffu, lse_m, o), os = __shfl_xor_sync(0xffffffffu, lse_s, o);
+                const float mm = fmaxf(lse_m, om);
+                const float s1 = lse_m == -INFINITY ? 0.f : lse_s * expf(lse_m - mm), s2 = om == -INFINITY ? 0.f : os * expf(om - mm);
+                lse_m = mm, lse_s = s1 + s2;
+            }
+            if (lane == 0) {
+                atomicMax(&hdr->best, best);
+                red[warp] = lse_m;
+                red[8 + warp] = lse_s;
+            }
+            mg_consumer_bar();
+            if (tid == 0) {
+                float mm = -INFINITY, ssum = 0.f;
+                for (int w = 0; w < MG_NW; ++w) mm = fmaxf(mm, red[w]);
+                for (int w = 0; w < MG_NW; ++w) ssum += red[w] == -INFINITY ? 0.f : red[8 + w] * expf(red[w] - mm);
+                ws.lse[blockIdx.x] = make_float2(mm, ssum);
+            }
+        }
+        grid_barrier();
+    }
+
+    // ================= finish: next token, probability, state =================
+    if (ok && blockIdx.x == 0 && warp == 0) {
+        float mm = -INFINITY, ssum = 0.f;
+        for (uint32_t c = lane; c < G; c += 32) mm = fmaxf(mm, __ldcg(&ws.lse[c].x));
+        mm = warp_max(mm);
+        for (uint32_t c = lane; c < G; c += 32) {
+            const float2 v = __ldcg(&ws.lse[c]);
+            ssum += v.x == -INFINITY ? 0.f : v.y * expf(v.x - mm);
+        }
+        ssum = warp_sum(ssum);
+        if (lane == 0) {
+            const unsigned long long b = ld_acquire_gpu(&hdr->best);
+            const uint32_t idx = ~static_cast<uint32_t>(b & 0xffffffffull);
+            *a.next = static_cast<int64_t>(idx);
+            *a.prob = 1.0f / ssum;     // exp(max - max) / sum
+            *a.token = static_cast<int64_t>(idx);
+            *a.pos = static_cast<int64_t>(pos) + 1;
+            hdr->best = 0ull;
+            *reinterpret_cast<volatile unsigned long long *>(&hdr->epoch) = epoch + static_cast<unsigned long long>(nbar) * G;
+        }
+    }
+    if (!ok && tid == 0) atomicExch(&s_mega_error, 1);
+}
+
+int mega_error_word() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, s_mega_error, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+}// namespace rg
+
+using namespace rg;
+
+static size_t mega_smem_bytes() {
+    return MG_STAGES * MG_STAGE_BYTES + 2 * MG_STAGES * 8 + (32 + 256 + 128) * 4 + MG_PART_UNITS * 4 * MG_NW * 4 + 16;
+}
+
+static int mega_validate(const rg_decode_step_params *p) {
+    if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return RG_ERR_DTYPE;
+    if (p->layers > MG_MAX_LAYERS || p->hidden == 0 || p->n_heads == 0 || p->n_kv_heads == 0 || p->n_heads % p->n_kv_heads) return RG_ERR_SHAPE;
+    if (p->head_dim != 128 && p->head_dim != 64) return RG_ERR_SHAPE;
+    const uint32_t qd = p->n_heads * p->head_dim;
+    if (p->hidden % 8 || p->ffn % 8 || qd % 8) return RG_ERR_SHAPE;
+    if (p->hidden > MG_KCH * 256 * 8 || p->ffn > MG_KCH * 256 * 8 || qd > MG_KCH * 256 * 8) return RG_ERR_SHAPE;
+    if (p->hidden * 4u > MG_STAGE_BYTES || p->ffn * 2u > MG_STAGE_BYTES || qd * 2u > MG_STAGE_BYTES) return RG_ERR_SHAPE;
+    if (p->n_heads > 128 || MG_TILE * p->head_dim * 2u * 2u > MG_STAGE_BYTES) return RG_ERR_SHAPE;
+    return RG_OK;
+}
+
+extern "C" {
+
+size_t rg_b200_decode_step_workspace(const rg_decode_step_params *p) {
+    if (!p) return 0;
+    return mega_ws_bytes(static_cast<uint32_t>(sm_count()), p->hidden, p->n_heads, p->head_dim, p->ffn);
+}
+
+int rg_b200_decode_step(const rg_decode_step_params *p, void *ws, const void *const *in, void *const *out, void *stream) {
+    if (!p || !in || !out || !ws) return RG_ERR_NULL;
+    const int rc = mega_validate(p);
+    if (rc != RG_OK) return rc;
+    const uint32_t G = static_cast<uint32_t>(sm_count());
+    // per-CTA bounds of the phase tables
+    const uint32_t g4 = 4;
+    const uint32_t max_units = std::max({(p->vocab + g4 - 1) / g4, p->ffn, (p->n_heads + 2 * p->n_kv_heads) * p->head_dim / 2, p->hidden});
+    if ((max_units + G - 1) / G + 1 > MG_PART_UNITS) return RG_ERR_SHAPE;
+    if (p->n_heads / G + 3 > MG_MAX_REC) return RG_ERR_SHAPE;
+    MegaArgs a = {};
+    // inputs: token, pos, embed, norm_f, lm_head, then per layer norm1, wqkv, wo, norm2, wgu, wd, k_cache, v_cache
+    a.token = static_cast<int64_t *>(const_cast<void *>(in[0]));
+    a.pos = static_cast<int64_t *>(const_cast<void *>(in[1]));
+    a.embed = in[2], a.norm_f = in[3], a.lm_head = in[4];
+    if (!a.token || !a.pos || !a.embed || !a.norm_f || !a.lm_head) return RG_ERR_NULL;
+    for (uint32_t l = 0; l < p->layers; ++l) {
+        const void *const *q = in + 5 + 8 * l;
+        for (int j = 0; j < 8; ++j)
+            if (!q[j]) return RG_ERR_NULL;
+        a.layer[l] = {q[0], q[1], q[2], q[3], q[4], q[5], const_cast<void *>(q[6]), const_cast<void *>(q[7])};
+        if (!aligned16(q[1]) || !aligned16(q[2]) || !aligned16(q[4]) || !aligned16(q[5]) || !aligned16(q[6]) || !aligned16(q[7])) return RG_ERR_ALIGN;
+    }
+    a.next = static_cast<int64_t *>(out[0]);
+    a.prob = static_cast<float *>(out[1]);
+    a.logits = out[2];
+    if (!a.next || !a.prob || !a.logits) return RG_ERR_NULL;
+    a.ws = static_cast<uint8_t *>(ws);
+    a.layers = p->layers, a.H = p->hidden, a.nH = p->n_heads, a.nKV = p->n_kv_heads, a.D = p->head_dim, a.F = p->ffn, a.V = p->vocab;
+    a.max_seq = p->max_seq;
+    a.eps = p->epsilon, a.log2_theta = log2f(p->theta), a.scale = 1.0f / sqrtf(static_cast<float>(p->head_dim));
+    const size_t smem = mega_smem_bytes();
+    void *kern = p->dtype == RG_FP16 ? reinterpret_cast<void *>(decode_mega_kernel<__half>) : reinterpret_cast<void *>(decode_mega_kernel<__nv_bfloat16>);
+    RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    // cooperative launch: all CTAs are resident together, which the grid barriers rely on
+    void *args[] = {&a};
+    RG_CHECK_CUDA(cudaLaunchCooperativeKernel(kern, dim3(G), dim3(MG_THREADS), args, smem, static_cast<cudaStream_t>(stream)));
+    count_launch();
+    return RG_OK;
+}
+}

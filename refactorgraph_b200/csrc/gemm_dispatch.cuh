@@ -11,4 +11,5 @@ int linear_error_word();
 int attn_error_word();
 int gemm_tc_error_word();
 int all_reduce_error_word();
+int mega_error_word();
 }// namespace rg

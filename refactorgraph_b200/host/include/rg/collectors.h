@@ -108,6 +108,16 @@ namespace refactor::kernel {
         explicit SwigluCollector(Target target) noexcept : InfoCollector(target) {}
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
+    // One whole batch-1 decode step in a single persistent kernel (rg_b200_decode_step).
+    // inputs {token, pos, embed, norm_f, lm_head, per layer: norm1, wqkv, wo, norm2, wgu, wd, k_cache, v_cache}
+    // outputs {next int64[1], prob fp32[1], logits[1, vocab]}; token and pos are state edges updated in place
+    struct DecodeStepCollector final : public InfoCollector {
+        dim_t nHeads, nKVHeads, headDim;
+        float epsilon, theta;
+        DecodeStepCollector(Target target, dim_t nHeads_, dim_t nKVHeads_, dim_t headDim_, float epsilon_, float theta_) noexcept
+            : InfoCollector(target), nHeads(nHeads_), nKVHeads(nKVHeads_), headDim(headDim_), epsilon(epsilon_), theta(theta_) {}
+        std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
+    };
     // In-place int64 state update: inputs {state, [src]}; state = (src ? src : state) + delta.  The routine writes
     // through inputs[0] (a state edge of the graph); it has no outputs.
     RG_COLLECTOR(StateUpdateCollector, int64_t, delta);

@@ -281,6 +281,22 @@ namespace refactor::computation {
             return one(in[0].get().dataType, o);
         }
     };
+    struct DecodeStep final : Operator {
+        dim_t nHeads, nKVHeads, headDim;
+        float epsilon, theta;
+        explicit DecodeStep(Attributes const &a)
+            : nHeads(static_cast<dim_t>(getInt(a, "n_heads", 0))), nKVHeads(static_cast<dim_t>(getInt(a, "n_kv_heads", 0))),
+              headDim(static_cast<dim_t>(getInt(a, "head_dim", 0))), epsilon(static_cast<float>(getFloat(a, "epsilon", 1e-5))),
+              theta(static_cast<float>(getFloat(a, "theta", 10000.0))) {}
+        RG_OP_NAME("DecodeStep")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<DecodeStepCollector>(t, nHeads, nKVHeads, headDim, epsilon, theta); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            ASSERT(in.size() >= 5 && (in.size() - 5) % 8 == 0, "DecodeStep: inputs are token, pos, embed, norm_f, lm_head + 8 per layer");
+            auto const &embed = in[2].get();
+            return {Tensor::share(DataType::I64, Shape{1}), Tensor::share(DataType::F32, Shape{1}),
+                    Tensor::share(embed.dataType, Shape{1, embed.shape[0]})};
+        }
+    };
     struct StateUpdate final : Operator {
         int64_t delta;
         explicit StateUpdate(int64_t d) : delta(d) {}
@@ -334,6 +350,7 @@ namespace refactor::computation {
             return std::make_unique<AttentionDecode>(static_cast<dim_t>(getInt(a, "max_len", 0)), static_cast<dim_t>(getInt(a, "page_size", 0)));
         if (is({"b200::QkvRopeAppend"})) return std::make_unique<QkvRopeAppend>(a);
         if (is({"b200::SwiGLU"})) return std::make_unique<Swiglu>();
+        if (is({"b200::DecodeStep"})) return std::make_unique<DecodeStep>(a);
         if (is({"b200::StateUpdate"})) return std::make_unique<StateUpdate>(getInt(a, "delta", 0));
         TODO("Unsupported operator " + type);
     }

@@ -540,6 +540,29 @@ namespace refactor::kernel {
         return ans;
     }
 
+    RG_SIMPLE_KERNEL(DecodeStepB200, rg_decode_step_params, rg_b200_decode_step, "Whole batch-1 decode step as one persistent kernel on B200");
+    std::vector<KernelBox> DecodeStepCollector::filter(TensorRefs inputs, TensorRefs) const {
+        std::vector<KernelBox> ans;
+        if (_target != Target::Nvidia || inputs.size() < 5 || (inputs.size() - 5) % 8 != 0) return ans;
+        auto const &embed = inputs[2].get();
+        if (!half(embed.dataType) || embed.shape.size() != 2) return ans;
+        rg_decode_step_params p{};
+        p.dtype = embed.dataType;
+        p.layers = static_cast<uint32_t>((inputs.size() - 5) / 8);
+        p.vocab = embed.shape[0], p.hidden = embed.shape[1];
+        p.n_heads = nHeads, p.n_kv_heads = nKVHeads, p.head_dim = headDim;
+        p.epsilon = epsilon, p.theta = theta;
+        if (p.layers) {
+            auto const &wgu = inputs[5 + 4].get();
+            auto const &kc = inputs[5 + 6].get();
+            if (wgu.shape.size() != 2 || kc.shape.size() != 4 || kc.shape[0] != 1) return ans;
+            p.ffn = wgu.shape[0] / 2;
+            p.max_seq = kc.shape[2];
+        }
+        ans.emplace_back(std::make_unique<DecodeStepB200>(p));
+        return ans;
+    }
+
     // state (outputs[0] aliases inputs[0] in the graph) = (src ? src : state) + delta
     std::vector<KernelBox> StateUpdateCollector::filter(TensorRefs inputs, TensorRefs) const {
         std::vector<KernelBox> ans;

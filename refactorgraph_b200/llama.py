@@ -112,6 +112,29 @@ def decode_step_graph(cfg: LlamaConfig, top_k: int = 1, sample: bool = False, te
     return g, index
 
 
+def decode_step_graph_single_kernel(cfg: LlamaConfig):
+    """The batch-1 greedy decode step as ONE node (b200::DecodeStep, a persistent cooperative kernel).  Inputs: token[1],
+    pos[1] (int64 state: id of the token to feed and the number of cached tokens; both advanced by the kernel),
+    weights, caches.  Outputs: next token, its probability, logits — the same values as `decode_step_graph`."""
+    assert cfg.batch == 1
+    g = GraphBuilder()
+    token = g.input("token", I64, (1,))
+    pos = g.input("pos", I64, (1,))
+    for name, shape in weight_inputs(cfg):
+        g.input(name, cfg.dtype, shape)
+    for l in range(cfg.layers):
+        g.input(f"l{l}.k_cache", cfg.dtype, (1, cfg.kv_heads, cfg.max_seq, cfg.head_dim))
+        g.input(f"l{l}.v_cache", cfg.dtype, (1, cfg.kv_heads, cfg.max_seq, cfg.head_dim))
+    ins = [token, pos, "embed", "norm_f", "lm_head"]
+    for l in range(cfg.layers):
+        ins += [f"l{l}.norm1", f"l{l}.wqkv", f"l{l}.wo", f"l{l}.norm2", f"l{l}.wgu", f"l{l}.wd", f"l{l}.k_cache", f"l{l}.v_cache"]
+    nxt, prob, logits = g.op("b200::DecodeStep", ins, n_out=3, n_heads=cfg.heads, n_kv_heads=cfg.kv_heads, head_dim=cfg.head_dim,
+                             epsilon=cfg.eps, theta=cfg.theta)
+    index = {"next": g.output(nxt), "probs": g.output(prob), "logits": g.output(logits)}
+    index.update({name: i for i, name in enumerate(g.inputs)})
+    return g, index
+
+
 def shard_config(cfg: LlamaConfig, world: int) -> LlamaConfig:
     """Per-rank shape of a tensor-parallel model: heads, kv heads and FFN columns split `world` ways."""
     assert cfg.heads % world == 0 and cfg.kv_heads % world == 0 and cfg.ffn % world == 0

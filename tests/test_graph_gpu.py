@@ -7,7 +7,8 @@ import torch
 
 from oracle import oracle_np as onp
 from refactorgraph_b200.graph_builder import F32, FP16, I64, GraphBuilder
-from refactorgraph_b200.llama import LlamaConfig, decode_step_graph, prefill_graph_reference_ops, seeded_weights, weight_inputs
+from refactorgraph_b200.llama import (LlamaConfig, decode_step_graph, decode_step_graph_single_kernel, prefill_graph_reference_ops,
+                                      seeded_weights, weight_inputs)
 
 from _decode_oracle import oracle_decode as _oracle_decode
 
@@ -117,3 +118,44 @@ def test_reference_attention_operator_with_inplace_cache():
         want, kc_ref, vc_ref = onp.attention(qn, kn, vn, past=step, k_cache=kc_ref, v_cache=vc_ref)
         np.testing.assert_allclose(ex.get_output(0), want, rtol=1e-4, atol=1e-5)
         np.testing.assert_array_equal(ex.get_output(1), kc_ref)
+
+
+@pytest.mark.parametrize("shape", [dict(heads=4, kv_heads=2, head_dim=128, hidden=512, ffn=1024, vocab=2000, past=70),
+                                   dict(heads=8, kv_heads=8, head_dim=128, hidden=1024, ffn=2752, vocab=32000, past=700),
+                                   dict(heads=4, kv_heads=4, head_dim=64, hidden=256, ffn=688, vocab=1000, past=0),
+                                   dict(heads=4, kv_heads=1, head_dim=128, hidden=512, ffn=1024, vocab=777, past=64)])
+def test_single_kernel_decode_step(shape):
+    """b200::DecodeStep (the whole step in one persistent kernel) against the numpy oracle and the multi-kernel graph."""
+    from refactorgraph_b200 import capi
+    past0 = shape.pop("past")
+    cfg = LlamaConfig(layers=3, max_seq=1024, batch=1, **shape)
+    w16 = seeded_weights(cfg, 0, np.float16)
+    rng = np.random.default_rng(1)
+    w16["lm_head"] = (0.1 * rng.standard_normal(w16["lm_head"].shape)).astype(np.float16)   # spread enough to avoid fp16 arg-max ties
+    w = {k: v.astype(np.float32) for k, v in w16.items()}
+    past = np.array([past0], np.int64)
+    kc = [rng.standard_normal((1, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+    vc = [rng.standard_normal((1, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+    token = rng.integers(0, cfg.vocab, (1,)).astype(np.int64)
+    steps = 5
+    want_tok, want_logits = _oracle_decode(cfg, w, kc, vc, token, past, steps)
+    g, index = decode_step_graph_single_kernel(cfg)
+    ex = g.compiler().compile("cuda", "flat", [])
+    assert ex.node_count() == 1
+    for name, _ in weight_inputs(cfg):
+        ex.set_input(index[name], w16[name])
+    for l in range(cfg.layers):
+        ex.set_input(index[f"l{l}.k_cache"], kc[l])
+        ex.set_input(index[f"l{l}.v_cache"], vc[l])
+    ex.set_input(index["token"], token)
+    ex.set_input(index["pos"], past)
+    for s in range(steps):
+        ex.run()
+        assert capi.load().rg_b200_error_state() == 0, "a bounded wait expired inside the decode-step kernel"
+        logits = ex.get_output(index["logits"]).astype(np.float32)
+        np.testing.assert_allclose(logits, want_logits[s], atol=2e-2, rtol=1e-2)
+        tok = ex.get_output(index["next"])
+        np.testing.assert_array_equal(tok, onp.topk(logits, 1)[1][0])          # arg-max of its own logits, bit-exact
+        np.testing.assert_array_equal(tok, want_tok[s])
+        p = ex.get_output(index["probs"])
+        np.testing.assert_allclose(p, onp.topk_softmax(logits, 1)[0][0], rtol=1e-4)
