@@ -296,6 +296,10 @@ typedef struct rg_decode_step_params {
     float epsilon, theta;
 } rg_decode_step_params;
 size_t rg_b200_decode_step_workspace(const rg_decode_step_params *);
+/* Diagnostics: timestamps (ns) of the last call, read back from its workspace: four per phase (entered, activations
+ * ready, units consumed, epilogue done; phases per layer: QKV, attention, O, gate/up, down; then the LM head) plus a final
+ * group whose first entry is the end of the last grid barrier.  Returns entries written. */
+size_t rg_b200_decode_step_timeline(const rg_decode_step_params *, const void *ws, uint64_t *out_ns, size_t capacity);
 int rg_b200_decode_step(const rg_decode_step_params *, void *ws, const void *const *in, void *const *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------------

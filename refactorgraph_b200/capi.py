@@ -125,7 +125,7 @@ OPS = {
 }
 # every symbol include/rg_b200.h declares
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_attn_decode_static",
-            "rg_b200_attn_decode_static_capacity", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_connect_ptrs",
+            "rg_b200_attn_decode_static_capacity", "rg_b200_decode_step_timeline", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_connect_ptrs",
             "rg_b200_comm_set_wait_ns",
             "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]
            + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])
@@ -153,6 +153,8 @@ def load() -> C.CDLL:
         lib.rg_b200_attn_decode_static_capacity.restype = C.c_size_t
         lib.rg_b200_attn_decode_static.restype = C.c_int
         lib.rg_b200_attn_decode_static.argtypes = [C.POINTER(AttnDecodeParams), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p]
+        lib.rg_b200_decode_step_timeline.restype = C.c_size_t
+        lib.rg_b200_decode_step_timeline.argtypes = [C.POINTER(DecodeStepParams), C.c_void_p, C.POINTER(C.c_uint64), C.c_size_t]
         lib.rg_b200_comm_create.argtypes = [C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
         lib.rg_b200_comm_connect.argtypes = [C.c_void_p, C.c_void_p]
         lib.rg_b200_comm_status.argtypes = [C.c_void_p]

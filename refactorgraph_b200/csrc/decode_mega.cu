@@ -5,7 +5,7 @@
 // one.  Here one CTA per SM runs the whole step:
 //   * warp 8 (one thread) is a producer that walks the step's entire schedule — for every layer the QKV, KV-cache,
 //     O, gate/up and down phases, then the LM head — and streams each CTA's share of the weights (and of the old
-//     KV tiles) into a 3 x 32 KiB shared-memory ring with cp.async.bulk + mbarriers.  It is throttled only by ring
+//     KV tiles) into a 6 x 32 KiB shared-memory ring with cp.async.bulk + mbarriers.  It is throttled only by ring
 //     space, never by a phase boundary, so HBM stays busy while the consumers synchronise.
 //   * warps 0-7 consume: per phase they (re)load the activation vector into registers (RMSNorm, or the merge of the
 //     attention partials), reduce their units, run the phase epilogue (RoPE + cache append, residual add, SiLU*up,
@@ -22,7 +22,7 @@ namespace rg {
 constexpr int MG_NW = 8;
 constexpr int MG_CONSUMERS = MG_NW * 32;
 constexpr int MG_THREADS = MG_CONSUMERS + 32;
-constexpr int MG_STAGES = 3;
+constexpr int MG_STAGES = 6;   // 192 KiB of weights in flight per SM: enough to ride through a grid barrier
 constexpr uint32_t MG_STAGE_BYTES = 32768;
 constexpr int MG_KCH = 6;          // k <= 6 * 256 * 8 = 12288
 constexpr int MG_MAX_LAYERS = 96;
@@ -59,11 +59,12 @@ struct MegaWs {
     float2 *lse;
     void *x, *h, *q, *u;
     float *rec;
+    unsigned long long *timeline;// [phases + 1][4] %globaltimer of CTA 0: phase entered, activations ready, units consumed, epilogue done
 };
 __host__ __device__ inline size_t mg_align(size_t v) { return (v + 255) / 256 * 256; }
 __host__ __device__ inline size_t mega_ws_bytes(uint32_t G, uint32_t H, uint32_t nH, uint32_t D, uint32_t F) {
     return 256 + mg_align(G * 8) + 2 * mg_align(H * 2) + mg_align(static_cast<size_t>(nH) * D * 2) + mg_align(F * 2) +
-           mg_align(static_cast<size_t>(G) * MG_MAX_REC * (D + 2) * 4);
+           mg_align(static_cast<size_t>(G) * MG_MAX_REC * (D + 2) * 4) + mg_align((MG_MAX_LAYERS * 5 + 2) * 4 * 8);
 }
 __device__ inline MegaWs mega_ws(uint8_t *p, uint32_t G, uint32_t H, uint32_t nH, uint32_t D, uint32_t F) {
     MegaWs w;
@@ -80,6 +81,8 @@ __device__ inline MegaWs mega_ws(uint8_t *p, uint32_t G, uint32_t H, uint32_t nH
     w.u = p;
     p += mg_align(F * 2);
     w.rec = reinterpret_cast<float *>(p);
+    p += mg_align(static_cast<size_t>(G) * MG_MAX_REC * (D + 2) * 4);
+    w.timeline = reinterpret_cast<unsigned long long *>(p);
     return w;
 }
 
@@ -104,10 +107,7 @@ __device__ inline Phase phase_of(const MegaArgs &a, uint32_t p, uint32_t T) {
     ph.type = ph.layer < a.layers ? static_cast<int>(p % 5) : PH_LM;
     ph.W = nullptr;
     ph.n = ph.k = ph.g = ph.segs = ph.units = 0;
-    if (ph.type == PH_ATT) {
-        ph.units = a.nH * T;
-        return ph;
-    }
+    if (ph.type == PH_ATT) return ph;// attention units are assigned by att_range, not by unit_range
     const MegaLayer &L = a.layer[ph.layer < a.layers ? ph.layer : 0];
     switch (ph.type) {
         case PH_QKV: ph.W = static_cast<const uint8_t *>(L.wqkv), ph.n = (a.nH + 2 * a.nKV) * a.D, ph.k = a.H, ph.segs = 2; break;
@@ -145,6 +145,20 @@ __device__ __forceinline__ void unit_range(uint32_t units, uint32_t &u0, uint32_
     u0 = static_cast<uint32_t>(static_cast<uint64_t>(units) * blockIdx.x / gridDim.x);
     u1 = static_cast<uint32_t>(static_cast<uint64_t>(units) * (blockIdx.x + 1) / gridDim.x);
 }
+// Attention work split: SPLITS = G / nH CTAs per head (the remaining CTAs idle in this phase); CTA c handles head
+// c / SPLITS and the tiles [NT*j/SPLITS, NT*(j+1)/SPLITS) with j = c % SPLITS.  One partial record per CTA.
+__host__ __device__ inline uint32_t att_splits(uint32_t G, uint32_t nH) {
+    const uint32_t s = G / nH;
+    return s > 8 ? 8 : s;
+}
+__device__ __forceinline__ bool att_range(const MegaArgs &a, uint32_t NT, uint32_t cta, uint32_t G, uint32_t &head, uint32_t &t0, uint32_t &t1) {
+    const uint32_t splits = att_splits(G, a.nH);
+    head = cta / splits;
+    if (head >= a.nH) return false;
+    const uint32_t j = cta % splits;
+    t0 = NT * j / splits, t1 = NT * (j + 1) / splits;
+    return t1 > t0;
+}
 __device__ __forceinline__ void mg_consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(MG_CONSUMERS) : "memory"); }
 
 __device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long *p) {
@@ -168,6 +182,43 @@ template<int V> __device__ __forceinline__ void mg_reduce_halving(float (&vals)[
         o >>= 1;
     }
     for (; o > 0; o >>= 1) vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], o);
+}
+
+// Consumes `nu` units of a linear phase from the ring: R rows per unit, KC live 16-byte chunks per thread along k.
+// part[(i*4 + row) * MG_NW + warp] receives each warp's partial row sums of local unit i.
+template<class T, int R, int KC>
+__device__ __forceinline__ bool mega_linear_units(const uint8_t *smem, uint64_t *full, uint64_t *empty, float *part,
+                                                  const float (&x)[MG_KCH][8], uint32_t nu, uint32_t &it, uint32_t k,
+                                                  uint32_t tid, uint32_t warp, uint32_t lane) {
+    const uint32_t kchunks = k / 8, row_bytes = k * 2u;
+    for (uint32_t i = 0; i < nu; ++i, ++it) {
+        const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
+        if (!mbar_wait(&full[s], par)) return false;
+        const uint8_t *st = smem + s * MG_STAGE_BYTES;
+        uint4 raw[R][KC];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < KC; ++c) {
+                const uint32_t ci = tid + c * MG_CONSUMERS;
+                raw[r][c] = ci < kchunks ? *reinterpret_cast<const uint4 *>(st + static_cast<size_t>(r) * row_bytes + ci * 16) : make_uint4(0, 0, 0, 0);
+            }
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < KC; ++c) {
+                float w[8];
+                unpack8<T>(raw[r][c], w);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[r] = fmaf(w[j], x[c][j], acc[r]);
+            }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+        mg_reduce_halving<4>(acc, static_cast<int>(lane));
+        if ((lane & 7u) == 0) part[(i * 4 + (lane >> 3)) * MG_NW + warp] = acc[0];
+    }
+    return true;
 }
 
 template<class T>
@@ -208,18 +259,22 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             bool ok = true;
             for (uint32_t p = 0; p < nphases && ok; ++p) {
                 const Phase ph = phase_of(a, p, NT);
-                uint32_t u0, u1;
-                unit_range(ph.units, u0, u1);
+                uint32_t u0, u1, att_head = 0;
+                if (ph.type == PH_ATT) {
+                    if (!att_range(a, NT, blockIdx.x, gridDim.x, att_head, u0, u1)) u0 = u1 = 0;
+                } else {
+                    unit_range(ph.units, u0, u1);
+                }
                 for (uint32_t u = u0; u < u1; ++u, ++it) {
                     const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
-                    if (!mbar_wait(&empty[s], par ^ 1u) || ld_volatile_int(&hdr->abort)) {
+                    if (!mbar_wait(&empty[s], par ^ 1u)) {
                         atomicExch(&hdr->abort, 1);
                         ok = false;
                         break;
                     }
                     uint8_t *st = smem + s * MG_STAGE_BYTES;
                     if (ph.type == PH_ATT) {
-                        const uint32_t h = u / NT, t = u % NT, kvh = h / (a.nH / a.nKV);
+                        const uint32_t h = att_head, t = u, kvh = h / (a.nH / a.nKV);
                         const uint32_t tok0 = t * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
                         const uint32_t bytes = ntok * a.D * 2u;
                         const size_t off = (static_cast<size_t>(kvh) * a.max_seq + tok0) * a.D * 2u;
@@ -253,12 +308,11 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
     float lse_m = -INFINITY, lse_s = 0.f;
 
     auto grid_barrier = [&]() {
-        // consumers of this CTA first, then all CTAs; bounded
-        __threadfence();
+        // consumers of this CTA first (bar.sync orders their global writes before thread 0's release), then all CTAs
         mg_consumer_bar();
         ++nbar;
         if (tid == 0) {
-            atomicAdd(&hdr->bar, 1ull);
+            asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(&hdr->bar), "l"(1ull) : "memory");
             const unsigned long long target = epoch + static_cast<unsigned long long>(nbar) * G;
             const uint64_t t0 = global_timer_ns();
             for (;;) {
@@ -272,50 +326,45 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
         }
         mg_consumer_bar();
         if (*s_fail) ok = false;
+        if (blockIdx.x == 0 && tid == 0) ws.timeline[nbar * 4] = global_timer_ns();
     };
+    auto stamp = [&](uint32_t p, uint32_t k) {
+        if (blockIdx.x == 0 && tid == 0) ws.timeline[p * 4 + k] = global_timer_ns();
+    };
+    stamp(0, 0);
 
     for (uint32_t p = 0; p < nphases && ok; ++p) {
         const Phase ph = phase_of(a, p, NT);
-        uint32_t u0, u1;
-        unit_range(ph.units, u0, u1);
+        uint32_t u0, u1, att_head = 0;
+        if (ph.type == PH_ATT) {
+            if (!att_range(a, NT, blockIdx.x, G, att_head, u0, u1)) u0 = u1 = 0;
+        } else {
+            unit_range(ph.units, u0, u1);
+        }
         const uint32_t nu = u1 - u0;
 
         if (ph.type == PH_ATT) {
-            // ---------------- attention over cached tokens: units = (head, tile) ----------------
+            // ---------------- attention over cached tokens: this CTA = one head, a run of 64-token tiles ----------
+            // Each warp owns 8 tokens of every tile and keeps its own online-softmax state, so a tile needs no CTA-wide
+            // barrier: four lanes per token for q.k (the lane's quarter of q stays in registers), then every lane
+            // accumulates its D/32 output dims over the warp's 8 tokens.
             const T *qbuf = static_cast<const T *>(ws.q);
-            float m_run = -INFINITY, l_run = 0.f;
-            float acc[8];
+            const uint32_t D = a.D, qd = lane & 3u, tl = lane >> 2, DPL = D / 4, CPT = DPL / 8, DV = D / 32;
+            const uint32_t swz = D == 128 ? (((tl & 1u) << 1) | (qd >> 1)) : (tl & 1u);
+            float qreg[32];
+            float m_w = -INFINITY, l_w = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (nu) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            const uint32_t CPR = a.D / 8;                   // 16-byte chunks per row (16 for D = 128)
-            const uint32_t cg = tid % CPR, tg = tid / CPR, NTG = MG_CONSUMERS / CPR;
-            uint32_t cur_h = 0xffffffffu, first_h = nu ? u0 / NT : 0;
-            auto flush = [&](uint32_t h) {
-                // reduce the token groups and write this CTA's record for head h
-                mg_consumer_bar();
+                for (int c = 0; c < 4; ++c) {
+                    if (c < static_cast<int>(CPT)) {
+                        float f[8];
+                        unpack8<T>(__ldcg(reinterpret_cast<const uint4 *>(qbuf + att_head * D + qd * DPL + c * 8)), f);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) part[tg * a.D + cg * 8 + j] = acc[j];
-                mg_consumer_bar();
-                float *rec = ws.rec + (static_cast<size_t>(blockIdx.x) * MG_MAX_REC + (h - first_h)) * (a.D + 2);
-                if (tid < a.D) {
-                    float o = 0.f;
-                    for (uint32_t gidx = 0; gidx < NTG; ++gidx) o += part[gidx * a.D + tid];
-                    rec[2 + tid] = o;
+                        for (int e = 0; e < 8; ++e) qreg[c * 8 + e] = f[e];
+                    }
                 }
-                if (tid == 0) rec[0] = m_run, rec[1] = l_run;
-                m_run = -INFINITY, l_run = 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            };
-            for (uint32_t u = u0; u < u1 && ok; ++u, ++it) {
-                const uint32_t h = u / NT, t = u % NT;
-                if (h != cur_h) {
-                    if (cur_h != 0xffffffffu) flush(cur_h);
-                    mg_consumer_bar();
-                    if (tid < a.D) qs[tid] = Num<T>::to_f(__ldcg(qbuf + h * a.D + tid));
-                    cur_h = h;
-                    mg_consumer_bar();
-                }
+            }
+            for (uint32_t t = u0; t < u1 && ok; ++t, ++it) {
                 const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
                 if (!mbar_wait(&full[s], par)) {
                     ok = false;
@@ -323,52 +372,91 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 }
                 const uint32_t tok0 = t * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
                 const uint8_t *ks = smem + s * MG_STAGE_BYTES, *vs = ks + MG_STAGE_BYTES / 2;
-                {   // scores: four threads per token, each a quarter of the row
-                    const uint32_t tk = tid >> 2, qd = tid & 3u, cpt = CPR / 4;
-                    const uint32_t swz = ((tk & 1u) << 1 | (qd >> 1)) & (cpt - 1);
-                    float dot = 0.f;
-                    if (tk < ntok) {
-                        for (uint32_t c = 0; c < cpt; ++c) {
-                            const uint32_t cc = qd * cpt + (c ^ swz);
+                const uint32_t tk = warp * 8 + tl;
+                float dot = 0.f;
+                if (tk < ntok) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        if (c < static_cast<int>(CPT)) {
+                            const uint32_t cs = static_cast<uint32_t>(c) ^ swz;
                             float kf[8];
-                            unpack8<T>(*reinterpret_cast<const uint4 *>(ks + tk * (a.D * 2) + cc * 16), kf);
-                            const float4 q0 = *reinterpret_cast<const float4 *>(qs + cc * 8);
-                            const float4 q1 = *reinterpret_cast<const float4 *>(qs + cc * 8 + 4);
-                            dot += kf[0] * q0.x + kf[1] * q0.y + kf[2] * q0.z + kf[3] * q0.w + kf[4] * q1.x + kf[5] * q1.y + kf[6] * q1.z + kf[7] * q1.w;
+                            unpack8<T>(*reinterpret_cast<const uint4 *>(ks + tk * (D * 2) + (qd * CPT + cs) * 16), kf);
+#pragma unroll
+                            for (int cc = 0; cc < 4; ++cc)
+                                if (static_cast<uint32_t>(cc) == cs) {
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) dot = fmaf(kf[e], qreg[cc * 8 + e], dot);
+                                }
                         }
                     }
-                    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-                    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                    if (qd == 0) sc[tk] = tk < ntok ? dot * a.scale : -INFINITY;
                 }
-                mg_consumer_bar();
-                const float s0 = sc[lane], s1 = sc[lane + 32];
-                const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
-                const float p0 = expf(s0 - m_new), p1 = expf(s1 - m_new);
-                const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
-                l_run = l_run * corr + warp_sum(p0 + p1);
-                m_run = m_new;
-                mg_consumer_bar();
-                if (tid < 32) sc[lane] = p0, sc[lane + 32] = p1;
-                mg_consumer_bar();
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                const float sco = tk < ntok ? dot * a.scale : -INFINITY;
+                float mx = sco;
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_new = fmaxf(m_w, mx);
+                const float pr = (sco == -INFINITY) ? 0.f : expf(sco - m_new);
+                const float corr = (m_w == -INFINITY) ? 0.f : expf(m_w - m_new);
+                l_w = l_w * corr + 0.25f * warp_sum(pr);// every token's probability sits in four lanes
+                m_w = m_new;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] *= corr;
-                for (uint32_t tk = tg; tk < ntok; tk += NTG) {
-                    const float pr = sc[tk];
-                    float vf[8];
-                    unpack8<T>(*reinterpret_cast<const uint4 *>(vs + tk * (a.D * 2) + cg * 16), vf);
+                for (int e = 0; e < 4; ++e) acc[e] *= corr;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = fmaf(pr, vf[j], acc[j]);
+                for (int t8 = 0; t8 < 8; ++t8) {
+                    const float pt = __shfl_sync(0xffffffffu, pr, t8 * 4);
+                    const uint32_t tok = warp * 8 + t8;
+                    if (tok < ntok) {
+                        const T *vr = reinterpret_cast<const T *>(vs + tok * (D * 2)) + lane * DV;
+                        if (DV == 4) {
+                            const uint2 raw = *reinterpret_cast<const uint2 *>(vr);
+                            const T *e4 = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) acc[e] = fmaf(pt, Num<T>::to_f(e4[e]), acc[e]);
+                        } else {
+                            const uint32_t raw = *reinterpret_cast<const uint32_t *>(vr);
+                            const T *e2 = reinterpret_cast<const T *>(&raw);
+                            acc[0] = fmaf(pt, Num<T>::to_f(e2[0]), acc[0]);
+                            acc[1] = fmaf(pt, Num<T>::to_f(e2[1]), acc[1]);
+                        }
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
-                mg_consumer_bar();// sc[] is rewritten by the next unit
             }
-            if (ok && cur_h != 0xffffffffu) flush(cur_h);
+            if (ok && nu) {
+                // merge the eight warps' states and write this CTA's record [m, l, -, -, acc[D]]
+                float *wst = part + warp * (D + 2);
+                if (lane == 0) wst[0] = m_w, wst[1] = l_w;
+                for (uint32_t e = 0; e < DV; ++e) wst[2 + lane * DV + e] = acc[e];
+                mg_consumer_bar();
+                float *rec = ws.rec + static_cast<size_t>(blockIdx.x) * (D + 4);
+                float M = -INFINITY;
+                for (int w = 0; w < MG_NW; ++w) M = fmaxf(M, part[w * (D + 2)]);
+                if (tid < D) {
+                    float o = 0.f;
+                    for (int w = 0; w < MG_NW; ++w) {
+                        const float mw = part[w * (D + 2)];
+                        if (mw != -INFINITY) o += part[w * (D + 2) + 2 + tid] * expf(mw - M);
+                    }
+                    rec[4 + tid] = o;
+                }
+                if (tid == 0) {
+                    float L = 0.f;
+                    for (int w = 0; w < MG_NW; ++w) {
+                        const float mw = part[w * (D + 2)];
+                        if (mw != -INFINITY) L += part[w * (D + 2) + 1] * expf(mw - M);
+                    }
+                    rec[0] = M, rec[1] = L;
+                }
+            }
             if (!ok) {
                 atomicExch(&hdr->abort, 1);
                 *s_fail = 1;
             }
+            stamp(p, 3);
             grid_barrier();
             continue;
         }
@@ -400,7 +488,21 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                     float d = 0.f;
                     if (h < a.nH) {
                         const T *kn = static_cast<const T *>(a.layer[ph.layer].kc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D;
-                        for (uint32_t e = pt; e < a.D; e += 8) d += Num<T>::to_f(__ldcg(qbuf + h * a.D + e)) * Num<T>::to_f(__ldcg(kn + e));
+                        // D/8 chunks of 8 elements, 8 threads per head: chunks pt, pt + 8 (both loads in flight together)
+                        uint4 qa = make_uint4(0, 0, 0, 0), ka = qa, qb = qa, kb = qa;
+                        qa = __ldcg(reinterpret_cast<const uint4 *>(qbuf + h * a.D + pt * 8));
+                        ka = __ldcg(reinterpret_cast<const uint4 *>(kn + pt * 8));
+                        if (a.D > 64) {
+                            qb = __ldcg(reinterpret_cast<const uint4 *>(qbuf + h * a.D + 64 + pt * 8));
+                            kb = __ldcg(reinterpret_cast<const uint4 *>(kn + 64 + pt * 8));
+                        }
+                        float qf[8], kf[8];
+                        unpack8<T>(qa, qf), unpack8<T>(ka, kf);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
+                        unpack8<T>(qb, qf), unpack8<T>(kb, kf);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
                     }
                     d += __shfl_xor_sync(0xffffffffu, d, 1);
                     d += __shfl_xor_sync(0xffffffffu, d, 2);
@@ -408,7 +510,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                     if (h < a.nH && pt == 0) sc[h] = d * a.scale;
                 }
                 mg_consumer_bar();
-                const uint32_t Uatt = a.nH * NT;
+                const uint32_t splits = att_splits(G, a.nH);
 #pragma unroll
                 for (int c = 0; c < MG_KCH; ++c) {
                     const uint32_t ci = tid + c * MG_CONSUMERS;
@@ -417,38 +519,45 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                     if (ci < kchunks) {
                         const uint32_t h = ci * 8 / a.D, d0 = ci * 8 % a.D;
                         const T *vn = static_cast<const T *>(a.layer[ph.layer].vc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D + d0;
-                        float mx = sc[h];
-                        // CTAs holding units of head h: those whose range intersects [h*T, (h+1)*T)
-                        uint32_t c_lo = 0, c_hi = 0;
-                        if (NT) {
-                            c_lo = static_cast<uint32_t>((static_cast<uint64_t>(h) * NT * G) / Uatt);
-                            while (c_lo > 0 && static_cast<uint64_t>(Uatt) * c_lo / G > static_cast<uint64_t>(h) * NT) --c_lo;
-                            while (static_cast<uint64_t>(Uatt) * (c_lo + 1) / G <= static_cast<uint64_t>(h) * NT) ++c_lo;
-                            c_hi = c_lo;
-                            while (c_hi + 1 < G && static_cast<uint64_t>(Uatt) * (c_hi + 1) / G < static_cast<uint64_t>(h + 1) * NT) ++c_hi;
-                            for (uint32_t cc = c_lo; cc <= c_hi; ++cc) {
-                                const uint32_t cu0 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * cc / G);
-                                const uint32_t cu1 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * (cc + 1) / G);
-                                if (cu1 <= cu0) continue;
-                                const float *rec = ws.rec + (static_cast<size_t>(cc) * MG_MAX_REC + (h - cu0 / NT)) * (a.D + 2);
-                                mx = fmaxf(mx, __ldcg(rec));
-                            }
-                        }
-                        float den = expf(sc[h] - mx);
+                        // start from the token produced in this step, then fold in the records of head h (CTAs
+                        // h*splits + j whose tile range is not empty) four at a time, rescaling to the running maximum
                         float vnf[8];
                         unpack8<T>(__ldcg(reinterpret_cast<const uint4 *>(vn)), vnf);
+                        float mx = sc[h], den = 1.f;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) x[c][j] = den * vnf[j];
-                        if (NT) {
-                            for (uint32_t cc = c_lo; cc <= c_hi; ++cc) {
-                                const uint32_t cu0 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * cc / G);
-                                const uint32_t cu1 = static_cast<uint32_t>(static_cast<uint64_t>(Uatt) * (cc + 1) / G);
-                                if (cu1 <= cu0) continue;
-                                const float *rec = ws.rec + (static_cast<size_t>(cc) * MG_MAX_REC + (h - cu0 / NT)) * (a.D + 2);
-                                const float w = expf(__ldcg(rec) - mx);
-                                den += __ldcg(rec + 1) * w;
+                        for (int j = 0; j < 8; ++j) x[c][j] = vnf[j];
+                        for (uint32_t j0 = 0; j0 < splits; j0 += 4) {
+                            float2 ml[4];
+                            float4 r0[4], r1[4];
+                            uint32_t live = 0;
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) x[c][j] += __ldcg(rec + 2 + d0 + j) * w;
+                            for (uint32_t jj = 0; jj < 4; ++jj) {
+                                const uint32_t j = j0 + jj;
+                                if (j < splits && NT * (j + 1) / splits > NT * j / splits) {
+                                    const float *rec = ws.rec + static_cast<size_t>(h * splits + j) * (a.D + 4);
+                                    ml[jj] = __ldcg(reinterpret_cast<const float2 *>(rec));
+                                    r0[jj] = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + d0));
+                                    r1[jj] = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + d0 + 4));
+                                    live |= 1u << jj;
+                                }
+                            }
+                            float nm = mx;
+#pragma unroll
+                            for (uint32_t jj = 0; jj < 4; ++jj)
+                                if (live >> jj & 1u) nm = fmaxf(nm, ml[jj].x);
+                            const float f = expf(mx - nm);
+                            den *= f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) x[c][j] *= f;
+                            mx = nm;
+#pragma unroll
+                            for (uint32_t jj = 0; jj < 4; ++jj) {
+                                if (live >> jj & 1u) {
+                                    const float w = expf(ml[jj].x - mx);
+                                    den += ml[jj].y * w;
+                                    x[c][0] += r0[jj].x * w, x[c][1] += r0[jj].y * w, x[c][2] += r0[jj].z * w, x[c][3] += r0[jj].w * w;
+                                    x[c][4] += r1[jj].x * w, x[c][5] += r1[jj].y * w, x[c][6] += r1[jj].z * w, x[c][7] += r1[jj].w * w;
+                                }
                             }
                         }
                         const float inv = 1.f / den;
@@ -495,41 +604,33 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             }
         }
 
-        const uint32_t R = ph.g * ph.segs, row_bytes = ph.k * 2u;
-        for (uint32_t i = 0; i < nu; ++i, ++it) {
-            const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
-            if (!mbar_wait(&full[s], par)) {
-                ok = false;
-                break;
-            }
-            const uint8_t *st = smem + s * MG_STAGE_BYTES;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                if (r < static_cast<int>(R)) {
-#pragma unroll
-                    for (int c = 0; c < MG_KCH; ++c) {
-                        const uint32_t ci = tid + c * MG_CONSUMERS;
-                        if (ci < kchunks) {
-                            float w[8];
-                            unpack8<T>(*reinterpret_cast<const uint4 *>(st + static_cast<size_t>(r) * row_bytes + ci * 16), w);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) acc[r] = fmaf(w[j], x[c][j], acc[r]);
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            mg_reduce_halving<4>(acc, static_cast<int>(lane));
-            if ((lane & 7u) == 0) part[(i * 4 + (lane >> 3)) * MG_NW + warp] = acc[0];
+        stamp(p, 1);
+        const uint32_t R = ph.g * ph.segs;
+        // the row count per unit (1, 2 or 4) and the number of live k-chunks per thread (2, 4 or 6) are fixed for a
+        // phase: dispatch once to a fully unrolled loop so that all shared-memory loads of a unit are in flight together
+        const uint32_t kc_live = (kchunks + MG_CONSUMERS - 1) / MG_CONSUMERS;
+#define RG_MG_RUN(R_, KC_) ok = mega_linear_units<T, R_, KC_>(smem, full, empty, part, x, nu, it, ph.k, tid, warp, lane)
+        if (R == 4) {
+            if (kc_live <= 2) RG_MG_RUN(4, 2);
+            else if (kc_live <= 4) RG_MG_RUN(4, 4);
+            else RG_MG_RUN(4, 6);
+        } else if (R == 2) {
+            if (kc_live <= 2) RG_MG_RUN(2, 2);
+            else if (kc_live <= 4) RG_MG_RUN(2, 4);
+            else RG_MG_RUN(2, 6);
+        } else {
+            if (kc_live <= 2) RG_MG_RUN(1, 2);
+            else if (kc_live <= 4) RG_MG_RUN(1, 4);
+            else RG_MG_RUN(1, 6);
         }
+#undef RG_MG_RUN
         if (!ok) {
             atomicExch(&hdr->abort, 1);
             *s_fail = 1;
         }
         mg_consumer_bar();
         if (*s_fail) ok = false;
+        stamp(p, 2);
 
         // ---------------- epilogue: one item = (local unit, row r within g) ----------------
         if (ok) {
@@ -622,6 +723,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 ws.lse[blockIdx.x] = make_float2(mm, ssum);
             }
         }
+        stamp(p, 3);
         grid_barrier();
     }
 
@@ -677,6 +779,21 @@ static int mega_validate(const rg_decode_step_params *p) {
 
 extern "C" {
 
+// Diagnostics: copies the per-phase timestamps (ns, %globaltimer of CTA 0) of the last call out of the workspace: four
+// entries per phase (entered, activations ready, units consumed, epilogue done; phases are, per layer, QKV, attention,
+// O, gate/up, down, then the LM head) and one more group whose first entry is the end of the last grid barrier.
+// Synchronises the device.  Returns the number of entries written.
+size_t rg_b200_decode_step_timeline(const rg_decode_step_params *p, const void *ws, uint64_t *out, size_t capacity) {
+    if (!p || !ws || !out) return 0;
+    const uint32_t G = static_cast<uint32_t>(sm_count());
+    const size_t off = mega_ws_bytes(G, p->hidden, p->n_heads, p->head_dim, p->ffn) - mg_align((MG_MAX_LAYERS * 5 + 2) * 4 * 8);
+    size_t n = (static_cast<size_t>(p->layers) * 5 + 2) * 4;
+    if (n > capacity) n = capacity;
+    if (cudaDeviceSynchronize() != cudaSuccess) return 0;
+    if (cudaMemcpy(out, static_cast<const uint8_t *>(ws) + off, n * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    return n;
+}
+
 size_t rg_b200_decode_step_workspace(const rg_decode_step_params *p) {
     if (!p) return 0;
     return mega_ws_bytes(static_cast<uint32_t>(sm_count()), p->hidden, p->n_heads, p->head_dim, p->ffn);
@@ -691,7 +808,7 @@ int rg_b200_decode_step(const rg_decode_step_params *p, void *ws, const void *co
     const uint32_t g4 = 4;
     const uint32_t max_units = std::max({(p->vocab + g4 - 1) / g4, p->ffn, (p->n_heads + 2 * p->n_kv_heads) * p->head_dim / 2, p->hidden});
     if ((max_units + G - 1) / G + 1 > MG_PART_UNITS) return RG_ERR_SHAPE;
-    if (p->n_heads / G + 3 > MG_MAX_REC) return RG_ERR_SHAPE;
+    if (p->n_heads > G) return RG_ERR_SHAPE;// the attention phase gives every head 1..8 CTAs
     MegaArgs a = {};
     // inputs: token, pos, embed, norm_f, lm_head, then per layer norm1, wqkv, wo, norm2, wgu, wd, k_cache, v_cache
     a.token = static_cast<int64_t *>(const_cast<void *>(in[0]));
