@@ -324,6 +324,19 @@ typedef struct rg_attention_params {
 size_t rg_b200_attention_workspace(const rg_attention_params *);
 int rg_b200_attention(const rg_attention_params *, void *ws, const void *const *in, void *const *out, void *stream);
 
+/* Causal flash attention with explicit element strides (head_dim 128, fp16 / bf16): what rg_b200_attention runs for
+ * prefill, exposed so that a fused QKV projection can be consumed in its token-major layout without transposes.
+ * strides[12] = {q, k, v, o} x {sequence, head, token}; the head dimension is contiguous and every stride a multiple of 8.
+ * Query row i of a sequence (absolute position past + i) attends keys j <= past + i, j < kv_capacity.
+ * inputs {q, k, v, past_seq_len (device int64[1]) or NULL}, outputs {o}. */
+typedef struct rg_attn_prefill_params {
+    int32_t dtype;
+    uint32_t batch, n_heads, n_kv_heads, seq_len, head_dim, kv_capacity;
+    int64_t strides[12];
+} rg_attn_prefill_params;
+size_t rg_b200_attn_prefill_workspace(const rg_attn_prefill_params *);
+int rg_b200_attn_prefill(const rg_attn_prefill_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
 /* Split-K flash-decoding over a (paged or contiguous) KV cache, one new token per sequence.
  *   inputs {q[batch, n_heads, D], k_cache, v_cache, seq_lens (device int64[batch]; keys [0, len) are attended,
  *           the new token's k/v already appended), block_table (int32) or NULL}

@@ -100,6 +100,11 @@ class AttentionParams(C.Structure):
                 ("seq_len", C.c_uint32), ("head_dim", C.c_uint32), ("max_seq", C.c_uint32), ("has_cache", C.c_int32)]
 
 
+class AttnPrefillParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint32), ("n_heads", C.c_uint32), ("n_kv_heads", C.c_uint32),
+                ("seq_len", C.c_uint32), ("head_dim", C.c_uint32), ("kv_capacity", C.c_uint32), ("strides", C.c_int64 * 12)]
+
+
 class AttnDecodeParams(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint32), ("n_heads", C.c_uint32), ("max_len", C.c_uint32),
                 ("kv", KvLayout)]
@@ -121,7 +126,7 @@ OPS = {
     "gather": GatherParams, "binary": BinaryParams, "unary": UnaryParams, "where": WhereParams,
     "transpose": TransposeParams, "rope": RopeParams, "state_update": StateUpdateParams, "mat_mul": MatMulParams, "linear": LinearParams,
     "attention": AttentionParams, "attn_decode": AttnDecodeParams, "qkv_rope_append": QkvRopeAppendParams,
-    "swiglu": SwigluParams, "decode_step": DecodeStepParams,
+    "swiglu": SwigluParams, "decode_step": DecodeStepParams, "attn_prefill": AttnPrefillParams,
 }
 # every symbol include/rg_b200.h declares
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_attn_decode_static",

@@ -343,6 +343,9 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const T *__restrict__ q,
     for (int e = 0; e < EP; ++e) o[row * D + lane * EP + e] = Num<T>::from_f(acc[e] / l);
 }
 
+int attn_prefill_ref_layout(int dtype, const void *q, const void *K, const void *V, void *o, const int64_t *past, uint32_t batch,
+                            uint32_t n_heads, uint32_t n_kv, uint32_t S, uint32_t kv_tokens, cudaStream_t st);
+
 template<class T>
 static int attention_launch(const rg_attention_params *p, const void *const *in, void *const *out, cudaStream_t st) {
     auto q = static_cast<const T *>(in[0]);
@@ -376,6 +379,9 @@ static int attention_launch(const rg_attention_params *p, const void *const *in,
     }
     const uint64_t rows = static_cast<uint64_t>(p->batch) * p->n_heads * p->seq_len;
     if (rows == 0) return RG_OK;
+    // tensor-core flash kernel for 16-bit types at head_dim 128 once there is a tile's worth of query rows
+    if (sizeof(T) == 2 && p->head_dim == 128 && p->seq_len >= 16 && aligned16(q) && aligned16(K) && aligned16(V) && aligned16(o))
+        return attn_prefill_ref_layout(p->dtype, q, K, V, o, past, p->batch, p->n_heads, p->n_kv_heads, p->seq_len, kv_tokens, st);
     const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
     const float scale = 1.0f / sqrtf(static_cast<float>(p->head_dim));
 #define RG_ATT(EP) attn_rows_kernel<T, EP><<<grid, 128, 0, st>>>(q, K, V, o, past, p->batch, p->n_heads, p->n_kv_heads, p->seq_len, kv_tokens, scale)

@@ -28,7 +28,8 @@ constexpr int MG_KCH = 6;          // k <= 6 * 256 * 8 = 12288
 constexpr int MG_MAX_LAYERS = 96;
 constexpr int MG_TILE = 64;        // tokens per attention unit
 constexpr int MG_PART_UNITS = 96;  // max units of one phase per CTA
-constexpr int MG_MAX_REC = 8;      // attention partial records per CTA
+constexpr int MG_MAX_REC = 8;
+constexpr int MG_L2_AHEAD = 14;    // units (32 KiB each) the L2 prefetch cursor runs ahead of the ring: 148 x 448 KiB = 66 MB of L2      // attention partial records per CTA
 
 static __device__ int s_mega_error;
 
@@ -253,46 +254,93 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
 
     if (warp == MG_NW) {
         // ================= producer: the whole step's stream for this CTA =================
+        // Two cursors walk the same schedule: `ld` issues the bulk copies into the ring as stages free up; `pf` runs
+        // MG_L2_AHEAD units ahead and only asks L2 to fetch (cp.async.bulk.prefetch.L2), so HBM keeps streaming while
+        // the ring is full (consumers at a grid barrier) and the later ring fills are L2 hits.
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_first();
-            uint32_t it = 0;
-            bool ok = true;
-            for (uint32_t p = 0; p < nphases && ok; ++p) {
-                const Phase ph = phase_of(a, p, NT);
-                uint32_t u0, u1, att_head = 0;
-                if (ph.type == PH_ATT) {
-                    if (!att_range(a, NT, blockIdx.x, gridDim.x, att_head, u0, u1)) u0 = u1 = 0;
-                } else {
-                    unit_range(ph.units, u0, u1);
-                }
-                for (uint32_t u = u0; u < u1; ++u, ++it) {
-                    const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
-                    if (!mbar_wait(&empty[s], par ^ 1u)) {
-                        atomicExch(&hdr->abort, 1);
-                        ok = false;
-                        break;
-                    }
-                    uint8_t *st = smem + s * MG_STAGE_BYTES;
-                    if (ph.type == PH_ATT) {
-                        const uint32_t h = att_head, t = u, kvh = h / (a.nH / a.nKV);
-                        const uint32_t tok0 = t * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
-                        const uint32_t bytes = ntok * a.D * 2u;
-                        const size_t off = (static_cast<size_t>(kvh) * a.max_seq + tok0) * a.D * 2u;
-                        mbar_arrive_expect_tx(&full[s], 2u * bytes);
-                        bulk_g2s(st, static_cast<const uint8_t *>(a.layer[ph.layer].kc) + off, bytes, &full[s]);
-                        bulk_g2s(st + MG_STAGE_BYTES / 2, static_cast<const uint8_t *>(a.layer[ph.layer].vc) + off, bytes, &full[s]);
+            struct Cursor {
+                uint32_t p, u, u1, head;
+                Phase ph;
+                bool done;
+            };
+            auto load_phase = [&](Cursor &c) {
+                for (; c.p < nphases; ++c.p) {
+                    c.ph = phase_of(a, c.p, NT);
+                    uint32_t u0;
+                    c.head = 0;
+                    if (c.ph.type == PH_ATT) {
+                        if (!att_range(a, NT, blockIdx.x, gridDim.x, c.head, u0, c.u1)) u0 = c.u1 = 0;
                     } else {
-                        const uint32_t row_bytes = ph.k * 2u;
-                        uint32_t rows;
-                        mega_unit_row(a, ph, u, 0, rows);
-                        const uint32_t seg_bytes = rows * row_bytes;
-                        mbar_arrive_expect_tx(&full[s], seg_bytes * ph.segs);
-                        for (uint32_t sg = 0; sg < ph.segs; ++sg) {
-                            uint32_t rr;
-                            const uint32_t row = mega_unit_row(a, ph, u, sg, rr);
-                            bulk_g2s_hint(st + sg * ph.g * row_bytes, ph.W + static_cast<uint64_t>(row) * row_bytes, seg_bytes, &full[s], policy);
-                        }
+                        unit_range(c.ph.units, u0, c.u1);
                     }
+                    c.u = u0;
+                    if (c.u < c.u1) return;
+                }
+                c.done = true;
+            };
+            auto advance = [&](Cursor &c) {
+                if (++c.u >= c.u1) {
+                    ++c.p;
+                    load_phase(c);
+                }
+            };
+            // the (up to two) contiguous pieces of a unit: returns the piece count, fills src / bytes / ring offset
+            auto pieces = [&](const Cursor &c, const uint8_t *(&src)[2], uint32_t (&bytes)[2], uint32_t (&dst)[2]) -> uint32_t {
+                if (c.ph.type == PH_ATT) {
+                    const uint32_t kvh = c.head / (a.nH / a.nKV);
+                    const uint32_t tok0 = c.u * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
+                    const size_t off = (static_cast<size_t>(kvh) * a.max_seq + tok0) * a.D * 2u;
+                    src[0] = static_cast<const uint8_t *>(a.layer[c.ph.layer].kc) + off;
+                    src[1] = static_cast<const uint8_t *>(a.layer[c.ph.layer].vc) + off;
+                    bytes[0] = bytes[1] = ntok * a.D * 2u;
+                    dst[0] = 0, dst[1] = MG_STAGE_BYTES / 2;
+                    return 2;
+                }
+                const uint32_t row_bytes = c.ph.k * 2u;
+                for (uint32_t sg = 0; sg < c.ph.segs; ++sg) {
+                    uint32_t rows;
+                    const uint32_t row = mega_unit_row(a, c.ph, c.u, sg, rows);
+                    src[sg] = c.ph.W + static_cast<uint64_t>(row) * row_bytes;
+                    bytes[sg] = rows * row_bytes;
+                    dst[sg] = sg * c.ph.g * row_bytes;
+                }
+                return c.ph.segs;
+            };
+            auto prefetch = [&](const Cursor &c) {
+                const uint8_t *src[2];
+                uint32_t bytes[2], dst[2];
+                const uint32_t n = pieces(c, src, bytes, dst);
+                for (uint32_t i = 0; i < n; ++i)
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src[i]), "r"(bytes[i]) : "memory");
+            };
+            Cursor ld{0, 0, 0, 0, {}, false}, pf{0, 0, 0, 0, {}, false};
+            load_phase(ld);
+            load_phase(pf);
+            for (int i = 0; i < MG_L2_AHEAD && !pf.done; ++i) {
+                if (i >= MG_STAGES) prefetch(pf);// the first MG_STAGES units go straight into the ring
+                advance(pf);
+            }
+            for (uint32_t it = 0; !ld.done; ++it) {
+                const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
+                if (!mbar_wait(&empty[s], par ^ 1u)) {
+                    atomicExch(&hdr->abort, 1);
+                    break;
+                }
+                uint8_t *st = smem + s * MG_STAGE_BYTES;
+                const uint8_t *src[2];
+                uint32_t bytes[2], dst[2];
+                const uint32_t n = pieces(ld, src, bytes, dst);
+                mbar_arrive_expect_tx(&full[s], n == 2 ? bytes[0] + bytes[1] : bytes[0]);
+                for (uint32_t i = 0; i < n; ++i) {
+                    if (ld.ph.type == PH_ATT) bulk_g2s(st + dst[i], src[i], bytes[i], &full[s]);
+                    else
+                        bulk_g2s_hint(st + dst[i], src[i], bytes[i], &full[s], policy);
+                }
+                advance(ld);
+                if (!pf.done) {
+                    prefetch(pf);
+                    advance(pf);
                 }
             }
         }
