@@ -29,7 +29,8 @@ constexpr int MG_MAX_LAYERS = 96;
 constexpr int MG_TILE = 64;        // tokens per attention unit
 constexpr int MG_PART_UNITS = 96;  // max units of one phase per CTA
 constexpr int MG_MAX_REC = 8;
-constexpr int MG_L2_AHEAD = 14;    // units (32 KiB each) the L2 prefetch cursor runs ahead of the ring: 148 x 448 KiB = 66 MB of L2      // attention partial records per CTA
+constexpr int MG_L2_AHEAD = 0;     // units the optional L2 prefetch cursor runs ahead of the ring; 0 = off (measured: 8 and 14
+                                   // units ahead slowed the step from 3.04 ms to 4.4 ms, so it stays off)
 
 static __device__ int s_mega_error;
 
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                         bulk_g2s_hint(st + dst[i], src[i], bytes[i], &full[s], policy);
                 }
                 advance(ld);
-                if (!pf.done) {
+                if (MG_L2_AHEAD > 0 && !pf.done) {
                     prefetch(pf);
                     advance(pf);
                 }
