@@ -47,7 +47,7 @@ def parse_args():
                     help="7b / tiny workloads: 'single' = the whole step as one persistent kernel (b200::DecodeStep); "
                          "'fused' = five fused launches per layer replayed as a CUDA graph")
     ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
-                             "gemm_skinny16", "gemm_skinny32"],
+                             "gemm_skinny16", "gemm_skinny32", "decode_step_timeline"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
     ap.add_argument("--launches", type=int, default=6)
     return ap.parse_args()
@@ -330,10 +330,58 @@ def time_linear_kernel(ex, index, cfg, torch, stream, reps=3):
             "avg_launch_us": 1000.0 * ms / len(calls), "gbs": bytes_total / (ms * 1e-3) / 1e9}
 
 
+def run_decode_step_timeline():
+    """Per-phase timeline of the single-kernel decode step at the 7B shape (KV 2048), read back from the kernel's own
+    %globaltimer stamps (rg_b200_decode_step_timeline)."""
+    import ctypes as C
+    import torch
+    from refactorgraph_b200 import capi
+    lib = capi.load()
+    torch.cuda.set_device(0)
+    torch.manual_seed(0)
+    dt, dev = torch.float16, "cuda"
+    L, H, nH, D, F, V, MS, pos0 = 32, 4096, 32, 128, 11008, 32000, 2560, 2048
+    p = capi.DecodeStepParams(capi.FP16, L, H, nH, nH, D, F, V, MS, 1e-6, 10000.0)
+    ws = torch.zeros(capi.workspace("decode_step", p), dtype=torch.uint8, device=dev)
+    rnd = lambda *s: (torch.randn(*s, device=dev) * 0.02).to(dt)
+    ones = lambda n: torch.ones(n, dtype=dt, device=dev)
+    tok, pos = torch.tensor([5], device=dev), torch.tensor([pos0], device=dev)
+    ins = [tok, pos, rnd(V, H), ones(H), rnd(V, H)]
+    for _ in range(L):
+        ins += [ones(H), rnd(3 * H, H), rnd(H, H), ones(H), rnd(2 * F, H), rnd(H, F),
+                torch.randn(1, nH, MS, D, device=dev).to(dt), torch.randn(1, nH, MS, D, device=dev).to(dt)]
+    outs = [torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, device=dev), torch.zeros(1, V, dtype=dt, device=dev)]
+    torch.cuda.synchronize()
+    for _ in range(4):
+        capi.call("decode_step", p, [t.data_ptr() for t in ins], [t.data_ptr() for t in outs], ws=ws.data_ptr())
+    torch.cuda.synchronize()
+    n_entries = (5 * L + 2) * 4
+    buf = (C.c_uint64 * n_entries)()
+    n = lib.rg_b200_decode_step_timeline(C.byref(p), ws.data_ptr(), buf, n_entries)
+    tt = np.array(buf[:n], dtype=np.float64).reshape(-1, 4)
+    sub = np.zeros((5 * L + 1, 4))
+    for ph in range(5 * L + 1):
+        e, xr, ud, ep = tt[ph]
+        nxt = tt[ph + 1, 0]
+        sub[ph] = [0, (ep - e) / 1e3, 0, (nxt - ep) / 1e3] if (ph % 5 == 1 and ph < 5 * L) else [(xr - e) / 1e3, (ud - xr) / 1e3, (ep - ud) / 1e3, (nxt - ep) / 1e3]
+    names = ["qkv", "attention", "o", "gate_up", "down"]
+    nbytes = [3 * H * H * 2, 2 * nH * pos0 * D * 2, H * H * 2, 2 * F * H * 2, F * H * 2]
+    out = {"case": "decode_step_timeline", "total_us": (tt[5 * L + 1, 0] - tt[0, 0]) / 1e3, "error_state": lib.rg_b200_error_state(),
+           "columns": ["x_ready_us", "units_us", "epilogue_us", "barrier_us", "phase_us", "GB/s"], "phases": {}}
+    for k, nm in enumerate(names):
+        m = sub[k:5 * L:5].mean(0)
+        out["phases"][nm] = [round(float(v), 2) for v in m] + [round(float(m.sum()), 2), round(nbytes[k] / m.sum() / 1e3)]
+    m = sub[5 * L]
+    out["phases"]["lm_head"] = [round(float(v), 2) for v in m] + [round(float(m.sum()), 2), round(V * H * 2 / m.sum() / 1e3)]
+    print(json.dumps(out), flush=True)
+
+
 def run_case(args):
     """One kernel alone at its Llama-7B decode shape, inputs rotated over buffers larger than L2 in total."""
     import torch
     from refactorgraph_b200 import capi
+    if args.case == "decode_step_timeline":
+        return run_decode_step_timeline()
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     torch.cuda.set_device(0)
     capi.load()
