@@ -31,6 +31,7 @@ if ROOT not in sys.path:
 import numpy as np
 
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TFLOPS = 1400.0
 
 
 def parse_args():
@@ -39,7 +40,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="7b", choices=["7b", "tiny", "7b-b32", "70b-tp"],
+    ap.add_argument("--workload", default="7b", choices=["7b", "tiny", "7b-4l", "7b-b32", "70b-tp", "7b-prefill"],
                     help="7b: batch-1 greedy decode (the reported configuration; N > 1 = independent replicas). "
                          "7b-b32: batch 32, paged KV, top-k 50 sampling.  70b-tp: 70B-shaped GQA decode, tensor-parallel over N GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -57,6 +58,8 @@ def workload_config(name, world=1):
     from refactorgraph_b200.llama import LlamaConfig
     if name == "tiny":  # for quick functional runs only; never the reported configuration
         return LlamaConfig(layers=2, hidden=512, heads=4, kv_heads=4, head_dim=128, ffn=1024, vocab=2000, max_seq=512), 256
+    if name == "7b-4l":  # four 7B-shaped layers (2.3 GB on the device): the size ncu captures of the decode step use
+        return LlamaConfig(layers=4, max_seq=2048 + 512), 2048
     if name == "7b-b32":
         return LlamaConfig(max_seq=4096 + 128, batch=32), 0
     if name == "70b-tp":
@@ -180,6 +183,8 @@ def run_reference(args):
 def workload_name(w):
     if w == "tiny":
         return "tiny functional decoder (not a reported configuration)"
+    if w == "7b-4l":
+        return "four Llama-7B-shaped layers + LM head, fp16 batch-1 greedy decode at KV 2048 (profiling size, not a reported configuration)"
     if w == "7b-b32":
         return "Llama-7B-shaped fp16 batch-32 decode, paged KV (16-token blocks), lengths uniform[512,4096], top-k 50 sampling"
     if w == "70b-tp":
@@ -501,6 +506,109 @@ def time_skinny_gemm(ex, index, cfg, torch, stream, reps=3):
             "avg_launch_us": 1000.0 * ms / len(calls), "gbs": bytes_total / (ms * 1e-3) / 1e9}
 
 
+def run_prefill(args, torch, dist, lib, rank, world, local):
+    """BASELINE configuration 4: 7B-shaped bf16 prefill, batch 4 x 2048 tokens, causal; one step = one prefill of all
+    8192 tokens (replicated per GPU when N > 1).  Tensor-bound: flops / time against the measured bf16 matmul peak."""
+    from refactorgraph_b200.graph_builder import BF16
+    from refactorgraph_b200.llama import LlamaConfig, prefill_graph, weight_inputs
+    B, S = 4, 2048
+    cfg = LlamaConfig(max_seq=S, batch=B, dtype=BF16)
+    g, index = prefill_graph(cfg, S)
+    ex = g.compiler().compile("cuda", "flat", [])
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(rank)
+    dt = torch.bfloat16
+    for name, shape in weight_inputs(cfg):
+        w = torch.empty(shape, dtype=torch.float32, device="cuda").normal_(0.0, 0.02, generator=gen)
+        if "norm" in name:
+            w += 1.0
+        w = w.to(dt)
+        ex.set_input_blob(index[name], w.data_ptr(), w.numel() * 2)
+        del w
+    torch.cuda.empty_cache()
+    rng = np.random.default_rng(rank)
+    ids = rng.integers(0, cfg.vocab, (B * S,)).astype(np.int64)
+    ex.set_input(index["positions"], np.tile(np.arange(S, dtype=np.int64), B))
+    ex.set_input(index["last"], (np.arange(B, dtype=np.int64) + 1) * S - 1)
+    ex.set_input(index["ids"], ids)
+    stream = torch.cuda.ExternalStream(ex.cuda_stream())
+    K, W = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    l0 = lib.rg_b200_launch_count()
+    ex.run()
+    ex.sync()
+    launches_per_step = int(lib.rg_b200_launch_count() - l0)
+    for _ in range(W):
+        ex.run()
+    ex.sync()
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(K):
+        ex.run()
+    e1.record(stream)
+    stream.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    logits_finite = bool(np.isfinite(ex.get_output(index["logits"]).astype(np.float32)).all())
+    # end to end: token ids from pinned host memory every step, next tokens read back
+    pin_in = torch.from_numpy(ids.copy()).pin_memory()
+    pin_out = torch.zeros(B, dtype=torch.int64).pin_memory()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        ex.set_input_async(index["ids"], pin_in.data_ptr(), ids.nbytes)
+        ex.run()
+        ex.get_output_into(index["next"], pin_out.data_ptr(), B * 8)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1000.0
+    clocks = sampler.stop()
+    barrier()
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        H, F, V, L, D = cfg.hidden, cfg.ffn, cfg.vocab, cfg.layers, cfg.head_dim
+        n = B * S
+        gemm_flops = 2.0 * n * L * (3 * H * H + H * H + 3 * H * F) + 2.0 * B * H * V     # LM head on the last token of each sequence
+        attn_flops = L * B * cfg.heads * 4.0 * D * (S * (S + 1) / 2.0)
+        flops = gemm_flops + attn_flops
+        peak = FALLBACK_TFLOPS
+        peak_kind = "fallback"
+        try:
+            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+            peak_kind = "measured sustained"
+        except Exception:
+            pass
+        tf = flops / (ms / K * 1e-3) / 1e12
+        tokens = K * n * world
+        line = {"metric": "prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
+                "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": "Llama-7B-shaped bf16 prefill, batch 4 x 2048 tokens, causal, LM head on the last token of each sequence",
+                           "logits_finite": logits_finite, "l2": "inputs larger than L2 (13.2 GB of weights, 64 MiB activations per tensor)",
+                           "parallelism": "one independent replica per GPU" if world > 1 else "single GPU"},
+                "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": B * 8},
+                "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "clocks": clocks,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                             "kernel": "whole prefill step (gemm_tc_kernel dominates)", "peak_source": peak_kind + " bf16 matmul",
+                             "flops_per_step": flops, "gemm_flops": gemm_flops, "attention_flops": attn_flops}}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+    del ex
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -517,6 +625,8 @@ def run_b200(args):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = capi.load()
+    if args.workload == "7b-prefill":
+        return run_prefill(args, torch, dist, lib, rank, world, local)
     tp = args.workload == "70b-tp"
     full_cfg, kv_len = workload_config(args.workload, world)
     comm = None
@@ -527,7 +637,7 @@ def run_b200(args):
             return out
         comm = capi.Comm(world, rank, full_cfg.batch * full_cfg.hidden * 2, exchange=exchange)
     ex, index, state = build_executor(full_cfg, kv_len, torch, args.workload, world, rank, args.graph)
-    single = args.workload in ("7b", "tiny") and args.graph == "single"
+    single = args.workload in ("7b", "tiny", "7b-4l") and args.graph == "single"
     cfg = state["cfg"]                      # per-rank shape
     if comm is not None:
         ex.set_communicator(comm.address)
@@ -605,7 +715,7 @@ def run_b200(args):
         e2e_ms = e2e_s * 1000.0
     lin = None
     if rank == 0:
-        lin = time_linear_kernel(ex, index, cfg, torch, stream) if args.workload in ("7b", "tiny") else time_skinny_gemm(ex, index, cfg, torch, stream)
+        lin = time_linear_kernel(ex, index, cfg, torch, stream) if args.workload in ("7b", "tiny", "7b-4l") else time_skinny_gemm(ex, index, cfg, torch, stream)
     comm_ok = comm.status() == capi.OK if comm is not None else True
     err_state = lib.rg_b200_error_state()
 
@@ -616,7 +726,7 @@ def run_b200(args):
         value = tokens / (ms * 1e-3)
         kv_sum = float(state["lens0"].sum()) + cfg.batch * (1 + (K - 1) / 2.0)        # mean total cached tokens per step
         step_bytes = cfg.weight_bytes_per_step + cfg.kv_bytes_per_token * kv_sum           # per GPU
-        kernel = "linear_stream_kernel" if args.workload in ("7b", "tiny") else "gemm_tc_kernel (activations on the N side)"
+        kernel = "linear_stream_kernel" if args.workload in ("7b", "tiny", "7b-4l") else "gemm_tc_kernel (activations on the N side)"
         roof = {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
                 "traffic": None, "kernel": kernel, "peak_source": peak_kind + " HBM copy bandwidth",
                 "avg_launch_us": lin["avg_launch_us"], "launches_timed": lin["launches"],
@@ -646,10 +756,10 @@ def run_b200(args):
                               "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak,
                               "frac_of_nominal_8tbs": step_bytes / (ms / K * 1e-3) / 1e9 / 8000.0},
         }
-        line["config"]["graph"] = args.graph if args.workload in ("7b", "tiny") else "batched"
+        line["config"]["graph"] = args.graph if args.workload in ("7b", "tiny", "7b-4l") else "batched"
         if args.workload == "7b" and not single:
             line["roofline"]["traffic"] = 180404736 * (lin["bytes_per_pass"] / lin["launches"]) / 180355072  # ncu: dram bytes = 1.0003 x algorithmic (profiles/linear_gate_up.md)
-        if not args.no_cpu_baseline and args.workload in ("7b", "tiny"):
+        if not args.no_cpu_baseline and args.workload in ("7b", "tiny", "7b-4l"):
             line["cpu_baseline"] = cpu_baseline(cfg, kv_len)
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -234,13 +234,15 @@ typedef struct rg_kv_layout {
 
 /* QKV split + RoPE + cache append for batched decode (no reference counterpart; what the m <= 4 linear kernel does in
  * its epilogue, as a separate launch behind a tensor-core GEMM).  qkv[tokens, (n_heads + 2 n_kv_heads) * D]: q heads
- * are rotated to q[tokens, n_heads * D]; k heads are rotated and v heads copied into the caches at positions[token].
+ * are rotated to q[tokens, n_heads * D]; k heads are rotated and v heads copied into the caches of the token's sequence
+ * (token / tokens_per_seq) at positions[token].
  * inputs {qkv, positions (int64[tokens]), block_table (int32) or NULL}, outputs {q, k_cache, v_cache}. */
 typedef struct rg_qkv_rope_append_params {
     int32_t dtype;
     uint32_t tokens, n_heads;
     float theta;
     rg_kv_layout kv;
+    uint32_t tokens_per_seq; /* 0 or 1: every token is its own sequence (decode); S: tokens [b*S, (b+1)*S) belong to sequence b (prefill) */
 } rg_qkv_rope_append_params;
 size_t rg_b200_qkv_rope_append_workspace(const rg_qkv_rope_append_params *);
 int rg_b200_qkv_rope_append(const rg_qkv_rope_append_params *, void *ws, const void *const *in, void *const *out, void *stream);

@@ -88,7 +88,8 @@ class LinearParams(C.Structure):
 
 
 class QkvRopeAppendParams(C.Structure):
-    _fields_ = [("dtype", C.c_int32), ("tokens", C.c_uint32), ("n_heads", C.c_uint32), ("theta", C.c_float), ("kv", KvLayout)]
+    _fields_ = [("dtype", C.c_int32), ("tokens", C.c_uint32), ("n_heads", C.c_uint32), ("theta", C.c_float), ("kv", KvLayout),
+                ("tokens_per_seq", C.c_uint32)]
 
 
 class SwigluParams(C.Structure):

@@ -198,7 +198,8 @@ __global__ void rope_kernel(const T *__restrict__ x, const int64_t *__restrict__
 template<class T>
 __global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t *__restrict__ pos,
                                        const int32_t *__restrict__ table, T *__restrict__ q, T *__restrict__ kc,
-                                       T *__restrict__ vc, uint32_t tokens, uint32_t nq, rg_kv_layout kv, float log2_theta) {
+                                       T *__restrict__ vc, uint32_t tokens, uint32_t nq, rg_kv_layout kv, float log2_theta,
+                                       uint32_t tokens_per_seq) {
     const uint32_t D = kv.head_dim, half = D / 2, nkv = kv.n_kv_heads, heads = nq + 2 * nkv;
     const uint64_t total = static_cast<uint64_t>(tokens) * heads * half;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
@@ -225,12 +226,13 @@ __global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t 
             const uint32_t kvh = is_k ? h - nq : h - nq - nkv;
             T *cache = is_k ? kc : vc;
             uint64_t base;
+            const uint32_t seq = tokens_per_seq > 1 ? m / tokens_per_seq : m;
             if (table) {
                 const uint32_t page = kv.page_size;
-                const int32_t blk = table[static_cast<uint64_t>(m) * kv.max_blocks_per_seq + static_cast<uint32_t>(p) / page];
+                const int32_t blk = table[static_cast<uint64_t>(seq) * kv.max_blocks_per_seq + static_cast<uint32_t>(p) / page];
                 base = ((static_cast<uint64_t>(blk) * nkv + kvh) * page + static_cast<uint32_t>(p) % page) * D;
             } else {
-                base = ((static_cast<uint64_t>(m) * nkv + kvh) * kv.max_seq + static_cast<uint64_t>(p)) * D;
+                base = ((static_cast<uint64_t>(seq) * nkv + kvh) * kv.max_seq + static_cast<uint64_t>(p)) * D;
             }
             cache[base + i] = Num<T>::from_f(lo);
             cache[base + i + half] = Num<T>::from_f(hi);
@@ -417,7 +419,7 @@ int rg_b200_qkv_rope_append(const rg_qkv_rope_append_params *p, void *, const vo
     const float l2t = log2f(p->theta);
     auto pos = static_cast<const int64_t *>(in[1]);
     auto tab = static_cast<const int32_t *>(in[2]);
-#define RG_QRA(T) qkv_rope_append_kernel<T><<<g, 256, 0, st>>>(static_cast<const T *>(in[0]), pos, tab, static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t)
+#define RG_QRA(T) qkv_rope_append_kernel<T><<<g, 256, 0, st>>>(static_cast<const T *>(in[0]), pos, tab, static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t, p->tokens_per_seq)
     switch (p->dtype) {
         case RG_F32: RG_QRA(float); break;
         case RG_FP16: RG_QRA(__half); break;

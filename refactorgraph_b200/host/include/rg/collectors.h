@@ -97,10 +97,19 @@ namespace refactor::kernel {
     // qkv[tokens, (nH + 2 nKV) * D] -> q[tokens, nH * D]; k (rotated) and v appended to the cache state edges.
     // inputs {qkv, positions, [block_table], k_cache, v_cache}, outputs {q}
     struct QkvRopeAppendCollector final : public InfoCollector {
-        dim_t nHeads, nKVHeads, headDim, pageSize;
+        dim_t nHeads, nKVHeads, headDim, pageSize, tokensPerSeq;
         float theta;
-        QkvRopeAppendCollector(Target target, dim_t nHeads_, dim_t nKVHeads_, dim_t headDim_, dim_t pageSize_, float theta_) noexcept
-            : InfoCollector(target), nHeads(nHeads_), nKVHeads(nKVHeads_), headDim(headDim_), pageSize(pageSize_), theta(theta_) {}
+        QkvRopeAppendCollector(Target target, dim_t nHeads_, dim_t nKVHeads_, dim_t headDim_, dim_t pageSize_, float theta_,
+                               dim_t tokensPerSeq_ = 0) noexcept
+            : InfoCollector(target), nHeads(nHeads_), nKVHeads(nKVHeads_), headDim(headDim_), pageSize(pageSize_),
+              tokensPerSeq(tokensPerSeq_), theta(theta_) {}
+        std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
+    };
+    // Causal flash attention over token-major activations: {q[B*S, nH*D], k_cache, v_cache [B, nKV, max_seq, D], [past]}
+    // -> {o[B*S, nH*D]}; sequence b owns tokens [b*S, (b+1)*S)
+    struct AttentionPrefillCollector final : public InfoCollector {
+        dim_t nHeads, seqLen;
+        AttentionPrefillCollector(Target target, dim_t nHeads_, dim_t seqLen_) noexcept : InfoCollector(target), nHeads(nHeads_), seqLen(seqLen_) {}
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
     // x[rows, 2f] -> silu(x[:, :f]) * x[:, f:]

@@ -258,18 +258,27 @@ namespace refactor::computation {
         std::vector<Arc<Tensor>> infer(TensorRefs in) const final { return one(in[0].get().dataType, in[0].get().shape); }
     };
     struct QkvRopeAppend final : Operator {
-        dim_t nHeads, nKVHeads, headDim, pageSize;
+        dim_t nHeads, nKVHeads, headDim, pageSize, tokensPerSeq;
         float theta;
         explicit QkvRopeAppend(Attributes const &a)
             : nHeads(static_cast<dim_t>(getInt(a, "n_heads", 0))), nKVHeads(static_cast<dim_t>(getInt(a, "n_kv_heads", 0))),
               headDim(static_cast<dim_t>(getInt(a, "head_dim", 0))), pageSize(static_cast<dim_t>(getInt(a, "page_size", 0))),
-              theta(static_cast<float>(getFloat(a, "theta", 10000.0))) {}
+              tokensPerSeq(static_cast<dim_t>(getInt(a, "tokens_per_seq", 0))), theta(static_cast<float>(getFloat(a, "theta", 10000.0))) {}
         RG_OP_NAME("QkvRopeAppend")
-        CollectorBox candidateKernels(Target t) const final { return std::make_unique<QkvRopeAppendCollector>(t, nHeads, nKVHeads, headDim, pageSize, theta); }
+        CollectorBox candidateKernels(Target t) const final {
+            return std::make_unique<QkvRopeAppendCollector>(t, nHeads, nKVHeads, headDim, pageSize, theta, tokensPerSeq);
+        }
         std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
             ASSERT(in[0].get().shape.size() == 2, "QkvRopeAppend: qkv must be [tokens, (nH + 2 nKV) * D]");
             return one(in[0].get().dataType, Shape{in[0].get().shape[0], nHeads * headDim});
         }
+    };
+    struct AttentionPrefill final : Operator {
+        dim_t nHeads, seqLen;
+        AttentionPrefill(dim_t h, dim_t s) : nHeads(h), seqLen(s) {}
+        RG_OP_NAME("AttentionPrefill")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<AttentionPrefillCollector>(t, nHeads, seqLen); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final { return one(in[0].get().dataType, in[0].get().shape); }
     };
     struct Swiglu final : Operator {
         RG_OP_NAME("SwiGLU")
@@ -350,6 +359,8 @@ namespace refactor::computation {
             return std::make_unique<AttentionDecode>(static_cast<dim_t>(getInt(a, "max_len", 0)), static_cast<dim_t>(getInt(a, "page_size", 0)));
         if (is({"b200::QkvRopeAppend"})) return std::make_unique<QkvRopeAppend>(a);
         if (is({"b200::SwiGLU"})) return std::make_unique<Swiglu>();
+        if (is({"b200::AttentionPrefill"}))
+            return std::make_unique<AttentionPrefill>(static_cast<dim_t>(getInt(a, "n_heads", 0)), static_cast<dim_t>(getInt(a, "seq_len", 0)));
         if (is({"b200::DecodeStep"})) return std::make_unique<DecodeStep>(a);
         if (is({"b200::StateUpdate"})) return std::make_unique<StateUpdate>(getInt(a, "delta", 0));
         TODO("Unsupported operator " + type);

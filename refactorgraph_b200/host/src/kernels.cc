@@ -516,6 +516,7 @@ namespace refactor::kernel {
         rg_qkv_rope_append_params p{};
         p.dtype = x.dataType;
         p.tokens = x.shape[0], p.n_heads = nHeads, p.theta = theta;
+        p.tokens_per_seq = tokensPerSeq;
         p.kv.n_kv_heads = nKVHeads, p.kv.head_dim = headDim;
         if (paged) {
             p.kv.page_size = pageSize ? pageSize : kc.shape[2];
@@ -524,6 +525,40 @@ namespace refactor::kernel {
             p.kv.max_seq = kc.shape[2];
         }
         ans.emplace_back(std::make_unique<QkvRopeAppendB200>(p, paged));
+        return ans;
+    }
+
+    struct AttentionPrefillB200 final : public Kernel {
+        rg_attn_prefill_params info;
+        bool hasPast;
+        AttentionPrefillB200(rg_attn_prefill_params p, bool hasPast_) noexcept : info(p), hasPast(hasPast_) {}
+        RG_KERNEL_IDS(AttentionPrefillB200, "Causal flash attention (prefill) on B200")
+        RoutineWorkspace lower(Resources &res) const final {
+            auto st = res.fetchOrStore<CudaStream>();
+            return RoutineWorkspace([info = info, hasPast = hasPast, st](Resources &, void *ws, void const *const *in, void *const *out) {
+                void const *in_[4] = {in[0], in[1], in[2], hasPast ? in[3] : nullptr};
+                check(rg_b200_attn_prefill(&info, ws, in_, out, st->stream), "rg_b200_attn_prefill");
+            });
+        }
+    };
+    std::vector<KernelBox> AttentionPrefillCollector::filter(TensorRefs inputs, TensorRefs) const {
+        std::vector<KernelBox> ans;
+        auto const &q = inputs[0].get();
+        auto const &kc = inputs[1].get();
+        if (_target != Target::Nvidia || !half(q.dataType) || q.shape.size() != 2 || kc.shape.size() != 4 || seqLen == 0) return ans;
+        if (inputs.size() != 3 && inputs.size() != 4) return ans;
+        const dim_t D = kc.shape[3], nKV = kc.shape[1], maxSeq = kc.shape[2], B = q.shape[0] / seqLen;
+        if (D != 128 || q.shape[1] != nHeads * D || B * seqLen != q.shape[0] || kc.shape[0] != B) return ans;
+        rg_attn_prefill_params p{};
+        p.dtype = q.dataType;
+        p.batch = B, p.n_heads = nHeads, p.n_kv_heads = nKV, p.seq_len = seqLen, p.head_dim = D, p.kv_capacity = maxSeq;
+        const int64_t qrow = static_cast<int64_t>(nHeads) * D;
+        const int64_t s[12] = {static_cast<int64_t>(seqLen) * qrow, D, qrow,
+                               static_cast<int64_t>(nKV) * maxSeq * D, static_cast<int64_t>(maxSeq) * D, D,
+                               static_cast<int64_t>(nKV) * maxSeq * D, static_cast<int64_t>(maxSeq) * D, D,
+                               static_cast<int64_t>(seqLen) * qrow, D, qrow};
+        for (int i = 0; i < 12; ++i) p.strides[i] = s[i];
+        ans.emplace_back(std::make_unique<AttentionPrefillB200>(p, inputs.size() == 4));
         return ans;
     }
 

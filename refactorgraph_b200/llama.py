@@ -135,6 +135,45 @@ def decode_step_graph_single_kernel(cfg: LlamaConfig):
     return g, index
 
 
+def prefill_graph(cfg: LlamaConfig, seq: int, top_k: int = 1):
+    """Causal prefill of `cfg.batch` sequences of `seq` tokens (token-major activations [B*S, hidden]): per layer
+    RmsNormalization, MatMul (tcgen05), QkvRopeAppend (writes the K/V caches), AttentionPrefill, MatMul, Add,
+    RmsNormalization, MatMul, SwiGLU, MatMul, Add; then the LM head on the last token of every sequence + TopK.
+    Inputs: ids[B*S], positions[B*S], last[B] (row index of each sequence's last token), weights, caches."""
+    g = GraphBuilder()
+    B, H, D, n = cfg.batch, cfg.hidden, cfg.head_dim, cfg.batch * seq
+    ids = g.input("ids", I64, (n,))
+    pos = g.input("positions", I64, (n,))
+    last = g.input("last", I64, (B,))
+    for name, shape in weight_inputs(cfg):
+        g.input(name, cfg.dtype, shape)
+    for l in range(cfg.layers):
+        g.input(f"l{l}.k_cache", cfg.dtype, (B, cfg.kv_heads, cfg.max_seq, D))
+        g.input(f"l{l}.v_cache", cfg.dtype, (B, cfg.kv_heads, cfg.max_seq, D))
+    x = g.op("onnx::Gather", ["embed", ids], axis=0)
+    for l in range(cfg.layers):
+        kc, vc = f"l{l}.k_cache", f"l{l}.v_cache"
+        n1 = g.op("llm::RmsNormalization", [x, f"l{l}.norm1"], epsilon=cfg.eps)
+        qkv = g.op("llm::MatMul", [n1, f"l{l}.wqkv"], transB=1)
+        q = g.op("b200::QkvRopeAppend", [qkv, pos, kc, vc], n_heads=cfg.heads, n_kv_heads=cfg.kv_heads, head_dim=D, theta=cfg.theta,
+                 tokens_per_seq=seq)
+        a = g.op("b200::AttentionPrefill", [q, kc, vc], n_heads=cfg.heads, seq_len=seq)
+        o = g.op("llm::MatMul", [a, f"l{l}.wo"], transB=1)
+        h = g.op("onnx::Add", [o, x])
+        n2 = g.op("llm::RmsNormalization", [h, f"l{l}.norm2"], epsilon=cfg.eps)
+        gu = g.op("llm::MatMul", [n2, f"l{l}.wgu"], transB=1)
+        u = g.op("b200::SwiGLU", [gu])
+        d = g.op("llm::MatMul", [u, f"l{l}.wd"], transB=1)
+        x = g.op("onnx::Add", [d, h])
+    xl = g.op("onnx::Gather", [x, last], axis=0)
+    xf = g.op("llm::RmsNormalization", [xl, "norm_f"], epsilon=cfg.eps)
+    logits = g.op("llm::MatMul", [xf, "lm_head"], transB=1)
+    probs, idx = g.op("llm::TopK", [logits], n_out=2, k=top_k, softmax=1)
+    index = {"next": g.output(idx), "probs": g.output(probs), "logits": g.output(logits)}
+    index.update({name: i for i, name in enumerate(g.inputs)})
+    return g, index
+
+
 def shard_config(cfg: LlamaConfig, world: int) -> LlamaConfig:
     """Per-rank shape of a tensor-parallel model: heads, kv heads and FFN columns split `world` ways."""
     assert cfg.heads % world == 0 and cfg.kv_heads % world == 0 and cfg.ffn % world == 0

@@ -132,3 +132,55 @@ def test_all_reduce_missing_peer_reports_timeout_instead_of_hanging():
     z = x + 1                                                   # the context is still alive
     assert float(z.sum()) == 512.0
     comm.destroy()
+
+
+@pytest.mark.parametrize("np_dtype", [np.float16])
+def test_prefill_graph(np_dtype):
+    """Token-major causal prefill (tensor-core MatMul + QkvRopeAppend + AttentionPrefill + SwiGLU): last-token logits and
+    the K/V caches it writes, against the numpy oracle."""
+    from refactorgraph_b200.llama import prefill_graph
+    cfg = LlamaConfig(layers=2, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=2)
+    S, B, D, nH, nKV = 80, 2, 128, 4, 2
+    rng = np.random.default_rng(11)
+    w16 = seeded_weights(cfg, 0, np_dtype)
+    w = {k: v.astype(np.float32) for k, v in w16.items()}
+    r16 = lambda a: np.asarray(a, np.float32).astype(np_dtype).astype(np.float32)
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    pos = np.tile(np.arange(S, dtype=np.int64), B)
+    # oracle
+    x = w["embed"][ids.ravel()]
+    k_want, v_want = [], []
+    for l in range(cfg.layers):
+        q, k, v = onp.linear_fused(x, w[f"l{l}.wqkv"], g=w[f"l{l}.norm1"], eps=cfg.eps, epilogue=3, n_heads=nH, n_kv=nKV, head_dim=D, positions=pos)
+        # the GPU path rounds the normalised activations and the projection before the rotation
+        n1 = r16(onp.rms_norm(x, w[f"l{l}.norm1"], cfg.eps))
+        qkv = r16(n1.astype(np.float64) @ w[f"l{l}.wqkv"].astype(np.float64).T)
+        q = r16(onp.rope(qkv[:, : nH * D].reshape(-1, nH, D), pos))
+        k = r16(onp.rope(qkv[:, nH * D: (nH + nKV) * D].reshape(-1, nKV, D), pos))
+        v = qkv[:, (nH + nKV) * D:].reshape(-1, nKV, D)
+        k_want.append(k), v_want.append(v)
+        to4 = lambda t, h: t.reshape(B, S, h, D).transpose(0, 2, 1, 3)
+        a, _, _ = onp.attention(to4(q, nH), to4(k, nKV), to4(v, nKV))
+        a = r16(a.transpose(0, 2, 1, 3).reshape(B * S, nH * D))
+        h = r16(r16(a.astype(np.float64) @ w[f"l{l}.wo"].astype(np.float64).T) + x)
+        n2 = r16(onp.rms_norm(h, w[f"l{l}.norm2"], cfg.eps))
+        gu = r16(n2.astype(np.float64) @ w[f"l{l}.wgu"].astype(np.float64).T)
+        u = r16(onp.silu(gu[:, : cfg.ffn]) * gu[:, cfg.ffn:])
+        x = r16(r16(u.astype(np.float64) @ w[f"l{l}.wd"].astype(np.float64).T) + h)
+    last = np.array([S - 1, 2 * S - 1], np.int64)
+    xf = r16(onp.rms_norm(x[last], w["norm_f"], cfg.eps))
+    want_logits = xf.astype(np.float64) @ w["lm_head"].astype(np.float64).T
+    # GPU
+    g, index = prefill_graph(cfg, S)
+    ex = g.compiler().compile("cuda", "flat", [])
+    for name, _ in weight_inputs(cfg):
+        ex.set_input(index[name], w16[name])
+    ex.set_input(index["ids"], ids.ravel())
+    ex.set_input(index["positions"], pos)
+    ex.set_input(index["last"], last)
+    ex.run()
+    logits = ex.get_output(index["logits"]).astype(np.float32)
+    np.testing.assert_allclose(logits, want_logits, atol=2e-2, rtol=1e-2)
+    ex.run()  # CUDA-graph replay: same bytes
+    np.testing.assert_array_equal(ex.get_output(index["logits"]).astype(np.float32), logits)
+    assert capi.load().rg_b200_error_state() == 0
