@@ -3,15 +3,16 @@
 // in tensor memory.  Replaces the cublasGemmEx call of MatMulCublas
 // (src/04kernel/src/kernels/mat_mul/cublas_kernel.cu:48-55) for prefill-sized products.
 //
-// One CTA computes one 128 x BN output tile (BN = 256 or 128; also used with the operands swapped so that a skinny
-// activation matrix becomes the N side of the instruction):
+// Persistent CTAs (one per SM) walk 128 x BN output tiles (BN = 256 or 128; 64 / 32 with the operands swapped so that a
+// skinny activation matrix becomes the N side of the instruction) in an L2-friendly grouped order:
 //   warp 4  (one thread): TMA producer — cp.async.bulk.tensor.2d loads of the A tile [128 x 64] and B tile [BN x 64]
 //                         with the 128-byte swizzle into a STAGES-deep shared-memory ring (full[] mbarriers).
 //   warp 5  (one thread): MMA issuer — per stage four tcgen05.mma.cta_group::1.kind::f16 (M 128, N BN, K 16) whose
 //                         shared-memory descriptors advance 32 bytes along K inside the swizzle atom; tcgen05.commit
 //                         releases the stage (empty[]) and finally signals the accumulator (acc_full).
 //   warps 0-3:            epilogue — tcgen05.ld of each warp's 32 TMEM lanes, alpha/beta/bias, conversion, stores.
-// Warp 5 also allocates and frees the BN TMEM columns.  Every mbarrier wait is bounded; on expiry the CTA records
+// The accumulator is double-buffered in tensor memory (2 x BN columns, acc_full[] / acc_empty[] mbarriers), so a tile's
+// epilogue overlaps the next tile's main loop.  Warp 5 also allocates and frees the TMEM columns.  Every mbarrier wait is bounded; on expiry the CTA records
 // an error word, still frees its tensor memory and exits.
 #include "gemm_dispatch.cuh"
 #include <cuda.h>
@@ -103,6 +104,20 @@ __host__ __device__ inline uint32_t instr_desc(int is_bf16, uint32_t M, uint32_t
     return d;
 }
 
+// Tile order: groups of TC_GROUP_M row tiles are walked column by column, so the CTAs running at the same time share
+// a few A row-panels and B column-panels in L2 instead of streaming all of B once per row tile.
+constexpr uint32_t TC_GROUP_M = 16;
+__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t m_tiles, uint32_t n_tiles, uint32_t &mt, uint32_t &nt) {
+    const uint32_t per_group = TC_GROUP_M * n_tiles;
+    const uint32_t grp = t / per_group, first = grp * TC_GROUP_M;
+    const uint32_t rows = m_tiles - first < TC_GROUP_M ? m_tiles - first : TC_GROUP_M;
+    const uint32_t r = t - grp * per_group;
+    mt = first + r % rows;
+    nt = r / rows;
+}
+
+// Persistent: CTA c computes tiles c, c + gridDim.x, ...  The accumulator is double-buffered in tensor memory (2 x BN
+// columns), so the epilogue of one tile (tcgen05.ld, conversion, stores) overlaps the MMA main loop of the next.
 template<class T, int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_b, const TcArgs a) {
@@ -112,12 +127,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
     uint64_t *empty = full + STAGES;
-    uint64_t *acc_full = empty + STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    uint64_t *acc_full = empty + STAGES; // [2]
+    uint64_t *acc_empty = acc_full + 2;  // [2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     int *failed = reinterpret_cast<int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const uint32_t m_tiles = (a.m + TC_BM - 1) / TC_BM, n_tiles = (a.n + BN - 1) / BN, tiles = m_tiles * n_tiles;
     const uint32_t kblocks = (a.k + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -125,12 +141,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);// one arrival per epilogue warp
+        }
         *failed = 0;
         fence_mbar_init();
     }
     if (warp == 5) {
-        tmem_alloc(tmem_slot, BN);
+        tmem_alloc(tmem_slot, 2 * BN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -140,63 +159,95 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 
     if (warp == 4) {
         if (lane == 0) {
-            for (uint32_t kb = 0; kb < kblocks; ++kb) {
-                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
-                if (!mbar_wait(&empty[s], ph ^ 1u)) {
-                    *failed = 1;
-                    break;
+            uint32_t it = 0;
+            for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+                uint32_t mt, nt;
+                tile_coords(tile, m_tiles, n_tiles, mt, nt);
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u)) {
+                        *failed = 1;
+                        tile = tiles;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                    uint8_t *st = smem + s * STAGE_BYTES;
+                    tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[s]);
+                    tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, nt * BN, &full[s]);
                 }
-                mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                uint8_t *st = smem + s * STAGE_BYTES;
-                tma_load_2d(st, &tmap_a, kb * TC_BK, m0, &full[s]);
-                tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, n0, &full[s]);
             }
         }
     } else if (warp == 5) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(a.is_bf16, TC_BM, BN);
+            uint32_t it = 0, local = 0;
             bool ok = true;
-            for (uint32_t kb = 0; kb < kblocks && ok; ++kb) {
-                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
-                if (!mbar_wait(&full[s], ph)) {
-                    *failed = 2;
-                    ok = false;
+            for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+                const uint32_t buf = local & 1u;
+                if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1u) ^ 1u)) {
+                    *failed = 4;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&full[s], ph)) {
+                        *failed = 2;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk) {
-                    const uint64_t ad = smem_desc_sw128(a_addr + kk * 32), bd = smem_desc_sw128(b_addr + kk * 32);
-                    tc_mma_f16(tmem_base, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < TC_BK / 16; ++kk) {
+                        const uint64_t ad = smem_desc_sw128(a_addr + kk * 32), bd = smem_desc_sw128(b_addr + kk * 32);
+                        tc_mma_f16(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&empty[s]);// frees the stage once these MMAs have read it
                 }
-                tc_commit(&empty[s]);// frees the stage once these MMAs have read it
+                tc_commit(&acc_full[buf]);// this tile's accumulator is complete when it arrives
             }
-            tc_commit(acc_full);     // all MMAs issued so far have completed when this arrives
         }
     } else {
         // ---- epilogue warps 0..3: TMEM lanes [32*warp, 32*warp + 32) = tile rows ----
-        const bool got = mbar_wait(acc_full, 0);
-        if (!got) *failed = 3;
-        tc_fence_after();
-        if (got) {
+        T *Y = static_cast<T *>(a.Y);
+        const T *C = static_cast<const T *>(a.C);
+        const bool c_rowmajor = C && a.c_col_stride == 1 && (a.c_row_stride % 8) == 0;
+        uint32_t local = 0;
+        for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            uint32_t mt, nt;
+            tile_coords(tile, m_tiles, n_tiles, mt, nt);
+            const uint32_t buf = local & 1u, m0 = mt * TC_BM, n0 = nt * BN;
+            if (!mbar_wait(&acc_full[buf], (local >> 1) & 1u)) {
+                *failed = 3;
+                break;
+            }
+            tc_fence_after();
             const uint32_t row = m0 + warp * 32 + lane;
-            T *Y = static_cast<T *>(a.Y);
-            const T *C = static_cast<const T *>(a.C);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((warp * 32u) << 16) + c0, r);
+                tmem_ld_32x32(tmem_base + buf * BN + ((warp * 32u) << 16) + c0, r);
                 tmem_ld_wait();
                 if (row < a.m) {
-                    if (a.y_col_stride == 1 && n0 + c0 + 32 <= a.n && (a.y_row_stride % 8) == 0 && !C) {
-                        // contiguous 64-byte run of this thread's row: four 16-byte stores
+                    if (a.y_col_stride == 1 && n0 + c0 + 32 <= a.n && (a.y_row_stride % 8) == 0 && (!C || c_rowmajor)) {
+                        // contiguous 64-byte run of this thread's row: four 16-byte stores (and loads of C)
                         T *dst = Y + static_cast<uint64_t>(row) * a.y_row_stride + n0 + c0;
+                        const T *csrc = C ? C + static_cast<uint64_t>(row) * a.c_row_stride + n0 + c0 : nullptr;
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             float f[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) f[e] = a.alpha * __uint_as_float(r[j + e]);
+                            if (csrc) {
+                                Vec16<T> cv;
+                                float cf[8];
+                                cv.load(csrc + j);
+                                cv.unpack(cf);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) f[e] += a.beta * cf[e];
+                            }
                             Vec16<T> v;
                             v.pack(f);
                             v.store(dst + j);
@@ -214,13 +265,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                 }
             }
+            // hand the accumulator buffer back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 5) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, 2 * BN);
     }
     if (threadIdx.x == 0 && *failed) atomicExch(&s_tc_error, *failed);
 }
@@ -270,11 +325,12 @@ bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *
 
 template<class T, int BN, int STAGES>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
-    constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<T, BN, STAGES>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    dim3 grid((a.n + BN - 1) / BN, (a.m + TC_BM - 1) / TC_BM);
-    kern<<<grid, TC_THREADS, smem, st>>>(ma, mb, a);
+    const uint32_t tiles = ((a.n + BN - 1) / BN) * ((a.m + TC_BM - 1) / TC_BM);
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    kern<<<tiles < sms ? tiles : sms, TC_THREADS, smem, st>>>(ma, mb, a);
     count_launch();
     return launch_status();
 }
