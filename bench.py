@@ -425,9 +425,11 @@ def run_case(args):
         p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y, p.force_kernel = capi.BF16, m, n, k, 1, 1.0, 1.0, 1, m * n, 3
         bytes_per = (m * k + n * k + m * n) * 2
         flops_per = 2.0 * m * n * k
+        nws = capi.workspace("mat_mul", p)
+        wsb = torch.zeros(max(nws, 1), dtype=torch.uint8, device=dev)
 
         def launch(i):
-            capi.call("mat_mul", p, [As[i % nb].data_ptr(), Bs[i % nb].data_ptr(), 0], [y.data_ptr()], stream=sid)
+            capi.call("mat_mul", p, [As[i % nb].data_ptr(), Bs[i % nb].data_ptr(), 0], [y.data_ptr()], ws=wsb.data_ptr() if nws else 0, stream=sid)
     elif args.case == "attn_decode":
         L, MS = 2112, 2560
         q = torch.randn(1, nH, D, device=dev).to(dt)
@@ -485,14 +487,17 @@ def time_skinny_gemm(ex, index, cfg, torch, stream, reps=3):
         p = capi.MatMulParams()
         p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y = capi.FP16, B, n, k, 1, 1.0, 1.0, 1, B * n
         xk = x[:, :k].contiguous() if k != x.shape[1] else x
-        calls.append((p, [xk.data_ptr(), ex.input_address(index[name]), 0], xk))
+        nws = capi.workspace("mat_mul", p)
+        wsb = torch.zeros(max(nws, 1), dtype=torch.uint8, device="cuda")
+        calls.append((p, [xk.data_ptr(), ex.input_address(index[name]), 0], xk, wsb, nws))
         bytes_total += n * k * 2
     sid = stream.cuda_stream
     outs = [y.data_ptr()]
+    torch.cuda.synchronize()
 
     def one_pass():
-        for p, ins, _keep in calls:
-            capi.call("mat_mul", p, ins, outs, stream=sid)
+        for p, ins, _keep, wsb, nws in calls:
+            capi.call("mat_mul", p, ins, outs, ws=wsb.data_ptr() if nws else 0, stream=sid)
     one_pass()
     stream.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

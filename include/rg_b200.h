@@ -203,7 +203,10 @@ int rg_b200_state_update(const rg_state_update_params *, void *ws, const void *c
  * Kernel selection (all hand-written, no vendor GEMM):
  *   - fp16/bf16, transA=0, transB=1, m <= 4: HBM-streaming GEMV (bulk-copy smem ring),
  *   - fp16/bf16, transA=0, transB=1, aligned, m*n large: tcgen05/TMEM tensor-core GEMM fed by TMA,
- *   - anything else: shared-memory tiled SIMT GEMM. */
+ *   - anything else: shared-memory tiled SIMT GEMM.
+ * Workspace: rg_b200_mat_mul_workspace bytes (split-K partials and arrival counters of the tensor-core kernel for skinny
+ * products); it must be zero on first use and is left ready for the next call.  Without a workspace such products fall
+ * back to the SIMT kernel. */
 typedef struct rg_mat_mul_params {
     int32_t dtype; /* RG_F32, RG_FP16, RG_BF16 */
     uint32_t m, n, k;

@@ -33,6 +33,9 @@ struct TcArgs {
     uint32_t c_row_stride, c_col_stride;
     uint64_t y_row_stride, y_col_stride;// element strides of Y over the kernel's (row, col) = lets swapped runs write Y^T
     int is_bf16;
+    uint32_t splits;   // k-splits per output tile (1 = none)
+    float *partial;    // [tiles][splits][128][BN] fp32, used when splits > 1
+    unsigned *counter; // [tiles] arrival counters, zero before the first call and left at zero
 };
 
 // ---- tcgen05 / TMA PTX ------------------------------------------------------------------------------------
@@ -134,7 +137,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (a.m + TC_BM - 1) / TC_BM, n_tiles = (a.n + BN - 1) / BN, tiles = m_tiles * n_tiles;
-    const uint32_t kblocks = (a.k + TC_BK - 1) / TC_BK;
+    const uint32_t kblocks = (a.k + TC_BK - 1) / TC_BK, items = tiles * a.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -160,14 +163,16 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     if (warp == 4) {
         if (lane == 0) {
             uint32_t it = 0;
-            for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
                 uint32_t mt, nt;
+                const uint32_t tile = item / a.splits, ks = item % a.splits;
                 tile_coords(tile, m_tiles, n_tiles, mt, nt);
-                for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
+                const uint32_t kb0 = kblocks * ks / a.splits, kb1 = kblocks * (ks + 1) / a.splits;
+                for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!mbar_wait(&empty[s], ph ^ 1u)) {
                         *failed = 1;
-                        tile = tiles;
+                        item = items;
                         break;
                     }
                     mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
@@ -182,15 +187,16 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             const uint32_t idesc = instr_desc(a.is_bf16, TC_BM, BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
-                const uint32_t buf = local & 1u;
+            for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x, ++local) {
+                const uint32_t buf = local & 1u, ks = item % a.splits;
+                const uint32_t kb0 = kblocks * ks / a.splits, kb1 = kblocks * (ks + 1) / a.splits;
                 if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1u) ^ 1u)) {
                     *failed = 4;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
+                for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!mbar_wait(&full[s], ph)) {
                         *failed = 2;
@@ -202,7 +208,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 #pragma unroll
                     for (int kk = 0; kk < TC_BK / 16; ++kk) {
                         const uint64_t ad = smem_desc_sw128(a_addr + kk * 32), bd = smem_desc_sw128(b_addr + kk * 32);
-                        tc_mma_f16(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        tc_mma_f16(d_tmem, ad, bd, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
                     }
                     tc_commit(&empty[s]);// frees the stage once these MMAs have read it
                 }
@@ -214,9 +220,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         T *Y = static_cast<T *>(a.Y);
         const T *C = static_cast<const T *>(a.C);
         const bool c_rowmajor = C && a.c_col_stride == 1 && (a.c_row_stride % 8) == 0;
+        __shared__ int s_last;
         uint32_t local = 0;
-        for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++local) {
             uint32_t mt, nt;
+            const uint32_t tile = item / a.splits, ks = item % a.splits;
             tile_coords(tile, m_tiles, n_tiles, mt, nt);
             const uint32_t buf = local & 1u, m0 = mt * TC_BM, n0 = nt * BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1u)) {
@@ -224,6 +232,53 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 break;
             }
             tc_fence_after();
+            if (a.splits > 1) {
+                // split-K: park this split's fp32 tile; the last split to arrive sums all of them in split order
+                const uint32_t trow = warp * 32 + lane;
+                float *mine = a.partial + (static_cast<size_t>(tile) * a.splits + ks) * (TC_BM * BN) + static_cast<size_t>(trow) * BN;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + buf * BN + ((warp * 32u) << 16) + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<uint4 *>(mine + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                __threadfence();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (threadIdx.x == 0) s_last = atomicAdd(&a.counter[tile], 1u) == a.splits - 1 ? 1 : 0;
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (!s_last) continue;
+                __threadfence();
+                const uint32_t row = m0 + trow;
+                const float *base = a.partial + static_cast<size_t>(tile) * a.splits * (TC_BM * BN) + static_cast<size_t>(trow) * BN;
+                if (row < a.m) {
+                    for (int c = 0; c < BN; c += 4) {
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (uint32_t sidx = 0; sidx < a.splits; ++sidx) {
+                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN) + c));
+                            acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                        }
+                        const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t col = n0 + c + j;
+                            if (col < a.n) {
+                                float v = a.alpha * vals[j];
+                                if (C) v += a.beta * Num<T>::to_f(C[static_cast<uint64_t>(row) * a.c_row_stride + static_cast<uint64_t>(col) * a.c_col_stride]);
+                                Y[static_cast<uint64_t>(row) * a.y_row_stride + static_cast<uint64_t>(col) * a.y_col_stride] = Num<T>::from_f(v);
+                            }
+                        }
+                    }
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (threadIdx.x == 0) a.counter[tile] = 0u;
+                continue;
+            }
             const uint32_t row = m0 + warp * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -323,21 +378,56 @@ bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *
     return encode_fn() != nullptr;
 }
 
+// k-splits for a skinny product.  Splitting costs a partial-tile round trip through L2 per item and was measured to slow
+// products that already have more tiles than SMs (22016 x 4096 at m = 16: 52 us unsplit, 65 us with 4 splits), so it is
+// used only when the tiles alone would leave more than half of the SMs idle; at least 8 k-blocks per item.
+static uint32_t tc_splits(uint32_t tiles, uint32_t kblocks) {
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    if (tiles * 2 > sms) return 1;
+    uint32_t s = sms / tiles;
+    const uint32_t cap = kblocks / 8 ? kblocks / 8 : 1;
+    if (s > cap) s = cap;
+    if (s > 16) s = 16;
+    return s ? s : 1;
+}
+struct TcPlan {
+    bool swap;
+    uint32_t bn, tiles, splits;
+    size_t counter_bytes, partial_bytes;
+};
+static TcPlan tc_plan(const rg_mat_mul_params *p) {
+    TcPlan pl;
+    pl.swap = p->m <= 64 && p->n >= 128;
+    const uint32_t km = pl.swap ? p->n : p->m, kn = pl.swap ? p->m : p->n;
+    pl.bn = pl.swap ? (p->m <= 32 ? 32 : 64) : (p->n >= 256 ? 256 : 128);
+    pl.tiles = ((km + TC_BM - 1) / TC_BM) * ((kn + pl.bn - 1) / pl.bn);
+    pl.splits = pl.swap ? tc_splits(pl.tiles, (p->k + TC_BK - 1) / TC_BK) : 1;
+    pl.counter_bytes = pl.splits > 1 ? (static_cast<size_t>(pl.tiles) * 4 + 255) / 256 * 256 : 0;
+    pl.partial_bytes = pl.splits > 1 ? static_cast<size_t>(pl.tiles) * pl.splits * TC_BM * pl.bn * 4 : 0;
+    return pl;
+}
+size_t gemm_tc_workspace(const rg_mat_mul_params *p) {
+    const TcPlan pl = tc_plan(p);
+    return pl.counter_bytes + pl.partial_bytes;
+}
+
 template<class T, int BN, int STAGES>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
     constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<T, BN, STAGES>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    const uint32_t tiles = ((a.n + BN - 1) / BN) * ((a.m + TC_BM - 1) / TC_BM);
+    const uint32_t items = ((a.n + BN - 1) / BN) * ((a.m + TC_BM - 1) / TC_BM) * a.splits;
     const uint32_t sms = static_cast<uint32_t>(sm_count());
-    kern<<<tiles < sms ? tiles : sms, TC_THREADS, smem, st>>>(ma, mb, a);
+    kern<<<items < sms ? items : sms, TC_THREADS, smem, st>>>(ma, mb, a);
     count_launch();
     return launch_status();
 }
 
-int gemm_tc(const rg_mat_mul_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st) {
     const int is_bf16 = p->dtype == RG_BF16;
     const size_t es = 2;
+    const TcPlan pl = tc_plan(p);
+    if (pl.splits > 1 && !ws) return RG_ERR_NULL;
     for (uint32_t b = 0; b < p->batch; ++b) {
         const uint8_t *A = static_cast<const uint8_t *>(in[0]) + b * p->stride_a * es;
         const uint8_t *B = static_cast<const uint8_t *>(in[1]) + b * p->stride_b * es;
@@ -345,9 +435,12 @@ int gemm_tc(const rg_mat_mul_params *p, const void *const *in, void *const *out,
         const uint8_t *C = p->has_bias ? static_cast<const uint8_t *>(in[2]) + b * p->stride_c * es : nullptr;
         TcArgs a = {};
         a.alpha = p->alpha, a.beta = p->beta, a.is_bf16 = is_bf16, a.k = p->k;
+        a.splits = pl.splits;
+        a.counter = static_cast<unsigned *>(ws);
+        a.partial = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + pl.counter_bytes);
         CUtensorMap ma, mb;
         // a skinny activation matrix (m <= 64) goes on the N side of the instruction: D^T[n, m] = W[n,k] X[m,k]^T
-        const bool swap = p->m <= 64 && p->n >= 128;
+        const bool swap = pl.swap;
         uint32_t bn;
         if (!swap) {
             bn = p->n >= 256 ? 256 : 128;

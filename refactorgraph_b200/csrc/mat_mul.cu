@@ -20,9 +20,13 @@ static int run_gemv(const rg_mat_mul_params *p, const void *const *in, void *con
 
 extern "C" {
 
-size_t rg_b200_mat_mul_workspace(const rg_mat_mul_params *) { return 0; }
+size_t rg_b200_mat_mul_workspace(const rg_mat_mul_params *p) {
+    // only the tensor-core kernel's split-K path needs scratch; sized for it whenever that kernel could be chosen
+    if (!p || (p->dtype != RG_FP16 && p->dtype != RG_BF16) || p->trans_a || !p->trans_b) return 0;
+    return gemm_tc_workspace(p);
+}
 
-int rg_b200_mat_mul(const rg_mat_mul_params *p, void *, const void *const *in, void *const *out, void *stream) {
+int rg_b200_mat_mul(const rg_mat_mul_params *p, void *ws, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out || !in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
     if (p->has_bias && !in[2]) return RG_ERR_NULL;
     if (p->dtype != RG_F32 && p->dtype != RG_FP16 && p->dtype != RG_BF16) return RG_ERR_DTYPE;
@@ -34,14 +38,14 @@ int rg_b200_mat_mul(const rg_mat_mul_params *p, void *, const void *const *in, v
         case 0: break;
         case 1: return gemm_simt(p, in, out, st);
         case 2: return gemv_shape(p) ? run_gemv(p, in, out, st) : RG_ERR_UNSUPPORTED;
-        case 3: return gemm_tc_supported(p, in, out) ? gemm_tc(p, in, out, st) : RG_ERR_UNSUPPORTED;
+        case 3: return gemm_tc_supported(p, in, out) ? gemm_tc(p, ws, in, out, st) : RG_ERR_UNSUPPORTED;
         default: return RG_ERR_UNSUPPORTED;
     }
     if (gemv_shape(p) && aligned16(in[0]) && aligned16(in[1])) {
         const int rc = run_gemv(p, in, out, st);
         if (rc != RG_ERR_SHAPE && rc != RG_ERR_UNSUPPORTED) return rc;
     }
-    if (gemm_tc_supported(p, in, out)) return gemm_tc(p, in, out, st);
+    if (gemm_tc_supported(p, in, out) && (ws || gemm_tc_workspace(p) == 0)) return gemm_tc(p, ws, in, out, st);
     return gemm_simt(p, in, out, st);
 }
 }

@@ -137,8 +137,8 @@ def decode_step_graph_single_kernel(cfg: LlamaConfig):
 
 def prefill_graph(cfg: LlamaConfig, seq: int, top_k: int = 1):
     """Causal prefill of `cfg.batch` sequences of `seq` tokens (token-major activations [B*S, hidden]): per layer
-    RmsNormalization, MatMul (tcgen05), QkvRopeAppend (writes the K/V caches), AttentionPrefill, MatMul, Add,
-    RmsNormalization, MatMul, SwiGLU, MatMul, Add; then the LM head on the last token of every sequence + TopK.
+    RmsNormalization, MatMul (tcgen05), QkvRopeAppend (writes the K/V caches), AttentionPrefill, MatMul(+residual),
+    RmsNormalization, MatMul, SwiGLU, MatMul(+residual); then the LM head on the last token of every sequence + TopK.
     Inputs: ids[B*S], positions[B*S], last[B] (row index of each sequence's last token), weights, caches."""
     g = GraphBuilder()
     B, H, D, n = cfg.batch, cfg.hidden, cfg.head_dim, cfg.batch * seq
@@ -158,13 +158,11 @@ def prefill_graph(cfg: LlamaConfig, seq: int, top_k: int = 1):
         q = g.op("b200::QkvRopeAppend", [qkv, pos, kc, vc], n_heads=cfg.heads, n_kv_heads=cfg.kv_heads, head_dim=D, theta=cfg.theta,
                  tokens_per_seq=seq)
         a = g.op("b200::AttentionPrefill", [q, kc, vc], n_heads=cfg.heads, seq_len=seq)
-        o = g.op("llm::MatMul", [a, f"l{l}.wo"], transB=1)
-        h = g.op("onnx::Add", [o, x])
+        h = g.op("llm::MatMul", [a, f"l{l}.wo", x], transB=1)           # Y = A W^T + 1 * C: the residual add rides in the epilogue
         n2 = g.op("llm::RmsNormalization", [h, f"l{l}.norm2"], epsilon=cfg.eps)
         gu = g.op("llm::MatMul", [n2, f"l{l}.wgu"], transB=1)
         u = g.op("b200::SwiGLU", [gu])
-        d = g.op("llm::MatMul", [u, f"l{l}.wd"], transB=1)
-        x = g.op("onnx::Add", [d, h])
+        x = g.op("llm::MatMul", [u, f"l{l}.wd", h], transB=1)
     xl = g.op("onnx::Gather", [x, last], axis=0)
     xf = g.op("llm::RmsNormalization", [xl, "norm_f"], epsilon=cfg.eps)
     logits = g.op("llm::MatMul", [xf, "lm_head"], transB=1)
@@ -232,13 +230,19 @@ def decode_step_graph_batched(cfg: LlamaConfig, world: int = 1, paged: bool = Fa
         q3 = g.op("onnx::Reshape", [q], shape=[B, cfg.heads, D])
         a = g.op("b200::AttentionDecode", [q3, kc, vc, lens] + ([table] if paged else []), max_len=cfg.max_seq, page_size=page if paged else 0)
         a2 = g.op("onnx::Reshape", [a], shape=[B, cfg.heads * D])
-        o = g.op("llm::MatMul", [a2, f"l{l}.wo"], transB=1)
-        h = g.op("onnx::AllReduceSum", [o, x]) if world > 1 else g.op("onnx::Add", [o, x])
+        if world > 1:
+            o = g.op("llm::MatMul", [a2, f"l{l}.wo"], transB=1)
+            h = g.op("onnx::AllReduceSum", [o, x])
+        else:
+            h = g.op("llm::MatMul", [a2, f"l{l}.wo", x], transB=1)      # residual add in the GEMM epilogue
         n2 = g.op("llm::RmsNormalization", [h, f"l{l}.norm2"], epsilon=cfg.eps)
         gu = g.op("llm::MatMul", [n2, f"l{l}.wgu"], transB=1)
         u = g.op("b200::SwiGLU", [gu])
-        d = g.op("llm::MatMul", [u, f"l{l}.wd"], transB=1)
-        x = g.op("onnx::AllReduceSum", [d, h]) if world > 1 else g.op("onnx::Add", [d, h])
+        if world > 1:
+            d = g.op("llm::MatMul", [u, f"l{l}.wd"], transB=1)
+            x = g.op("onnx::AllReduceSum", [d, h])
+        else:
+            x = g.op("llm::MatMul", [u, f"l{l}.wd", h], transB=1)
     xf = g.op("llm::RmsNormalization", [x, "norm_f"], epsilon=cfg.eps)
     logits = g.op("llm::MatMul", [xf, "lm_head"], transB=1)
     index = {}

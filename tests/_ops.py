@@ -151,7 +151,10 @@ def mat_mul(a, b, c=None, trans_a=False, trans_b=False, alpha=1.0, beta=1.0, for
         cs = _bstrides(c.shape, (m, n))
         p.bias_row_stride, p.bias_col_stride = cs[0], cs[1]
         p.stride_c = 0
-    capi.call("mat_mul", p, [ptr(a), ptr(b), ptr(c)], [ptr(y)], stream=stream())
+    nws = capi.workspace("mat_mul", p)
+    ws = torch.zeros(max(nws, 1), dtype=torch.uint8, device=a.device)
+    capi.call("mat_mul", p, [ptr(a), ptr(b), ptr(c)], [ptr(y)], ws=ptr(ws) if nws else 0, stream=stream())
+    torch.cuda.current_stream().synchronize()  # the workspace is released on return
     return y
 
 
