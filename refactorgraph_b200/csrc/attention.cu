@@ -343,6 +343,11 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const T *__restrict__ q,
     for (int e = 0; e < EP; ++e) o[row * D + lane * EP + e] = Num<T>::from_f(acc[e] / l);
 }
 
+// grouped-query variant (attn_decode_gqa.cu): one CTA serves all query heads of a KV head
+bool attn_decode_gqa_applies(const rg_attn_decode_params *p);
+size_t attn_decode_gqa_workspace(const rg_attn_decode_params *p);
+int attn_decode_gqa_launch(const rg_attn_decode_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st, bool pdl);
+
 int attn_prefill_ref_layout(int dtype, const void *q, const void *K, const void *V, void *o, const int64_t *past, uint32_t batch,
                             uint32_t n_heads, uint32_t n_kv, uint32_t S, uint32_t kv_tokens, cudaStream_t st);
 
@@ -435,7 +440,12 @@ int rg_b200_attention(const rg_attention_params *p, void *, const void *const *i
 size_t rg_b200_attn_decode_workspace(const rg_attn_decode_params *p) {
     if (!p) return 0;
     const DecodePlan pl = decode_plan(p);
-    return pl.cnt_bytes + pl.part_bytes;
+    size_t bytes = pl.cnt_bytes + pl.part_bytes;
+    if (attn_decode_gqa_applies(p)) {
+        const size_t g = attn_decode_gqa_workspace(p);
+        bytes = g > bytes ? g : bytes;
+    }
+    return bytes;
 }
 int rg_b200_attn_decode(const rg_attn_decode_params *p, void *ws, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out || !in[0] || !in[1] || !in[2] || !in[3] || !out[0] || !ws) return RG_ERR_NULL;
@@ -451,6 +461,7 @@ int rg_b200_attn_decode(const rg_attn_decode_params *p, void *ws, const void *co
     if (!aligned16(in[1]) || !aligned16(in[2])) return RG_ERR_ALIGN;
     auto st = static_cast<cudaStream_t>(stream);
     const bool pdl = attn_pdl_enabled();
+    if (attn_decode_gqa_applies(p)) return attn_decode_gqa_launch(p, ws, in, out, st, pdl);
     if (p->dtype == RG_FP16) {
         if (p->kv.head_dim == 128) return decode_launch<__half, 128>(p, ws, in, out, st, pdl);
         if (p->kv.head_dim == 64) return decode_launch<__half, 64>(p, ws, in, out, st, pdl);

@@ -15,6 +15,7 @@
 // epilogue overlaps the next tile's main loop.  Warp 5 also allocates and frees the TMEM columns.  Every mbarrier wait is bounded; on expiry the CTA records
 // an error word, still frees its tensor memory and exits.
 #include "gemm_dispatch.cuh"
+#include <cstdlib>
 #include <cuda.h>
 
 namespace rg {
@@ -248,29 +249,43 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                __threadfence();
+                // the barrier orders the 128 threads' stores before thread 0's release-increment (cumulative at gpu scope)
                 asm volatile("bar.sync 2, 128;" ::: "memory");
-                if (threadIdx.x == 0) s_last = atomicAdd(&a.counter[tile], 1u) == a.splits - 1 ? 1 : 0;
+                if (threadIdx.x == 0) {
+                    unsigned old;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(a.counter + tile) : "memory");
+                    s_last = old == a.splits - 1 ? 1 : 0;
+                }
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (!s_last) continue;
-                __threadfence();
                 const uint32_t row = m0 + trow;
                 const float *base = a.partial + static_cast<size_t>(tile) * a.splits * (TC_BM * BN) + static_cast<size_t>(trow) * BN;
-                if (row < a.m) {
-                    for (int c = 0; c < BN; c += 4) {
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (uint32_t sidx = 0; sidx < a.splits; ++sidx) {
-                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN) + c));
-                            acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
-                        }
-                        const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+                if constexpr (BN <= 64) {// split-K is only planned for the skinny (swapped) shapes
+                    if (row < a.m) {
+                        // this thread's row of every split: the BN/4 loads of one split are independent, so the sum
+                        // costs one L2 round trip per split (fixed split order => deterministic)
+                        float4 acc[BN / 4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t col = n0 + c + j;
-                            if (col < a.n) {
-                                float v = a.alpha * vals[j];
-                                if (C) v += a.beta * Num<T>::to_f(C[static_cast<uint64_t>(row) * a.c_row_stride + static_cast<uint64_t>(col) * a.c_col_stride]);
-                                Y[static_cast<uint64_t>(row) * a.y_row_stride + static_cast<uint64_t>(col) * a.y_col_stride] = Num<T>::from_f(v);
+                        for (int c = 0; c < BN / 4; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (uint32_t sidx = 0; sidx < a.splits; ++sidx) {
+                            const float4 *src = reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN));
+                            float4 v[BN / 4];
+#pragma unroll
+                            for (int c = 0; c < BN / 4; ++c) v[c] = __ldcg(src + c);
+#pragma unroll
+                            for (int c = 0; c < BN / 4; ++c) acc[c].x += v[c].x, acc[c].y += v[c].y, acc[c].z += v[c].z, acc[c].w += v[c].w;
+                        }
+#pragma unroll
+                        for (int c = 0; c < BN / 4; ++c) {
+                            const float vals[4] = {acc[c].x, acc[c].y, acc[c].z, acc[c].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t col = n0 + c * 4 + j;
+                                if (col < a.n) {
+                                    float v = a.alpha * vals[j];
+                                    if (C) v += a.beta * Num<T>::to_f(C[static_cast<uint64_t>(row) * a.c_row_stride + static_cast<uint64_t>(col) * a.c_col_stride]);
+                                    Y[static_cast<uint64_t>(row) * a.y_row_stride + static_cast<uint64_t>(col) * a.y_col_stride] = Num<T>::from_f(v);
+                                }
                             }
                         }
                     }
@@ -378,16 +393,21 @@ bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *
     return encode_fn() != nullptr;
 }
 
-// k-splits for a skinny product.  Splitting costs a partial-tile round trip through L2 per item and was measured to slow
-// products that already have more tiles than SMs (22016 x 4096 at m = 16: 52 us unsplit, 65 us with 4 splits), so it is
-// used only when the tiles alone would leave more than half of the SMs idle; at least 8 k-blocks per item.
+// k-splits for a skinny product.  Every extra item costs a partial-tile round trip through L2 and ~5 us of epilogue
+// (22016 x 4096 at m = 16: 52.6 us unsplit, 46.6 / 52.8 / 88.9 us with 2 / 3 / 6 splits), so splits are used sparingly:
+// up to SMs/tiles when the tiles alone leave more than half of the SMs idle, else 2 only to repair a bad last wave.
 static uint32_t tc_splits(uint32_t tiles, uint32_t kblocks) {
     const uint32_t sms = static_cast<uint32_t>(sm_count());
-    if (tiles * 2 > sms) return 1;
-    uint32_t s = sms / tiles;
     const uint32_t cap = kblocks / 8 ? kblocks / 8 : 1;
+    if (tiles * 2 > sms) {
+        // more tiles than half the SMs: a 2-way split only pays when it repairs the last, mostly empty wave
+        // (172 tiles on 148 SMs: 58 % -> 77 % of the slots busy; measured 52.6 us -> 46.6 us)
+        auto busy = [&](uint32_t items) { return static_cast<float>(items) / static_cast<float>((items + sms - 1) / sms * sms); };
+        return (cap >= 2 && tiles < 2 * sms && busy(2 * tiles) > busy(tiles) + 0.15f) ? 2 : 1;
+    }
+    uint32_t s = sms / tiles;
     if (s > cap) s = cap;
-    if (s > 16) s = 16;
+    if (s > 8) s = 8;
     return s ? s : 1;
 }
 struct TcPlan {
@@ -402,6 +422,13 @@ static TcPlan tc_plan(const rg_mat_mul_params *p) {
     pl.bn = pl.swap ? (p->m <= 32 ? 32 : 64) : (p->n >= 256 ? 256 : 128);
     pl.tiles = ((km + TC_BM - 1) / TC_BM) * ((kn + pl.bn - 1) / pl.bn);
     pl.splits = pl.swap ? tc_splits(pl.tiles, (p->k + TC_BK - 1) / TC_BK) : 1;
+    if (pl.swap) {// tuning knob: RG_B200_TC_SPLITS=<n> forces the split count of skinny products
+        static const char *force = std::getenv("RG_B200_TC_SPLITS");
+        if (force && force[0]) {
+            const uint32_t f = static_cast<uint32_t>(std::atoi(force)), kb = (p->k + TC_BK - 1) / TC_BK;
+            if (f >= 1) pl.splits = f > kb ? kb : f;
+        }
+    }
     pl.counter_bytes = pl.splits > 1 ? (static_cast<size_t>(pl.tiles) * 4 + 255) / 256 * 256 : 0;
     pl.partial_bytes = pl.splits > 1 ? static_cast<size_t>(pl.tiles) * pl.splits * TC_BM * pl.bn * 4 : 0;
     return pl;

@@ -398,6 +398,38 @@ def test_attn_decode_paged(dtype):
     close_half(o, want)
 
 
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("B,nH,nKV,lens,paged", [(16, 8, 1, "4096", False), (3, 64, 8, "mixed", False), (4, 32, 16, "mixed", True),
+                                                (2, 16, 1, "mixed", True), (5, 8, 2, "short", False)])
+def test_attn_decode_grouped_query(dtype, B, nH, nKV, lens, paged):
+    """Grouped-query decode (2..16 query heads per KV head): the kernel that serves a whole group from one K/V tile."""
+    rng = np.random.default_rng(B * nH + nKV)
+    D, page = 128, 16
+    L = {"4096": np.full(B, 4097), "mixed": rng.integers(1, 3000, (B,)), "short": np.array([1, 15, 16, 64, 65])[:B]}[lens].astype(np.int64)
+    max_len = int(L.max())
+    q = rnd16(rng.standard_normal((B, nH, D)).astype(np.float32), dtype)
+    if paged:
+        max_blocks = (max_len + page - 1) // page
+        n_blocks = B * max_blocks
+        table = rng.permutation(n_blocks).reshape(B, max_blocks).astype(np.int32)
+        kc = torch.from_numpy(rng.standard_normal((n_blocks, nKV, page, D)).astype(np.float32)).to(dtype)
+        vc = torch.from_numpy(rng.standard_normal((n_blocks, nKV, page, D)).astype(np.float32)).to(dtype)
+        kv = ops.kv_layout(nKV, D, 0, page, max_blocks)
+        o, ws = ops.attn_decode(ops.dev(q, dtype), kc.cuda(), vc.cuda(), ops.dev(L), kv, max_len, table=ops.dev(table))
+        want = onp.attn_decode(q, kc.float().numpy(), vc.float().numpy(), L, block_table=table, page=page)
+    else:
+        max_seq = max_len + 7
+        kc = torch.from_numpy(rng.standard_normal((B, nKV, max_seq, D)).astype(np.float32)).to(dtype)
+        vc = torch.from_numpy(rng.standard_normal((B, nKV, max_seq, D)).astype(np.float32)).to(dtype)
+        kv = ops.kv_layout(nKV, D, max_seq)
+        kcd, vcd, qd, Ld = kc.cuda(), vc.cuda(), ops.dev(q, dtype), ops.dev(L)
+        o, ws = ops.attn_decode(qd, kcd, vcd, Ld, kv, max_len)
+        want = onp.attn_decode(q, kc.float().numpy(), vc.float().numpy(), L)
+        o2, _ = ops.attn_decode(qd, kcd, vcd, Ld, kv, max_len, ws=ws)   # counters were left at zero
+        assert torch.equal(o, o2)
+    close_half(o, want)
+
+
 def test_no_bounded_wait_expired():
     # all the kernels above ran; none of their bounded device-side waits may have expired
     torch.cuda.synchronize()
