@@ -743,6 +743,9 @@ def run_b200(args):
                     "kernel": "decode_mega_kernel (one launch per token)", "peak_source": peak_kind + " HBM copy bandwidth",
                     "avg_launch_us": 1000.0 * ms / K, "launches_timed": K, "algorithmic_bytes_per_launch": step_bytes,
                     "linear_stream_kernel_alone_gbs": lin["gbs"]}
+            # ncu (profiles/decode_mega_7b_4layers_ncu.md): DRAM bytes read+written = 1.0022 x algorithmic on a 4-layer
+            # capture; traffic grows in proportion to the layer count
+            roof["traffic"] = step_bytes * (2.015606e9 + 4.392448e6) / 2.0155e9
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
