@@ -368,7 +368,7 @@ def run_decode_step_timeline():
     for ph in range(5 * L + 1):
         e, xr, ud, ep = tt[ph]
         nxt = tt[ph + 1, 0]
-        sub[ph] = [0, (ep - e) / 1e3, 0, (nxt - ep) / 1e3] if (ph % 5 == 1 and ph < 5 * L) else [(xr - e) / 1e3, (ud - xr) / 1e3, (ep - ud) / 1e3, (nxt - ep) / 1e3]
+        sub[ph] = [(xr - e) / 1e3, (ud - xr) / 1e3, (ep - ud) / 1e3, (nxt - ep) / 1e3]
     names = ["qkv", "attention", "o", "gate_up", "down"]
     nbytes = [3 * H * H * 2, 2 * nH * pos0 * D * 2, H * H * 2, 2 * F * H * 2, F * H * 2]
     out = {"case": "decode_step_timeline", "total_us": (tt[5 * L + 1, 0] - tt[0, 0]) / 1e3, "error_state": lib.rg_b200_error_state(),

@@ -29,8 +29,10 @@ constexpr int MG_MAX_LAYERS = 96;
 constexpr int MG_TILE = 64;        // tokens per attention unit
 constexpr int MG_PART_UNITS = 96;  // max units of one phase per CTA
 constexpr int MG_MAX_REC = 8;
-constexpr int MG_L2_AHEAD = 0;     // units the optional L2 prefetch cursor runs ahead of the ring; 0 = off (measured: 8 and 14
-                                   // units ahead slowed the step from 3.04 ms to 4.4 ms, so it stays off)
+// Measured and removed: asking L2 to fetch further ahead than the ring (cp.async.bulk.prefetch.L2 by the producer, 8 or 14
+// units ahead: step +45 %; prefetch.global.L2 by a consumer warp while a grid barrier completes, 2..16 units: +6..50 %).
+// Every extra request in flight queues in front of the barrier's atomics and polls and lengthens the barrier.  Limiting the
+// producer to 2..4 copies in flight instead of 6 changed neither the barrier time nor the step time.
 
 static __device__ int s_mega_error;
 
@@ -161,6 +163,57 @@ __device__ __forceinline__ bool att_range(const MegaArgs &a, uint32_t NT, uint32
     t0 = NT * j / splits, t1 = NT * (j + 1) / splits;
     return t1 > t0;
 }
+// Position in a CTA's share of the step's schedule: phase p, unit u of [.., u1) (attention: tiles of `head`).
+struct MegaCursor {
+    uint32_t p, u, u1, head;
+    Phase ph;
+    bool done;
+};
+// Moves to the first phase >= c.p in which this CTA has units.
+__device__ inline void mega_cursor_seek(const MegaArgs &a, MegaCursor &c, uint32_t nphases, uint32_t NT) {
+    for (; c.p < nphases; ++c.p) {
+        c.ph = phase_of(a, c.p, NT);
+        uint32_t u0;
+        c.head = 0;
+        if (c.ph.type == PH_ATT) {
+            if (!att_range(a, NT, blockIdx.x, gridDim.x, c.head, u0, c.u1)) u0 = c.u1 = 0;
+        } else {
+            unit_range(c.ph.units, u0, c.u1);
+        }
+        c.u = u0;
+        if (c.u < c.u1) return;
+    }
+    c.done = true;
+}
+__device__ __forceinline__ void mega_cursor_advance(const MegaArgs &a, MegaCursor &c, uint32_t nphases, uint32_t NT) {
+    if (++c.u >= c.u1) {
+        ++c.p;
+        mega_cursor_seek(a, c, nphases, NT);
+    }
+}
+// The (up to two) contiguous pieces of the cursor's unit: returns the piece count, fills source, bytes and ring offset.
+__device__ __forceinline__ uint32_t mega_pieces(const MegaArgs &a, const MegaCursor &c, uint32_t pos, const uint8_t *(&src)[2],
+                                               uint32_t (&bytes)[2], uint32_t (&dst)[2]) {
+    if (c.ph.type == PH_ATT) {
+        const uint32_t kvh = c.head / (a.nH / a.nKV);
+        const uint32_t tok0 = c.u * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
+        const size_t off = (static_cast<size_t>(kvh) * a.max_seq + tok0) * a.D * 2u;
+        src[0] = static_cast<const uint8_t *>(a.layer[c.ph.layer].kc) + off;
+        src[1] = static_cast<const uint8_t *>(a.layer[c.ph.layer].vc) + off;
+        bytes[0] = bytes[1] = ntok * a.D * 2u;
+        dst[0] = 0, dst[1] = MG_STAGE_BYTES / 2;
+        return 2;
+    }
+    const uint32_t row_bytes = c.ph.k * 2u;
+    for (uint32_t sg = 0; sg < c.ph.segs; ++sg) {
+        uint32_t rows;
+        const uint32_t row = mega_unit_row(a, c.ph, c.u, sg, rows);
+        src[sg] = c.ph.W + static_cast<uint64_t>(row) * row_bytes;
+        bytes[sg] = rows * row_bytes;
+        dst[sg] = sg * c.ph.g * row_bytes;
+    }
+    return c.ph.segs;
+}
 __device__ __forceinline__ void mg_consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(MG_CONSUMERS) : "memory"); }
 
 __device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long *p) {
@@ -184,6 +237,28 @@ template<int V> __device__ __forceinline__ void mg_reduce_halving(float (&vals)[
         o >>= 1;
     }
     for (; o > 0; o >>= 1) vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], o);
+}
+
+template<class T> __device__ __forceinline__ float2 unpack2(uint32_t w);
+template<> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+    __half2 h;
+    *reinterpret_cast<uint32_t *>(&h) = w;
+    return __half22float2(h);
+}
+template<> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+// D += A(16x16, row) * B(16x8, col) on the warp-level tensor path, 16-bit inputs, fp32 accumulators
+template<class T> __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template<> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template<> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 // Consumes `nu` units of a linear phase from the ring: R rows per unit, KC live 16-byte chunks per thread along k.
@@ -255,73 +330,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
 
     if (warp == MG_NW) {
         // ================= producer: the whole step's stream for this CTA =================
-        // Two cursors walk the same schedule: `ld` issues the bulk copies into the ring as stages free up; `pf` runs
-        // MG_L2_AHEAD units ahead and only asks L2 to fetch (cp.async.bulk.prefetch.L2), so HBM keeps streaming while
-        // the ring is full (consumers at a grid barrier) and the later ring fills are L2 hits.
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_first();
-            struct Cursor {
-                uint32_t p, u, u1, head;
-                Phase ph;
-                bool done;
-            };
-            auto load_phase = [&](Cursor &c) {
-                for (; c.p < nphases; ++c.p) {
-                    c.ph = phase_of(a, c.p, NT);
-                    uint32_t u0;
-                    c.head = 0;
-                    if (c.ph.type == PH_ATT) {
-                        if (!att_range(a, NT, blockIdx.x, gridDim.x, c.head, u0, c.u1)) u0 = c.u1 = 0;
-                    } else {
-                        unit_range(c.ph.units, u0, c.u1);
-                    }
-                    c.u = u0;
-                    if (c.u < c.u1) return;
-                }
-                c.done = true;
-            };
-            auto advance = [&](Cursor &c) {
-                if (++c.u >= c.u1) {
-                    ++c.p;
-                    load_phase(c);
-                }
-            };
-            // the (up to two) contiguous pieces of a unit: returns the piece count, fills src / bytes / ring offset
-            auto pieces = [&](const Cursor &c, const uint8_t *(&src)[2], uint32_t (&bytes)[2], uint32_t (&dst)[2]) -> uint32_t {
-                if (c.ph.type == PH_ATT) {
-                    const uint32_t kvh = c.head / (a.nH / a.nKV);
-                    const uint32_t tok0 = c.u * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
-                    const size_t off = (static_cast<size_t>(kvh) * a.max_seq + tok0) * a.D * 2u;
-                    src[0] = static_cast<const uint8_t *>(a.layer[c.ph.layer].kc) + off;
-                    src[1] = static_cast<const uint8_t *>(a.layer[c.ph.layer].vc) + off;
-                    bytes[0] = bytes[1] = ntok * a.D * 2u;
-                    dst[0] = 0, dst[1] = MG_STAGE_BYTES / 2;
-                    return 2;
-                }
-                const uint32_t row_bytes = c.ph.k * 2u;
-                for (uint32_t sg = 0; sg < c.ph.segs; ++sg) {
-                    uint32_t rows;
-                    const uint32_t row = mega_unit_row(a, c.ph, c.u, sg, rows);
-                    src[sg] = c.ph.W + static_cast<uint64_t>(row) * row_bytes;
-                    bytes[sg] = rows * row_bytes;
-                    dst[sg] = sg * c.ph.g * row_bytes;
-                }
-                return c.ph.segs;
-            };
-            auto prefetch = [&](const Cursor &c) {
-                const uint8_t *src[2];
-                uint32_t bytes[2], dst[2];
-                const uint32_t n = pieces(c, src, bytes, dst);
-                for (uint32_t i = 0; i < n; ++i)
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src[i]), "r"(bytes[i]) : "memory");
-            };
-            Cursor ld{0, 0, 0, 0, {}, false}, pf{0, 0, 0, 0, {}, false};
-            load_phase(ld);
-            load_phase(pf);
-            for (int i = 0; i < MG_L2_AHEAD && !pf.done; ++i) {
-                if (i >= MG_STAGES) prefetch(pf);// the first MG_STAGES units go straight into the ring
-                advance(pf);
-            }
+            MegaCursor ld{0, 0, 0, 0, {}, false};
+            mega_cursor_seek(a, ld, nphases, NT);
             for (uint32_t it = 0; !ld.done; ++it) {
                 const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
                 if (!mbar_wait(&empty[s], par ^ 1u)) {
@@ -331,18 +343,14 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 uint8_t *st = smem + s * MG_STAGE_BYTES;
                 const uint8_t *src[2];
                 uint32_t bytes[2], dst[2];
-                const uint32_t n = pieces(ld, src, bytes, dst);
+                const uint32_t n = mega_pieces(a, ld, pos, src, bytes, dst);
                 mbar_arrive_expect_tx(&full[s], n == 2 ? bytes[0] + bytes[1] : bytes[0]);
                 for (uint32_t i = 0; i < n; ++i) {
                     if (ld.ph.type == PH_ATT) bulk_g2s(st + dst[i], src[i], bytes[i], &full[s]);
                     else
                         bulk_g2s_hint(st + dst[i], src[i], bytes[i], &full[s], policy);
                 }
-                advance(ld);
-                if (MG_L2_AHEAD > 0 && !pf.done) {
-                    prefetch(pf);
-                    advance(pf);
-                }
+                mega_cursor_advance(a, ld, nphases, NT);
             }
         }
         return;
@@ -356,12 +364,69 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
     unsigned long long best = 0ull;
     float lse_m = -INFINITY, lse_s = 0.f;
 
-    auto grid_barrier = [&]() {
+    // Values of the NEXT phase that do not depend on the phase being finished are fetched between the arrival at a
+    // grid barrier and the wait for it: the RMSNorm weights of a norm-prologue phase, or (before the O projection) the
+    // new token's V row and its score against every head's query (q, K and V of the new token were published by the
+    // barrier before the attention phase).
+    uint4 pre[MG_KCH];
+    auto prework = [&](uint32_t pn) {
+        const uint32_t layer = pn / 5;
+        const int type = layer < a.layers ? static_cast<int>(pn % 5) : PH_LM;
+        if (type == PH_QKV || type == PH_GU || type == PH_LM) {
+            const T *gamma = static_cast<const T *>(type == PH_LM ? a.norm_f : type == PH_QKV ? a.layer[layer].norm1 : a.layer[layer].norm2);
+#pragma unroll
+            for (int c = 0; c < MG_KCH; ++c) {
+                const uint32_t ci = tid + c * MG_CONSUMERS;
+                pre[c] = ci < a.H / 8 ? __ldg(reinterpret_cast<const uint4 *>(gamma + ci * 8)) : make_uint4(0, 0, 0, 0);
+            }
+        } else if (type == PH_O) {
+            const T *qbuf = static_cast<const T *>(ws.q);
+            const uint32_t kvrep = a.nH / a.nKV;
+#pragma unroll
+            for (int c = 0; c < MG_KCH; ++c) {
+                const uint32_t ci = tid + c * MG_CONSUMERS;
+                pre[c] = make_uint4(0, 0, 0, 0);
+                if (ci < a.nH * a.D / 8) {
+                    const uint32_t h = ci * 8 / a.D, d0 = ci * 8 % a.D;
+                    pre[c] = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const T *>(a.layer[layer].vc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D + d0));
+                }
+            }
+            // score of the new token for every head: 8 threads per head
+            for (uint32_t hb = 0; hb < a.nH; hb += MG_CONSUMERS / 8) {
+                const uint32_t h = hb + tid / 8, pt = tid % 8;
+                float d = 0.f;
+                if (h < a.nH) {
+                    const T *kn = static_cast<const T *>(a.layer[layer].kc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D;
+                    // D/8 chunks of 8 elements, 8 threads per head: chunks pt, pt + 8 (both loads in flight together)
+                    uint4 qa = make_uint4(0, 0, 0, 0), ka = qa, qb = qa, kb = qa;
+                    qa = __ldcg(reinterpret_cast<const uint4 *>(qbuf + h * a.D + pt * 8));
+                    ka = __ldcg(reinterpret_cast<const uint4 *>(kn + pt * 8));
+                    if (a.D > 64) {
+                        qb = __ldcg(reinterpret_cast<const uint4 *>(qbuf + h * a.D + 64 + pt * 8));
+                        kb = __ldcg(reinterpret_cast<const uint4 *>(kn + 64 + pt * 8));
+                    }
+                    float qf[8], kf[8];
+                    unpack8<T>(qa, qf), unpack8<T>(ka, kf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
+                    unpack8<T>(qb, qf), unpack8<T>(kb, kf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
+                }
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                if (h < a.nH && pt == 0) sc[h] = d * a.scale;
+            }
+        }
+    };
+    auto grid_barrier = [&](uint32_t pnext) {
         // consumers of this CTA first (bar.sync orders their global writes before thread 0's release), then all CTAs
         mg_consumer_bar();
         ++nbar;
+        if (tid == 0) asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(&hdr->bar), "l"(1ull) : "memory");
+        if (pnext < nphases) prework(pnext);
         if (tid == 0) {
-            asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(&hdr->bar), "l"(1ull) : "memory");
             const unsigned long long target = epoch + static_cast<unsigned long long>(nbar) * G;
             const uint64_t t0 = global_timer_ns();
             for (;;) {
@@ -373,7 +438,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 }
             }
         }
-        mg_consumer_bar();
+        mg_consumer_bar();// also publishes the scores prework wrote to shared memory
         if (*s_fail) ok = false;
         if (blockIdx.x == 0 && tid == 0) ws.timeline[nbar * 4] = global_timer_ns();
     };
@@ -381,6 +446,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
         if (blockIdx.x == 0 && tid == 0) ws.timeline[p * 4 + k] = global_timer_ns();
     };
     stamp(0, 0);
+    prework(0);
 
     for (uint32_t p = 0; p < nphases && ok; ++p) {
         const Phase ph = phase_of(a, p, NT);
@@ -394,87 +460,103 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
 
         if (ph.type == PH_ATT) {
             // ---------------- attention over cached tokens: this CTA = one head, a run of 64-token tiles ----------
-            // Each warp owns 8 tokens of every tile and keeps its own online-softmax state, so a tile needs no CTA-wide
-            // barrier: four lanes per token for q.k (the lane's quarter of q stays in registers), then every lane
-            // accumulates its D/32 output dims over the warp's 8 tokens.
+            // Tiles are taken from the ring two at a time.  Each warp owns 8 tokens of either tile = the 16 rows of one
+            // mma.sync.m16n8k16 whose B operand is the query: row r reads its 32-byte k-chunks in the order s ^ (r % 8)
+            // (no bank conflicts although the rows lie 2*D bytes apart) and column n of B holds the query permuted the
+            // same way, so C[r][r % 8] is the score of row r.  Each warp keeps its own online-softmax state, so a tile
+            // needs no CTA-wide barrier; P.V runs on the FMA pipe, every lane accumulating its D/32 output dims.
             const T *qbuf = static_cast<const T *>(ws.q);
-            const uint32_t D = a.D, qd = lane & 3u, tl = lane >> 2, DPL = D / 4, CPT = DPL / 8, DV = D / 32;
-            const uint32_t swz = D == 128 ? (((tl & 1u) << 1) | (qd >> 1)) : (tl & 1u);
-            float qreg[32];
+            const uint32_t D = a.D, DV = D / 32, NCH = D / 16, gq = lane >> 2, kq = lane & 3u, pg = gq % NCH;
+            const bool own = kq == (gq >> 1);// this lane's c[gq & 1] / c[2 + (gq & 1)] are the scores of rows gq / gq + 8
+            uint32_t qb[8][2];
             float m_w = -INFINITY, l_w = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (nu) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    if (c < static_cast<int>(CPT)) {
-                        float f[8];
-                        unpack8<T>(__ldcg(reinterpret_cast<const uint4 *>(qbuf + att_head * D + qd * DPL + c * 8)), f);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) qreg[c * 8 + e] = f[e];
+                for (int st = 0; st < 8; ++st) {
+                    qb[st][0] = qb[st][1] = 0u;
+                    if (st < static_cast<int>(NCH)) {
+                        const uint32_t ch = static_cast<uint32_t>(st) ^ pg, hs = (NCH == 8 ? ch >> 2 : gq >> 2) & 1u;
+                        const T *qp = qbuf + att_head * D + (ch * 16 + 2 * kq);
+                        qb[st][0] = __ldcg(reinterpret_cast<const uint32_t *>(qp + (hs ? 8 : 0)));
+                        qb[st][1] = __ldcg(reinterpret_cast<const uint32_t *>(qp + (hs ? 0 : 8)));
                     }
                 }
             }
-            for (uint32_t t = u0; t < u1 && ok; ++t, ++it) {
-                const uint32_t s = it % MG_STAGES, par = (it / MG_STAGES) & 1u;
-                if (!mbar_wait(&full[s], par)) {
+            for (uint32_t t = u0; t < u1 && ok;) {
+                const uint32_t nb = u1 - t >= 2 ? 2u : 1u;
+                const uint32_t sA = it % MG_STAGES, sB = (it + 1) % MG_STAGES;
+                if (!mbar_wait(&full[sA], (it / MG_STAGES) & 1u) || (nb == 2 && !mbar_wait(&full[sB], ((it + 1) / MG_STAGES) & 1u))) {
                     ok = false;
                     break;
                 }
-                const uint32_t tok0 = t * MG_TILE, ntok = pos - tok0 < MG_TILE ? pos - tok0 : MG_TILE;
-                const uint8_t *ks = smem + s * MG_STAGE_BYTES, *vs = ks + MG_STAGE_BYTES / 2;
-                const uint32_t tk = warp * 8 + tl;
-                float dot = 0.f;
-                if (tk < ntok) {
+                if (t == u0) stamp(p, 1);// first tiles have landed
+                const uint32_t tokA = t * MG_TILE, ntA = pos - tokA < MG_TILE ? pos - tokA : MG_TILE;
+                const uint32_t tokB = tokA + MG_TILE, ntB = nb == 2 ? (pos - tokB < MG_TILE ? pos - tokB : MG_TILE) : 0u;
+                const uint8_t *ksA = smem + sA * MG_STAGE_BYTES, *ksB = smem + sB * MG_STAGE_BYTES;
+                const uint32_t tk = warp * 8 + gq;// this lane's row in either tile
+                const bool vA = tk < ntA, vB = tk < ntB;
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};// two chains: mma latency, not issue, bounds this
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        if (c < static_cast<int>(CPT)) {
-                            const uint32_t cs = static_cast<uint32_t>(c) ^ swz;
-                            float kf[8];
-                            unpack8<T>(*reinterpret_cast<const uint4 *>(ks + tk * (D * 2) + (qd * CPT + cs) * 16), kf);
-#pragma unroll
-                            for (int cc = 0; cc < 4; ++cc)
-                                if (static_cast<uint32_t>(cc) == cs) {
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e) dot = fmaf(kf[e], qreg[cc * 8 + e], dot);
-                                }
-                        }
+                for (int st = 0; st < 8; ++st) {
+                    if (st < static_cast<int>(NCH)) {
+                        // the two 16-byte halves of a chunk swap roles (in A and in B alike) where that keeps the 32 lanes of
+                        // one load on 32 different banks
+                        const uint32_t ch = static_cast<uint32_t>(st) ^ pg, hs = (NCH == 8 ? ch >> 2 : gq >> 2) & 1u;
+                        const uint32_t off = tk * (D * 2) + ch * 32 + kq * 4, o0 = off + (hs ? 16u : 0u), o1 = off + (hs ? 0u : 16u);
+                        uint32_t af[4];
+                        af[0] = vA ? *reinterpret_cast<const uint32_t *>(ksA + o0) : 0u;
+                        af[2] = vA ? *reinterpret_cast<const uint32_t *>(ksA + o1) : 0u;
+                        af[1] = vB ? *reinterpret_cast<const uint32_t *>(ksB + o0) : 0u;
+                        af[3] = vB ? *reinterpret_cast<const uint32_t *>(ksB + o1) : 0u;
+                        if (st & 1) mma16816<T>(c2, af, qb[st][0], qb[st][1]);
+                        else
+                            mma16816<T>(c, af, qb[st][0], qb[st][1]);
                     }
                 }
-                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                const float sco = tk < ntok ? dot * a.scale : -INFINITY;
-                float mx = sco;
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                const float m_new = fmaxf(m_w, mx);
-                const float pr = (sco == -INFINITY) ? 0.f : expf(sco - m_new);
-                const float corr = (m_w == -INFINITY) ? 0.f : expf(m_w - m_new);
-                l_w = l_w * corr + 0.25f * warp_sum(pr);// every token's probability sits in four lanes
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c[e] += c2[e];
+                const float sa = (own && vA) ? ((gq & 1u) ? c[1] : c[0]) * a.scale : -INFINITY;
+                const float sb = (own && vB) ? ((gq & 1u) ? c[3] : c[2]) * a.scale : -INFINITY;
+                const float m_new = fmaxf(m_w, warp_max(fmaxf(sa, sb)));
+                const float pa = (sa == -INFINITY) ? 0.f : __expf(sa - m_new);
+                const float pb = (sb == -INFINITY) ? 0.f : __expf(sb - m_new);
+                const float corr = (m_w == -INFINITY) ? 0.f : __expf(m_w - m_new);
+                l_w = l_w * corr + warp_sum(pa + pb);
                 m_w = m_new;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[e] *= corr;
+                // P.V: all 16 loads of the warp's rows first (rows past the end of the sequence read as zero: no branch
+                // separates the loads), then the multiply-adds
+                uint2 vraw[16];
 #pragma unroll
-                for (int t8 = 0; t8 < 8; ++t8) {
-                    const float pt = __shfl_sync(0xffffffffu, pr, t8 * 4);
-                    const uint32_t tok = warp * 8 + t8;
-                    if (tok < ntok) {
-                        const T *vr = reinterpret_cast<const T *>(vs + tok * (D * 2)) + lane * DV;
-                        if (DV == 4) {
-                            const uint2 raw = *reinterpret_cast<const uint2 *>(vr);
-                            const T *e4 = reinterpret_cast<const T *>(&raw);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) acc[e] = fmaf(pt, Num<T>::to_f(e4[e]), acc[e]);
-                        } else {
-                            const uint32_t raw = *reinterpret_cast<const uint32_t *>(vr);
-                            const T *e2 = reinterpret_cast<const T *>(&raw);
-                            acc[0] = fmaf(pt, Num<T>::to_f(e2[0]), acc[0]);
-                            acc[1] = fmaf(pt, Num<T>::to_f(e2[1]), acc[1]);
-                        }
+                for (int j = 0; j < 16; ++j) {
+                    const uint8_t *vs = (j < 8 ? ksA : ksB) + MG_STAGE_BYTES / 2;
+                    const uint32_t tok = warp * 8 + (j & 7);
+                    const bool live = tok < (j < 8 ? ntA : ntB);
+                    vraw[j] = make_uint2(0u, 0u);
+                    if (DV == 4) {
+                        if (live) vraw[j] = *reinterpret_cast<const uint2 *>(vs + tok * (D * 2) + lane * 8);
+                    } else {
+                        if (live) vraw[j].x = *reinterpret_cast<const uint32_t *>(vs + tok * (D * 2) + lane * 4);
                     }
                 }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float pt = __shfl_sync(0xffffffffu, j < 8 ? pa : pb, (j & 7) * 4 + (j & 7) / 2);
+                    const float2 lo = unpack2<T>(vraw[j].x), hi = unpack2<T>(vraw[j].y);
+                    acc[0] = fmaf(pt, lo.x, acc[0]);
+                    acc[1] = fmaf(pt, lo.y, acc[1]);
+                    acc[2] = fmaf(pt, hi.x, acc[2]);
+                    acc[3] = fmaf(pt, hi.y, acc[3]);
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
+                if (lane == 0) {
+                    mbar_arrive(&empty[sA]);
+                    if (nb == 2) mbar_arrive(&empty[sB]);
+                }
+                t += nb, it += nb;
             }
+            stamp(p, 2);
             if (ok && nu) {
                 // merge the eight warps' states and write this CTA's record [m, l, -, -, acc[D]]
                 float *wst = part + warp * (D + 2);
@@ -506,7 +588,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 *s_fail = 1;
             }
             stamp(p, 3);
-            grid_barrier();
+            grid_barrier(p + 1);
             continue;
         }
 
@@ -528,37 +610,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 gamma = static_cast<const T *>(a.norm_f);
             }
             if (ph.type == PH_O) {
-                // x = attention output = merge of the partial records + the token produced in this step
-                const T *qbuf = static_cast<const T *>(ws.q);
+                // x = attention output = merge of the partial records + the token produced in this step (its V row is in
+                // pre[], its scores in sc[]: see prework)
                 const uint32_t kvrep = a.nH / a.nKV;
-                // score of the new token for every head: 8 threads per head
-                for (uint32_t hb = 0; hb < a.nH; hb += MG_CONSUMERS / 8) {
-                    const uint32_t h = hb + tid / 8, pt = tid % 8;
-                    float d = 0.f;
-                    if (h < a.nH) {
-                        const T *kn = static_cast<const T *>(a.layer[ph.layer].kc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D;
-                        // D/8 chunks of 8 elements, 8 threads per head: chunks pt, pt + 8 (both loads in flight together)
-                        uint4 qa = make_uint4(0, 0, 0, 0), ka = qa, qb = qa, kb = qa;
-                        qa = __ldcg(reinterpret_cast<const uint4 *>(qbuf + h * a.D + pt * 8));
-                        ka = __ldcg(reinterpret_cast<const uint4 *>(kn + pt * 8));
-                        if (a.D > 64) {
-                            qb = __ldcg(reinterpret_cast<const uint4 *>(qbuf + h * a.D + 64 + pt * 8));
-                            kb = __ldcg(reinterpret_cast<const uint4 *>(kn + 64 + pt * 8));
-                        }
-                        float qf[8], kf[8];
-                        unpack8<T>(qa, qf), unpack8<T>(ka, kf);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
-                        unpack8<T>(qb, qf), unpack8<T>(kb, kf);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
-                    }
-                    d += __shfl_xor_sync(0xffffffffu, d, 1);
-                    d += __shfl_xor_sync(0xffffffffu, d, 2);
-                    d += __shfl_xor_sync(0xffffffffu, d, 4);
-                    if (h < a.nH && pt == 0) sc[h] = d * a.scale;
-                }
-                mg_consumer_bar();
+                (void) kvrep;
                 const uint32_t splits = att_splits(G, a.nH);
 #pragma unroll
                 for (int c = 0; c < MG_KCH; ++c) {
@@ -567,11 +622,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                     for (int j = 0; j < 8; ++j) x[c][j] = 0.f;
                     if (ci < kchunks) {
                         const uint32_t h = ci * 8 / a.D, d0 = ci * 8 % a.D;
-                        const T *vn = static_cast<const T *>(a.layer[ph.layer].vc) + (static_cast<size_t>(h / kvrep) * a.max_seq + pos) * a.D + d0;
                         // start from the token produced in this step, then fold in the records of head h (CTAs
                         // h*splits + j whose tile range is not empty) four at a time, rescaling to the running maximum
                         float vnf[8];
-                        unpack8<T>(__ldcg(reinterpret_cast<const uint4 *>(vn)), vnf);
+                        unpack8<T>(pre[c], vnf);
                         float mx = sc[h], den = 1.f;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) x[c][j] = vnf[j];
@@ -615,7 +669,6 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                         for (int j = 0; j < 8; ++j) x[c][j] = Num<T>::to_f(Num<T>::from_f(x[c][j] * inv));
                     }
                 }
-                mg_consumer_bar();// sc[] free again
             } else {
                 float ss = 0.f;
 #pragma unroll
@@ -644,7 +697,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                         const uint32_t ci = tid + c * MG_CONSUMERS;
                         if (ci < kchunks) {
                             float gw[8];
-                            unpack8<T>(*reinterpret_cast<const uint4 *>(gamma + ci * 8), gw);
+                            unpack8<T>(pre[c], gw);
 #pragma unroll
                             for (int j = 0; j < 8; ++j) x[c][j] *= rstd * gw[j];
                         }
@@ -773,7 +826,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             }
         }
         stamp(p, 3);
-        grid_barrier();
+        grid_barrier(p + 1);
     }
 
     // ================= finish: next token, probability, state =================

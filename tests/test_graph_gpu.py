@@ -123,12 +123,16 @@ def test_reference_attention_operator_with_inplace_cache():
 @pytest.mark.parametrize("shape", [dict(heads=4, kv_heads=2, head_dim=128, hidden=512, ffn=1024, vocab=2000, past=70),
                                    dict(heads=8, kv_heads=8, head_dim=128, hidden=1024, ffn=2752, vocab=32000, past=700),
                                    dict(heads=4, kv_heads=4, head_dim=64, hidden=256, ffn=688, vocab=1000, past=0),
-                                   dict(heads=4, kv_heads=1, head_dim=128, hidden=512, ffn=1024, vocab=777, past=64)])
+                                   dict(heads=4, kv_heads=1, head_dim=128, hidden=512, ffn=1024, vocab=777, past=64),
+                                   # three cached tiles per CTA: one pair and one single tile per attention pass
+                                   dict(heads=4, kv_heads=2, head_dim=128, hidden=512, ffn=1024, vocab=2000, past=1500, max_seq=2048),
+                                   dict(heads=4, kv_heads=2, head_dim=64, hidden=256, ffn=688, vocab=1000, past=1100, max_seq=2048)])
 def test_single_kernel_decode_step(shape):
     """b200::DecodeStep (the whole step in one persistent kernel) against the numpy oracle and the multi-kernel graph."""
     from refactorgraph_b200 import capi
+    shape = dict(shape)
     past0 = shape.pop("past")
-    cfg = LlamaConfig(layers=3, max_seq=1024, batch=1, **shape)
+    cfg = LlamaConfig(layers=3, max_seq=shape.pop("max_seq", 1024), batch=1, **shape)
     w16 = seeded_weights(cfg, 0, np.float16)
     rng = np.random.default_rng(1)
     w16["lm_head"] = (0.1 * rng.standard_normal(w16["lm_head"].shape)).astype(np.float16)   # spread enough to avoid fp16 arg-max ties
