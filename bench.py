@@ -47,8 +47,8 @@ def parse_args():
     ap.add_argument("--graph", default="single", choices=["single", "fused"],
                     help="7b / tiny workloads: 'single' = the whole step as one persistent kernel (b200::DecodeStep); "
                          "'fused' = five fused launches per layer replayed as a CUDA graph")
-    ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
-                             "gemm_skinny16", "gemm_skinny32", "decode_step_timeline"],
+    ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "attn_decode_b32", "attn_decode_gqa", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
+                             "gemm_skinny16", "gemm_skinny32", "gemm_tp8", "decode_step_timeline"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
     ap.add_argument("--launches", type=int, default=6)
     return ap.parse_args()
@@ -381,12 +381,50 @@ def run_decode_step_timeline():
     print(json.dumps(out), flush=True)
 
 
+def run_gemm_tp8(args):
+    """The four matrix products one rank runs per layer of the 70B-shaped model at tensor-parallel 8 (16 tokens, fp16),
+    each timed alone over weight buffers that together exceed L2."""
+    import torch
+    from refactorgraph_b200 import capi
+    torch.cuda.set_device(0)
+    capi.load()
+    dev, dt, m = "cuda", torch.float16, 16
+    sid = torch.cuda.current_stream().cuda_stream
+    out = {"case": "gemm_tp8", "launches": args.launches, "products": {}}
+    for name, n, k in (("qkv", 1280, 8192), ("o", 8192, 1024), ("gate_up", 7168, 8192), ("down", 8192, 3584)):
+        nb = max(2, int(400e6 // (n * k * 2)))
+        As = [torch.randn(m, k, device=dev).to(dt) for _ in range(2)]
+        Bs = [(0.02 * torch.randn(n, k, device=dev)).to(dt) for _ in range(nb)]
+        y = torch.empty(m, n, dtype=dt, device=dev)
+        p = capi.MatMulParams()
+        p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y, p.force_kernel = capi.FP16, m, n, k, 1, 1.0, 0.0, 1, m * n, 0
+        nws = capi.workspace("mat_mul", p)
+        wsb = torch.zeros(max(nws, 1), dtype=torch.uint8, device=dev)
+
+        def launch(i):
+            capi.call("mat_mul", p, [As[i % 2].data_ptr(), Bs[i % nb].data_ptr(), 0], [y.data_ptr()], ws=wsb.data_ptr() if nws else 0, stream=sid)
+        for i in range(3):
+            launch(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.launches):
+            launch(i)
+        e1.record()
+        torch.cuda.synchronize()
+        us = 1000.0 * e0.elapsed_time(e1) / args.launches
+        out["products"][name] = {"n": n, "k": k, "us": round(us, 2), "gbs": round(n * k * 2 / us / 1e3)}
+    print(json.dumps(out), flush=True)
+
+
 def run_case(args):
     """One kernel alone at its Llama-7B decode shape, inputs rotated over buffers larger than L2 in total."""
     import torch
     from refactorgraph_b200 import capi
     if args.case == "decode_step_timeline":
         return run_decode_step_timeline()
+    if args.case == "gemm_tp8":
+        return run_gemm_tp8(args)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     torch.cuda.set_device(0)
     capi.load()
@@ -439,6 +477,38 @@ def run_case(args):
         p = capi.AttnDecodeParams(capi.FP16, 1, nH, MS, capi.KvLayout(nH, D, MS, 0, 0))
         wsb = torch.zeros(capi.workspace("attn_decode", p), dtype=torch.uint8, device=dev)
         bytes_per = 2 * nH * L * D * 2
+
+        def launch(i):
+            kc, vc = caches[i % len(caches)]
+            capi.call("attn_decode", p, [q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), 0], [o.data_ptr()], ws=wsb.data_ptr(), stream=sid)
+    elif args.case == "attn_decode_b32":
+        # the attention launch of the batch-32 workload: 32 sequences, lengths uniform[512, 4096], 16-token pages
+        B, page, MS = 32, 16, 4096 + 128
+        lens_h = np.random.default_rng(0).integers(512, 4097, (B,)).astype(np.int64)
+        max_blocks = MS // page
+        n_blocks = B * max_blocks
+        table = torch.from_numpy(np.random.default_rng(1).permutation(n_blocks).reshape(B, max_blocks).astype(np.int32)).to(dev)
+        q = torch.randn(B, nH, D, device=dev).to(dt)
+        caches = [(torch.randn(n_blocks, nH, page, D, device=dev).to(dt), torch.randn(n_blocks, nH, page, D, device=dev).to(dt)) for _ in range(2)]
+        lens = torch.from_numpy(lens_h).to(dev)
+        o = torch.empty_like(q)
+        p = capi.AttnDecodeParams(capi.FP16, B, nH, MS, capi.KvLayout(nH, D, MS, page, max_blocks))
+        wsb = torch.zeros(capi.workspace("attn_decode", p), dtype=torch.uint8, device=dev)
+        bytes_per = 2 * nH * int(lens_h.sum()) * D * 2
+
+        def launch(i):
+            kc, vc = caches[i % len(caches)]
+            capi.call("attn_decode", p, [q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), table.data_ptr()], [o.data_ptr()], ws=wsb.data_ptr(), stream=sid)
+    elif args.case == "attn_decode_gqa":
+        # one rank's attention launch of the 70B-shaped model at tensor-parallel 8: 16 sequences x 4096 tokens, 8 query heads on 1 KV head
+        B, L, MS, nq, nkv = 16, 4096, 4096 + 128, 8, 1
+        q = torch.randn(B, nq, D, device=dev).to(dt)
+        caches = [(torch.randn(B, nkv, MS, D, device=dev).to(dt), torch.randn(B, nkv, MS, D, device=dev).to(dt)) for _ in range(8)]
+        lens = torch.full((B,), L, device=dev, dtype=torch.int64)
+        o = torch.empty_like(q)
+        p = capi.AttnDecodeParams(capi.FP16, B, nq, MS, capi.KvLayout(nkv, D, MS, 0, 0))
+        wsb = torch.zeros(capi.workspace("attn_decode", p), dtype=torch.uint8, device=dev)
+        bytes_per = 2 * nkv * B * L * D * 2
 
         def launch(i):
             kc, vc = caches[i % len(caches)]

@@ -57,6 +57,7 @@ __device__ __forceinline__ float ar_combine(int op, float a, float b) {
 
 template<class T>
 __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) {
+    pdl_enter();
     constexpr int N = Vec16<T>::N;
     ArHeader *hdr = reinterpret_cast<ArHeader *>(a.mine);
     unsigned long long *my_flags = reinterpret_cast<unsigned long long *>(a.mine + AR_HEADER_BYTES);
@@ -286,9 +287,9 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
     if (grid > 128) grid = 128;
     auto st = static_cast<cudaStream_t>(stream);
     switch (p->dtype) {
-        case RG_F32: all_reduce_kernel<float><<<static_cast<unsigned>(grid), AR_THREADS, 0, st>>>(a); break;
-        case RG_FP16: all_reduce_kernel<__half><<<static_cast<unsigned>(grid), AR_THREADS, 0, st>>>(a); break;
-        default: all_reduce_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), AR_THREADS, 0, st>>>(a); break;
+        case RG_F32: launch_pdl(all_reduce_kernel<float>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
+        case RG_FP16: launch_pdl(all_reduce_kernel<__half>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
+        default: launch_pdl(all_reduce_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
     }
     count_launch();
     return launch_status();

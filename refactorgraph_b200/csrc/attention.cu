@@ -200,16 +200,24 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
     if (!s_last) return;
     __threadfence();
     if (tid < D) {
+        // whole warps (D is 64 or 128): a lane reads one record header per round, so all headers cost one round trip to
+        // L2; the accumulator loads of different splits are independent and unrolled
+        const float *base = a.part + rec * (D + 2);
         float mx = -INFINITY;
-        for (uint32_t sidx = 0; sidx < nsplit; ++sidx) mx = fmaxf(mx, __ldcg(a.part + (rec + sidx) * (D + 2)));
+        for (uint32_t s0 = 0; s0 < nsplit; s0 += 32)
+            if (s0 + lane < nsplit) mx = fmaxf(mx, __ldcg(base + static_cast<size_t>(s0 + lane) * (D + 2)));
+        mx = warp_max(mx);
         float num = 0.f, den = 0.f;
-        for (uint32_t sidx = 0; sidx < nsplit; ++sidx) {
-            const float *r = a.part + (rec + sidx) * (D + 2);
-            const float w = expf(__ldcg(r) - mx);
-            den += __ldcg(r + 1) * w;
-            num += __ldcg(r + 2 + tid) * w;
+        for (uint32_t s0 = 0; s0 < nsplit; s0 += 32) {
+            float2 ml = make_float2(-INFINITY, 0.f);
+            if (s0 + lane < nsplit) ml = __ldcg(reinterpret_cast<const float2 *>(base + static_cast<size_t>(s0 + lane) * (D + 2)));
+            const float w = ml.x == -INFINITY ? 0.f : expf(ml.x - mx);
+            den += ml.y * w;
+            const uint32_t cnt = nsplit - s0 < 32 ? nsplit - s0 : 32;
+#pragma unroll 8
+            for (uint32_t j = 0; j < cnt; ++j) num += __ldcg(base + static_cast<size_t>(s0 + j) * (D + 2) + 2 + tid) * __shfl_sync(0xffffffffu, w, j);
         }
-        o[tid] = Num<T>::from_f(num / den);
+        o[tid] = Num<T>::from_f(num / warp_sum(den));
     }
     if (tid == 0) a.cnt[static_cast<size_t>(b) * a.n_heads + h] = 0u;
 }

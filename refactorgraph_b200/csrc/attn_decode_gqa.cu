@@ -12,6 +12,7 @@
 namespace rg {
 
 constexpr int GQ_THREADS = 128, GQ_TILE = 64, GQ_D = 128;
+constexpr int GQ_REC = GQ_D + 4;// floats per split record: max, sum, 2 pad, accumulator (16-byte aligned)
 
 struct GqaArgs {
     const void *q, *kc, *vc;
@@ -228,8 +229,8 @@ __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaAr
         if (nsplit == 1) {
             O[r * GQ_D + threadIdx.x] = Num<T>::from_f(acc / L);
         } else {
-            float *rec = a.part + (rec0 + static_cast<size_t>(r) * a.max_splits + split) * (GQ_D + 2);
-            rec[2 + threadIdx.x] = acc;
+            float *rec = a.part + (rec0 + static_cast<size_t>(r) * a.max_splits + split) * GQ_REC;
+            rec[4 + threadIdx.x] = acc;
             if (threadIdx.x == 0) rec[0] = M, rec[1] = L;
         }
     }
@@ -240,18 +241,33 @@ __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaAr
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (uint32_t r = 0; r < gq; ++r) {
-        const float *base = a.part + (rec0 + static_cast<size_t>(r) * a.max_splits) * (GQ_D + 2);
+    // The last CTA of the group merges the records: warp w takes heads w, w + 4, ...; a lane reads one record header per
+    // round (all headers in one round trip), then owns four output dims and streams the records with independent
+    // 16-byte loads (a dependent chain of loads here costs a round trip to L2 per split).
+    for (uint32_t r = warp; r < gq; r += GQ_THREADS / 32) {
+        const float *base = a.part + (rec0 + static_cast<size_t>(r) * a.max_splits) * GQ_REC;
         float M = -INFINITY;
-        for (uint32_t sidx = 0; sidx < nsplit; ++sidx) M = fmaxf(M, __ldcg(base + static_cast<size_t>(sidx) * (GQ_D + 2)));
-        float num = 0.f, den = 0.f;
-        for (uint32_t sidx = 0; sidx < nsplit; ++sidx) {
-            const float *rec = base + static_cast<size_t>(sidx) * (GQ_D + 2);
-            const float w = exp2f(__ldcg(rec) - M);
-            den += __ldcg(rec + 1) * w;
-            num += __ldcg(rec + 2 + threadIdx.x) * w;
+        for (uint32_t s0 = 0; s0 < nsplit; s0 += 32)
+            if (s0 + lane < nsplit) M = fmaxf(M, __ldcg(base + static_cast<size_t>(s0 + lane) * GQ_REC));
+        M = warp_max(M);
+        float den = 0.f;
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s0 = 0; s0 < nsplit; s0 += 32) {
+            float2 ml = make_float2(-INFINITY, 0.f);
+            if (s0 + lane < nsplit) ml = __ldcg(reinterpret_cast<const float2 *>(base + static_cast<size_t>(s0 + lane) * GQ_REC));
+            const float w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+            den += ml.y * w;
+            const uint32_t cnt = nsplit - s0 < 32 ? nsplit - s0 : 32;
+#pragma unroll 8
+            for (uint32_t j = 0; j < cnt; ++j) {
+                const float wj = __shfl_sync(0xffffffffu, w, j);
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(base + static_cast<size_t>(s0 + j) * GQ_REC + 4 + lane * 4));
+                num.x += v.x * wj, num.y += v.y * wj, num.z += v.z * wj, num.w += v.w * wj;
+            }
         }
-        O[r * GQ_D + threadIdx.x] = Num<T>::from_f(num / den);
+        const float inv = 1.f / warp_sum(den);
+        T ov[4] = {Num<T>::from_f(num.x * inv), Num<T>::from_f(num.y * inv), Num<T>::from_f(num.z * inv), Num<T>::from_f(num.w * inv)};
+        *reinterpret_cast<uint2 *>(O + r * GQ_D + lane * 4) = *reinterpret_cast<const uint2 *>(ov);
     }
     if (threadIdx.x == 0) a.cnt[static_cast<size_t>(b) * nkv + kvh] = 0u;
 }
@@ -270,14 +286,15 @@ static GqaPlan gqa_plan(const rg_attn_decode_params *p) {
     pl.tiles_per_split = total_tiles ? (total_tiles + want - 1) / want : 1;
     pl.max_splits = total_tiles ? (total_tiles + pl.tiles_per_split - 1) / pl.tiles_per_split : 1;
     pl.cnt_bytes = (groups * 4 + 255) / 256 * 256;
-    pl.part_bytes = static_cast<size_t>(p->batch) * p->n_heads * pl.max_splits * (GQ_D + 2) * 4;
+    pl.part_bytes = static_cast<size_t>(p->batch) * p->n_heads * pl.max_splits * GQ_REC * 4;
     return pl;
 }
 
 bool attn_decode_gqa_applies(const rg_attn_decode_params *p) {
     if (p->kv.head_dim != GQ_D || p->kv.n_kv_heads == 0) return false;
     const uint32_t gq = p->n_heads / p->kv.n_kv_heads;
-    return gq >= 2 && gq <= 16 && (p->dtype == RG_FP16 || p->dtype == RG_BF16);
+    static const uint32_t gq_min = getenv("RG_B200_GQA_MIN") ? static_cast<uint32_t>(atoi(getenv("RG_B200_GQA_MIN"))) : 2u;
+    return gq >= gq_min && gq <= 16 && (p->dtype == RG_FP16 || p->dtype == RG_BF16);
 }
 size_t attn_decode_gqa_workspace(const rg_attn_decode_params *p) {
     const GqaPlan pl = gqa_plan(p);

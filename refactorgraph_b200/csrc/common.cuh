@@ -6,6 +6,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <cstdlib>
+#include <utility>
 
 namespace rg {
 
@@ -192,6 +194,33 @@ __device__ __forceinline__ void bulk_g2s_hint(void *dst, const void *src, uint32
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// First statement of a kernel launched through launch_pdl: lets the next kernel of the stream be scheduled, then waits
+// until the previous one has completed and its writes are visible.  Everything before the call overlaps the predecessor.
+__device__ __forceinline__ void pdl_enter() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+// RG_B200_PDL=0 turns programmatic dependent launch off (every kernel then waits for its predecessor to drain).
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("RG_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+// Launch with the programmatic-stream-serialization attribute: the kernel may start while its predecessor in the stream is
+// still running and must call pdl_enter() (or pdl_wait()) before it touches anything the predecessor wrote.
+template<class... K, class... A>
+inline cudaError_t launch_pdl(void (*kern)(K...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<A>(args)...);
 }
 
 }// namespace rg

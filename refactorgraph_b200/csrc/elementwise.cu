@@ -16,6 +16,7 @@ static unsigned grid_for(size_t work_items, unsigned threads) {
 template<class U, class I>
 __global__ void gather_kernel(const U *__restrict__ data, const I *__restrict__ idx, U *__restrict__ out,
                               uint32_t prefix, uint32_t mid_in, uint32_t mid_out, uint64_t units) {
+    pdl_enter();
     const uint64_t total = static_cast<uint64_t>(prefix) * mid_out * units;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
          t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
@@ -34,7 +35,7 @@ static int gather_launch(const rg_gather_params *p, const void *const *in, void 
     const uint64_t rows = static_cast<uint64_t>(p->prefix) * p->mid_out;
     auto idx = static_cast<const I *>(in[1]);
 #define RG_GATHER(U)                                                                                      \
-    gather_kernel<U, I><<<grid_for(rows * (pb / sizeof(U)), 256), 256, 0, st>>>(                          \
+    launch_pdl(gather_kernel<U, I>, dim3(grid_for(rows * (pb / sizeof(U)), 256)), dim3(256), 0, st,                           \
         static_cast<const U *>(in[0]), idx, static_cast<U *>(out[0]), p->prefix, p->mid_in, p->mid_out,   \
         pb / sizeof(U))
     if (v16) RG_GATHER(uint4);
@@ -200,6 +201,7 @@ __global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t 
                                        const int32_t *__restrict__ table, T *__restrict__ q, T *__restrict__ kc,
                                        T *__restrict__ vc, uint32_t tokens, uint32_t nq, rg_kv_layout kv, float log2_theta,
                                        uint32_t tokens_per_seq) {
+    pdl_enter();
     const uint32_t D = kv.head_dim, half = D / 2, nkv = kv.n_kv_heads, heads = nq + 2 * nkv;
     const uint64_t total = static_cast<uint64_t>(tokens) * heads * half;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
@@ -243,6 +245,7 @@ __global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t 
 // y[r, j] = silu(x[r, j]) * x[r, f + j]
 template<class T>
 __global__ void swiglu_kernel(const T *__restrict__ x, T *__restrict__ y, uint32_t rows, uint32_t f) {
+    pdl_enter();
     const uint64_t total = static_cast<uint64_t>(rows) * f;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
          t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
@@ -254,6 +257,7 @@ __global__ void swiglu_kernel(const T *__restrict__ x, T *__restrict__ y, uint32
 
 __global__ void state_update_kernel(const int64_t *__restrict__ src, int64_t *__restrict__ state, uint32_t n,
                                     int64_t delta) {
+    pdl_enter();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) state[i] = (src ? src[i] : state[i]) + delta;
 }
@@ -400,7 +404,7 @@ size_t rg_b200_state_update_workspace(const rg_state_update_params *) { return 0
 int rg_b200_state_update(const rg_state_update_params *p, void *, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out || !out[0]) return RG_ERR_NULL;
     if (p->n == 0) return RG_OK;
-    state_update_kernel<<<(p->n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(state_update_kernel, dim3((p->n + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), 
         static_cast<const int64_t *>(in[0]), static_cast<int64_t *>(out[0]), p->n, p->delta);
     count_launch();
     return launch_status();
@@ -419,7 +423,7 @@ int rg_b200_qkv_rope_append(const rg_qkv_rope_append_params *p, void *, const vo
     const float l2t = log2f(p->theta);
     auto pos = static_cast<const int64_t *>(in[1]);
     auto tab = static_cast<const int32_t *>(in[2]);
-#define RG_QRA(T) qkv_rope_append_kernel<T><<<g, 256, 0, st>>>(static_cast<const T *>(in[0]), pos, tab, static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t, p->tokens_per_seq)
+#define RG_QRA(T) launch_pdl(qkv_rope_append_kernel<T>, dim3(g), dim3(256), 0, st, static_cast<const T *>(in[0]), pos, tab, static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t, p->tokens_per_seq)
     switch (p->dtype) {
         case RG_F32: RG_QRA(float); break;
         case RG_FP16: RG_QRA(__half); break;
@@ -439,9 +443,9 @@ int rg_b200_swiglu(const rg_swiglu_params *p, void *, const void *const *in, voi
     auto st = static_cast<cudaStream_t>(stream);
     const unsigned g = grid_for(total, 256);
     switch (p->dtype) {
-        case RG_F32: swiglu_kernel<float><<<g, 256, 0, st>>>(static_cast<const float *>(in[0]), static_cast<float *>(out[0]), p->rows, p->f); break;
-        case RG_FP16: swiglu_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half *>(in[0]), static_cast<__half *>(out[0]), p->rows, p->f); break;
-        case RG_BF16: swiglu_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(in[0]), static_cast<__nv_bfloat16 *>(out[0]), p->rows, p->f); break;
+        case RG_F32: launch_pdl(swiglu_kernel<float>, dim3(g), dim3(256), 0, st, static_cast<const float *>(in[0]), static_cast<float *>(out[0]), p->rows, p->f); break;
+        case RG_FP16: launch_pdl(swiglu_kernel<__half>, dim3(g), dim3(256), 0, st, static_cast<const __half *>(in[0]), static_cast<__half *>(out[0]), p->rows, p->f); break;
+        case RG_BF16: launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, st, static_cast<const __nv_bfloat16 *>(in[0]), static_cast<__nv_bfloat16 *>(out[0]), p->rows, p->f); break;
         default: return RG_ERR_DTYPE;
     }
     count_launch();

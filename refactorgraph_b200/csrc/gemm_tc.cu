@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_enter();// barriers, tensor memory and descriptors are set up while the previous kernel of the stream drains
 
     if (warp == 4) {
         if (lane == 0) {
@@ -445,7 +446,7 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs 
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const uint32_t items = ((a.n + BN - 1) / BN) * ((a.m + TC_BM - 1) / TC_BM) * a.splits;
     const uint32_t sms = static_cast<uint32_t>(sm_count());
-    kern<<<items < sms ? items : sms, TC_THREADS, smem, st>>>(ma, mb, a);
+    RG_CHECK_CUDA(launch_pdl(kern, dim3(items < sms ? items : sms), dim3(TC_THREADS), smem, st, ma, mb, a));
     count_launch();
     return launch_status();
 }

@@ -280,15 +280,6 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const LinearA
 }
 
 // ---- host ---------------------------------------------------------------------------------------
-static bool pdl_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = std::getenv("RG_B200_PDL");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
-}
-
 template<class Kern>
 static int launch_stream_kernel(Kern kern, const LinearArgs &a, unsigned grid, size_t smem, cudaStream_t st) {
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

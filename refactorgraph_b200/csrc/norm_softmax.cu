@@ -13,6 +13,7 @@ template<class T, int CH, bool RES>
 __global__ void __launch_bounds__(256) rms_norm_vec_kernel(const T *__restrict__ x, const T *__restrict__ w,
                                                            const T *__restrict__ r, T *__restrict__ y,
                                                            T *__restrict__ s, uint32_t dim, float eps) {
+    pdl_enter();
     constexpr int N = Vec16<T>::N;
     __shared__ float red[33];
     const size_t row = blockIdx.x;
@@ -65,6 +66,7 @@ __global__ void __launch_bounds__(256) rms_norm_vec_kernel(const T *__restrict__
 template<class T, bool RES>
 __global__ void rms_norm_scalar_kernel(const T *__restrict__ x, const T *__restrict__ w, const T *__restrict__ r,
                                        T *__restrict__ y, T *__restrict__ s, uint32_t dim, float eps) {
+    pdl_enter();
     __shared__ float red[33];
     const size_t row = blockIdx.x;
     float ss = 0.f;
@@ -103,14 +105,14 @@ static int rms_norm_launch(const rg_rms_norm_params *p, const void *const *in, v
         if (threads > 256) threads = 256;
         if (threads < 32) threads = 32;
         switch (ch) {
-            case 1: rms_norm_vec_kernel<T, 1, RES><<<p->rows, threads, 0, st>>>(x, w, r, y, s, p->dim, p->epsilon); break;
-            case 2: rms_norm_vec_kernel<T, 2, RES><<<p->rows, threads, 0, st>>>(x, w, r, y, s, p->dim, p->epsilon); break;
-            case 4: rms_norm_vec_kernel<T, 4, RES><<<p->rows, threads, 0, st>>>(x, w, r, y, s, p->dim, p->epsilon); break;
-            default: rms_norm_vec_kernel<T, 8, RES><<<p->rows, threads, 0, st>>>(x, w, r, y, s, p->dim, p->epsilon); break;
+            case 1: launch_pdl(rms_norm_vec_kernel<T, 1, RES>, dim3(p->rows), dim3(threads), 0, st, x, w, r, y, s, p->dim, p->epsilon); break;
+            case 2: launch_pdl(rms_norm_vec_kernel<T, 2, RES>, dim3(p->rows), dim3(threads), 0, st, x, w, r, y, s, p->dim, p->epsilon); break;
+            case 4: launch_pdl(rms_norm_vec_kernel<T, 4, RES>, dim3(p->rows), dim3(threads), 0, st, x, w, r, y, s, p->dim, p->epsilon); break;
+            default: launch_pdl(rms_norm_vec_kernel<T, 8, RES>, dim3(p->rows), dim3(threads), 0, st, x, w, r, y, s, p->dim, p->epsilon); break;
         }
     } else {
         uint32_t threads = p->dim >= 1024 ? 256 : ((p->dim + 31) / 32 * 32 > 256 ? 256 : (p->dim + 31) / 32 * 32);
-        rms_norm_scalar_kernel<T, RES><<<p->rows, threads, 0, st>>>(x, w, r, y, s, p->dim, p->epsilon);
+        launch_pdl(rms_norm_scalar_kernel<T, RES>, dim3(p->rows), dim3(threads), 0, st, x, w, r, y, s, p->dim, p->epsilon);
     }
     count_launch();
     return launch_status();

@@ -138,6 +138,7 @@ template<class T, bool SOFTMAX>
 __global__ void __launch_bounds__(TOPK_THREADS) topk_kernel(const T *__restrict__ x, void *__restrict__ values,
                                                             int64_t *__restrict__ indices, uint32_t n, uint32_t k,
                                                             int staged) {
+    pdl_enter();
     extern __shared__ __align__(16) uint32_t skeys[];
     __shared__ TopkShared sh;
     const T *xr = x + static_cast<size_t>(blockIdx.x) * n;
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_sample_kernel(const T *__re
                                                                    const uint64_t *__restrict__ step,
                                                                    int64_t *__restrict__ token, uint32_t n, uint32_t k,
                                                                    float inv_temp, uint64_t seed, int staged) {
+    pdl_enter();
     extern __shared__ __align__(16) uint32_t skeys[];
     __shared__ TopkShared sh;
     const T *xr = x + static_cast<size_t>(blockIdx.x) * n;
@@ -223,10 +225,10 @@ static int topk_launch(const rg_topk_params *p, const void *const *in, void *con
     auto idx = static_cast<int64_t *>(out[1]);
     if (p->softmax) {
         RG_CHECK_CUDA(cudaFuncSetAttribute(topk_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 163840));
-        topk_kernel<T, true><<<p->rows, topk_threads(p->n), smem, st>>>(x, out[0], idx, p->n, p->k, staged);
+        launch_pdl(topk_kernel<T, true>, dim3(p->rows), dim3(topk_threads(p->n)), smem, st, x, out[0], idx, p->n, p->k, staged);
     } else {
         RG_CHECK_CUDA(cudaFuncSetAttribute(topk_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 163840));
-        topk_kernel<T, false><<<p->rows, topk_threads(p->n), smem, st>>>(x, out[0], idx, p->n, p->k, staged);
+        launch_pdl(topk_kernel<T, false>, dim3(p->rows), dim3(topk_threads(p->n)), smem, st, x, out[0], idx, p->n, p->k, staged);
     }
     count_launch();
     return launch_status();
@@ -237,7 +239,7 @@ static int topk_sample_launch(const rg_topk_sample_params *p, const void *const 
     const int staged = p->n <= TOPK_STAGE_MAX;
     const size_t smem = staged ? static_cast<size_t>(p->n) * 4 : 0;
     RG_CHECK_CUDA(cudaFuncSetAttribute(topk_sample_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 163840));
-    topk_sample_kernel<T><<<p->rows, topk_threads(p->n), smem, st>>>(
+    launch_pdl(topk_sample_kernel<T>, dim3(p->rows), dim3(topk_threads(p->n)), smem, st, 
         static_cast<const T *>(in[0]), static_cast<const uint64_t *>(in[1]), static_cast<int64_t *>(out[0]), p->n, p->k,
         1.0f / p->temperature, p->seed, staged);
     count_launch();
