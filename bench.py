@@ -48,7 +48,7 @@ def parse_args():
                     help="7b / tiny workloads: 'single' = the whole step as one persistent kernel (b200::DecodeStep); "
                          "'fused' = five fused launches per layer replayed as a CUDA graph")
     ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "attn_decode_b32", "attn_decode_gqa", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
-                             "gemm_skinny16", "gemm_skinny32", "gemm_tp8", "decode_step_timeline"],
+                             "gemm_skinny16", "gemm_skinny32", "gemm_tp8", "all_reduce", "decode_step_timeline"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
     ap.add_argument("--launches", type=int, default=6)
     return ap.parse_args()
@@ -381,6 +381,44 @@ def run_decode_step_timeline():
     print(json.dumps(out), flush=True)
 
 
+def run_all_reduce_case(args, torch, dist, rank, world):
+    """The all-reduce of the tensor-parallel step alone (16 tokens x 8192, fp16, residual add fused), `--launches` calls
+    back to back on every rank: device time per call, max over ranks."""
+    from refactorgraph_b200 import capi
+    count = 16 * 8192
+
+    def exchange(handle):
+        out = [None] * world
+        dist.all_gather_object(out, handle)
+        return out
+    comm = capi.Comm(world, rank, count * 2, exchange=exchange if world > 1 else None)
+    x = torch.randn(count, device="cuda").to(torch.float16)
+    r = torch.randn(count, device="cuda").to(torch.float16)
+    y = torch.empty_like(x)
+    sid = torch.cuda.current_stream().cuda_stream
+    for _ in range(5):
+        comm.all_reduce(capi.FP16, 0, count, x.data_ptr(), y.data_ptr(), r.data_ptr(), stream=sid)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.launches):
+        comm.all_reduce(capi.FP16, 0, count, x.data_ptr(), y.data_ptr(), r.data_ptr(), stream=sid)
+    e1.record()
+    torch.cuda.synchronize()
+    us = torch.tensor([1000.0 * e0.elapsed_time(e1) / args.launches], device="cuda")
+    if world > 1:
+        dist.all_reduce(us, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps({"case": "all_reduce", "n_gpus": world, "count": count, "launches": args.launches, "us_per_call": round(float(us.item()), 2),
+                          "comm_status": comm.status()}), flush=True)
+    if world > 1:
+        dist.barrier()
+    comm.destroy()
+
+
 def run_gemm_tp8(args):
     """The four matrix products one rank runs per layer of the 70B-shaped model at tensor-parallel 8 (16 tokens, fp16),
     each timed alone over weight buffers that together exceed L2."""
@@ -700,6 +738,8 @@ def run_b200(args):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = capi.load()
+    if args.case == "all_reduce":
+        return run_all_reduce_case(args, torch, dist, rank, world)
     if args.workload == "7b-prefill":
         return run_prefill(args, torch, dist, lib, rank, world, local)
     tp = args.workload == "70b-tp"
@@ -851,7 +891,7 @@ def run_b200(args):
 
 def main():
     args = parse_args()
-    if args.case:
+    if args.case and args.case != "all_reduce":   # all_reduce needs the process group: run_b200 dispatches it
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)

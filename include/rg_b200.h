@@ -381,7 +381,7 @@ int rg_b200_attn_decode_static(const rg_attn_decode_params *, const void *const 
  * (src/04kernel/src/kernels/all_reduce/nccl_kernel.cu:9-19, src/04kernel/src/utilities/cuda/nccl_communicator.cu:11-44).
  * One process per GPU.  rg_b200_comm_create allocates this rank's symmetric buffer and returns an opaque
  * 64-byte IPC handle; the caller exchanges handles out of band (any host transport) and calls
- * rg_b200_comm_connect with all ranks' handles.  The reduction is a one-shot pull over NVLink peer memory
+ * rg_b200_comm_connect with all ranks' handles.  The reduction is a one-shot push over NVLink peer memory
  * with plain loads, summed in fp32 in rank order (bit-identical on every rank).  Device-side waits on peer
  * flags are bounded; on expiry the status word is set and the call that observes it returns RG_ERR_TIMEOUT.
  * op uses AllReduceType (src/04kernel/include/kernel/attributes/communication.h:5-11): 0 Sum, 1 Avg, 2 Min, 3 Max, 4 Prod.
@@ -392,6 +392,7 @@ int rg_b200_comm_create(int world, int rank, size_t capacity_bytes, rg_comm **ou
 int rg_b200_comm_connect(rg_comm *, const void *all_handles /* world * 64 bytes */);
 /* Same-process wiring: bases[r] = rg_b200_comm_base of rank r's communicator (peer access already enabled). */
 void *rg_b200_comm_base(rg_comm *);
+size_t rg_b200_comm_bytes(rg_comm *); /* size of the symmetric allocation behind rg_b200_comm_base (what a stand-in peer buffer must provide) */
 int rg_b200_comm_connect_ptrs(rg_comm *, const void *const *bases);
 /* Bound of the device-side wait for a peer, in nanoseconds (default 2 s). */
 int rg_b200_comm_set_wait_ns(rg_comm *, uint64_t ns);

@@ -131,7 +131,7 @@ OPS = {
 }
 # every symbol include/rg_b200.h declares
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_attn_decode_static",
-            "rg_b200_attn_decode_static_capacity", "rg_b200_decode_step_timeline", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_connect_ptrs",
+            "rg_b200_attn_decode_static_capacity", "rg_b200_decode_step_timeline", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_bytes", "rg_b200_comm_connect_ptrs",
             "rg_b200_comm_set_wait_ns",
             "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]
            + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])
@@ -166,6 +166,8 @@ def load() -> C.CDLL:
         lib.rg_b200_comm_status.argtypes = [C.c_void_p]
         lib.rg_b200_comm_base.restype = C.c_void_p
         lib.rg_b200_comm_base.argtypes = [C.c_void_p]
+        lib.rg_b200_comm_bytes.restype = C.c_size_t
+        lib.rg_b200_comm_bytes.argtypes = [C.c_void_p]
         lib.rg_b200_comm_connect_ptrs.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         lib.rg_b200_comm_set_wait_ns.argtypes = [C.c_void_p, C.c_uint64]
         lib.rg_b200_comm_destroy.argtypes = [C.c_void_p]
@@ -239,6 +241,9 @@ class Comm:
 
     def base(self) -> int:
         return load().rg_b200_comm_base(self._ptr)
+
+    def nbytes(self) -> int:
+        return load().rg_b200_comm_bytes(self._ptr)
 
     def set_wait_ns(self, ns: int):
         load().rg_b200_comm_set_wait_ns(self._ptr, ns)

@@ -1,14 +1,17 @@
 // AllReduce across the GPUs of one NVSwitch box, one process per GPU.  Replaces AllReduceNccl + NcclCommunicator
 // (src/04kernel/src/kernels/all_reduce/nccl_kernel.cu:9-19, src/04kernel/src/utilities/cuda/nccl_communicator.cu:11-44).
 //
-// One-shot pull over peer memory: every rank owns a "symmetric" allocation (header, per-CTA flags, two data slots)
-// that its peers map through CUDA IPC.  Call number s (kept in device memory, so a captured CUDA graph can replay
-// it): CTA c of every rank copies its 16-byte chunks of the input into slot s&1 of its own allocation, publishes
-// flags[c] = s with a system-scope release, waits (bounded) until flags[c] >= s is visible in every peer's
-// allocation, then loads the same chunks from all ranks with plain 128-bit loads, combines them in fp32 in rank
-// order (so all ranks get bit-identical results) and writes the output.  Slot s&1 is not rewritten before call
-// s+2, which cannot start on any rank before every rank has finished call s+1's wait, i.e. finished reading
-// call s.  No TMA and no multicast instructions touch peer memory.
+// One-shot push over peer memory with the flag inside the data: every rank owns a "symmetric" allocation (header, data
+// slots [parity][source rank]) that its peers map through CUDA IPC.  Call number s (kept in device memory, so a captured
+// CUDA graph can replay it): every thread takes 16-byte chunks of the input, pairs each 32-bit word with the 32-bit call
+// number and stores the resulting 32 bytes into slot [s&1][rank] of EVERY peer (two 16-byte stores over NVLink; an
+// aligned 8-byte {data, flag} pair is written as one unit), then polls the same 32 bytes of every peer's slot in its OWN
+// allocation until all four flags carry s, and combines the values in fp32 in rank order (so all ranks get bit-identical
+// results).  There is no fence, no separate flag and no barrier on the path: the latency is one NVLink store flight.
+// Parity s&1 is not rewritten before call s+2, which no rank starts before it has finished call s+1, whose data it sends
+// only after it has read everything of call s.  Measured for 256 KiB per rank: a pull design (remote flag polls and remote
+// loads) 26 / 49 us on 2 / 8 GPUs; push with a system fence and one flag per CTA 20 / 26 us.
+// No TMA and no multicast instructions touch peer memory.
 #include "gemm_dispatch.cuh"
 #include <cstring>
 #include <new>
@@ -16,10 +19,8 @@
 namespace rg {
 
 constexpr int AR_MAX_RANKS = 8;
-constexpr int AR_MAX_CTAS = 512;
 constexpr int AR_THREADS = 256;
 constexpr size_t AR_HEADER_BYTES = 4096;
-constexpr size_t AR_FLAGS_BYTES = AR_MAX_CTAS * sizeof(unsigned long long);
 
 struct ArHeader {
     unsigned long long seq;// number of the call in flight (starts at 1)
@@ -29,7 +30,7 @@ struct ArHeader {
 
 struct ArArgs {
     uint8_t *mine;
-    const uint8_t *peer[AR_MAX_RANKS];// peer[rank] = mine
+    uint8_t *peer[AR_MAX_RANKS];// peer[rank] = mine
     const void *x, *res;
     void *y;
     uint64_t count;
@@ -38,14 +39,6 @@ struct ArArgs {
     uint64_t wait_ns;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ float ar_combine(int op, float a, float b) {
     switch (op) {
         case 2: return fminf(a, b);
@@ -55,78 +48,97 @@ __device__ __forceinline__ float ar_combine(int op, float a, float b) {
     }
 }
 
+// byte offset of the slot that holds rank `src`'s input of a call with parity q, inside any rank's allocation; a slot is
+// 2 * capacity bytes because every 4 data bytes travel with a 4-byte flag
+__device__ __forceinline__ size_t ar_slot_off(const ArArgs &a, unsigned q, int src) {
+    return AR_HEADER_BYTES + (static_cast<size_t>(q) * a.world + src) * (2 * a.capacity);
+}
+__device__ __forceinline__ void st_volatile_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 template<class T>
 __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) {
     pdl_enter();
     constexpr int N = Vec16<T>::N;
     ArHeader *hdr = reinterpret_cast<ArHeader *>(a.mine);
-    unsigned long long *my_flags = reinterpret_cast<unsigned long long *>(a.mine + AR_HEADER_BYTES);
     __shared__ unsigned long long s_seq;
-    __shared__ int s_ok;
     if (threadIdx.x == 0) {
-        s_seq = *reinterpret_cast<volatile unsigned long long *>(&hdr->seq);
-        s_ok = 1;
-    }
-    __syncthreads();
-    const unsigned long long seq = s_seq;
-    const size_t slot_off = AR_HEADER_BYTES + AR_FLAGS_BYTES + (seq & 1ull) * a.capacity;
-    const uint64_t chunks = (a.count + N - 1) / N;// the last chunk may run past count: buffers are padded to 16 B
-    const uint64_t per = (chunks + gridDim.x - 1) / gridDim.x;
-    const uint64_t c0 = per * blockIdx.x, c1 = c0 + per < chunks ? c0 + per : chunks;
-    const T *x = static_cast<const T *>(a.x);
-    const T *res = static_cast<const T *>(a.res);
-    T *y = static_cast<T *>(a.y);
-    T *slot = reinterpret_cast<T *>(a.mine + slot_off);
-    const uint64_t full_chunks = a.count / N;
-
-    // 1. publish my part of the input
-    for (uint64_t c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
-        if (c < full_chunks) {
-            *reinterpret_cast<uint4 *>(slot + c * N) = *reinterpret_cast<const uint4 *>(x + c * N);
-        } else {
-            for (uint64_t e = c * N; e < a.count; ++e) slot[e] = x[e];
-        }
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        st_release_sys(&my_flags[blockIdx.x], seq);
+        const unsigned long long sq = *reinterpret_cast<volatile unsigned long long *>(&hdr->seq);
+        s_seq = sq;
         // the last CTA to have read seq advances it for the next call
         if (atomicAdd(&hdr->done, 1u) == gridDim.x - 1) {
             hdr->done = 0;
             __threadfence();
-            *reinterpret_cast<volatile unsigned long long *>(&hdr->seq) = seq + 1;
-        }
-    }
-    // 2. wait for the same part of every peer (bounded)
-    if (threadIdx.x < static_cast<unsigned>(a.world) && static_cast<int>(threadIdx.x) != a.rank) {
-        const unsigned long long *pf = reinterpret_cast<const unsigned long long *>(a.peer[threadIdx.x] + AR_HEADER_BYTES) + blockIdx.x;
-        const uint64_t t0 = global_timer_ns();
-        bool ok = false;
-        for (;;) {
-            if (ld_acquire_sys(pf) >= seq) {
-                ok = true;
-                break;
-            }
-            if (global_timer_ns() - t0 > a.wait_ns) break;
-        }
-        if (!ok) {
-            s_ok = 0;
-            hdr->status = 1;
+            *reinterpret_cast<volatile unsigned long long *>(&hdr->seq) = sq + 1;
         }
     }
     __syncthreads();
-    if (!s_ok) return;// leave the output untouched; the host sees the status word
-    // 3. pull and combine in rank order
+    const unsigned long long seq = s_seq;
+    const unsigned q = static_cast<unsigned>(seq & 1ull);
+    const uint32_t flag = static_cast<uint32_t>(seq);// never 0 for the first 2^32 - 1 calls; slots start zeroed
+    const uint64_t chunks = (a.count + N - 1) / N, full_chunks = a.count / N;
+    const T *x = static_cast<const T *>(a.x);
+    const T *res = static_cast<const T *>(a.res);
+    T *y = static_cast<T *>(a.y);
+    const size_t my_off = ar_slot_off(a, q, a.rank);
     const float scale = a.op == 1 ? 1.0f / static_cast<float>(a.world) : 1.0f;
-    for (uint64_t c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+    const uint64_t t0 = global_timer_ns();
+
+    for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks; c += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        // 1. push chunk c of my input, every 32-bit word paired with the call's flag, into slot [q][rank] of every peer
+        uint4 mine4 = make_uint4(0u, 0u, 0u, 0u);
+        if (c < full_chunks) {
+            mine4 = *reinterpret_cast<const uint4 *>(x + c * N);
+        } else {
+            T *tail = reinterpret_cast<T *>(&mine4);
+            for (uint64_t e = c * N; e < a.count; ++e) tail[e - c * N] = x[e];
+        }
+#pragma unroll
+        for (int r = 0; r < AR_MAX_RANKS; ++r) {
+            if (r < a.world && r != a.rank) {
+                uint8_t *dst = a.peer[r] + my_off + c * 32;
+                st_volatile_v4(dst, mine4.x, flag, mine4.y, flag);
+                st_volatile_v4(dst + 16, mine4.z, flag, mine4.w, flag);
+            }
+        }
+        // 2. the same chunk of every peer lands in my allocation: poll local memory until all four flags of a line match
+        uint4 raw[AR_MAX_RANKS];
+        bool ok = true;
+#pragma unroll
+        for (int r = 0; r < AR_MAX_RANKS; ++r) {
+            raw[r] = mine4;
+            if (r < a.world && r != a.rank && ok) {
+                const uint8_t *src = a.mine + ar_slot_off(a, q, r) + c * 32;
+                for (uint32_t spin = 1;; ++spin) {
+                    const uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 16);
+                    if (lo.y == flag && lo.w == flag && hi.y == flag && hi.w == flag) {
+                        raw[r] = make_uint4(lo.x, lo.z, hi.x, hi.z);
+                        break;
+                    }
+                    if ((spin & 63u) == 0 && global_timer_ns() - t0 > a.wait_ns) {
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            hdr->status = 1;// the output stays untouched; the host sees the status word
+            return;
+        }
+        // 3. combine in rank order, so that every rank computes bit-identical results
         float acc[N];
 #pragma unroll
         for (int r = 0; r < AR_MAX_RANKS; ++r) {
             if (r < a.world) {
-                const T *src = reinterpret_cast<const T *>(a.peer[r] + slot_off) + c * N;
                 Vec16<T> v;
-                v.raw = *reinterpret_cast<const uint4 *>(src);
+                v.raw = raw[r];
                 float f[N];
                 v.unpack(f);
 #pragma unroll
@@ -149,6 +161,133 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) 
             o.store(y + c * N);
         } else {
             for (uint64_t e = c * N; e < a.count; ++e) y[e] = Num<T>::from_f(acc[e - c * N]);
+        }
+    }
+}
+
+// Two-shot variant for large groups: a one-shot push moves (world - 1) x the vector out of every GPU, which on 8 GPUs costs
+// more than a second NVLink flight.  Here warp-sized runs of 32 chunks have an owner rank ((c / 32) % world): every rank
+// sends its chunk to the owner only; the owner combines the world values in rank order, adds the residual, and pushes the
+// finished 16 bytes to every peer, which copies them to its output.  Same flag-in-data lines, same parity rule, a second
+// slot (B) for the finished values.  Every thread sends before it waits, and all ranks walk the chunks in the same order.
+template<class T>
+__global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const ArArgs a) {
+    pdl_enter();
+    constexpr int N = Vec16<T>::N;
+    ArHeader *hdr = reinterpret_cast<ArHeader *>(a.mine);
+    __shared__ unsigned long long s_seq;
+    if (threadIdx.x == 0) {
+        const unsigned long long sq = *reinterpret_cast<volatile unsigned long long *>(&hdr->seq);
+        s_seq = sq;
+        if (atomicAdd(&hdr->done, 1u) == gridDim.x - 1) {
+            hdr->done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned long long *>(&hdr->seq) = sq + 1;
+        }
+    }
+    __syncthreads();
+    const unsigned long long seq = s_seq;
+    const unsigned q = static_cast<unsigned>(seq & 1ull);
+    const uint32_t flag = static_cast<uint32_t>(seq);
+    const uint64_t chunks = (a.count + N - 1) / N, full_chunks = a.count / N;
+    const T *x = static_cast<const T *>(a.x);
+    const T *res = static_cast<const T *>(a.res);
+    T *y = static_cast<T *>(a.y);
+    const size_t my_off = ar_slot_off(a, q, a.rank);
+    const size_t b_off = ar_slot_off(a, 2, 0) + static_cast<size_t>(q) * (2 * a.capacity);// slot B follows the 2 * world A slots
+    const float scale = a.op == 1 ? 1.0f / static_cast<float>(a.world) : 1.0f;
+    const uint64_t t0 = global_timer_ns();
+
+    for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks; c += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const int owner = static_cast<int>((c / 32) % static_cast<uint64_t>(a.world));
+        uint4 mine4 = make_uint4(0u, 0u, 0u, 0u);
+        if (c < full_chunks) {
+            mine4 = *reinterpret_cast<const uint4 *>(x + c * N);
+        } else {
+            T *tail = reinterpret_cast<T *>(&mine4);
+            for (uint64_t e = c * N; e < a.count; ++e) tail[e - c * N] = x[e];
+        }
+        uint4 out4;
+        bool ok = true;
+        if (owner != a.rank) {
+            uint8_t *dst = a.peer[owner] + my_off + c * 32;
+            st_volatile_v4(dst, mine4.x, flag, mine4.y, flag);
+            st_volatile_v4(dst + 16, mine4.z, flag, mine4.w, flag);
+            const uint8_t *src = a.mine + b_off + c * 32;
+            for (uint32_t spin = 1;; ++spin) {
+                const uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 16);
+                if (lo.y == flag && lo.w == flag && hi.y == flag && hi.w == flag) {
+                    out4 = make_uint4(lo.x, lo.z, hi.x, hi.z);
+                    break;
+                }
+                if ((spin & 63u) == 0 && global_timer_ns() - t0 > a.wait_ns) {
+                    ok = false;
+                    break;
+                }
+            }
+        } else {
+            uint4 raw[AR_MAX_RANKS];
+#pragma unroll
+            for (int r = 0; r < AR_MAX_RANKS; ++r) {
+                raw[r] = mine4;
+                if (r < a.world && r != a.rank && ok) {
+                    const uint8_t *src = a.mine + ar_slot_off(a, q, r) + c * 32;
+                    for (uint32_t spin = 1;; ++spin) {
+                        const uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 16);
+                        if (lo.y == flag && lo.w == flag && hi.y == flag && hi.w == flag) {
+                            raw[r] = make_uint4(lo.x, lo.z, hi.x, hi.z);
+                            break;
+                        }
+                        if ((spin & 63u) == 0 && global_timer_ns() - t0 > a.wait_ns) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+            }
+            float acc[N];
+#pragma unroll
+            for (int r = 0; r < AR_MAX_RANKS; ++r) {
+                if (r < a.world) {
+                    Vec16<T> v;
+                    v.raw = raw[r];
+                    float f[N];
+                    v.unpack(f);
+#pragma unroll
+                    for (int j = 0; j < N; ++j) acc[j] = r == 0 ? f[j] : ar_combine(a.op, acc[j], f[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[j] *= scale;
+            if (res) {
+                for (int j = 0; j < N; ++j) {
+                    const uint64_t e = c * N + j;
+                    if (e < a.count) acc[j] = Num<T>::to_f(Num<T>::from_f(acc[j])) + Num<T>::to_f(res[e]);
+                }
+            }
+            Vec16<T> o;
+            o.pack(acc);
+            out4 = o.raw;
+            if (ok) {
+#pragma unroll
+                for (int r = 0; r < AR_MAX_RANKS; ++r) {
+                    if (r < a.world && r != a.rank) {
+                        uint8_t *dst = a.peer[r] + b_off + c * 32;
+                        st_volatile_v4(dst, out4.x, flag, out4.y, flag);
+                        st_volatile_v4(dst + 16, out4.z, flag, out4.w, flag);
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            hdr->status = 1;// the output stays untouched; the host sees the status word
+            return;
+        }
+        if (c < full_chunks) {
+            *reinterpret_cast<uint4 *>(y + c * N) = out4;
+        } else {
+            const T *tail = reinterpret_cast<const T *>(&out4);
+            for (uint64_t e = c * N; e < a.count; ++e) y[e] = tail[e - c * N];
         }
     }
 }
@@ -178,7 +317,8 @@ int rg_b200_comm_create(int world, int rank, size_t capacity_bytes, rg_comm **ou
     if (!c) return RG_ERR_CUDA;
     c->world = world, c->rank = rank;
     c->capacity = (capacity_bytes + 255) / 256 * 256;
-    c->total_bytes = AR_HEADER_BYTES + AR_FLAGS_BYTES + 2 * c->capacity;
+    // [2 parities][world] slots A of 2 * capacity, then [2 parities] slots B (finished values of the two-shot variant)
+    c->total_bytes = AR_HEADER_BYTES + 4 * static_cast<size_t>(world + 1) * c->capacity;
     c->wait_ns = 2000000000ull;
     void *p = nullptr;
     if (cudaMalloc(&p, c->total_bytes) != cudaSuccess) {
@@ -223,6 +363,7 @@ int rg_b200_comm_connect(rg_comm *c, const void *all_handles) {
 // Same-process wiring (one thread per GPU, as the reference's own all-reduce test runs, or a test double for a
 // peer): bases[r] is the value rg_b200_comm_base returned for rank r; peer access must already be enabled.
 void *rg_b200_comm_base(rg_comm *c) { return c ? c->mine : nullptr; }
+size_t rg_b200_comm_bytes(rg_comm *c) { return c ? c->total_bytes : 0; }
 int rg_b200_comm_connect_ptrs(rg_comm *c, const void *const *bases) {
     if (!c || !bases) return RG_ERR_NULL;
     for (int r = 0; r < c->world; ++r) {
@@ -282,10 +423,22 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
     a.wait_ns = c->wait_ns;
     const uint64_t chunks = bytes / 16;
     // every rank derives the same grid from the same count: CTA c of one rank pairs with CTA c of the others
-    uint64_t grid = (chunks + AR_THREADS * 2 - 1) / (AR_THREADS * 2);
+    uint64_t grid = (chunks + AR_THREADS - 1) / AR_THREADS;
     if (grid < 1) grid = 1;
     if (grid > 128) grid = 128;
     auto st = static_cast<cudaStream_t>(stream);
+    // every rank must take the same variant: it depends on the group size and on RG_B200_AR_ALGO (1 one-shot, 2 two-shot) only
+    static const int algo_env = std::getenv("RG_B200_AR_ALGO") ? atoi(std::getenv("RG_B200_AR_ALGO")) : 0;
+    const bool two_shot = c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world > 4));
+    if (two_shot) {
+        switch (p->dtype) {
+            case RG_F32: launch_pdl(all_reduce_two_shot_kernel<float>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
+            case RG_FP16: launch_pdl(all_reduce_two_shot_kernel<__half>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
+            default: launch_pdl(all_reduce_two_shot_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
+        }
+        count_launch();
+        return launch_status();
+    }
     switch (p->dtype) {
         case RG_F32: launch_pdl(all_reduce_kernel<float>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
         case RG_FP16: launch_pdl(all_reduce_kernel<__half>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;

@@ -121,7 +121,7 @@ def test_all_reduce_missing_peer_reports_timeout_instead_of_hanging():
     buffer stands in for the peer).  The device-side wait is bounded (20 ms here); the kernel returns, the status
     word says so, and the context stays usable."""
     comm = capi.Comm(2, 0, 1 << 12)
-    fake_peer = torch.zeros(4096 + 4096 + 2 * 4096, dtype=torch.uint8, device="cuda")
+    fake_peer = torch.zeros(comm.nbytes(), dtype=torch.uint8, device="cuda")       # rank 0 stores its input there
     comm.connect_ptrs([comm.base(), fake_peer.data_ptr()])
     comm.set_wait_ns(20_000_000)
     x = torch.ones(256, device="cuda")

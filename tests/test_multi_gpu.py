@@ -26,9 +26,10 @@ def _exchange(handle: bytes):
     return out
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, algo):
     try:
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        # RG_B200_AR_ALGO picks the all-reduce variant (1 = one-shot push, 2 = two-shot); the library reads it once
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", RG_B200_AR_ALGO=algo)
         import sys
         sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
         torch.cuda.set_device(rank)
@@ -106,11 +107,12 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs on one box")
-def test_two_ranks_all_reduce_and_tensor_parallel_decode():
+@pytest.mark.parametrize("algo", ["1", "2"])
+def test_two_ranks_all_reduce_and_tensor_parallel_decode(algo):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, algo)) for r in range(2)]
     for p in procs:
         p.start()
     results = dict(q.get(timeout=600) for _ in procs)
