@@ -436,6 +436,7 @@ def run_gemm_tp8(args):
         y = torch.empty(m, n, dtype=dt, device=dev)
         p = capi.MatMulParams()
         p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y, p.force_kernel = capi.FP16, m, n, k, 1, 1.0, 0.0, 1, m * n, 0
+        p.flags = 0 if os.environ.get("RG_BENCH_NO_STATIC") else capi.MM_B_STATIC      # B is a weight, as in the decode graph
         nws = capi.workspace("mat_mul", p)
         wsb = torch.zeros(max(nws, 1), dtype=torch.uint8, device=dev)
 

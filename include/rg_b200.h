@@ -218,7 +218,10 @@ typedef struct rg_mat_mul_params {
     uint32_t bias_row_stride, bias_col_stride; /* element strides of C over (m, n); 0 = broadcast */
     uint64_t stride_c;
     int32_t force_kernel; /* 0 auto, 1 SIMT tile, 2 streaming GEMV, 3 tcgen05 */
+    uint32_t flags;       /* RG_MM_B_STATIC: B is a weight - no kernel earlier in the stream writes it - so its tiles may be
+                             fetched while the preceding kernel is still running (programmatic dependent launch) */
 } rg_mat_mul_params;
+#define RG_MM_B_STATIC 1u
 size_t rg_b200_mat_mul_workspace(const rg_mat_mul_params *);
 int rg_b200_mat_mul(const rg_mat_mul_params *, void *ws, const void *const *in, void *const *out, void *stream);
 

@@ -73,7 +73,10 @@ class MatMulParams(C.Structure):
                 ("trans_a", C.c_int32), ("trans_b", C.c_int32), ("alpha", C.c_float), ("beta", C.c_float),
                 ("batch", C.c_uint32), ("stride_a", C.c_uint64), ("stride_b", C.c_uint64), ("stride_y", C.c_uint64),
                 ("has_bias", C.c_int32), ("bias_row_stride", C.c_uint32), ("bias_col_stride", C.c_uint32),
-                ("stride_c", C.c_uint64), ("force_kernel", C.c_int32)]
+                ("stride_c", C.c_uint64), ("force_kernel", C.c_int32), ("flags", C.c_uint32)]
+
+
+MM_B_STATIC = 1
 
 
 class KvLayout(C.Structure):

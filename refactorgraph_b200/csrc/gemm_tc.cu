@@ -37,6 +37,7 @@ struct TcArgs {
     uint32_t splits;   // k-splits per output tile (1 = none)
     float *partial;    // [tiles][splits][128][BN] fp32, used when splits > 1
     unsigned *counter; // [tiles] arrival counters, zero before the first call and left at zero
+    uint32_t early;    // operand that no earlier kernel of the stream writes (a weight): 1 = A, 2 = B, 0 = neither
 };
 
 // ---- tcgen05 / TMA PTX ------------------------------------------------------------------------------------
@@ -160,11 +161,28 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_enter();// barriers, tensor memory and descriptors are set up while the previous kernel of the stream drains
+    // Programmatic dependent launch: everything up to here, and the first stages of a weight operand, overlap the previous
+    // kernel of the stream; each role waits for that kernel right before it first touches memory the kernel may write.
+    pdl_launch_dependents();
 
     if (warp == 4) {
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, pre = 0;
+            if (a.early && blockIdx.x < items) {
+                // weight tiles of this CTA's first item go in flight before the wait; their partner tiles follow after it
+                uint32_t mt, nt;
+                const uint32_t tile = blockIdx.x / a.splits, ks = blockIdx.x % a.splits;
+                tile_coords(tile, m_tiles, n_tiles, mt, nt);
+                const uint32_t kb0 = kblocks * ks / a.splits, kb1 = kblocks * (ks + 1) / a.splits;
+                for (uint32_t kb = kb0; kb < kb1 && pre < STAGES; ++kb, ++pre) {
+                    mbar_arrive_expect_tx(&full[pre], STAGE_BYTES);
+                    uint8_t *st = smem + pre * STAGE_BYTES;
+                    if (a.early == 1) tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[pre]);
+                    else
+                        tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, nt * BN, &full[pre]);
+                }
+            }
+            pdl_wait();
             for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
                 uint32_t mt, nt;
                 const uint32_t tile = item / a.splits, ks = item % a.splits;
@@ -172,13 +190,19 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 const uint32_t kb0 = kblocks * ks / a.splits, kb1 = kblocks * (ks + 1) / a.splits;
                 for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    uint8_t *st = smem + s * STAGE_BYTES;
+                    if (it < pre) {// stage armed and half filled above
+                        if (a.early == 1) tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, nt * BN, &full[s]);
+                        else
+                            tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[s]);
+                        continue;
+                    }
                     if (!mbar_wait(&empty[s], ph ^ 1u)) {
                         *failed = 1;
                         item = items;
                         break;
                     }
                     mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                    uint8_t *st = smem + s * STAGE_BYTES;
                     tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[s]);
                     tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, nt * BN, &full[s]);
                 }
@@ -219,6 +243,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         }
     } else {
         // ---- epilogue warps 0..3: TMEM lanes [32*warp, 32*warp + 32) = tile rows ----
+        pdl_wait();// C, Y and the split-K workspace may still be in use by the previous kernel
         T *Y = static_cast<T *>(a.Y);
         const T *C = static_cast<const T *>(a.C);
         const bool c_rowmajor = C && a.c_col_stride == 1 && (a.c_row_stride % 8) == 0;
@@ -268,6 +293,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                         float4 acc[BN / 4];
 #pragma unroll
                         for (int c = 0; c < BN / 4; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
                         for (uint32_t sidx = 0; sidx < a.splits; ++sidx) {
                             const float4 *src = reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN));
                             float4 v[BN / 4];
@@ -394,22 +420,29 @@ bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *
     return encode_fn() != nullptr;
 }
 
-// k-splits for a skinny product.  Every extra item costs a partial-tile round trip through L2 and ~5 us of epilogue
-// (22016 x 4096 at m = 16: 52.6 us unsplit, 46.6 / 52.8 / 88.9 us with 2 / 3 / 6 splits), so splits are used sparingly:
-// up to SMs/tiles when the tiles alone leave more than half of the SMs idle, else 2 only to repair a bad last wave.
+// k-splits for a skinny product.  Stamps inside the kernel (16 tokens, 8192 x 1024 ... 7168 x 8192 weights) show where the time
+// goes: one CTA streams its operands at ~60 GB/s (its ring of stages in flight / the memory latency), and a split product pays
+// ~3 us more (partial tile to L2, release/acquire counter, the last arriver's sum) plus ~0.5 us per split summed.  The split
+// count minimises that estimate; products with more tiles than half the SMs only get a 2-way split when it repairs a mostly
+// empty last wave (22016 x 4096 at m = 16: 52.6 us unsplit, 46.6 / 52.8 / 88.9 us with 2 / 3 / 6 splits).
 static uint32_t tc_splits(uint32_t tiles, uint32_t kblocks) {
     const uint32_t sms = static_cast<uint32_t>(sm_count());
     const uint32_t cap = kblocks / 8 ? kblocks / 8 : 1;
     if (tiles * 2 > sms) {
-        // more tiles than half the SMs: a 2-way split only pays when it repairs the last, mostly empty wave
-        // (172 tiles on 148 SMs: 58 % -> 77 % of the slots busy; measured 52.6 us -> 46.6 us)
         auto busy = [&](uint32_t items) { return static_cast<float>(items) / static_cast<float>((items + sms - 1) / sms * sms); };
         return (cap >= 2 && tiles < 2 * sms && busy(2 * tiles) > busy(tiles) + 0.15f) ? 2 : 1;
     }
-    uint32_t s = sms / tiles;
-    if (s > cap) s = cap;
-    if (s > 8) s = 8;
-    return s ? s : 1;
+    uint32_t smax = sms / tiles;
+    if (smax > cap) smax = cap;
+    if (smax > 16) smax = 16;
+    const float tile_us = static_cast<float>(kblocks) * (TC_BM * TC_BK * 2) / 60000.f;// one CTA streaming a whole tile's k range
+    uint32_t best = 1;
+    float best_us = tile_us;
+    for (uint32_t s = 2; s <= smax; ++s) {
+        const float us = tile_us / static_cast<float>(s) + 3.0f + 0.5f * static_cast<float>(s);
+        if (us < best_us) best_us = us, best = s;
+    }
+    return best;
 }
 struct TcPlan {
     bool swap;
@@ -473,12 +506,14 @@ int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *c
         if (!swap) {
             bn = p->n >= 256 ? 256 : 128;
             a.m = p->m, a.n = p->n;
+            a.early = (p->flags & RG_MM_B_STATIC) ? 2u : 0u;
             a.Y = Y, a.y_row_stride = p->n, a.y_col_stride = 1;
             a.C = C, a.c_row_stride = p->bias_row_stride, a.c_col_stride = p->bias_col_stride;
             if (!make_map(&ma, A, is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, B, is_bf16, p->n, p->k, p->k, bn)) return RG_ERR_CUDA;
         } else {
             bn = p->m <= 32 ? 32 : 64;
             a.m = p->n, a.n = p->m;
+            a.early = (p->flags & RG_MM_B_STATIC) ? 1u : 0u;
             a.Y = Y, a.y_row_stride = 1, a.y_col_stride = p->n;
             a.C = C, a.c_row_stride = p->bias_col_stride, a.c_col_stride = p->bias_row_stride;
             if (!make_map(&ma, B, is_bf16, p->n, p->k, p->k, TC_BM) || !make_map(&mb, A, is_bf16, p->m, p->k, p->k, bn)) return RG_ERR_CUDA;

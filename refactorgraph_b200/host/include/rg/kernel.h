@@ -3,6 +3,7 @@
 //   kernel::Kernel          src/04kernel/include/kernel/kernel.h:12-27
 //   kernel::InfoCollector   src/04kernel/include/kernel/collector.h:10-24
 #pragma once
+#include <vector>
 #include "runtime.h"
 
 namespace refactor::hardware {
@@ -52,6 +53,9 @@ namespace refactor::kernel {
         virtual size_t kernelTypeId() const = 0;
         virtual std::string_view description() const = 0;
         virtual RoutineWorkspace lower(Resources &) const { RUNTIME_ERROR("lower not implemented for this kernel"); }
+        // Called once by the graph lowering, before lower(): isStatic[i] says that input i is a graph input which no node
+        // of the graph writes (a weight).  A kernel may use it to fetch that operand while its predecessor still runs.
+        virtual void hintStaticInputs(std::vector<bool> const &) {}
         template<class T, class... Args> bool is(Args &&...args) const noexcept {
             return this->kernelTypeId() == T::typeId(std::forward<Args>(args)...);
         }

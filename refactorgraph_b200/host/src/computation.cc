@@ -393,6 +393,16 @@ namespace refactor::computation {
             alias[i] = i;
             g.edges.push_back({edges[i].tensor, edges[i].name});
         }
+        // A graph input that only matrix products read is a weight: nothing in the graph writes it (caches, states and
+        // other inputs updated in place are consumed by at least one other kind of node).
+        std::vector<char> isWeight(edges.size(), 0);
+        for (auto e : globalInputs) isWeight[e] = 1;
+        for (auto const &n : nodes) {
+            const bool product = dynamic_cast<MatMul const *>(n.op.get()) != nullptr;
+            for (auto e : n.inputs)
+                if (!product) isWeight[e] = 0;
+            for (auto e : n.outputs) isWeight[e] = 0;
+        }
         std::string missing;
         for (auto const &n : nodes) {
             if (n.op->isIdentity()) {
@@ -409,6 +419,11 @@ namespace refactor::computation {
             }
             kernel::Graph::Node kn;
             kn.kernel = std::move(candidates.front());
+            {
+                std::vector<bool> isStatic;
+                for (auto e : n.inputs) isStatic.push_back(isWeight[e] != 0);
+                kn.kernel->hintStaticInputs(isStatic);
+            }
             kn.name = n.name;
             for (auto e : n.inputs) kn.inputs.push_back(alias[e]);
             for (auto e : n.outputs) kn.outputs.push_back(alias[e]);

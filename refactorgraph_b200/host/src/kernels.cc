@@ -267,6 +267,9 @@ namespace refactor::kernel {
         std::vector<std::pair<uint64_t, uint64_t>> offsets;// per output matrix (a, b) element offsets; empty = strided
         MatMulB200(rg_mat_mul_params p, decltype(offsets) o) noexcept : info(p), offsets(std::move(o)) {}
         RG_KERNEL_IDS(MatMulB200, "MatMul on B200 (tcgen05 / streaming GEMV / tiled CUDA-core kernels, no vendor GEMM)")
+        void hintStaticInputs(std::vector<bool> const &isStatic) final {
+            if (isStatic.size() > 1 && isStatic[1]) info.flags |= RG_MM_B_STATIC;
+        }
         RoutineWorkspace lower(Resources &res) const final {
             auto st = res.fetchOrStore<CudaStream>();
             return RoutineWorkspace(
