@@ -627,7 +627,7 @@ def run_prefill(args, torch, dist, lib, rank, world, local):
     from refactorgraph_b200.llama import LlamaConfig, prefill_graph, weight_inputs
     B, S = 4, 2048
     cfg = LlamaConfig(max_seq=S, batch=B, dtype=BF16)
-    g, index = prefill_graph(cfg, S)
+    g, index = prefill_graph(cfg, S, fused_rope=not os.environ.get("RG_BENCH_UNFUSED_ROPE"))
     ex = g.compiler().compile("cuda", "flat", [])
     gen = torch.Generator(device="cuda")
     gen.manual_seed(rank)

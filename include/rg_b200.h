@@ -265,7 +265,8 @@ int rg_b200_swiglu(const rg_swiglu_params *, void *ws, const void *const *in, vo
 
 /* Fused decode linear layer  Y = epilogue( prologue(X) * W^T ),  W[n,k] row-major (the reference MatMul with
  * transB = 1), X[m,k], m <= 4.  One launch replaces RmsNormalization + MatMul + (Add | Sigmoid,Mul,Mul |
- * RoPE + cache append) of the reference graph.
+ * RoPE + cache append) of the reference graph.  With m > 64, prologue 0, epilogue 3 and head_dim 128 (prefill) the product
+ * runs on the tcgen05 GEMM and the split, rotation and cache append are its epilogue.
  *   prologue: 0 none; 1 RMSNorm with weight g[k] and epsilon (fp32 statistics).
  *   epilogue: 0 none                      outputs {Y[m,n]}
  *             1 residual add              inputs + {R[m,n]}; Y = R + X*W^T
@@ -282,6 +283,7 @@ typedef struct rg_linear_params {
     uint32_t n_heads; /* epilogue 3: query heads; n = (n_heads + 2*kv.n_kv_heads) * kv.head_dim */
     float theta;
     rg_kv_layout kv;
+    uint32_t tokens_per_seq; /* epilogue 3 with m > 64: token t belongs to sequence t / tokens_per_seq (0 or 1: one token per sequence) */
 } rg_linear_params;
 size_t rg_b200_linear_workspace(const rg_linear_params *);
 int rg_b200_linear(const rg_linear_params *, void *ws, const void *const *in, void *const *out, void *stream);

@@ -87,7 +87,7 @@ class KvLayout(C.Structure):
 class LinearParams(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
                 ("prologue", C.c_int32), ("epilogue", C.c_int32), ("epsilon", C.c_float), ("n_heads", C.c_uint32),
-                ("theta", C.c_float), ("kv", KvLayout)]
+                ("theta", C.c_float), ("kv", KvLayout), ("tokens_per_seq", C.c_uint32)]
 
 
 class QkvRopeAppendParams(C.Structure):

@@ -195,34 +195,45 @@ __global__ void rope_kernel(const T *__restrict__ x, const int64_t *__restrict__
 }
 
 // ---- QKV split + RoPE + cache append (batched decode; the m <= 4 path fuses this into the linear kernel) -----
-// One thread per (token, head, i < D/2) of the fused projection qkv[m, (nH + 2 nKV) * D].
-template<class T>
+// One thread per (token, head, run of N pair indices i < D/2) of the fused projection qkv[m, (nH + 2 nKV) * D]; N = one
+// 16-byte vector when the rows allow it (VEC), else 1.
+template<class T, bool VEC>
 __global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t *__restrict__ pos,
                                        const int32_t *__restrict__ table, T *__restrict__ q, T *__restrict__ kc,
                                        T *__restrict__ vc, uint32_t tokens, uint32_t nq, rg_kv_layout kv, float log2_theta,
                                        uint32_t tokens_per_seq) {
     pdl_enter();
-    const uint32_t D = kv.head_dim, half = D / 2, nkv = kv.n_kv_heads, heads = nq + 2 * nkv;
-    const uint64_t total = static_cast<uint64_t>(tokens) * heads * half;
+    constexpr int N = VEC ? Vec16<T>::N : 1;
+    const uint32_t D = kv.head_dim, half = D / 2, nkv = kv.n_kv_heads, heads = nq + 2 * nkv, cph = half / N;
+    const uint64_t total = static_cast<uint64_t>(tokens) * heads * cph;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
          t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
-        const uint32_t i = static_cast<uint32_t>(t % half);
-        const uint32_t h = static_cast<uint32_t>((t / half) % heads);
-        const uint32_t m = static_cast<uint32_t>(t / half / heads);
+        const uint32_t i0 = static_cast<uint32_t>(t % cph) * N;
+        const uint32_t h = static_cast<uint32_t>((t / cph) % heads);
+        const uint32_t m = static_cast<uint32_t>(t / cph / heads);
         const T *src = qkv + (static_cast<uint64_t>(m) * heads + h) * D;
-        float lo = Num<T>::to_f(src[i]), hi = Num<T>::to_f(src[i + half]);
+        float lo[N], hi[N];
+        if constexpr (VEC) {
+            Vec16<T> a, b;
+            a.load(src + i0), b.load(src + i0 + half);
+            a.unpack(lo), b.unpack(hi);
+        } else {
+            lo[0] = Num<T>::to_f(src[i0]), hi[0] = Num<T>::to_f(src[i0 + half]);
+        }
         const int64_t p = pos[m];
         if (h < nq + nkv) {
-            const float inv_freq = exp2f(-log2_theta * (2.0f * static_cast<float>(i) / static_cast<float>(D)));
-            float sn, cs;
-            sincosf(static_cast<float>(p) * inv_freq, &sn, &cs);
-            const float a0 = lo * cs - hi * sn, b0 = hi * cs + lo * sn;
-            lo = a0, hi = b0;
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+                const float inv_freq = exp2f(-log2_theta * (2.0f * static_cast<float>(i0 + j) / static_cast<float>(D)));
+                float sn, cs;
+                sincosf(static_cast<float>(p) * inv_freq, &sn, &cs);
+                const float a0 = lo[j] * cs - hi[j] * sn, b0 = hi[j] * cs + lo[j] * sn;
+                lo[j] = a0, hi[j] = b0;
+            }
         }
+        T *dst;
         if (h < nq) {
-            T *dst = q + (static_cast<uint64_t>(m) * nq + h) * D;
-            dst[i] = Num<T>::from_f(lo);
-            dst[i + half] = Num<T>::from_f(hi);
+            dst = q + (static_cast<uint64_t>(m) * nq + h) * D;
         } else {
             const bool is_k = h < nq + nkv;
             const uint32_t kvh = is_k ? h - nq : h - nq - nkv;
@@ -236,22 +247,43 @@ __global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t 
             } else {
                 base = ((static_cast<uint64_t>(seq) * nkv + kvh) * kv.max_seq + static_cast<uint64_t>(p)) * D;
             }
-            cache[base + i] = Num<T>::from_f(lo);
-            cache[base + i + half] = Num<T>::from_f(hi);
+            dst = cache + base;
+        }
+        if constexpr (VEC) {
+            Vec16<T> a, b;
+            a.pack(lo), b.pack(hi);
+            a.store(dst + i0), b.store(dst + i0 + half);
+        } else {
+            dst[i0] = Num<T>::from_f(lo[0]);
+            dst[i0 + half] = Num<T>::from_f(hi[0]);
         }
     }
 }
 
-// y[r, j] = silu(x[r, j]) * x[r, f + j]
-template<class T>
+// y[r, j] = silu(x[r, j]) * x[r, f + j]; one 16-byte vector per thread when f and the pointers allow it (VEC)
+template<class T, bool VEC>
 __global__ void swiglu_kernel(const T *__restrict__ x, T *__restrict__ y, uint32_t rows, uint32_t f) {
     pdl_enter();
-    const uint64_t total = static_cast<uint64_t>(rows) * f;
+    constexpr int N = VEC ? Vec16<T>::N : 1;
+    const uint32_t cpr = f / N;
+    const uint64_t total = static_cast<uint64_t>(rows) * cpr;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
          t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
-        const uint64_t r = t / f, j = t % f;
-        const float g = Num<T>::to_f(x[r * 2 * f + j]), u = Num<T>::to_f(x[r * 2 * f + f + j]);
-        y[t] = Num<T>::from_f(g / (1.f + expf(-g)) * u);
+        const uint64_t r = t / cpr, j = (t % cpr) * N;
+        const T *gp = x + r * 2 * f + j;
+        if constexpr (VEC) {
+            Vec16<T> gv, uv, o;
+            gv.load(gp), uv.load(gp + f);
+            float g[N], u[N];
+            gv.unpack(g), uv.unpack(u);
+#pragma unroll
+            for (int e = 0; e < N; ++e) g[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+            o.pack(g);
+            o.store(y + r * f + j);
+        } else {
+            const float g = Num<T>::to_f(gp[0]), u = Num<T>::to_f(gp[f]);
+            y[r * f + j] = Num<T>::from_f(g / (1.f + expf(-g)) * u);
+        }
     }
 }
 
@@ -419,11 +451,19 @@ int rg_b200_qkv_rope_append(const rg_qkv_rope_append_params *p, void *, const vo
     const uint64_t total = static_cast<uint64_t>(p->tokens) * (p->n_heads + 2 * p->kv.n_kv_heads) * (D / 2);
     if (total == 0) return RG_OK;
     auto st = static_cast<cudaStream_t>(stream);
-    const unsigned g = grid_for(total, 256);
     const float l2t = log2f(p->theta);
     auto pos = static_cast<const int64_t *>(in[1]);
     auto tab = static_cast<const int32_t *>(in[2]);
-#define RG_QRA(T) launch_pdl(qkv_rope_append_kernel<T>, dim3(g), dim3(256), 0, st, static_cast<const T *>(in[0]), pos, tab, static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t, p->tokens_per_seq)
+    const unsigned esz = p->dtype == RG_F32 ? 4u : 2u, vn = 16u / esz;
+    const bool vec = (D / 2) % vn == 0 && aligned16(in[0]) && aligned16(out[0]) && aligned16(out[1]) && aligned16(out[2]);
+    const unsigned g = grid_for(vec ? total / vn : total, 256);
+#define RG_QRA(T)                                                                                                                      \
+    (vec ? launch_pdl(qkv_rope_append_kernel<T, true>, dim3(g), dim3(256), 0, st, static_cast<const T *>(in[0]), pos, tab,            \
+                      static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t, \
+                      p->tokens_per_seq)                                                                                               \
+         : launch_pdl(qkv_rope_append_kernel<T, false>, dim3(g), dim3(256), 0, st, static_cast<const T *>(in[0]), pos, tab,           \
+                      static_cast<T *>(out[0]), static_cast<T *>(out[1]), static_cast<T *>(out[2]), p->tokens, p->n_heads, p->kv, l2t, \
+                      p->tokens_per_seq))
     switch (p->dtype) {
         case RG_F32: RG_QRA(float); break;
         case RG_FP16: RG_QRA(__half); break;
@@ -441,13 +481,21 @@ int rg_b200_swiglu(const rg_swiglu_params *p, void *, const void *const *in, voi
     const uint64_t total = static_cast<uint64_t>(p->rows) * p->f;
     if (total == 0) return RG_OK;
     auto st = static_cast<cudaStream_t>(stream);
-    const unsigned g = grid_for(total, 256);
+    const unsigned vn = p->dtype == RG_F32 ? 4u : 8u;
+    const bool vec = p->f % vn == 0 && aligned16(in[0]) && aligned16(out[0]);
+    const unsigned g = grid_for(vec ? total / vn : total, 256);
+#define RG_SWIGLU(T)                                                                                                               \
+    (vec ? launch_pdl(swiglu_kernel<T, true>, dim3(g), dim3(256), 0, st, static_cast<const T *>(in[0]), static_cast<T *>(out[0]), \
+                      p->rows, p->f)                                                                                               \
+         : launch_pdl(swiglu_kernel<T, false>, dim3(g), dim3(256), 0, st, static_cast<const T *>(in[0]), static_cast<T *>(out[0]), \
+                      p->rows, p->f))
     switch (p->dtype) {
-        case RG_F32: launch_pdl(swiglu_kernel<float>, dim3(g), dim3(256), 0, st, static_cast<const float *>(in[0]), static_cast<float *>(out[0]), p->rows, p->f); break;
-        case RG_FP16: launch_pdl(swiglu_kernel<__half>, dim3(g), dim3(256), 0, st, static_cast<const __half *>(in[0]), static_cast<__half *>(out[0]), p->rows, p->f); break;
-        case RG_BF16: launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, st, static_cast<const __nv_bfloat16 *>(in[0]), static_cast<__nv_bfloat16 *>(out[0]), p->rows, p->f); break;
+        case RG_F32: RG_SWIGLU(float); break;
+        case RG_FP16: RG_SWIGLU(__half); break;
+        case RG_BF16: RG_SWIGLU(__nv_bfloat16); break;
         default: return RG_ERR_DTYPE;
     }
+#undef RG_SWIGLU
     count_launch();
     return launch_status();
 }

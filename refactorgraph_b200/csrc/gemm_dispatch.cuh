@@ -6,6 +6,8 @@ int gemm_simt(const rg_mat_mul_params *p, const void *const *in, void *const *ou
 int linear_stream(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
 // tcgen05/TMEM GEMM: Y[m,n] = alpha * A[m,k] * B[n,k]^T (+ beta*C), fp16/bf16, fp32 accumulation in TMEM.
 int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st);
+int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
+int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
 size_t gemm_tc_workspace(const rg_mat_mul_params *p);// split-K partials + arrival counters (zero before first use)
 bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *const *out);
 int linear_error_word();

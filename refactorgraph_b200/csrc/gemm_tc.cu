@@ -38,6 +38,15 @@ struct TcArgs {
     float *partial;    // [tiles][splits][128][BN] fp32, used when splits > 1
     unsigned *counter; // [tiles] arrival counters, zero before the first call and left at zero
     uint32_t early;    // operand that no earlier kernel of the stream writes (a weight): 1 = A, 2 = B, 0 = neither
+    // QKV epilogue (rope != 0): columns are [q heads | k heads | v heads] of head_dim 128, rows are tokens; q is rotated into
+    // q_out[token, nq * 128], k rotated and v copied into the caches at pos[token] of sequence token / tokens_per_seq
+    uint32_t swiglu;   // != 0: B tile = 128 gate rows + the matching 128 up rows (swiglu rows further down B); Y[m, n / 2] = silu(g) * u
+    uint32_t rope, nq, tokens_per_seq;
+    float log2_theta;
+    const int64_t *pos;
+    const int32_t *table;
+    void *q_out, *kc, *vc;
+    rg_kv_layout kv;
 };
 
 // ---- tcgen05 / TMA PTX ------------------------------------------------------------------------------------
@@ -168,6 +177,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     if (warp == 4) {
         if (lane == 0) {
             uint32_t it = 0, pre = 0;
+            // B tile of column tile nt: BN consecutive rows of B, or (SiLU-gate form) 128 gate rows and their 128 up rows
+            auto load_b = [&](uint8_t *dst, uint32_t kb, uint32_t nt, uint64_t *bar) {
+                if (BN == 256 && a.swiglu) {
+                    tma_load_2d(dst, &tmap_b, kb * TC_BK, nt * 128, bar);
+                    tma_load_2d(dst + 128 * TC_BK * 2, &tmap_b, kb * TC_BK, a.swiglu + nt * 128, bar);
+                } else {
+                    tma_load_2d(dst, &tmap_b, kb * TC_BK, nt * BN, bar);
+                }
+            };
             if (a.early && blockIdx.x < items) {
                 // weight tiles of this CTA's first item go in flight before the wait; their partner tiles follow after it
                 uint32_t mt, nt;
@@ -179,7 +197,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     uint8_t *st = smem + pre * STAGE_BYTES;
                     if (a.early == 1) tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[pre]);
                     else
-                        tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, nt * BN, &full[pre]);
+                        load_b(st + A_BYTES, kb, nt, &full[pre]);
                 }
             }
             pdl_wait();
@@ -192,7 +210,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     uint8_t *st = smem + s * STAGE_BYTES;
                     if (it < pre) {// stage armed and half filled above
-                        if (a.early == 1) tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, nt * BN, &full[s]);
+                        if (a.early == 1) load_b(st + A_BYTES, kb, nt, &full[s]);
                         else
                             tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[s]);
                         continue;
@@ -204,7 +222,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                     mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
                     tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[s]);
-                    tma_load_2d(st + A_BYTES, &tmap_b, kb * TC_BK, nt * BN, &full[s]);
+                    load_b(st + A_BYTES, kb, nt, &full[s]);
                 }
             }
         }
@@ -322,6 +340,109 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 continue;
             }
             const uint32_t row = m0 + warp * 32 + lane;
+            if constexpr (BN == 256) {
+                if (a.swiglu) {
+                    // accumulator columns [0, 128) = gate, [128, 256) = up of output columns n0/2 .. n0/2 + 127
+                    const uint32_t j0 = (n0 / 256) * 128, f = a.n / 2;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < 128; c0 += 32) {
+                        uint32_t gt[32], up[32];
+                        const uint32_t taddr = tmem_base + buf * BN + ((warp * 32u) << 16) + c0;
+                        tmem_ld_32x32(taddr, gt);
+                        tmem_ld_32x32(taddr + 128, up);
+                        tmem_ld_wait();
+                        if (row < a.m && j0 + c0 < f) {
+                            T *dst = Y + static_cast<uint64_t>(row) * f + j0 + c0;
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                float o[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const float g = a.alpha * __uint_as_float(gt[j + e]), u = a.alpha * __uint_as_float(up[j + e]);
+                                    o[e] = g / (1.f + expf(-g)) * u;
+                                }
+                                Vec16<T> v;
+                                v.pack(o);
+                                v.store(dst + j);
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    continue;
+                }
+            }
+            if constexpr (BN >= 128) {
+                if (a.rope) {
+                    // this thread's token: rotate the pairs (i, i + 64) of every q and k head of the tile, copy v heads, and
+                    // write each head straight to its destination (q buffer or KV cache, contiguous or paged)
+                    const bool live = row < a.m;
+                    const int64_t p = live ? a.pos[row] : 0;
+                    const uint32_t seq = a.tokens_per_seq > 1 ? row / a.tokens_per_seq : row, nkv = a.kv.n_kv_heads;
+                    uint64_t cache_row = 0;// element offset of (seq, kv head 0, p) in a cache, without the head term
+                    uint32_t head_pitch = 0;
+                    if (live) {
+                        if (a.table) {
+                            const uint32_t page = a.kv.page_size;
+                            const int32_t blk = a.table[static_cast<uint64_t>(seq) * a.kv.max_blocks_per_seq + static_cast<uint32_t>(p) / page];
+                            cache_row = (static_cast<uint64_t>(blk) * nkv * page + static_cast<uint32_t>(p) % page) * 128u;
+                            head_pitch = page * 128u;
+                        } else {
+                            cache_row = (static_cast<uint64_t>(seq) * nkv * a.kv.max_seq + static_cast<uint64_t>(p)) * 128u;
+                            head_pitch = a.kv.max_seq * 128u;
+                        }
+                    }
+#pragma unroll 1
+                    for (int pc = 0; pc < 2; ++pc) {
+                        float cs[32], sn[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float inv_freq = exp2f(-a.log2_theta * (2.0f * static_cast<float>(pc * 32 + j) / 128.0f));
+                            sincosf(static_cast<float>(p) * inv_freq, &sn[j], &cs[j]);
+                        }
+#pragma unroll 1
+                        for (int hh = 0; hh < BN / 128; ++hh) {
+                            const uint32_t col0 = n0 + hh * 128;
+                            if (col0 >= a.n) break;
+                            uint32_t lo[32], hi[32];
+                            const uint32_t taddr = tmem_base + buf * BN + ((warp * 32u) << 16) + hh * 128 + pc * 32;
+                            tmem_ld_32x32(taddr, lo);
+                            tmem_ld_32x32(taddr + 64, hi);
+                            tmem_ld_wait();
+                            if (!live) continue;
+                            const uint32_t gh = col0 / 128;
+                            T *dst;
+                            if (gh < a.nq) {
+                                dst = static_cast<T *>(a.q_out) + (static_cast<uint64_t>(row) * a.nq + gh) * 128u;
+                            } else {
+                                const bool is_k = gh < a.nq + nkv;
+                                const uint32_t kvh = is_k ? gh - a.nq : gh - a.nq - nkv;
+                                dst = static_cast<T *>(is_k ? a.kc : a.vc) + cache_row + static_cast<uint64_t>(kvh) * head_pitch;
+                            }
+                            const bool rotate = gh < a.nq + nkv;
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                float fl[8], fh[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const float x0 = a.alpha * __uint_as_float(lo[j + e]), x1 = a.alpha * __uint_as_float(hi[j + e]);
+                                    fl[e] = rotate ? x0 * cs[j + e] - x1 * sn[j + e] : x0;
+                                    fh[e] = rotate ? x1 * cs[j + e] + x0 * sn[j + e] : x1;
+                                }
+                                Vec16<T> vl, vh;
+                                vl.pack(fl), vh.pack(fh);
+                                vl.store(dst + pc * 32 + j);
+                                vh.store(dst + 64 + pc * 32 + j);
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    continue;
+                }
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -527,6 +648,49 @@ int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *c
         if (rc != RG_OK) return rc;
     }
     return RG_OK;
+}
+
+// Y = X W^T with the QKV split, rotation and cache append in the epilogue (rg_b200_linear, epilogue 3, more than 64 tokens).
+int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+    if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return RG_ERR_DTYPE;
+    const uint32_t nq = p->n_heads, nkv = p->kv.n_kv_heads;
+    if (p->kv.head_dim != 128 || nkv == 0 || nq == 0 || p->n != (nq + 2 * nkv) * 128u || p->m <= 64) return RG_ERR_SHAPE;
+    if (p->prologue != 0 || p->k % 8 != 0 || p->k < 64 || !(p->theta > 0.f)) return RG_ERR_UNSUPPORTED;
+    if (!in[0] || !in[1] || !in[4] || !out[0] || !out[1] || !out[2]) return RG_ERR_NULL;
+    if (in[5] && p->kv.page_size == 0) return RG_ERR_SHAPE;
+    if (!aligned16(in[0]) || !aligned16(in[1]) || !aligned16(out[0]) || !aligned16(out[1]) || !aligned16(out[2])) return RG_ERR_ALIGN;
+    if (!encode_fn()) return RG_ERR_UNSUPPORTED;
+    const int is_bf16 = p->dtype == RG_BF16;
+    TcArgs a = {};
+    a.alpha = 1.f, a.beta = 0.f, a.is_bf16 = is_bf16, a.k = p->k, a.m = p->m, a.n = p->n;
+    a.splits = 1, a.early = 2;
+    a.Y = out[0], a.y_row_stride = p->n, a.y_col_stride = 1;
+    a.rope = 1, a.nq = nq, a.tokens_per_seq = p->tokens_per_seq, a.log2_theta = log2f(p->theta);
+    a.pos = static_cast<const int64_t *>(in[4]), a.table = static_cast<const int32_t *>(in[5]);
+    a.q_out = out[0], a.kc = out[1], a.vc = out[2], a.kv = p->kv;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, in[0], is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, in[1], is_bf16, p->n, p->k, p->k, 256)) return RG_ERR_CUDA;
+    return is_bf16 ? tc_launch<__nv_bfloat16, 256, 4>(ma, mb, a, st) : tc_launch<__half, 256, 4>(ma, mb, a, st);
+}
+
+// Y[m, n/2] = silu(X Wg^T) * (X Wu^T), W = [gate rows ; up rows] (rg_b200_linear, epilogue 2, more than 64 tokens): one B tile
+// pairs 128 gate rows with their 128 up rows, so both halves of an output column meet in one accumulator.
+int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+    if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return RG_ERR_DTYPE;
+    const uint32_t f = p->n / 2;
+    if (p->m <= 64 || p->n % 2 != 0 || f % 128 != 0) return RG_ERR_SHAPE;
+    if (p->prologue != 0 || p->k % 8 != 0 || p->k < 64) return RG_ERR_UNSUPPORTED;
+    if (!in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
+    if (!aligned16(in[0]) || !aligned16(in[1]) || !aligned16(out[0])) return RG_ERR_ALIGN;
+    if (!encode_fn()) return RG_ERR_UNSUPPORTED;
+    const int is_bf16 = p->dtype == RG_BF16;
+    TcArgs a = {};
+    a.alpha = 1.f, a.beta = 0.f, a.is_bf16 = is_bf16, a.k = p->k, a.m = p->m, a.n = p->n;
+    a.splits = 1, a.early = 2, a.swiglu = f;
+    a.Y = out[0], a.y_row_stride = f, a.y_col_stride = 1;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, in[0], is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, in[1], is_bf16, p->n, p->k, p->k, 128)) return RG_ERR_CUDA;
+    return is_bf16 ? tc_launch<__nv_bfloat16, 256, 4>(ma, mb, a, st) : tc_launch<__half, 256, 4>(ma, mb, a, st);
 }
 
 int gemm_tc_error_word() {

@@ -16,7 +16,7 @@
 //  * programmatic dependent launch: the weight stream does not depend on the previous kernel, so the producer
 //    starts immediately and only the consumers execute griddepcontrol.wait before touching activations.
 //  * every mbarrier wait is bounded (~2 s); on expiry the kernel records an error word and leaves normally.
-#include "common.cuh"
+#include "gemm_dispatch.cuh"
 #include <cstdlib>
 
 namespace rg {
@@ -404,6 +404,9 @@ extern "C" {
 size_t rg_b200_linear_workspace(const rg_linear_params *) { return 0; }
 int rg_b200_linear(const rg_linear_params *p, void *, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out) return RG_ERR_NULL;
+    // many tokens (prefill): the QKV projection runs on the tensor cores with the same epilogue
+    if (p->m > 64 && p->epilogue == 3) return gemm_tc_qkv_rope(p, in, out, static_cast<cudaStream_t>(stream));
+    if (p->m > 64 && p->epilogue == 2) return gemm_tc_swiglu(p, in, out, static_cast<cudaStream_t>(stream));
     return linear_stream(p, in, out, static_cast<cudaStream_t>(stream));
 }
 }

@@ -80,11 +80,12 @@ namespace refactor::kernel {
     struct FusedLinearCollector final : public InfoCollector {
         int prologue, epilogue;
         float epsilon, theta;
-        dim_t nHeads, nKVHeads, headDim, maxSeq, pageSize;
+        dim_t nHeads, nKVHeads, headDim, maxSeq, pageSize, tokensPerSeq;
         FusedLinearCollector(Target target, int prologue_, int epilogue_, float epsilon_, float theta_, dim_t nHeads_,
-                             dim_t nKVHeads_, dim_t headDim_, dim_t maxSeq_, dim_t pageSize_) noexcept
+                             dim_t nKVHeads_, dim_t headDim_, dim_t maxSeq_, dim_t pageSize_, dim_t tokensPerSeq_ = 0) noexcept
             : InfoCollector(target), prologue(prologue_), epilogue(epilogue_), epsilon(epsilon_), theta(theta_),
-              nHeads(nHeads_), nKVHeads(nKVHeads_), headDim(headDim_), maxSeq(maxSeq_), pageSize(pageSize_) {}
+              nHeads(nHeads_), nKVHeads(nKVHeads_), headDim(headDim_), maxSeq(maxSeq_), pageSize(pageSize_),
+              tokensPerSeq(tokensPerSeq_) {}
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
     // Split-K flash-decoding (rg_b200_attn_decode): {q[B,nH,D], k_cache, v_cache, seq_lens int64[B], [block_table]} -> {o}

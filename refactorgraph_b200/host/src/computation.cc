@@ -229,16 +229,16 @@ namespace refactor::computation {
     struct FusedLinear final : Operator {
         int prologue, epilogue;
         float epsilon, theta;
-        dim_t nHeads, nKVHeads, headDim, maxSeq, pageSize;
+        dim_t nHeads, nKVHeads, headDim, maxSeq, pageSize, tokensPerSeq;
         explicit FusedLinear(Attributes const &a)
             : prologue(static_cast<int>(getInt(a, "prologue", 0))), epilogue(static_cast<int>(getInt(a, "epilogue", 0))),
               epsilon(static_cast<float>(getFloat(a, "epsilon", 1e-5))), theta(static_cast<float>(getFloat(a, "theta", 10000.0))),
               nHeads(static_cast<dim_t>(getInt(a, "n_heads", 0))), nKVHeads(static_cast<dim_t>(getInt(a, "n_kv_heads", 0))),
               headDim(static_cast<dim_t>(getInt(a, "head_dim", 0))), maxSeq(static_cast<dim_t>(getInt(a, "max_seq", 0))),
-              pageSize(static_cast<dim_t>(getInt(a, "page_size", 0))) {}
+              pageSize(static_cast<dim_t>(getInt(a, "page_size", 0))), tokensPerSeq(static_cast<dim_t>(getInt(a, "tokens_per_seq", 0))) {}
         RG_OP_NAME("FusedLinear")
         CollectorBox candidateKernels(Target t) const final {
-            return std::make_unique<FusedLinearCollector>(t, prologue, epilogue, epsilon, theta, nHeads, nKVHeads, headDim, maxSeq, pageSize);
+            return std::make_unique<FusedLinearCollector>(t, prologue, epilogue, epsilon, theta, nHeads, nKVHeads, headDim, maxSeq, pageSize, tokensPerSeq);
         }
         std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
             auto const &x = in[0].get();

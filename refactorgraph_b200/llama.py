@@ -135,9 +135,10 @@ def decode_step_graph_single_kernel(cfg: LlamaConfig):
     return g, index
 
 
-def prefill_graph(cfg: LlamaConfig, seq: int, top_k: int = 1):
+def prefill_graph(cfg: LlamaConfig, seq: int, top_k: int = 1, fused_rope: bool = True):   # fused_rope: GEMM-epilogue fusions on
     """Causal prefill of `cfg.batch` sequences of `seq` tokens (token-major activations [B*S, hidden]): per layer
-    RmsNormalization, MatMul (tcgen05), QkvRopeAppend (writes the K/V caches), AttentionPrefill, MatMul(+residual),
+    RmsNormalization, Linear (tcgen05 QKV product whose epilogue splits the heads, rotates q and k and writes the K/V
+    caches; with `fused_rope=False`, head_dim != 128 or fewer than 65 tokens: MatMul + QkvRopeAppend), AttentionPrefill, MatMul(+residual),
     RmsNormalization, MatMul, SwiGLU, MatMul(+residual); then the LM head on the last token of every sequence + TopK.
     Inputs: ids[B*S], positions[B*S], last[B] (row index of each sequence's last token), weights, caches."""
     g = GraphBuilder()
@@ -154,14 +155,22 @@ def prefill_graph(cfg: LlamaConfig, seq: int, top_k: int = 1):
     for l in range(cfg.layers):
         kc, vc = f"l{l}.k_cache", f"l{l}.v_cache"
         n1 = g.op("llm::RmsNormalization", [x, f"l{l}.norm1"], epsilon=cfg.eps)
-        qkv = g.op("llm::MatMul", [n1, f"l{l}.wqkv"], transB=1)
-        q = g.op("b200::QkvRopeAppend", [qkv, pos, kc, vc], n_heads=cfg.heads, n_kv_heads=cfg.kv_heads, head_dim=D, theta=cfg.theta,
-                 tokens_per_seq=seq)
+        if fused_rope and D == 128 and n > 64:
+            # QKV projection on the tcgen05 GEMM with the head split, rotation and cache append as its epilogue
+            q = g.op("b200::Linear", [n1, f"l{l}.wqkv", pos, kc, vc], prologue=0, epilogue=3, n_heads=cfg.heads, n_kv_heads=cfg.kv_heads,
+                     head_dim=D, theta=cfg.theta, max_seq=cfg.max_seq, tokens_per_seq=seq)
+        else:
+            qkv = g.op("llm::MatMul", [n1, f"l{l}.wqkv"], transB=1)
+            q = g.op("b200::QkvRopeAppend", [qkv, pos, kc, vc], n_heads=cfg.heads, n_kv_heads=cfg.kv_heads, head_dim=D, theta=cfg.theta,
+                     tokens_per_seq=seq)
         a = g.op("b200::AttentionPrefill", [q, kc, vc], n_heads=cfg.heads, seq_len=seq)
         h = g.op("llm::MatMul", [a, f"l{l}.wo", x], transB=1)           # Y = A W^T + 1 * C: the residual add rides in the epilogue
         n2 = g.op("llm::RmsNormalization", [h, f"l{l}.norm2"], epsilon=cfg.eps)
-        gu = g.op("llm::MatMul", [n2, f"l{l}.wgu"], transB=1)
-        u = g.op("b200::SwiGLU", [gu])
+        if fused_rope and cfg.ffn % 128 == 0 and n > 64:
+            u = g.op("b200::Linear", [n2, f"l{l}.wgu"], prologue=0, epilogue=2)     # silu(gate) * up in the GEMM epilogue
+        else:
+            gu = g.op("llm::MatMul", [n2, f"l{l}.wgu"], transB=1)
+            u = g.op("b200::SwiGLU", [gu])
         x = g.op("llm::MatMul", [u, f"l{l}.wd", h], transB=1)
     xl = g.op("onnx::Gather", [x, last], axis=0)
     xf = g.op("llm::RmsNormalization", [xl, "norm_f"], epsilon=cfg.eps)

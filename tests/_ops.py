@@ -163,10 +163,11 @@ def kv_layout(n_kv, d, max_seq=0, page=0, max_blocks=0):
 
 
 def linear(x, w, g=None, eps=1e-6, residual=None, epilogue=0, n_heads=0, kv=None, positions=None, table=None,
-           k_cache=None, v_cache=None, theta=10000.0, check=True):
+           k_cache=None, v_cache=None, theta=10000.0, check=True, tokens_per_seq=0):
     m, k = x.shape
     n = w.shape[0]
     p = capi.LinearParams()
+    p.tokens_per_seq = tokens_per_seq
     p.dtype, p.m, p.n, p.k = DT[x.dtype], m, n, k
     p.prologue, p.epilogue, p.epsilon, p.n_heads, p.theta = int(g is not None), epilogue, eps, n_heads, theta
     if kv is not None:

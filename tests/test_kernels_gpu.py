@@ -325,6 +325,62 @@ def test_linear_qkv_rope_append(dtype, paged, nq, nkv, m):
     assert int((kc != 0).sum()) <= m * nkv * D and int((vc != 0).sum()) <= m * nkv * D
 
 
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("paged", [False, True])
+@pytest.mark.parametrize("nq,nkv,seqs,S", [(4, 2, 2, 96), (3, 1, 1, 130), (2, 2, 3, 70)])
+def test_linear_qkv_rope_append_many_tokens(dtype, paged, nq, nkv, seqs, S):
+    """More than 64 tokens (prefill): the same operator runs on the tcgen05 GEMM and splits, rotates and appends in its
+    epilogue.  Token t belongs to sequence t // S; an odd head count leaves the last 256-column tile half empty."""
+    rng = np.random.default_rng(nq * 7 + nkv + S)
+    D, k, m = 128, 512, seqs * S
+    n = (nq + 2 * nkv) * D
+    x = rnd16(rng.standard_normal((m, k)).astype(np.float32), dtype)
+    w = rnd16((0.05 * rng.standard_normal((n, k))).astype(np.float32), dtype)
+    start = rng.integers(0, 40, (seqs,))
+    pos = np.concatenate([start[b] + np.arange(S) for b in range(seqs)]).astype(np.int64)
+    q_want, k_want, v_want = onp.linear_fused(x, w, epilogue=3, n_heads=nq, n_kv=nkv, head_dim=D, positions=pos)
+    seq_of = np.arange(m) // S
+    if paged:
+        page, max_blocks = 16, 16
+        n_blocks = seqs * max_blocks
+        table = rng.permutation(n_blocks).reshape(seqs, max_blocks).astype(np.int32)
+        kc = torch.zeros(n_blocks, nkv, page, D, dtype=dtype, device="cuda")
+        vc = torch.zeros_like(kc)
+        kv = ops.kv_layout(nkv, D, 0, page, max_blocks)
+        q = ops.linear(ops.dev(x, dtype), ops.dev(w, dtype), epilogue=3, n_heads=nq, kv=kv, positions=ops.dev(pos), table=ops.dev(table),
+                       k_cache=kc, v_cache=vc, tokens_per_seq=S)
+        k_got = torch.stack([kc[table[seq_of[i], pos[i] // page], :, pos[i] % page] for i in range(m)])
+        v_got = torch.stack([vc[table[seq_of[i], pos[i] // page], :, pos[i] % page] for i in range(m)])
+    else:
+        max_seq = 256
+        kc = torch.zeros(seqs, nkv, max_seq, D, dtype=dtype, device="cuda")
+        vc = torch.zeros_like(kc)
+        kv = ops.kv_layout(nkv, D, max_seq)
+        q = ops.linear(ops.dev(x, dtype), ops.dev(w, dtype), epilogue=3, n_heads=nq, kv=kv, positions=ops.dev(pos), k_cache=kc, v_cache=vc,
+                       tokens_per_seq=S)
+        k_got = torch.stack([kc[seq_of[i], :, pos[i]] for i in range(m)])
+        v_got = torch.stack([vc[seq_of[i], :, pos[i]] for i in range(m)])
+    close_half(q.reshape(m, nq, D), q_want)
+    close_half(k_got, k_want)
+    close_half(v_got, v_want)
+    assert int((kc != 0).sum()) <= m * nkv * D and int((vc != 0).sum()) <= m * nkv * D   # nothing else was touched
+    assert capi.load().rg_b200_error_state() == 0
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("m,f,k", [(200, 256, 512), (65, 384, 64), (300, 128, 1024)])
+def test_linear_silu_gate_many_tokens(dtype, m, f, k):
+    """More than 64 tokens: silu(gate) * up computed in the epilogue of the tcgen05 GEMM (a B tile pairs 128 gate rows
+    with their 128 up rows)."""
+    rng = np.random.default_rng(m + f + k)
+    x = rnd16(rng.standard_normal((m, k)).astype(np.float32), dtype)
+    w = rnd16((0.05 * rng.standard_normal((2 * f, k))).astype(np.float32), dtype)
+    y = ops.linear(ops.dev(x, dtype), ops.dev(w, dtype), epilogue=2)
+    assert tuple(y.shape) == (m, f)
+    close_half(y, onp.linear_fused(x, w, epilogue=2))
+    assert capi.load().rg_b200_error_state() == 0
+
+
 def test_linear_rejects_what_it_cannot_do():
     x = torch.zeros(5, 4096, dtype=torch.float16, device="cuda")
     w = torch.zeros(64, 4096, dtype=torch.float16, device="cuda")
