@@ -239,28 +239,6 @@ template<int V> __device__ __forceinline__ void mg_reduce_halving(float (&vals)[
     for (; o > 0; o >>= 1) vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], o);
 }
 
-template<class T> __device__ __forceinline__ float2 unpack2(uint32_t w);
-template<> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
-    __half2 h;
-    *reinterpret_cast<uint32_t *>(&h) = w;
-    return __half22float2(h);
-}
-template<> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
-    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-}
-// D += A(16x16, row) * B(16x8, col) on the warp-level tensor path, 16-bit inputs, fp32 accumulators
-template<class T> __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
-template<> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-template<> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
 // Consumes `nu` units of a linear phase from the ring: R rows per unit, KC live 16-byte chunks per thread along k.
 // part[(i*4 + row) * MG_NW + warp] receives each warp's partial row sums of local unit i.
 template<class T, int R, int KC>
