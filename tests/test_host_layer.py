@@ -4,7 +4,7 @@ import pytest
 
 from refactorgraph_b200 import python_ffi as ffi
 from refactorgraph_b200.graph_builder import F32, FP16, I64, GraphBuilder
-from refactorgraph_b200.llama import LlamaConfig, decode_step_graph, prefill_graph_reference_ops, seeded_weights
+from refactorgraph_b200.llama import LlamaConfig, decode_step_graph, prefill_graph, prefill_graph_reference_ops, seeded_weights
 
 
 def test_module_surface_matches_the_reference_names():
@@ -72,3 +72,17 @@ def test_decoder_graphs_assemble():
     assert set(idx2) == {"logits", "topk_idx", "topk_val"}
     with pytest.raises(RuntimeError, match="No kernel selected"):
         g2.compiler().compile("cpu", "flat", [])  # shape inference over the whole graph ran before this error
+
+
+def test_prefill_graph_with_fused_epilogues_assembles():
+    """More than 64 tokens and head_dim 128: the QKV and gate/up products are b200::Linear nodes (GEMM epilogues do the
+    RoPE + cache append and the SiLU gate); otherwise MatMul + QkvRopeAppend / SwiGLU.  Shape inference runs for both."""
+    cfg = LlamaConfig(layers=2, hidden=256, heads=2, kv_heads=1, head_dim=128, ffn=512, vocab=1000, max_seq=128, batch=2)
+    for fused, seq in ((True, 64), (False, 64), (True, 16)):
+        g, index = prefill_graph(cfg, seq, fused_rope=fused)
+        assert {"next", "probs", "logits", "ids", "positions", "last"} <= set(index)
+        kinds = {name.split("_", 1)[1] for name in g.nodes}          # node names are "<number>_<operator>"
+        assert ("Linear" in kinds) == (fused and cfg.batch * seq > 64)
+        assert ("QkvRopeAppend" in kinds) != ("Linear" in kinds)
+        with pytest.raises(RuntimeError, match="No kernel selected"):
+            g.compiler().compile("cpu", "flat", [])
