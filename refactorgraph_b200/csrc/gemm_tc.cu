@@ -34,7 +34,8 @@ struct TcArgs {
     uint32_t c_row_stride, c_col_stride;
     uint64_t y_row_stride, y_col_stride;// element strides of Y over the kernel's (row, col) = lets swapped runs write Y^T
     int is_bf16;
-    uint32_t splits;   // k-splits per output tile (1 = none)
+    uint32_t splits;   // partial slots per output tile: the k-splits (1 = none), or with streamk the most CTAs a tile can span
+    uint32_t streamk;  // != 0: CTA c owns the contiguous run [U c / G, U (c+1) / G) of the U = tiles * kblocks (tile, k-block) units
     float *partial;    // [tiles][splits][128][BN] fp32, used when splits > 1
     unsigned *counter; // [tiles] arrival counters, zero before the first call and left at zero
     uint32_t early;    // operand that no earlier kernel of the stream writes (a weight): 1 = A, 2 = B, 0 = neither
@@ -130,6 +131,48 @@ __device__ __forceinline__ void tile_coords(uint32_t t, uint32_t m_tiles, uint32
     nt = r / rows;
 }
 
+// One CTA's work, as (tile, k-block range) segments.  Split mode: items c, c + G, ... of tiles * splits, item = (tile, split).
+// Stream-K mode: a contiguous run of (tile, k-block) units, so every CTA streams the same number of bytes whatever the tile
+// count; a tile that spans several CTAs is summed by the last of them to arrive (ord = this CTA's place among them).
+struct TcSeg {
+    uint32_t tile, kb0, kb1, ord, ncontrib;
+};
+struct TcWalk {
+    uint32_t streamk, splits, kblocks, items, item, G;
+    uint64_t U, u, u1;
+    __device__ __forceinline__ void init(const TcArgs &a, uint32_t tiles, uint32_t kblocks_) {
+        streamk = a.streamk, splits = a.splits, kblocks = kblocks_, G = gridDim.x;
+        items = tiles * a.splits, item = blockIdx.x;
+        U = static_cast<uint64_t>(tiles) * kblocks_;
+        u = U * blockIdx.x / G, u1 = U * (blockIdx.x + 1) / G;
+    }
+    // CTA that owns unit x: the largest c with floor(U c / G) <= x
+    __device__ __forceinline__ uint32_t owner(uint64_t x) const { return static_cast<uint32_t>(((x + 1) * G + U - 1) / U - 1); }
+    __device__ __forceinline__ bool next(TcSeg &s) {
+        if (!streamk) {
+            if (item >= items) return false;
+            const uint32_t ks = item % splits;
+            s.tile = item / splits, s.kb0 = kblocks * ks / splits, s.kb1 = kblocks * (ks + 1) / splits;
+            s.ord = ks, s.ncontrib = splits;
+            item += G;
+            return true;
+        }
+        if (u >= u1) return false;
+        s.tile = static_cast<uint32_t>(u / kblocks), s.kb0 = static_cast<uint32_t>(u % kblocks);
+        const uint64_t left = u1 - u;
+        s.kb1 = left < kblocks - s.kb0 ? s.kb0 + static_cast<uint32_t>(left) : kblocks;
+        u += s.kb1 - s.kb0;
+        if (s.kb0 == 0 && s.kb1 == kblocks) {
+            s.ord = 0, s.ncontrib = 1;
+        } else {
+            const uint64_t x0 = static_cast<uint64_t>(s.tile) * kblocks;
+            const uint32_t cf = owner(x0), cl = owner(x0 + kblocks - 1);
+            s.ord = blockIdx.x - cf, s.ncontrib = cl - cf + 1;
+        }
+        return true;
+    }
+};
+
 // Persistent: CTA c computes tiles c, c + gridDim.x, ...  The accumulator is double-buffered in tensor memory (2 x BN
 // columns), so the epilogue of one tile (tcgen05.ld, conversion, stores) overlaps the MMA main loop of the next.
 template<class T, int BN, int STAGES>
@@ -186,27 +229,30 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     tma_load_2d(dst, &tmap_b, kb * TC_BK, nt * BN, bar);
                 }
             };
-            if (a.early && blockIdx.x < items) {
-                // weight tiles of this CTA's first item go in flight before the wait; their partner tiles follow after it
-                uint32_t mt, nt;
-                const uint32_t tile = blockIdx.x / a.splits, ks = blockIdx.x % a.splits;
-                tile_coords(tile, m_tiles, n_tiles, mt, nt);
-                const uint32_t kb0 = kblocks * ks / a.splits, kb1 = kblocks * (ks + 1) / a.splits;
-                for (uint32_t kb = kb0; kb < kb1 && pre < STAGES; ++kb, ++pre) {
-                    mbar_arrive_expect_tx(&full[pre], STAGE_BYTES);
-                    uint8_t *st = smem + pre * STAGE_BYTES;
-                    if (a.early == 1) tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[pre]);
-                    else
-                        load_b(st + A_BYTES, kb, nt, &full[pre]);
+            TcWalk walk;
+            walk.init(a, tiles, kblocks);
+            TcSeg sg;
+            if (a.early) {
+                // weight tiles of this CTA's first segment go in flight before the wait; their partner tiles follow after it
+                TcWalk peek = walk;
+                if (peek.next(sg)) {
+                    uint32_t mt, nt;
+                    tile_coords(sg.tile, m_tiles, n_tiles, mt, nt);
+                    for (uint32_t kb = sg.kb0; kb < sg.kb1 && pre < STAGES; ++kb, ++pre) {
+                        mbar_arrive_expect_tx(&full[pre], STAGE_BYTES);
+                        uint8_t *st = smem + pre * STAGE_BYTES;
+                        if (a.early == 1) tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[pre]);
+                        else
+                            load_b(st + A_BYTES, kb, nt, &full[pre]);
+                    }
                 }
             }
             pdl_wait();
-            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+            bool good = true;
+            while (good && walk.next(sg)) {
                 uint32_t mt, nt;
-                const uint32_t tile = item / a.splits, ks = item % a.splits;
-                tile_coords(tile, m_tiles, n_tiles, mt, nt);
-                const uint32_t kb0 = kblocks * ks / a.splits, kb1 = kblocks * (ks + 1) / a.splits;
-                for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
+                tile_coords(sg.tile, m_tiles, n_tiles, mt, nt);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     uint8_t *st = smem + s * STAGE_BYTES;
                     if (it < pre) {// stage armed and half filled above
@@ -217,7 +263,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                     if (!mbar_wait(&empty[s], ph ^ 1u)) {
                         *failed = 1;
-                        item = items;
+                        good = false;
                         break;
                     }
                     mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
@@ -231,9 +277,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             const uint32_t idesc = instr_desc(a.is_bf16, TC_BM, BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x, ++local) {
-                const uint32_t buf = local & 1u, ks = item % a.splits;
-                const uint32_t kb0 = kblocks * ks / a.splits, kb1 = kblocks * (ks + 1) / a.splits;
+            TcWalk walk;
+            walk.init(a, tiles, kblocks);
+            TcSeg sg;
+            for (; ok && walk.next(sg); ++local) {
+                const uint32_t buf = local & 1u, kb0 = sg.kb0, kb1 = sg.kb1;
                 if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1u) ^ 1u)) {
                     *failed = 4;
                     break;
@@ -267,9 +315,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         const bool c_rowmajor = C && a.c_col_stride == 1 && (a.c_row_stride % 8) == 0;
         __shared__ int s_last;
         uint32_t local = 0;
-        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++local) {
+        TcWalk walk;
+        walk.init(a, tiles, kblocks);
+        TcSeg sg;
+        for (; walk.next(sg); ++local) {
             uint32_t mt, nt;
-            const uint32_t tile = item / a.splits, ks = item % a.splits;
+            const uint32_t tile = sg.tile, ks = sg.ord;
             tile_coords(tile, m_tiles, n_tiles, mt, nt);
             const uint32_t buf = local & 1u, m0 = mt * TC_BM, n0 = nt * BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1u)) {
@@ -277,7 +328,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 break;
             }
             tc_fence_after();
-            if (a.splits > 1) {
+            if (sg.ncontrib > 1) {
                 // split-K: park this split's fp32 tile; the last split to arrive sums all of them in split order
                 const uint32_t trow = warp * 32 + lane;
                 float *mine = a.partial + (static_cast<size_t>(tile) * a.splits + ks) * (TC_BM * BN) + static_cast<size_t>(trow) * BN;
@@ -298,7 +349,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 if (threadIdx.x == 0) {
                     unsigned old;
                     asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(a.counter + tile) : "memory");
-                    s_last = old == a.splits - 1 ? 1 : 0;
+                    s_last = old == sg.ncontrib - 1 ? 1 : 0;
                 }
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (!s_last) continue;
@@ -312,7 +363,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 #pragma unroll
                         for (int c = 0; c < BN / 4; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 2
-                        for (uint32_t sidx = 0; sidx < a.splits; ++sidx) {
+                        for (uint32_t sidx = 0; sidx < sg.ncontrib; ++sidx) {
                             const float4 *src = reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN));
                             float4 v[BN / 4];
 #pragma unroll
@@ -568,6 +619,7 @@ static uint32_t tc_splits(uint32_t tiles, uint32_t kblocks) {
 struct TcPlan {
     bool swap;
     uint32_t bn, tiles, splits;
+    uint32_t streamk_grid;// != 0: stream-K over this many CTAs; `splits` is then the partial slots per tile
     size_t counter_bytes, partial_bytes;
 };
 static TcPlan tc_plan(const rg_mat_mul_params *p) {
@@ -576,12 +628,27 @@ static TcPlan tc_plan(const rg_mat_mul_params *p) {
     const uint32_t km = pl.swap ? p->n : p->m, kn = pl.swap ? p->m : p->n;
     pl.bn = pl.swap ? (p->m <= 32 ? 32 : 64) : (p->n >= 256 ? 256 : 128);
     pl.tiles = ((km + TC_BM - 1) / TC_BM) * ((kn + pl.bn - 1) / pl.bn);
-    pl.splits = pl.swap ? tc_splits(pl.tiles, (p->k + TC_BK - 1) / TC_BK) : 1;
-    if (pl.swap) {// tuning knob: RG_B200_TC_SPLITS=<n> forces the split count of skinny products
+    const uint32_t kblocks = (p->k + TC_BK - 1) / TC_BK;
+    pl.splits = pl.swap ? tc_splits(pl.tiles, kblocks) : 1;
+    pl.streamk_grid = 0;
+    if (pl.swap) {// tuning knobs: RG_B200_TC_SPLITS=<n> forces the split count of skinny products, RG_B200_TC_STREAMK=0/1 the mode
         static const char *force = std::getenv("RG_B200_TC_SPLITS");
+        static const char *sk = std::getenv("RG_B200_TC_STREAMK");
+        const uint32_t sms = static_cast<uint32_t>(sm_count());
+        const uint64_t units = static_cast<uint64_t>(pl.tiles) * kblocks;
+        // stream-K when every SM gets a run of at least 64 k-blocks (1 MiB of weights): below that the partial-tile round
+        // trips of up to two boundary tiles per CTA cost more than the imbalance they remove (measured at 16 / 32 tokens:
+        // 22016 x 4096, 74 k-blocks per SM: 44.5 -> 41.6 us; 8192 x 3584, 24 per SM: 17.8 -> 20.0 us; 7168 x 8192, 48: equal)
+        bool streamk = units / sms >= 64;
+        if (sk && sk[0]) streamk = sk[0] != '0' && units >= sms;
         if (force && force[0]) {
-            const uint32_t f = static_cast<uint32_t>(std::atoi(force)), kb = (p->k + TC_BK - 1) / TC_BK;
-            if (f >= 1) pl.splits = f > kb ? kb : f;
+            const uint32_t f = static_cast<uint32_t>(std::atoi(force));
+            if (f >= 1) pl.splits = f > kblocks ? kblocks : f, streamk = false;
+        }
+        if (streamk) {
+            const uint32_t per = static_cast<uint32_t>(units / sms);// the shortest run
+            const uint32_t slots = (kblocks + per - 1) / per + 1;   // the most CTAs one tile can span
+            if (slots <= 8) pl.streamk_grid = sms, pl.splits = slots;// deeper tiles keep the uniform split (cheaper sums)
         }
     }
     pl.counter_bytes = pl.splits > 1 ? (static_cast<size_t>(pl.tiles) * 4 + 255) / 256 * 256 : 0;
@@ -600,7 +667,8 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs 
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const uint32_t items = ((a.n + BN - 1) / BN) * ((a.m + TC_BM - 1) / TC_BM) * a.splits;
     const uint32_t sms = static_cast<uint32_t>(sm_count());
-    RG_CHECK_CUDA(launch_pdl(kern, dim3(items < sms ? items : sms), dim3(TC_THREADS), smem, st, ma, mb, a));
+    const uint32_t grid = a.streamk ? a.streamk : (items < sms ? items : sms);
+    RG_CHECK_CUDA(launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, st, ma, mb, a));
     count_launch();
     return launch_status();
 }
@@ -617,7 +685,7 @@ int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *c
         const uint8_t *C = p->has_bias ? static_cast<const uint8_t *>(in[2]) + b * p->stride_c * es : nullptr;
         TcArgs a = {};
         a.alpha = p->alpha, a.beta = p->beta, a.is_bf16 = is_bf16, a.k = p->k;
-        a.splits = pl.splits;
+        a.splits = pl.splits, a.streamk = pl.streamk_grid;
         a.counter = static_cast<unsigned *>(ws);
         a.partial = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + pl.counter_bytes);
         CUtensorMap ma, mb;
