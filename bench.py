@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--graph", default="single", choices=["single", "fused"],
                     help="7b / tiny workloads: 'single' = the whole step as one persistent kernel (b200::DecodeStep); "
                          "'fused' = five fused launches per layer replayed as a CUDA graph")
-    ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "attn_decode_b32", "attn_decode_gqa", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
+    ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "attn_decode_b32", "attn_decode_gqa", "attn_decode_gqa_tp2", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
                              "gemm_skinny16", "gemm_skinny32", "gemm_tp8", "all_reduce", "decode_step_timeline"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
     ap.add_argument("--launches", type=int, default=6)
@@ -538,9 +538,10 @@ def run_case(args):
         def launch(i):
             kc, vc = caches[i % len(caches)]
             capi.call("attn_decode", p, [q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), table.data_ptr()], [o.data_ptr()], ws=wsb.data_ptr(), stream=sid)
-    elif args.case == "attn_decode_gqa":
-        # one rank's attention launch of the 70B-shaped model at tensor-parallel 8: 16 sequences x 4096 tokens, 8 query heads on 1 KV head
-        B, L, MS, nq, nkv = 16, 4096, 4096 + 128, 8, 1
+    elif args.case in ("attn_decode_gqa", "attn_decode_gqa_tp2"):
+        # one rank's attention launch of the 70B-shaped model at tensor-parallel 8 (or 2): 16 sequences x 4096 tokens, 8 query
+        # heads on 1 KV head (32 on 4)
+        B, L, MS, nq, nkv = (16, 4096, 4096 + 128, 8, 1) if args.case == "attn_decode_gqa" else (16, 4096, 4096 + 128, 32, 4)
         q = torch.randn(B, nq, D, device=dev).to(dt)
         caches = [(torch.randn(B, nkv, MS, D, device=dev).to(dt), torch.randn(B, nkv, MS, D, device=dev).to(dt)) for _ in range(8)]
         lens = torch.full((B,), L, device=dev, dtype=torch.int64)
