@@ -445,7 +445,7 @@ static DecodePlan decode_plan(const rg_attn_decode_params *p) {
     DecodePlan pl;
     const uint32_t total_tiles = (p->max_len + AD_TILE - 1) / AD_TILE;
     const uint64_t rows = static_cast<uint64_t>(p->batch) * p->n_heads;
-    uint32_t want = static_cast<uint32_t>((4ull * sm_count() + rows - 1) / (rows ? rows : 1));
+    uint32_t want = static_cast<uint32_t>(4ull * sm_count() / (rows ? rows : 1));// rounded down: the CTAs of a launch fit the slots
     if (want < 1) want = 1;
     if (want > total_tiles) want = total_tiles ? total_tiles : 1;
     pl.tiles_per_split = total_tiles ? (total_tiles + want - 1) / want : 1;
