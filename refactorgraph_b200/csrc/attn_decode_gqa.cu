@@ -12,6 +12,7 @@
 namespace rg {
 
 constexpr int GQ_THREADS = 128, GQ_TILE = 64, GQ_D = 128;
+constexpr int GQ_STAGES = 3;// K/V tile buffers: two tiles in flight while one is consumed (2 CTAs per SM)
 constexpr int GQ_REC = GQ_D + 4;// floats per split record: max, sum, 2 pad, accumulator (16-byte aligned)
 
 struct GqaArgs {
@@ -64,7 +65,7 @@ __device__ __forceinline__ uint32_t g_sw(uint32_t r, uint32_t c) { return r * 25
 template<class T>
 __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t sQ = smem_u32(smem), sK = sQ + 4096, sV = sK + 2 * 16384;
+    const uint32_t sQ = smem_u32(smem), sK = sQ + 4096, sV = sK + GQ_STAGES * 16384;
     float *mbuf = reinterpret_cast<float *>(smem + 4096);// [4 warps][16 rows][D + 2], aliases the K/V tiles after the loop
     __shared__ int s_last;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -117,8 +118,10 @@ __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaAr
         g_cp_async16(sQ + g_sw(r, c), Q + static_cast<size_t>(r < gq ? r : 0) * GQ_D + c * 8, r < gq);
     }
     load_tile(t0, 0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");// group 0: queries + first tile
+    if (t0 + 1 < t1) load_tile(t0 + 1, 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");// group 1: second tile (possibly empty)
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
 
     uint32_t qf[8][4];
@@ -133,8 +136,10 @@ __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaAr
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     for (uint32_t tile = t0; tile < t1; ++tile) {
-        const uint32_t buf = (tile - t0) & 1u;
-        if (tile + 1 < t1) load_tile(tile + 1, buf ^ 1u);
+        // on entry tile `tile` has landed and every thread is past the previous tile's math, so the buffer that tile held
+        // ((i + 2) % 3) can take tile + 2: two tiles stay in flight while this one is consumed
+        const uint32_t buf = (tile - t0) % GQ_STAGES;
+        if (tile + 2 < t1) load_tile(tile + 2, (tile - t0 + 2) % GQ_STAGES);
         asm volatile("cp.async.commit_group;" ::: "memory");
         const uint32_t sKb = sK + buf * 16384, sVb = sV + buf * 16384;
         const uint32_t m = lane >> 3, rin = lane & 7u;
@@ -195,7 +200,7 @@ __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaAr
             GMma<T>::run(o[db], pf, vf[0], vf[1]);
             GMma<T>::run(o[db + 1], pf, vf[2], vf[3]);
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");// all but the newest group: the next tile is there
         __syncthreads();
     }
     // ---- merge the four warps (each saw a quarter of every tile) ----
@@ -280,9 +285,9 @@ static GqaPlan gqa_plan(const rg_attn_decode_params *p) {
     GqaPlan pl;
     const uint32_t total_tiles = (p->max_len + GQ_TILE - 1) / GQ_TILE;
     const uint64_t groups = static_cast<uint64_t>(p->batch) * p->kv.n_kv_heads;
-    // All CTAs of the launch should be resident together (3 per SM): one CTA more than the slots and the launch takes two
+    // All CTAs of the launch should be resident together (2 per SM with three 32 KiB tile buffers): one CTA more than the slots and the launch takes two
     // rounds (16 sequences x 4 KV heads: 7 splits = 448 CTAs on 444 slots took 41 us).
-    const uint64_t slots = 3ull * sm_count();
+    const uint64_t slots = 2ull * sm_count();
     uint32_t want = static_cast<uint32_t>(slots / (groups ? groups : 1));
     if (want < 1) want = 1;
     if (want > total_tiles) want = total_tiles ? total_tiles : 1;
@@ -317,7 +322,7 @@ int attn_decode_gqa_launch(const rg_attn_decode_params *p, void *ws, const void 
     a.tiles_per_split = pl.tiles_per_split, a.max_splits = pl.max_splits;
     a.kv = p->kv;
     a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(GQ_D));
-    const size_t smem = 4096 + 4 * 16384;
+    const size_t smem = 4096 + 2 * GQ_STAGES * 16384;
     void (*kern)(const GqaArgs) = p->dtype == RG_FP16 ? attn_decode_gqa_kernel<__half> : attn_decode_gqa_kernel<__nv_bfloat16>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     cudaLaunchConfig_t cfg = {};
