@@ -65,6 +65,28 @@ def test_skinny_swapped_operands(dtype, m, n, k):
 
 
 @pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("m,n,k,residual", [(16, 22016, 4096, False), (32, 32000, 4096, True), (8, 20000, 4104, False)])
+def test_skinny_stream_k(dtype, m, n, k, residual):
+    """Skinny products with at least 64 k-blocks per SM run in stream-K mode: every CTA owns one contiguous run of
+    (tile, k-block) units and tiles that span CTAs are summed by the last to arrive.  The last case has a ragged last
+    row tile and a partial last k-block."""
+    rng = np.random.default_rng(m + n + k)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype).cuda()
+    b = torch.from_numpy((0.02 * rng.standard_normal((n, k))).astype(np.float32)).to(dtype).cuda()
+    want = a.float() @ b.float().T
+    if residual:
+        c = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(dtype).cuda()
+        y = ops.mat_mul(a, b, c=c, trans_b=True, force=3)
+        want = want + c.float()
+    else:
+        y = ops.mat_mul(a, b, trans_b=True, force=3)
+    assert _ok()
+    torch.testing.assert_close(y.float(), want, atol=2e-2, rtol=1e-2)
+    y2 = ops.mat_mul(a, b, c=c, trans_b=True, force=3) if residual else ops.mat_mul(a, b, trans_b=True, force=3)
+    assert torch.equal(y, y2)          # fixed summation order: a second call gives the same bits
+
+
+@pytest.mark.parametrize("dtype", HALF)
 def test_prefill_sized_and_auto_route(dtype):
     torch.backends.cuda.matmul.allow_tf32 = False
     g = torch.Generator(device="cuda").manual_seed(0)
