@@ -419,7 +419,9 @@ def test_attention_reference_layout(dtype, N, nH, nKV, S, D, past):
 @pytest.mark.parametrize("dtype", HALF)
 @pytest.mark.parametrize("B,nH,nKV,D,lens", [
     (1, 32, 32, 128, [2049]), (1, 32, 32, 128, [1]), (3, 8, 2, 128, [64, 65, 1000]), (2, 4, 4, 64, [63, 129]),
-    (4, 8, 1, 128, [512, 4096, 777, 16])])
+    (4, 8, 1, 128, [512, 4096, 777, 16]),
+    # enough tiles (4 x 32 heads x 64) for the tensor-path kernel with the two-stage ring; ragged lengths, one single token
+    (4, 32, 32, 128, [4096, 1, 65, 1000])])
 def test_attn_decode_contiguous(dtype, B, nH, nKV, D, lens):
     rng = np.random.default_rng(sum(lens) + B)
     max_seq = max(lens) + 5
