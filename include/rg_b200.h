@@ -52,9 +52,13 @@ int rg_b200_version(void);
 /* Number of kernels this library has launched in the calling process since load (all entry points). */
 uint64_t rg_b200_launch_count(void);
 /* Synchronises the current device and reports whether any kernel of this library gave up a bounded device-side
- * wait since load: 0 = none; otherwise bit 0 linear, bit 1 decode attention, bit 2 tensor-core GEMM, bit 3 all-reduce, bit 4 decode step;
- * negative = the device could not be queried. */
+ * wait since load: 0 = none; otherwise bit 0 linear, bit 1 decode attention, bit 2 tensor-core GEMM, bit 3 all-reduce, bit 4 decode step,
+ * bit 5 a device-read index (position, sequence length, token id, block-table entry) was out of range and the access
+ * was skipped or clamped; negative = the device could not be queried.  The words are sticky until rg_b200_error_clear. */
 int rg_b200_error_state(void);
+/* Synchronises the current device and clears the words rg_b200_error_state reports (not a communicator's status:
+ * see rg_b200_comm_status).  Returns RG_OK or RG_ERR_CUDA. */
+int rg_b200_error_clear(void);
 
 /* ---------------------------------------------------------------------------------------------
  * RmsNormalization.  Replaces RmsNormalizationCuda
@@ -236,7 +240,11 @@ typedef struct rg_kv_layout {
     uint32_t max_seq;            /* contiguous: tokens per (b, head) */
     uint32_t page_size;          /* paged: tokens per block (16) ; 0 = contiguous */
     uint32_t max_blocks_per_seq; /* paged: row length of the block table */
+    uint32_t n_blocks;           /* paged: blocks in the cache; block-table entries are checked against it (0 = only their sign is checked) */
 } rg_kv_layout;
+/* Every kernel that reads a position, sequence length, token id or block-table entry from device memory checks it
+ * against these bounds (and the vocabulary) before using it: an out-of-range value is never used for an access —
+ * the store is skipped, or the read range is clamped — and bit 5 of rg_b200_error_state is set. */
 
 /* QKV split + RoPE + cache append for batched decode (no reference counterpart; what the m <= 4 linear kernel does in
  * its epilogue, as a separate launch behind a tensor-core GEMM).  qkv[tokens, (n_heads + 2 n_kv_heads) * D]: q heads
@@ -299,7 +307,9 @@ int rg_b200_linear(const rg_linear_params *, void *ws, const void *const *in, vo
  *          lm_head[vocab,hidden], then per layer: norm1, wqkv, wo, norm2, wgu, wd, k_cache, v_cache}
  * outputs {next (int64[1]), prob (fp32[1], softmax probability of the chosen token), logits[vocab]}
  * The workspace must be zero on first use and is left ready for the next call.  Launched cooperatively with one CTA
- * per SM; grid-barrier waits are bounded (RG error state bit 4). */
+ * per SM; grid-barrier waits are bounded (RG error state bit 4).  After rg_b200_error_state has reported bit 4 the
+ * workspace's barrier state is undefined: zero-fill it again before the next call.  A step whose position is not below
+ * max_seq, or whose token id is not below vocab, does nothing (outputs and state untouched) and sets bit 5. */
 typedef struct rg_decode_step_params {
     int32_t dtype; /* RG_FP16, RG_BF16 */
     uint32_t layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_seq;
@@ -386,12 +396,23 @@ int rg_b200_attn_decode_static(const rg_attn_decode_params *, const void *const 
  * (src/04kernel/src/kernels/all_reduce/nccl_kernel.cu:9-19, src/04kernel/src/utilities/cuda/nccl_communicator.cu:11-44).
  * One process per GPU.  rg_b200_comm_create allocates this rank's symmetric buffer and returns an opaque
  * 64-byte IPC handle; the caller exchanges handles out of band (any host transport) and calls
- * rg_b200_comm_connect with all ranks' handles.  The reduction is a one-shot push over NVLink peer memory
- * with plain loads, summed in fp32 in rank order (bit-identical on every rank).  Device-side waits on peer
- * flags are bounded; on expiry the status word is set and the call that observes it returns RG_ERR_TIMEOUT.
+ * rg_b200_comm_connect with all ranks' handles.  The reduction is a push over NVLink peer memory with ordinary
+ * stores (every 32-bit word travels with the call's 32-bit flag; the receiver polls its own memory): up to 4 ranks every
+ * rank sends its whole input to every peer (one-shot); above that each run of chunks has an owner rank that combines
+ * and sends the finished values back (two-shot).  Values are combined in rank order, so every rank gets bit-identical
+ * results.  No TMA and no multicast instruction touches peer memory.
+ * dtype: RG_F32, RG_FP16, RG_BF16 (combined in fp32), RG_F64, RG_U8, RG_I8, RG_I32, RG_U32, RG_I64 (combined in their
+ * own type; integer Sum / Prod wrap, integer Avg divides) — the set AllReduceNccl accepts (nccl_kernel.cc:14-17).
  * op uses AllReduceType (src/04kernel/include/kernel/attributes/communication.h:5-11): 0 Sum, 1 Avg, 2 Min, 3 Max, 4 Prod.
  * inputs {x, residual or NULL}, outputs {y}; y = reduce(x) (+ residual, added after the reduced value has been rounded
- * to the storage type); bytes <= the capacity given at create.  Every rank must issue the same sequence of calls. */
+ * to the storage type); bytes <= the capacity given at create.  Every rank must issue the same sequence of calls.
+ * Waits: a kernel waits for its peers' data for at most the bound set by rg_b200_comm_set_wait_ns (default 2 s),
+ * measured from the moment THIS rank's kernel starts — so ranks must reach matching calls within that bound of one
+ * another (raise it if one process may stall longer, e.g. while it instantiates a CUDA graph).  When the wait runs out
+ * the kernel leaves its output untouched and sets the communicator's status word; from then on the communicator is out
+ * of step with its peers: every later all-reduce on it is a no-op on the device, rg_b200_comm_status and
+ * rg_b200_all_reduce return RG_ERR_TIMEOUT, and bit 3 of rg_b200_error_state stays set until the communicator is
+ * destroyed and a new one is created on every rank.  Call numbers are 64-bit; the 32-bit flag derived from them is never 0. */
 typedef struct rg_comm rg_comm;
 int rg_b200_comm_create(int world, int rank, size_t capacity_bytes, rg_comm **out, void *handle64);
 int rg_b200_comm_connect(rg_comm *, const void *all_handles /* world * 64 bytes */);
@@ -401,7 +422,7 @@ size_t rg_b200_comm_bytes(rg_comm *); /* size of the symmetric allocation behind
 int rg_b200_comm_connect_ptrs(rg_comm *, const void *const *bases);
 /* Bound of the device-side wait for a peer, in nanoseconds (default 2 s). */
 int rg_b200_comm_set_wait_ns(rg_comm *, uint64_t ns);
-int rg_b200_comm_status(rg_comm *); /* RG_OK, or RG_ERR_TIMEOUT once a kernel gave up waiting for a peer; synchronises the device */
+int rg_b200_comm_status(rg_comm *); /* RG_OK, or RG_ERR_TIMEOUT once a kernel gave up waiting for a peer (sticky); synchronises the device */
 int rg_b200_comm_destroy(rg_comm *);
 typedef struct rg_all_reduce_params {
     int32_t dtype, op;

@@ -81,7 +81,7 @@ MM_B_STATIC = 1
 
 class KvLayout(C.Structure):
     _fields_ = [("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("max_seq", C.c_uint32),
-                ("page_size", C.c_uint32), ("max_blocks_per_seq", C.c_uint32)]
+                ("page_size", C.c_uint32), ("max_blocks_per_seq", C.c_uint32), ("n_blocks", C.c_uint32)]
 
 
 class LinearParams(C.Structure):
@@ -133,7 +133,7 @@ OPS = {
     "swiglu": SwigluParams, "decode_step": DecodeStepParams, "attn_prefill": AttnPrefillParams,
 }
 # every symbol include/rg_b200.h declares
-SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_attn_decode_static",
+SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_error_clear", "rg_b200_attn_decode_static",
             "rg_b200_attn_decode_static_capacity", "rg_b200_decode_step_timeline", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_bytes", "rg_b200_comm_connect_ptrs",
             "rg_b200_comm_set_wait_ns",
             "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]

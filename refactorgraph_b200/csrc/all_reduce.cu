@@ -14,7 +14,9 @@
 // No TMA and no multicast instructions touch peer memory.
 #include "gemm_dispatch.cuh"
 #include <cstring>
+#include <mutex>
 #include <new>
+#include <vector>
 
 namespace rg {
 
@@ -39,7 +41,32 @@ struct ArArgs {
     uint64_t wait_ns;
 };
 
-__device__ __forceinline__ float ar_combine(int op, float a, float b) {
+// Element traits: A is the type the combine runs in.  16-bit floats combine in fp32; every other type combines in its
+// own type, as the NCCL call this replaces does (integer sums and products wrap).
+template<class T> struct ArElem {
+    using A = T;
+    static __device__ __forceinline__ A up(T v) { return v; }
+    static __device__ __forceinline__ T down(A v) { return v; }
+};
+template<> struct ArElem<__half> {
+    using A = float;
+    static __device__ __forceinline__ A up(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half down(A v) { return __float2half_rn(v); }
+};
+template<> struct ArElem<__nv_bfloat16> {
+    using A = float;
+    static __device__ __forceinline__ A up(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 down(A v) { return __float2bfloat16_rn(v); }
+};
+template<class A> __device__ __forceinline__ A ar_combine(int op, A a, A b) {
+    switch (op) {
+        case 2: return a < b ? a : b;
+        case 3: return a > b ? a : b;
+        case 4: return a * b;
+        default: return a + b;
+    }
+}
+template<> __device__ __forceinline__ float ar_combine<float>(int op, float a, float b) {
     switch (op) {
         case 2: return fminf(a, b);
         case 3: return fmaxf(a, b);
@@ -47,12 +74,56 @@ __device__ __forceinline__ float ar_combine(int op, float a, float b) {
         default: return a + b;
     }
 }
+template<> __device__ __forceinline__ double ar_combine<double>(int op, double a, double b) {
+    switch (op) {
+        case 2: return fmin(a, b);
+        case 3: return fmax(a, b);
+        case 4: return a * b;
+        default: return a + b;
+    }
+}
+// Avg: floating types multiply by 1 / world (fp32 for the 16-bit types and float, fp64 for double); integers divide.
+template<class A> __device__ __forceinline__ A ar_average(A v, int world) { return v / static_cast<A>(world); }
+template<> __device__ __forceinline__ float ar_average<float>(float v, int world) { return v * (1.0f / static_cast<float>(world)); }
+template<> __device__ __forceinline__ double ar_average<double>(double v, int world) { return v * (1.0 / static_cast<double>(world)); }
+
+// Combines the world chunks in rank order (bit-identical on every rank), applies Avg, then the optional residual: the reduced
+// value is rounded to the storage type before the residual is added, exactly as if the all-reduce and the Add were two operators.
+template<class T>
+__device__ __forceinline__ uint4 ar_reduce_chunk(const uint4 (&raw)[8], int world, int op, const T *res, uint64_t e0, uint64_t count) {
+    constexpr int N = 16 / sizeof(T);
+    using A = typename ArElem<T>::A;
+    A acc[N];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        if (r < world) {
+            const T *v = reinterpret_cast<const T *>(&raw[r]);
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[j] = r == 0 ? ArElem<T>::up(v[j]) : ar_combine<A>(op, acc[j], ArElem<T>::up(v[j]));
+        }
+    }
+    if (op == 1) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = ar_average<A>(acc[j], world);
+    }
+    uint4 out;
+    T *o = reinterpret_cast<T *>(&out);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+        o[j] = ArElem<T>::down(acc[j]);
+        if (res && e0 + j < count) o[j] = ArElem<T>::down(ArElem<T>::up(o[j]) + ArElem<T>::up(res[e0 + j]));
+    }
+    return out;
+}
 
 // byte offset of the slot that holds rank `src`'s input of a call with parity q, inside any rank's allocation; a slot is
 // 2 * capacity bytes because every 4 data bytes travel with a 4-byte flag
 __device__ __forceinline__ size_t ar_slot_off(const ArArgs &a, unsigned q, int src) {
     return AR_HEADER_BYTES + (static_cast<size_t>(q) * a.world + src) * (2 * a.capacity);
 }
+// Flag of call number seq: never 0 (slots start zeroed, so memory no call has written can never look complete) and
+// different from the flag two calls earlier, which is what a slot of the same parity may still hold.
+__device__ __forceinline__ uint32_t ar_flag(unsigned long long seq) { return static_cast<uint32_t>(seq % 0xffffffffull) + 1u; }
 __device__ __forceinline__ void st_volatile_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -65,7 +136,7 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void *p) {
 template<class T>
 __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) {
     pdl_enter();
-    constexpr int N = Vec16<T>::N;
+    constexpr int N = 16 / sizeof(T);
     ArHeader *hdr = reinterpret_cast<ArHeader *>(a.mine);
     __shared__ unsigned long long s_seq;
     if (threadIdx.x == 0) {
@@ -79,15 +150,17 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) 
         }
     }
     __syncthreads();
+    // A communicator whose earlier call gave up a wait is out of step with its peers for good: every later call is a no-op
+    // (outputs untouched, status still set) until the host destroys and recreates it.
+    if (*reinterpret_cast<volatile int *>(&hdr->status) != 0) return;
     const unsigned long long seq = s_seq;
     const unsigned q = static_cast<unsigned>(seq & 1ull);
-    const uint32_t flag = static_cast<uint32_t>(seq);// never 0 for the first 2^32 - 1 calls; slots start zeroed
+    const uint32_t flag = ar_flag(seq);
     const uint64_t chunks = (a.count + N - 1) / N, full_chunks = a.count / N;
     const T *x = static_cast<const T *>(a.x);
     const T *res = static_cast<const T *>(a.res);
     T *y = static_cast<T *>(a.y);
     const size_t my_off = ar_slot_off(a, q, a.rank);
-    const float scale = a.op == 1 ? 1.0f / static_cast<float>(a.world) : 1.0f;
     const uint64_t t0 = global_timer_ns();
 
     for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks; c += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
@@ -133,34 +206,12 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) 
             return;
         }
         // 3. combine in rank order, so that every rank computes bit-identical results
-        float acc[N];
-#pragma unroll
-        for (int r = 0; r < AR_MAX_RANKS; ++r) {
-            if (r < a.world) {
-                Vec16<T> v;
-                v.raw = raw[r];
-                float f[N];
-                v.unpack(f);
-#pragma unroll
-                for (int j = 0; j < N; ++j) acc[j] = r == 0 ? f[j] : ar_combine(a.op, acc[j], f[j]);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] *= scale;
-        if (res) {
-            // the reduced value is rounded to the storage type before the residual is added, exactly as if the
-            // all-reduce and the Add were two operators
-            for (int j = 0; j < N; ++j) {
-                const uint64_t e = c * N + j;
-                if (e < a.count) acc[j] = Num<T>::to_f(Num<T>::from_f(acc[j])) + Num<T>::to_f(res[e]);
-            }
-        }
+        const uint4 out4 = ar_reduce_chunk<T>(raw, a.world, a.op, res, c * N, a.count);
         if (c < full_chunks) {
-            Vec16<T> o;
-            o.pack(acc);
-            o.store(y + c * N);
+            *reinterpret_cast<uint4 *>(y + c * N) = out4;
         } else {
-            for (uint64_t e = c * N; e < a.count; ++e) y[e] = Num<T>::from_f(acc[e - c * N]);
+            const T *tail = reinterpret_cast<const T *>(&out4);
+            for (uint64_t e = c * N; e < a.count; ++e) y[e] = tail[e - c * N];
         }
     }
 }
@@ -173,7 +224,7 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) 
 template<class T>
 __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const ArArgs a) {
     pdl_enter();
-    constexpr int N = Vec16<T>::N;
+    constexpr int N = 16 / sizeof(T);
     ArHeader *hdr = reinterpret_cast<ArHeader *>(a.mine);
     __shared__ unsigned long long s_seq;
     if (threadIdx.x == 0) {
@@ -186,16 +237,18 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const A
         }
     }
     __syncthreads();
+    // A communicator whose earlier call gave up a wait is out of step with its peers for good: every later call is a no-op
+    // (outputs untouched, status still set) until the host destroys and recreates it.
+    if (*reinterpret_cast<volatile int *>(&hdr->status) != 0) return;
     const unsigned long long seq = s_seq;
     const unsigned q = static_cast<unsigned>(seq & 1ull);
-    const uint32_t flag = static_cast<uint32_t>(seq);
+    const uint32_t flag = ar_flag(seq);
     const uint64_t chunks = (a.count + N - 1) / N, full_chunks = a.count / N;
     const T *x = static_cast<const T *>(a.x);
     const T *res = static_cast<const T *>(a.res);
     T *y = static_cast<T *>(a.y);
     const size_t my_off = ar_slot_off(a, q, a.rank);
     const size_t b_off = ar_slot_off(a, 2, 0) + static_cast<size_t>(q) * (2 * a.capacity);// slot B follows the 2 * world A slots
-    const float scale = a.op == 1 ? 1.0f / static_cast<float>(a.world) : 1.0f;
     const uint64_t t0 = global_timer_ns();
 
     for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks; c += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
@@ -245,29 +298,7 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const A
                     }
                 }
             }
-            float acc[N];
-#pragma unroll
-            for (int r = 0; r < AR_MAX_RANKS; ++r) {
-                if (r < a.world) {
-                    Vec16<T> v;
-                    v.raw = raw[r];
-                    float f[N];
-                    v.unpack(f);
-#pragma unroll
-                    for (int j = 0; j < N; ++j) acc[j] = r == 0 ? f[j] : ar_combine(a.op, acc[j], f[j]);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < N; ++j) acc[j] *= scale;
-            if (res) {
-                for (int j = 0; j < N; ++j) {
-                    const uint64_t e = c * N + j;
-                    if (e < a.count) acc[j] = Num<T>::to_f(Num<T>::from_f(acc[j])) + Num<T>::to_f(res[e]);
-                }
-            }
-            Vec16<T> o;
-            o.pack(acc);
-            out4 = o.raw;
+            out4 = ar_reduce_chunk<T>(raw, a.world, a.op, res, c * N, a.count);
             if (ok) {
 #pragma unroll
                 for (int r = 0; r < AR_MAX_RANKS; ++r) {
@@ -292,14 +323,14 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const A
     }
 }
 
-int all_reduce_error_word() { return 0; }// per-communicator status words are read by rg_b200_comm_status
 
 }// namespace rg
 
 using namespace rg;
 
 struct rg_comm {
-    int world, rank;
+    int world, rank, device;
+    bool failed;// a timeout has been observed by the host: every later call is refused
     size_t capacity, total_bytes;
     uint8_t *mine;
     uint8_t *peers[AR_MAX_RANKS];
@@ -307,6 +338,35 @@ struct rg_comm {
     bool connected;
     uint64_t wait_ns;
 };
+
+// Live communicators of this process, so that rg_b200_error_state can report a timed-out all-reduce (bit 3).
+static std::mutex g_comms_mutex;
+static std::vector<rg_comm *> g_comms;
+
+static int comm_read_status(rg_comm *c) {
+    int st = 0;
+    if (cudaMemcpy(&st, c->mine + offsetof(ArHeader, status), sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (st) c->failed = true;
+    return st;
+}
+
+namespace rg {
+// 1 when any communicator that lives on the current device has given up a wait; the status is a property of the communicator
+// (out of step with its peers), so `clear` does not reset it.
+int all_reduce_error_word(bool) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    std::lock_guard<std::mutex> lock(g_comms_mutex);
+    int any = 0;
+    for (rg_comm *c : g_comms) {
+        if (c->device != dev) continue;
+        const int st = comm_read_status(c);
+        if (st < 0) return -1;
+        any |= st ? 1 : 0;
+    }
+    return any;
+}
+}// namespace rg
 
 extern "C" {
 
@@ -316,6 +376,10 @@ int rg_b200_comm_create(int world, int rank, size_t capacity_bytes, rg_comm **ou
     auto *c = new (std::nothrow) rg_comm();
     if (!c) return RG_ERR_CUDA;
     c->world = world, c->rank = rank;
+    if (cudaGetDevice(&c->device) != cudaSuccess) {
+        delete c;
+        return RG_ERR_CUDA;
+    }
     c->capacity = (capacity_bytes + 255) / 256 * 256;
     // [2 parities][world] slots A of 2 * capacity, then [2 parities] slots B (finished values of the two-shot variant)
     c->total_bytes = AR_HEADER_BYTES + 4 * static_cast<size_t>(world + 1) * c->capacity;
@@ -341,6 +405,10 @@ int rg_b200_comm_create(int world, int rank, size_t capacity_bytes, rg_comm **ou
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
     std::memcpy(handle64, &h, 64);
     c->connected = world == 1;
+    {
+        std::lock_guard<std::mutex> lock(g_comms_mutex);
+        g_comms.push_back(c);
+    }
     *out = c;
     return RG_OK;
 }
@@ -385,13 +453,21 @@ int rg_b200_comm_set_wait_ns(rg_comm *c, uint64_t ns) {
 int rg_b200_comm_status(rg_comm *c) {
     if (!c) return RG_ERR_NULL;
     if (cudaDeviceSynchronize() != cudaSuccess) return RG_ERR_CUDA;
-    int st = 0;
-    if (cudaMemcpy(&st, c->mine + offsetof(ArHeader, status), sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return RG_ERR_CUDA;
-    return st ? RG_ERR_TIMEOUT : RG_OK;
+    const int st = comm_read_status(c);
+    if (st < 0) return RG_ERR_CUDA;
+    return (st || c->failed) ? RG_ERR_TIMEOUT : RG_OK;
 }
 
 int rg_b200_comm_destroy(rg_comm *c) {
     if (!c) return RG_ERR_NULL;
+    {
+        std::lock_guard<std::mutex> lock(g_comms_mutex);
+        for (size_t i = 0; i < g_comms.size(); ++i)
+            if (g_comms[i] == c) {
+                g_comms.erase(g_comms.begin() + static_cast<long>(i));
+                break;
+            }
+    }
     cudaDeviceSynchronize();
     for (int r = 0; r < c->world; ++r)
         if (r != c->rank && c->opened[r]) cudaIpcCloseMemHandle(c->peers[r]);
@@ -404,10 +480,13 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
     if (!c || !p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
     if (!c->connected) return RG_ERR_UNSUPPORTED;
     if (p->op < 0 || p->op > 4) return RG_ERR_UNSUPPORTED;
+    if (c->failed) return RG_ERR_TIMEOUT;// out of step with its peers since a wait expired: destroy and recreate
     size_t es;
     switch (p->dtype) {
-        case RG_F32: es = 4; break;
+        case RG_U8: case RG_I8: es = 1; break;
         case RG_FP16: case RG_BF16: es = 2; break;
+        case RG_F32: case RG_I32: case RG_U32: es = 4; break;
+        case RG_I64: case RG_F64: es = 8; break;
         default: return RG_ERR_DTYPE;
     }
     if (p->count == 0) return RG_OK;
@@ -430,20 +509,22 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
     // every rank must take the same variant: it depends on the group size and on RG_B200_AR_ALGO (1 one-shot, 2 two-shot) only
     static const int algo_env = std::getenv("RG_B200_AR_ALGO") ? atoi(std::getenv("RG_B200_AR_ALGO")) : 0;
     const bool two_shot = c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world > 4));
-    if (two_shot) {
-        switch (p->dtype) {
-            case RG_F32: launch_pdl(all_reduce_two_shot_kernel<float>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
-            case RG_FP16: launch_pdl(all_reduce_two_shot_kernel<__half>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
-            default: launch_pdl(all_reduce_two_shot_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
-        }
-        count_launch();
-        return launch_status();
-    }
+    const dim3 g(static_cast<unsigned>(grid)), b(AR_THREADS);
+    cudaError_t e;
+#define RG_AR(T) e = two_shot ? launch_pdl(all_reduce_two_shot_kernel<T>, g, b, 0, st, a) : launch_pdl(all_reduce_kernel<T>, g, b, 0, st, a)
     switch (p->dtype) {
-        case RG_F32: launch_pdl(all_reduce_kernel<float>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
-        case RG_FP16: launch_pdl(all_reduce_kernel<__half>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
-        default: launch_pdl(all_reduce_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(grid)), dim3(AR_THREADS), 0, st, a); break;
+        case RG_F32: RG_AR(float); break;
+        case RG_FP16: RG_AR(__half); break;
+        case RG_BF16: RG_AR(__nv_bfloat16); break;
+        case RG_U8: RG_AR(uint8_t); break;
+        case RG_I8: RG_AR(int8_t); break;
+        case RG_I32: RG_AR(int32_t); break;
+        case RG_U32: RG_AR(uint32_t); break;
+        case RG_I64: RG_AR(long long); break;
+        default: RG_AR(double); break;
     }
+#undef RG_AR
+    if (e != cudaSuccess) return RG_ERR_CUDA;
     count_launch();
     return launch_status();
 }

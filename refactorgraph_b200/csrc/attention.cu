@@ -16,6 +16,7 @@
 namespace rg {
 
 static __device__ int s_attn_error;
+static __device__ int s_attn_index_error;// a sequence length or block-table entry was out of range (length clamped, block 0 read instead)
 
 constexpr int AD_THREADS = 128;
 constexpr int AD_TILE = 64;
@@ -27,7 +28,7 @@ struct DecodeArgs {
     void *o;
     float *part;
     unsigned *cnt;
-    uint32_t batch, n_heads, tiles_per_split, max_splits;
+    uint32_t batch, n_heads, tiles_per_split, max_splits, max_len;
     rg_kv_layout kv;
     float scale;
 };
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
     pdl_wait();
 
     const int64_t len64 = a.lens[b];
-    const uint32_t len = len64 > 0 ? static_cast<uint32_t>(len64) : 0u;
+    const uint32_t len = kv_len_clamped(len64, a.max_len, a.kv, a.table != nullptr, &s_attn_index_error);
     const uint32_t ntiles = (len + AD_TILE - 1) / AD_TILE;
     const uint32_t nsplit = (ntiles + a.tiles_per_split - 1) / a.tiles_per_split;
     T *o = static_cast<T *>(a.o) + (static_cast<size_t>(b) * a.n_heads + h) * D;
@@ -91,7 +92,8 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
             for (uint32_t done = 0; done < ntok; done += step) {
                 const uint32_t tok = tok0 + done;
                 const uint32_t n = ntok - done < step ? ntok - done : step;
-                const int32_t blk = a.table[static_cast<size_t>(b) * a.kv.max_blocks_per_seq + tok / page];
+                int32_t blk = a.table[static_cast<size_t>(b) * a.kv.max_blocks_per_seq + tok / page];
+                if (!kv_block_ok(blk, a.kv)) s_attn_index_error = 1, blk = 0;
                 const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * page + tok % page) * D * 2;
                 bulk_g2s(ks + done * D * 2, kc + off, n * D * 2u, &full[s]);
                 bulk_g2s(vs + done * D * 2, vc + off, n * D * 2u, &full[s]);
@@ -259,7 +261,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const Decod
     pdl_wait();
 
     const int64_t len64 = a.lens[b];
-    const uint32_t len = len64 > 0 ? static_cast<uint32_t>(len64) : 0u;
+    const uint32_t len = kv_len_clamped(len64, a.max_len, a.kv, a.table != nullptr, &s_attn_index_error);
     const uint32_t ntiles = (len + AD_TILE - 1) / AD_TILE;
     const uint32_t nsplit = (ntiles + a.tiles_per_split - 1) / a.tiles_per_split;
     T *o = static_cast<T *>(a.o) + (static_cast<size_t>(b) * a.n_heads + h) * D;
@@ -291,7 +293,8 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const Decod
                     const uint32_t page = a.kv.page_size, step = page < AD_TILE ? page : AD_TILE;
                     for (uint32_t done = 0; done < ntok; done += step) {
                         const uint32_t tok = tok0 + done, n = ntok - done < step ? ntok - done : step;
-                        const int32_t blk = a.table[static_cast<size_t>(b) * a.kv.max_blocks_per_seq + tok / page];
+                        int32_t blk = a.table[static_cast<size_t>(b) * a.kv.max_blocks_per_seq + tok / page];
+                        if (!kv_block_ok(blk, a.kv)) s_attn_index_error = 1, blk = 0;
                         const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * page + tok % page) * D * 2;
                         bulk_g2s(ks + done * D * 2, kc + off, n * D * 2u, &full[s]);
                         bulk_g2s(vs + done * D * 2, vc + off, n * D * 2u, &full[s]);
@@ -471,7 +474,7 @@ static int decode_launch(const rg_attn_decode_params *p, void *ws, const void *c
     a.cnt = static_cast<unsigned *>(ws);
     a.part = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + pl.cnt_bytes);
     a.batch = p->batch, a.n_heads = p->n_heads;
-    a.tiles_per_split = pl.tiles_per_split, a.max_splits = pl.max_splits;
+    a.tiles_per_split = pl.tiles_per_split, a.max_splits = pl.max_splits, a.max_len = p->max_len;
     a.kv = p->kv;
     a.scale = 1.0f / sqrtf(static_cast<float>(D));
     // The tensor-path kernel pays for its larger prologue only when there is enough work to stream (batch-1 launches of
@@ -508,7 +511,7 @@ template<class T>
 __global__ void kv_append_kernel(const T *__restrict__ k, const T *__restrict__ v, T *__restrict__ kc,
                                  T *__restrict__ vc, const int64_t *__restrict__ past_p, uint32_t nh, uint32_t S,
                                  uint32_t D, uint32_t max_seq, uint64_t total) {
-    const uint32_t past = past_p ? static_cast<uint32_t>(*past_p) : 0u;
+    const uint32_t past = past_clamped(past_p, max_seq);
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
          t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
         const uint32_t d = static_cast<uint32_t>(t % D);
@@ -526,7 +529,7 @@ template<class T>
 __global__ void kv_prefix_copy_kernel(const T *__restrict__ src, T *__restrict__ dst,
                                       const int64_t *__restrict__ past_p, uint32_t D, uint32_t max_seq,
                                       uint64_t heads) {
-    const uint32_t past = past_p ? static_cast<uint32_t>(*past_p) : 0u;
+    const uint32_t past = past_clamped(past_p, max_seq);
     const uint64_t per = static_cast<uint64_t>(past) * D, total = heads * per;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
          t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
@@ -544,7 +547,7 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const T *__restrict__ q,
                                                         uint32_t kv_tokens /* tokens per (n, kv head) in K/V */,
                                                         float scale) {
     constexpr int D = EP * 32;
-    const uint32_t past = past_p ? static_cast<uint32_t>(*past_p) : 0u;
+    const uint32_t past = past_clamped(past_p, kv_tokens);
     const uint32_t lane = threadIdx.x & 31;
     const uint64_t row = static_cast<uint64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);// (n, h, i)
     if (row >= static_cast<uint64_t>(batch) * n_heads * S) return;
@@ -583,6 +586,7 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const T *__restrict__ q,
 // grouped-query variant (attn_decode_gqa.cu): one CTA serves all query heads of a KV head
 bool attn_decode_gqa_applies(const rg_attn_decode_params *p);
 size_t attn_decode_gqa_workspace(const rg_attn_decode_params *p);
+size_t attn_decode_gqa_counter_bytes(const rg_attn_decode_params *p);
 int attn_decode_gqa_launch(const rg_attn_decode_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st, bool pdl);
 
 int attn_prefill_ref_layout(int dtype, const void *q, const void *K, const void *V, void *o, const int64_t *past, uint32_t batch,
@@ -639,11 +643,8 @@ static int attention_launch(const rg_attention_params *p, const void *const *in,
     return launch_status();
 }
 
-int attn_error_word() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, s_attn_error, sizeof(int)) != cudaSuccess) return -1;
-    return v;
-}
+int attn_error_word(bool clear) { return error_symbol(s_attn_error, clear); }
+int attn_index_error_word(bool clear) { return error_symbol(s_attn_index_error, clear); }
 
 }// namespace rg
 
@@ -722,9 +723,15 @@ static __device__ __align__(256) unsigned char s_decode_scratch[RG_DECODE_STATIC
 size_t rg_b200_attn_decode_static_capacity(void) { return RG_DECODE_STATIC_SCRATCH_BYTES; }
 
 int rg_b200_attn_decode_static(const rg_attn_decode_params *p, const void *const *in, void *const *out, void *stream) {
-    if (!p) return RG_ERR_NULL;
-    const DecodePlan pl = decode_plan(p);
-    if (pl.cnt_bytes + pl.part_bytes > RG_DECODE_STATIC_SCRATCH_BYTES) return RG_ERR_LIMIT;
+    // Validation first: nothing is written to the shared array for a request that cannot run.
+    if (!p || !in || !out || !in[0] || !in[1] || !in[2] || !in[3] || !out[0]) return RG_ERR_NULL;
+    if (p->kv.n_kv_heads == 0 || p->n_heads % p->kv.n_kv_heads != 0 || p->max_len == 0) return RG_ERR_SHAPE;
+    if (p->batch == 0) return RG_OK;
+    if (p->batch > 65535 || p->n_heads > 65535) return RG_ERR_SHAPE;
+    // The limit is the size the workspace entry point asks for: the larger of the general and the grouped-query
+    // kernel's layouts, whichever of the two the dispatch below picks.
+    const size_t need = rg_b200_attn_decode_workspace(p);
+    if (need > RG_DECODE_STATIC_SCRATCH_BYTES) return RG_ERR_LIMIT;
     // In host code `s_decode_scratch` names a host-side shadow of the symbol, not device memory, so the device
     // address is looked up once per device (with that device current) and remembered.
     static void *scratch_of_device[64] = {nullptr};
@@ -737,9 +744,16 @@ int rg_b200_attn_decode_static(const rg_attn_decode_params *p, const void *const
     }
     void *ws = scratch_of_device[dev];
     auto st = static_cast<cudaStream_t>(stream);
-    // the array keeps whatever the previous call left: the arrival counters have to start at zero
-    if (cudaMemsetAsync(ws, 0, pl.cnt_bytes, st) != cudaSuccess) return RG_ERR_CUDA;
+    // The array keeps whatever the previous call left, and the previous call may have used the other kernel's layout:
+    // clear the arrival counters of both (each sits at the start of the array).
+    const DecodePlan pl = decode_plan(p);
+    size_t cnt = pl.cnt_bytes;
+    if (attn_decode_gqa_applies(p)) {
+        const size_t g = attn_decode_gqa_counter_bytes(p);
+        cnt = g > cnt ? g : cnt;
+    }
+    if (cnt > need) cnt = need;
+    if (cudaMemsetAsync(ws, 0, cnt, st) != cudaSuccess) return RG_ERR_CUDA;
     return rg_b200_attn_decode(p, ws, in, out, stream);
 }
 }
-

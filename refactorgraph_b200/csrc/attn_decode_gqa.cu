@@ -15,6 +15,9 @@ constexpr int GQ_THREADS = 128, GQ_TILE = 64, GQ_D = 128;
 constexpr int GQ_STAGES = 3;// K/V tile buffers: two tiles in flight while one is consumed (2 CTAs per SM)
 constexpr int GQ_REC = GQ_D + 4;// floats per split record: max, sum, 2 pad, accumulator (16-byte aligned)
 
+static __device__ int s_gqa_index_error;// a sequence length or block-table entry was out of range (length clamped, block 0 read instead)
+int gqa_index_error_word(bool clear) { return error_symbol(s_gqa_index_error, clear); }
+
 struct GqaArgs {
     const void *q, *kc, *vc;
     const int64_t *lens;
@@ -22,7 +25,7 @@ struct GqaArgs {
     void *o;
     float *part;
     unsigned *cnt;
-    uint32_t batch, n_heads, tiles_per_split, max_splits;
+    uint32_t batch, n_heads, tiles_per_split, max_splits, max_len;
     rg_kv_layout kv;
     float scale_log2e;
 };
@@ -75,7 +78,7 @@ __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaAr
     pdl_launch_dependents();
     pdl_wait();
     const int64_t len64 = a.lens[b];
-    const uint32_t len = len64 > 0 ? static_cast<uint32_t>(len64) : 0u;
+    const uint32_t len = kv_len_clamped(len64, a.max_len, a.kv, a.table != nullptr, &s_gqa_index_error);
     const uint32_t ntiles = (len + GQ_TILE - 1) / GQ_TILE;
     const uint32_t nsplit = (ntiles + a.tiles_per_split - 1) / a.tiles_per_split;
     T *O = static_cast<T *>(a.o) + (static_cast<size_t>(b) * a.n_heads + h0) * GQ_D;
@@ -101,7 +104,8 @@ __global__ void __launch_bounds__(GQ_THREADS) attn_decode_gqa_kernel(const GqaAr
             if (valid) {
                 if (a.table) {
                     const uint32_t page = a.kv.page_size;
-                    const int32_t blk = a.table[static_cast<size_t>(b) * a.kv.max_blocks_per_seq + key / page];
+                    int32_t blk = a.table[static_cast<size_t>(b) * a.kv.max_blocks_per_seq + key / page];
+                    if (!kv_block_ok(blk, a.kv)) s_gqa_index_error = 1, blk = 0;
                     off = ((static_cast<size_t>(blk) * nkv + kvh) * page + key % page) * GQ_D;
                 } else {
                     off = ((static_cast<size_t>(b) * nkv + kvh) * a.kv.max_seq + key) * GQ_D;
@@ -308,6 +312,7 @@ size_t attn_decode_gqa_workspace(const rg_attn_decode_params *p) {
     const GqaPlan pl = gqa_plan(p);
     return pl.cnt_bytes + pl.part_bytes;
 }
+size_t attn_decode_gqa_counter_bytes(const rg_attn_decode_params *p) { return gqa_plan(p).cnt_bytes; }
 
 int attn_decode_gqa_launch(const rg_attn_decode_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st, bool pdl) {
     const GqaPlan pl = gqa_plan(p);
@@ -319,7 +324,7 @@ int attn_decode_gqa_launch(const rg_attn_decode_params *p, void *ws, const void 
     a.cnt = static_cast<unsigned *>(ws);
     a.part = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + pl.cnt_bytes);
     a.batch = p->batch, a.n_heads = p->n_heads;
-    a.tiles_per_split = pl.tiles_per_split, a.max_splits = pl.max_splits;
+    a.tiles_per_split = pl.tiles_per_split, a.max_splits = pl.max_splits, a.max_len = p->max_len;
     a.kv = p->kv;
     a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(GQ_D));
     const size_t smem = 4096 + 2 * GQ_STAGES * 16384;

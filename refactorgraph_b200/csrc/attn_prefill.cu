@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PrefillA
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t qb = blockIdx.x, h = blockIdx.y, n = blockIdx.z;
     const uint32_t kvh = h / (a.n_heads / a.n_kv);
-    const uint32_t past = a.past ? static_cast<uint32_t>(*a.past) : 0u;
+    const uint32_t past = past_clamped(a.past, a.kv_cap);
     const uint32_t q0 = qb * PF_BM;
     const uint32_t kv_len = past + a.S < a.kv_cap ? past + a.S : a.kv_cap;
     uint32_t last_key = past + q0 + PF_BM;// exclusive bound of keys any row of this tile may see

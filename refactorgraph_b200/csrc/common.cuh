@@ -23,6 +23,17 @@ int sm_count();                   // multiProcessorCount of the current device (
 
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? RG_OK : RG_ERR_CUDA; }
 
+// Reads (and optionally zeroes) one of the per-file `static __device__ int` error words.
+template<class T> inline int error_symbol(const T &sym, bool clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, sym, sizeof(int)) != cudaSuccess) return -1;
+    if (clear && v) {
+        const int z = 0;
+        if (cudaMemcpyToSymbol(sym, &z, sizeof(int)) != cudaSuccess) return -1;
+    }
+    return v;
+}
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- dtype traits ----------------------------------------------------------------------------
@@ -99,6 +110,38 @@ template<> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4]
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// ---- device-read indices ----------------------------------------------------------------------
+// Positions, sequence lengths, token ids and block-table entries are read from device memory that a generation
+// loop advances on its own, so no kernel trusts them: an index that does not fit its buffer is never used for an
+// access.  The kernel records the fact in its file's index-error word (reported as bit 5 of rg_b200_error_state),
+// skips the store (or clamps the read range) and carries on; nothing traps.
+__device__ __forceinline__ bool kv_pos_ok(int64_t p, const rg_kv_layout &kv, bool paged) {
+    if (p < 0) return false;
+    if (paged) return kv.page_size != 0 && static_cast<uint64_t>(p) / kv.page_size < kv.max_blocks_per_seq;
+    return static_cast<uint64_t>(p) < kv.max_seq;
+}
+__device__ __forceinline__ bool kv_block_ok(int32_t blk, const rg_kv_layout &kv) {
+    return blk >= 0 && (kv.n_blocks == 0 || static_cast<uint32_t>(blk) < kv.n_blocks);
+}
+// The reference-layout operator's past_seq_len (a device scalar): negative counts as 0, anything beyond the cache as full.
+__device__ __forceinline__ uint32_t past_clamped(const int64_t *p, uint32_t cap) {
+    if (!p) return 0u;
+    const int64_t v = *p;
+    return v <= 0 ? 0u : (static_cast<uint64_t>(v) > cap ? cap : static_cast<uint32_t>(v));
+}
+// Number of cached tokens a decode kernel may read for a sequence whose device-side length is len64.
+__device__ __forceinline__ uint32_t kv_len_clamped(int64_t len64, uint32_t max_len, const rg_kv_layout &kv, bool paged, int *err) {
+    if (len64 <= 0) return 0u;
+    uint64_t cap = max_len;
+    const uint64_t room = paged ? static_cast<uint64_t>(kv.page_size) * kv.max_blocks_per_seq : kv.max_seq;
+    if (room < cap) cap = room;
+    if (static_cast<uint64_t>(len64) > cap) {
+        *err = 1;
+        return static_cast<uint32_t>(cap);
+    }
+    return static_cast<uint32_t>(len64);
 }
 
 // ---- reductions ------------------------------------------------------------------------------

@@ -36,6 +36,7 @@ constexpr int MG_MAX_REC = 8;
 // FMA (fma.rn.f32.f16 on the raw cache values, no conversions) left the attention loop at 6.4 us per layer.
 
 static __device__ int s_mega_error;
+static __device__ int s_mega_index_error;// the step's position or token id did not fit the cache / vocabulary: the step did nothing
 
 struct MegaLayer {
     const void *norm1, *wqkv, *wo, *norm2, *wgu, *wd;
@@ -291,8 +292,15 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, G = gridDim.x;
     const MegaWs ws = mega_ws(a.ws, G, a.H, a.nH, a.D, a.F);
     MegaHeader *hdr = ws.hdr;
-    const uint32_t pos = static_cast<uint32_t>(*a.pos);            // tokens already cached; the new token sits at pos
-    const int64_t token = *a.token;
+    const int64_t pos64 = *a.pos, token = *a.token;
+    // Both are device state a generation loop advances by itself.  Every CTA reads the same two words before any CTA can
+    // reach the end of the step (where they are rewritten), so the decision is uniform: a step whose new token would not
+    // fit the cache, or whose token id is outside the vocabulary, touches nothing and returns before the first barrier.
+    if (pos64 < 0 || pos64 >= static_cast<int64_t>(a.max_seq) || token < 0 || token >= static_cast<int64_t>(a.V)) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) s_mega_index_error = 1;
+        return;
+    }
+    const uint32_t pos = static_cast<uint32_t>(pos64);            // tokens already cached; the new token sits at pos
     const uint32_t NT = (pos + MG_TILE - 1) / MG_TILE;              // attention tiles over [0, pos)
     const uint32_t nphases = a.layers * 5 + 1;
     const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long *>(&hdr->epoch);
@@ -832,11 +840,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
     if (!ok && tid == 0) atomicExch(&s_mega_error, 1);
 }
 
-int mega_error_word() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, s_mega_error, sizeof(int)) != cudaSuccess) return -1;
-    return v;
-}
+int mega_error_word(bool clear) { return error_symbol(s_mega_error, clear); }
+int mega_index_error_word(bool clear) { return error_symbol(s_mega_index_error, clear); }
 
 }// namespace rg
 

@@ -5,6 +5,9 @@
 
 namespace rg {
 
+static __device__ int s_elementwise_index_error;// a gathered index, append position or block-table entry was out of range (access skipped)
+int elementwise_index_error_word(bool clear) { return error_symbol(s_elementwise_index_error, clear); }
+
 static unsigned grid_for(size_t work_items, unsigned threads) {
     const size_t want = (work_items + threads - 1) / threads;
     const size_t cap = static_cast<size_t>(sm_count()) * 16;
@@ -24,6 +27,10 @@ __global__ void gather_kernel(const U *__restrict__ data, const I *__restrict__ 
         const uint64_t i = row % mid_out, p = row / mid_out;
         int64_t k = static_cast<int64_t>(idx[i]);
         if (k < 0) k += mid_in;
+        if (k < 0 || k >= static_cast<int64_t>(mid_in)) {// the row is left unwritten
+            s_elementwise_index_error = 1;
+            continue;
+        }
         out[t] = data[(p * mid_in + static_cast<uint64_t>(k)) * units + u];
     }
 }
@@ -240,9 +247,17 @@ __global__ void qkv_rope_append_kernel(const T *__restrict__ qkv, const int64_t 
             T *cache = is_k ? kc : vc;
             uint64_t base;
             const uint32_t seq = tokens_per_seq > 1 ? m / tokens_per_seq : m;
+            if (!kv_pos_ok(p, kv, table != nullptr)) {
+                s_elementwise_index_error = 1;
+                continue;
+            }
             if (table) {
                 const uint32_t page = kv.page_size;
                 const int32_t blk = table[static_cast<uint64_t>(seq) * kv.max_blocks_per_seq + static_cast<uint32_t>(p) / page];
+                if (!kv_block_ok(blk, kv)) {
+                    s_elementwise_index_error = 1;
+                    continue;
+                }
                 base = ((static_cast<uint64_t>(blk) * nkv + kvh) * page + static_cast<uint32_t>(p) % page) * D;
             } else {
                 base = ((static_cast<uint64_t>(seq) * nkv + kvh) * kv.max_seq + static_cast<uint64_t>(p)) * D;

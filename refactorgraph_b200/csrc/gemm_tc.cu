@@ -21,6 +21,7 @@
 namespace rg {
 
 static __device__ int s_tc_error;
+static __device__ int s_tc_index_error;// a cache-append position or block-table entry was out of range (store skipped)
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;// 64 x 2 B = one 128-byte swizzle row
@@ -433,11 +434,20 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     const uint32_t seq = a.tokens_per_seq > 1 ? row / a.tokens_per_seq : row, nkv = a.kv.n_kv_heads;
                     uint64_t cache_row = 0;// element offset of (seq, kv head 0, p) in a cache, without the head term
                     uint32_t head_pitch = 0;
-                    if (live) {
+                    bool cache_ok = live;// false: this token's k / v heads are not stored
+                    if (live && !kv_pos_ok(p, a.kv, a.table != nullptr)) {
+                        s_tc_index_error = 1;
+                        cache_ok = false;
+                    }
+                    if (cache_ok) {
                         if (a.table) {
                             const uint32_t page = a.kv.page_size;
                             const int32_t blk = a.table[static_cast<uint64_t>(seq) * a.kv.max_blocks_per_seq + static_cast<uint32_t>(p) / page];
-                            cache_row = (static_cast<uint64_t>(blk) * nkv * page + static_cast<uint32_t>(p) % page) * 128u;
+                            if (!kv_block_ok(blk, a.kv)) {
+                                s_tc_index_error = 1;
+                                cache_ok = false;
+                            }
+                            cache_row = (static_cast<uint64_t>(cache_ok ? blk : 0) * nkv * page + static_cast<uint32_t>(p) % page) * 128u;
                             head_pitch = page * 128u;
                         } else {
                             cache_row = (static_cast<uint64_t>(seq) * nkv * a.kv.max_seq + static_cast<uint64_t>(p)) * 128u;
@@ -467,6 +477,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                             if (gh < a.nq) {
                                 dst = static_cast<T *>(a.q_out) + (static_cast<uint64_t>(row) * a.nq + gh) * 128u;
                             } else {
+                                if (!cache_ok) continue;
                                 const bool is_k = gh < a.nq + nkv;
                                 const uint32_t kvh = is_k ? gh - a.nq : gh - a.nq - nkv;
                                 dst = static_cast<T *>(is_k ? a.kc : a.vc) + cache_row + static_cast<uint64_t>(kvh) * head_pitch;
@@ -761,10 +772,7 @@ int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const
     return is_bf16 ? tc_launch<__nv_bfloat16, 256, 4>(ma, mb, a, st) : tc_launch<__half, 256, 4>(ma, mb, a, st);
 }
 
-int gemm_tc_error_word() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, s_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    return v;
-}
+int gemm_tc_error_word(bool clear) { return error_symbol(s_tc_error, clear); }
+int gemm_tc_index_error_word(bool clear) { return error_symbol(s_tc_index_error, clear); }
 
 }// namespace rg

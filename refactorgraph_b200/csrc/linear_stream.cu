@@ -29,6 +29,7 @@ constexpr uint32_t LS_STAGE_BYTES = 32768;
 constexpr uint32_t LS_PART_MAX_BYTES = 64 * 1024;
 
 static __device__ int s_linear_error;// 0 ok; 1 consumer wait expired; 2 producer wait expired
+static __device__ int s_linear_index_error;// a cache-append position or block-table entry was out of range (store skipped)
 
 struct LinearArgs {
     const void *W, *X, *G, *R;
@@ -265,9 +266,17 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const LinearA
                 const uint32_t kvh = is_k ? h - nq : h - nq - nkv;
                 T *cache = static_cast<T *>(is_k ? a.kc : a.vc);
                 size_t base;
+                if (!kv_pos_ok(t, a.kv, a.table != nullptr)) {
+                    s_linear_index_error = 1;
+                    continue;
+                }
                 if (a.table) {
                     const uint32_t page = a.kv.page_size;
                     const int32_t blk = a.table[static_cast<size_t>(m) * a.kv.max_blocks_per_seq + static_cast<uint32_t>(t) / page];
+                    if (!kv_block_ok(blk, a.kv)) {
+                        s_linear_index_error = 1;
+                        continue;
+                    }
                     base = ((static_cast<size_t>(blk) * nkv + kvh) * page + static_cast<uint32_t>(t) % page) * D;
                 } else {
                     base = ((static_cast<size_t>(m) * nkv + kvh) * a.kv.max_seq + static_cast<size_t>(t)) * D;
@@ -390,11 +399,8 @@ int linear_stream(const rg_linear_params *p, const void *const *in, void *const 
     return p->dtype == RG_FP16 ? linear_dispatch<__half>(a, pl, mm, st) : linear_dispatch<__nv_bfloat16>(a, pl, mm, st);
 }
 
-int linear_error_word() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, s_linear_error, sizeof(int)) != cudaSuccess) return -1;
-    return v;
-}
+int linear_error_word(bool clear) { return error_symbol(s_linear_error, clear); }
+int linear_index_error_word(bool clear) { return error_symbol(s_linear_index_error, clear); }
 
 }// namespace rg
 

@@ -451,6 +451,7 @@ namespace refactor::kernel {
             if (kc.shape.size() != 4) return ans;
             if (paged) {
                 p.kv.max_blocks_per_seq = inputs[inputs.size() - 3].get().shape.back();
+                p.kv.n_blocks = kc.shape[0];
                 if (!p.kv.page_size) p.kv.page_size = kc.shape[2];
             } else if (!p.kv.max_seq) {
                 p.kv.max_seq = kc.shape[2];
@@ -492,6 +493,7 @@ namespace refactor::kernel {
         if (paged) {
             p.kv.page_size = pageSize ? pageSize : kc.shape[2];
             p.kv.max_blocks_per_seq = inputs[4].get().shape.back();
+            p.kv.n_blocks = kc.shape[0];
         } else {
             p.kv.max_seq = kc.shape[2];
         }
@@ -530,6 +532,7 @@ namespace refactor::kernel {
         if (paged) {
             p.kv.page_size = pageSize ? pageSize : kc.shape[2];
             p.kv.max_blocks_per_seq = inputs[2].get().shape.back();
+            p.kv.n_blocks = kc.shape[0];
         } else {
             p.kv.max_seq = kc.shape[2];
         }
@@ -643,7 +646,7 @@ namespace refactor::kernel {
         rg_all_reduce_params info;
         bool hasResidual;
         AllReduceB200(rg_all_reduce_params p, bool r) noexcept : info(p), hasResidual(r) {}
-        RG_KERNEL_IDS(AllReduceB200, "AllReduce over NVLink peer memory on B200 (one-shot pull, fp32 accumulation)")
+        RG_KERNEL_IDS(AllReduceB200, "AllReduce over NVLink peer memory on B200 (flag-in-data push, one- or two-shot, rank-order combine)")
         RoutineWorkspace lower(Resources &res) const final {
             auto st = res.fetchOrStore<CudaStream>();
             return RoutineWorkspace([info = info, r = hasResidual, st](Resources &res, void *, void const *const *in, void *const *out) {
@@ -658,7 +661,11 @@ namespace refactor::kernel {
         std::vector<KernelBox> ans;
         auto const &x = inputs[0].get();
         auto const &y = outputs[0].get();
-        if (_target != Target::Nvidia || !halfOrFloat(x.dataType)) return ans;
+        if (_target != Target::Nvidia) return ans;
+        switch (x.dataType) {// the set the reference's communicator maps to NCCL types
+            case RG_F32: case RG_FP16: case RG_BF16: case RG_F64: case RG_U8: case RG_I8: case RG_I32: case RG_U32: case RG_I64: break;
+            default: return ans;
+        }
         if (x.elementsSize() != y.elementsSize() || x.dataType != y.dataType) return ans;// nccl_kernel.cc:14-17
         rg_all_reduce_params p{};
         p.dtype = x.dataType;

@@ -158,8 +158,8 @@ def mat_mul(a, b, c=None, trans_a=False, trans_b=False, alpha=1.0, beta=1.0, for
     return y
 
 
-def kv_layout(n_kv, d, max_seq=0, page=0, max_blocks=0):
-    return capi.KvLayout(n_kv, d, max_seq, page, max_blocks)
+def kv_layout(n_kv, d, max_seq=0, page=0, max_blocks=0, n_blocks=0):
+    return capi.KvLayout(n_kv, d, max_seq, page, max_blocks, n_blocks)
 
 
 def linear(x, w, g=None, eps=1e-6, residual=None, epilogue=0, n_heads=0, kv=None, positions=None, table=None,

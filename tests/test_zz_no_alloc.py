@@ -44,3 +44,29 @@ def test_static_scratch_rejects_requests_beyond_its_capacity():
     p = capi.AttnDecodeParams(capi.FP16, 1024, 128, 16384, kv)
     assert capi.workspace("attn_decode", p) > capi.load().rg_b200_attn_decode_static_capacity()
     assert capi.attn_decode_static(p, [1, 1, 1, 1, 0], [1], check=False) == capi.ERR_LIMIT
+
+
+def test_static_scratch_limit_follows_the_kernel_that_will_run():
+    # Grouped-query shapes use a different record size than the general kernel.  In the window where only the
+    # grouped-query layout exceeds the array, the call must be refused (return code only: nothing is launched).
+    lib = capi.load()
+    cap = lib.rg_b200_attn_decode_static_capacity()
+    refused = fits = 0
+    for batch in range(470, 520, 2):
+        p = capi.AttnDecodeParams(capi.FP16, batch, 32, 1024, ops.kv_layout(4, 128, 1024))
+        need = capi.workspace("attn_decode", p)
+        if need > cap:
+            assert capi.attn_decode_static(p, [1, 1, 1, 1, 0], [1], check=False) == capi.ERR_LIMIT, (batch, need)
+            refused += 1
+        else:
+            fits += 1
+    assert refused and fits, "the sweep should straddle the capacity"
+    # a grouped-query case just below the limit runs, and matches the workspace entry point
+    q, kc, vc, lens_d, kv, max_len = _case(7, 24, 32, 4, 128, [40 + 3 * i for i in range(24)])
+    want, _ = ops.attn_decode(q, kc, vc, lens_d, kv, max_len)
+    p = capi.AttnDecodeParams(ops.DT[q.dtype], q.shape[0], q.shape[1], max_len, kv)
+    got = torch.full_like(q, float("nan"))
+    capi.attn_decode_static(p, [q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens_d.data_ptr(), 0], [got.data_ptr()],
+                            stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
