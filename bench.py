@@ -1,17 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the decoder hot path.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload 7b|tiny]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl b200|reference] [--workload ...]
 
-Workload at N = 1 (BASELINE.json configs[1]): Llama-7B-shaped fp16 batch-1 greedy decode (32 layers, hidden 4096,
+Headline workload (BASELINE.json configs[1]): Llama-7B-shaped fp16 batch-1 greedy decode (32 layers, hidden 4096,
 32 heads x 128, FFN 11008, vocab 32000), KV cache prefilled to 2048 tokens with N(0,1), random weights N(0,0.02);
 one "step" = one generated token through executor.run().  Prints ONE JSON line (rank 0).
 
-value  : tokens/s with token / position / cache state resident on the device (CUDA-graph replays only).
+value  : tokens/s with token / position / cache state resident on the device (CUDA-graph replays only).  The timed
+         block of K steps is repeated R times, every block bracketed by barrier + synchronise and timed with CUDA events;
+         ms_per_step is the median block / K, and the line lists every block with the SM clock sampled in it.
 e2e    : tokens/s when every step's input token comes from pinned host memory (H2D inside the timed region)
          and the sampled token is read back (D2H + synchronise) through the executor API.
-roofline: the weight-streaming linear kernel, timed live with CUDA events over one pass of every linear launch
-         of a step on the real weights (13.2 GB, far larger than L2), against the measured HBM copy peak.
+roofline: the dominant kernel's algorithmic bytes per launch / its CUDA-event duration against the measured HBM copy
+         peak (the one-kernel step itself; the weight-streaming linear kernel alone is timed next to it).
+workloads / tensor_parallel (default workload only, same JSON line): the batch-32 paged decode and the bf16 prefill
+         (one GPU), and the 70B-shaped grouped-query model — a 10-layer slice on one GPU, tensor-parallel over the N
+         GPUs otherwise, with a parity check of the all-reduce and of a sharded decode step before its timed loop.
+         With N > 1 `value` remains N independent replicas of the headline workload.
 cpu_baseline / --impl reference: the reference's own CPU kernels (oracle/_ref, else the C port) on the host.
 """
 from __future__ import annotations
@@ -44,6 +50,10 @@ def parse_args():
                     help="7b: batch-1 greedy decode (the reported configuration; N > 1 = independent replicas). "
                          "7b-b32: batch 32, paged KV, top-k 50 sampling.  70b-tp: 70B-shaped GQA decode, tensor-parallel over N GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="the timed block of --steps steps is run this many times; ms_per_step is the median block / steps")
+    ap.add_argument("--only-headline", action="store_true",
+                    help="default workload only: skip the other configurations that are otherwise attached to the same JSON line")
     ap.add_argument("--graph", default="single", choices=["single", "fused"],
                     help="7b / tiny workloads: 'single' = the whole step as one persistent kernel (b200::DecodeStep); "
                          "'fused' = five fused launches per layer replayed as a CUDA graph")
@@ -55,7 +65,7 @@ def parse_args():
 
 
 def workload_config(name, world=1):
-    from refactorgraph_b200.llama import LlamaConfig
+    from refactorgraph_b200.config import LlamaConfig      # pure Python: the reference arm must not load the kernel library
     if name == "tiny":  # for quick functional runs only; never the reported configuration
         return LlamaConfig(layers=2, hidden=512, heads=4, kv_heads=4, head_dim=128, ffn=1024, vocab=2000, max_seq=512), 256
     if name == "7b-4l":  # four 7B-shaped layers (2.3 GB on the device): the size ncu captures of the decode step use
@@ -194,8 +204,9 @@ def workload_name(w):
 
 # ----------------------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi sampling during the timed region (read-only)."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    """nvidia-smi sampling during the timed region (read-only): SM clock, its maximum, power and the throttle reasons,
+    every 50 ms, each sample with its wall-clock time so that it can be attributed to one timed block."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
@@ -203,36 +214,54 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
     def stop(self):
+        """Returns (summary for the JSON line, [(unix time, sm MHz)] samples)."""
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}, []
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             self.proc.kill()
             out = ""
-        sm, mx, reasons = [], [], set()
+        import datetime
+        sm, mx, reasons, samples = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in out.strip().splitlines():
             f = [x.strip() for x in ln.split(",")]
-            if len(f) < 7:
+            if len(f) < 8:
                 continue
             try:
-                sm.append(float(f[0]))
-                mx.append(float(f[1]))
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
             except ValueError:
                 continue
-            for nm, v in zip(names, f[3:7]):
+            try:
+                samples.append((datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp(), sm[-1]))
+            except ValueError:
+                pass
+            for nm, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm)}, samples
+
+    @staticmethod
+    def window_mhz(samples, window):
+        """Median SM clock of the samples taken inside [t0, t1]; the nearest sample when the window saw none."""
+        if not samples:
+            return None
+        t0, t1 = window
+        inside = [m for t, m in samples if t0 <= t <= t1]
+        if inside:
+            return statistics.median(inside)
+        mid = 0.5 * (t0 + t1)
+        return min(samples, key=lambda tm: abs(tm[0] - mid))[1]
 
 
 def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0, graph="single"):
@@ -464,7 +493,6 @@ def run_case(args):
         return run_decode_step_timeline()
     if args.case == "gemm_tp8":
         return run_gemm_tp8(args)
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
     torch.cuda.set_device(0)
     capi.load()
     dt, dev = torch.float16, "cuda"
@@ -621,7 +649,72 @@ def time_skinny_gemm(ex, index, cfg, torch, stream, reps=3):
             "avg_launch_us": 1000.0 * ms / len(calls), "gbs": bytes_total / (ms * 1e-3) / 1e9}
 
 
-def run_prefill(args, torch, dist, lib, rank, world, local):
+def _barrier(torch, dist, world):
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def _max_over_ranks(torch, dist, world, values):
+    if world == 1:
+        return [float(v) for v in values]
+    t = torch.tensor(list(values), device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def timed_blocks(torch, dist, world, stream, sampler, repeats, before_block, run_block):
+    """`repeats` timed blocks; each block is bracketed by barrier + synchronize on both sides and timed with CUDA events on
+    the executor's stream.  Returns per-block milliseconds (max over ranks) and the wall-clock window of every block (for
+    binning the clock samples)."""
+    ms, windows = [], []
+    for _ in range(repeats):
+        before_block()
+        _barrier(torch, dist, world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        e0.record(stream)
+        run_block()
+        e1.record(stream)
+        stream.synchronize()
+        w1 = time.time()
+        _barrier(torch, dist, world)
+        ms.append(e0.elapsed_time(e1))
+        windows.append((w0, w1))
+    ms = _max_over_ranks(torch, dist, world, ms)
+    return ms, windows
+
+
+def block_summary(ms_blocks, windows, steps, sampler_samples):
+    """Median block and what the others looked like: per-repeat ms/step, spread, SM clock seen in each window."""
+    per_step = [m / steps for m in ms_blocks]
+    med = statistics.median(per_step)
+    mhz = [ClockSampler.window_mhz(sampler_samples, w) for w in windows]
+    return med, {"repeats": len(ms_blocks), "repeat_ms_per_step": [round(v, 5) for v in per_step],
+                 "repeat_spread": round((max(per_step) - min(per_step)) / med, 5) if med else None,
+                 "repeat_sm_mhz": mhz,
+                 "repeat_ms_times_mhz": [round(v * m, 2) if m else None for v, m in zip(per_step, mhz)]}
+
+
+def tensor_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"]), "measured sustained"
+    except Exception:
+        return FALLBACK_TFLOPS, "fallback"
+
+
+def ncu_traffic_ratio(name):
+    """DRAM bytes (read + written) per algorithmic byte from the tracked ncu summary of a kernel (profiles/<name>.json,
+    written next to the text summary of the same capture); None when there is no such record."""
+    try:
+        rec = json.load(open(os.path.join(ROOT, "profiles", name + ".json")))
+        return (float(rec["dram_bytes_read"]) + float(rec["dram_bytes_write"])) / float(rec["algorithmic_bytes"])
+    except Exception:
+        return None
+
+
+def measure_prefill(args, torch, dist, lib, rank, world, local, steps, warmup, repeats):
     """BASELINE configuration 4: 7B-shaped bf16 prefill, batch 4 x 2048 tokens, causal; one step = one prefill of all
     8192 tokens (replicated per GPU when N > 1).  Tensor-bound: flops / time against the measured bf16 matmul peak."""
     from refactorgraph_b200.graph_builder import BF16
@@ -647,13 +740,7 @@ def run_prefill(args, torch, dist, lib, rank, world, local):
     ex.set_input(index["last"], (np.arange(B, dtype=np.int64) + 1) * S - 1)
     ex.set_input(index["ids"], ids)
     stream = torch.cuda.ExternalStream(ex.cuda_stream())
-    K, W = args.steps, max(args.warmup, 3)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    K, W = steps, max(warmup, 3)
     l0 = lib.rg_b200_launch_count()
     ex.run()
     ex.sync()
@@ -662,21 +749,18 @@ def run_prefill(args, torch, dist, lib, rank, world, local):
         ex.run()
     ex.sync()
     sampler = ClockSampler(local)
-    barrier()
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(K):
-        ex.run()
-    e1.record(stream)
-    stream.synchronize()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    logits_finite = bool(np.isfinite(ex.get_output(index["logits"]).astype(np.float32)).all())
+
+    def block():
+        for _ in range(K):
+            ex.run()
+    ms_blocks, windows = timed_blocks(torch, dist, world, stream, sampler, repeats, lambda: None, block)
+    raw = ex.get_output(index["logits"])
+    logits_finite = bool(torch.isfinite(torch.from_numpy(raw.view(np.int16)).view(torch.bfloat16).float()).all())
     # end to end: token ids from pinned host memory every step, next tokens read back
     pin_in = torch.from_numpy(ids.copy()).pin_memory()
     pin_out = torch.zeros(B, dtype=torch.int64).pin_memory()
-    barrier()
+    _barrier(torch, dist, world)
     t0 = time.perf_counter()
     for _ in range(K):
         ex.set_input_async(index["ids"], pin_in.data_ptr(), ids.nbytes)
@@ -684,44 +768,265 @@ def run_prefill(args, torch, dist, lib, rank, world, local):
         ex.get_output_into(index["next"], pin_out.data_ptr(), B * 8)
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1000.0
-    clocks = sampler.stop()
-    barrier()
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+    clocks, samples = sampler.stop()
+    _barrier(torch, dist, world)
+    (e2e_ms,) = _max_over_ranks(torch, dist, world, [e2e_ms])
+    del ex
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    ms_step, rep = block_summary(ms_blocks, windows, K, samples)
+    H, F, V, L, D = cfg.hidden, cfg.ffn, cfg.vocab, cfg.layers, cfg.head_dim
+    n = B * S
+    gemm_flops = 2.0 * n * L * (3 * H * H + H * H + 3 * H * F) + 2.0 * B * H * V     # LM head on the last token of each sequence
+    attn_flops = L * B * cfg.heads * 4.0 * D * (S * (S + 1) / 2.0)
+    flops = gemm_flops + attn_flops
+    peak, peak_kind = tensor_peak()
+    tf = flops / (ms_step * 1e-3) / 1e12
+    line = {"metric": "prefill_tokens_per_s", "value": n * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": workload_name("7b-prefill"),
+                       "logits_finite": logits_finite, "l2": "inputs larger than L2 (13.2 GB of weights, 64 MiB activations per tensor)",
+                       "parallelism": "one independent replica per GPU" if world > 1 else "single GPU"},
+            "e2e": {"value": K * n * world / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": B * 8},
+            "gpu_launches": launches_per_step * K * repeats, "launches_per_step": launches_per_step, "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                         "kernel": "whole prefill step (gemm_tc_kernel dominates)", "peak_source": peak_kind + " bf16 matmul",
+                         "flops_per_step": flops, "gemm_flops": gemm_flops, "attention_flops": attn_flops}}
+    line.update(rep)
+    return line
+
+
+def tp_parity_check(torch, dist, lib, comm, rank, world):
+    """Outside every timed region: (1) the reference's all-reduce test vector, {2,3} + {5,6} = {7,9}
+    (src/04kernel/test/kernels/all_reduce/test_allreduce_nccl.cpp:44-47), continued to `world` ranks (rank r holds
+    {2 + 3r, 3 + 3r}); (2) one decode step of a small 2-layer model sharded over the ranks against the oracle's
+    tensor-parallel restatement (rank 0 runs it), logits within max-abs 2e-2 / relative 1e-2 and bit-identical on every
+    rank.  The oracle is used here as the checker only."""
+    from refactorgraph_b200 import capi
+    from refactorgraph_b200.llama import LlamaConfig, decode_step_graph_batched, seeded_weights, shard_config, shard_weights, weight_inputs
+    out = {}
+    x = torch.tensor([2.0 + 3 * rank, 3.0 + 3 * rank], device="cuda")
+    y = torch.zeros_like(x)
+    comm.all_reduce(capi.F32, 0, 2, x.data_ptr(), y.data_ptr())
+    torch.cuda.synchronize()
+    want = [sum(2.0 + 3 * r for r in range(world)), sum(3.0 + 3 * r for r in range(world))]
+    out["all_reduce_kat"] = y.cpu().tolist() == want
+    cfg = LlamaConfig(layers=2, hidden=512, heads=16, kv_heads=8, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=16)
+    rng = np.random.default_rng(3)
+    w16 = seeded_weights(cfg, 0, np.float16)
+    w16["lm_head"] = (0.2 * rng.standard_normal(w16["lm_head"].shape)).astype(np.float16)
+    B = cfg.batch
+    past = rng.integers(1, 100, (B,)).astype(np.int64)
+    kc = [rng.standard_normal((B, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+    vc = [rng.standard_normal((B, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
+    token = rng.integers(0, cfg.vocab, (B,)).astype(np.int64)
+    sc, kr = shard_config(cfg, world), cfg.kv_heads // world
+    ws = shard_weights(cfg, w16, world, rank)
+    g, index = decode_step_graph_batched(sc, world=world)
+    ex = g.compiler().compile("cuda", "flat", [])
+    ex.set_communicator(comm.address)
+    for name, _ in weight_inputs(sc):
+        ex.set_input(index[name], np.ascontiguousarray(ws[name]))
+    for l in range(cfg.layers):
+        ex.set_input(index[f"l{l}.k_cache"], np.ascontiguousarray(kc[l][:, rank * kr:(rank + 1) * kr]))
+        ex.set_input(index[f"l{l}.v_cache"], np.ascontiguousarray(vc[l][:, rank * kr:(rank + 1) * kr]))
+    ex.set_input(index["token"], token)
+    ex.set_input(index["pos"], past)
+    ex.set_input(index["lens"], past + 1)
+    dist.barrier()
+    ex.run()
+    logits = ex.get_output(index["logits"])
+    gathered = [None] * world
+    dist.all_gather_object(gathered, logits.tobytes())
+    out["bit_identical_across_ranks"] = all(gb == gathered[0] for gb in gathered)
     if rank == 0:
-        H, F, V, L, D = cfg.hidden, cfg.ffn, cfg.vocab, cfg.layers, cfg.head_dim
-        n = B * S
-        gemm_flops = 2.0 * n * L * (3 * H * H + H * H + 3 * H * F) + 2.0 * B * H * V     # LM head on the last token of each sequence
-        attn_flops = L * B * cfg.heads * 4.0 * D * (S * (S + 1) / 2.0)
-        flops = gemm_flops + attn_flops
-        peak = FALLBACK_TFLOPS
-        peak_kind = "fallback"
-        try:
-            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
-            peak_kind = "measured sustained"
-        except Exception:
-            pass
-        tf = flops / (ms / K * 1e-3) / 1e12
-        tokens = K * n * world
-        line = {"metric": "prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
-                "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic",
-                "config": {"workload": "Llama-7B-shaped bf16 prefill, batch 4 x 2048 tokens, causal, LM head on the last token of each sequence",
-                           "logits_finite": logits_finite, "l2": "inputs larger than L2 (13.2 GB of weights, 64 MiB activations per tensor)",
-                           "parallelism": "one independent replica per GPU" if world > 1 else "single GPU"},
-                "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": B * 8},
-                "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "clocks": clocks,
-                "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
-                             "kernel": "whole prefill step (gemm_tc_kernel dominates)", "peak_source": peak_kind + " bf16 matmul",
-                             "flops_per_step": flops, "gemm_flops": gemm_flops, "attention_flops": attn_flops}}
-        print(json.dumps(line), flush=True)
+        from oracle.decode_loop import KvHistory, oracle_decode_step_rounded
+        r16 = lambda a: np.asarray(a, np.float32).astype(np.float16).astype(np.float32)
+        kh = [[KvHistory(kc[l][b], past[b]) for b in range(B)] for l in range(cfg.layers)]
+        vh = [[KvHistory(vc[l][b], past[b]) for b in range(B)] for l in range(cfg.layers)]
+        wf = {k: v.astype(np.float32) for k, v in w16.items()}
+        want_logits = oracle_decode_step_rounded(cfg, wf, kh, vh, token, past, r16, world=world)
+        got = logits.astype(np.float32)
+        out["max_abs_err_vs_oracle"] = float(np.abs(got - want_logits).max())
+        out["decode_step_vs_oracle"] = bool(np.allclose(got, want_logits, atol=2e-2, rtol=1e-2))
+    flags = [None] * world
+    dist.all_gather_object(flags, out)
+    del ex
+    merged = dict(flags[0])
+    merged["all_reduce_kat"] = all(f["all_reduce_kat"] for f in flags)
+    merged["bit_identical_across_ranks"] = all(f["bit_identical_across_ranks"] for f in flags)
+    merged["ok"] = bool(merged["all_reduce_kat"] and merged["bit_identical_across_ranks"] and merged.get("decode_step_vs_oracle", False))
+    return merged
+
+
+def time_all_reduce(torch, dist, comm, rank, world, count, launches=50):
+    """The all-reduce of the tensor-parallel step alone (fp16, residual add fused), `launches` calls back to back on every
+    rank: device microseconds per call, max over ranks."""
+    from refactorgraph_b200 import capi
+    x = torch.randn(count, device="cuda").to(torch.float16)
+    r = torch.randn(count, device="cuda").to(torch.float16)
+    y = torch.empty_like(x)
+    sid = torch.cuda.current_stream().cuda_stream
+    for _ in range(5):
+        comm.all_reduce(capi.FP16, 0, count, x.data_ptr(), y.data_ptr(), r.data_ptr(), stream=sid)
+    _barrier(torch, dist, world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        comm.all_reduce(capi.FP16, 0, count, x.data_ptr(), y.data_ptr(), r.data_ptr(), stream=sid)
+    e1.record()
+    torch.cuda.synchronize()
+    (us,) = _max_over_ranks(torch, dist, world, [1000.0 * e0.elapsed_time(e1) / launches])
+    return us
+
+
+def measure_decode(args, torch, dist, lib, rank, world, local, workload, steps, warmup, repeats, with_cpu_baseline):
+    """One decode workload: device-resident loop (`value`), host-fed loop (`e2e`), the dominant kernel alone (`roofline`).
+    `7b` at world > 1 = one independent replica per GPU; `70b-tp` = one model sharded over the ranks."""
+    from refactorgraph_b200 import capi
+    tp = workload == "70b-tp"
+    full_cfg, kv_len = workload_config(workload, world)
+    comm, parity, ar_us = None, None, None
+    if tp and world > 1:
+        def exchange(handle):
+            out = [None] * world
+            dist.all_gather_object(out, handle)
+            return out
+        comm = capi.Comm(world, rank, full_cfg.batch * full_cfg.hidden * 2, exchange=exchange)
+        parity = tp_parity_check(torch, dist, lib, comm, rank, world)
+        ar_us = time_all_reduce(torch, dist, comm, rank, world, full_cfg.batch * full_cfg.hidden)
+    ex, index, state = build_executor(full_cfg, kv_len, torch, workload, world, rank, args.graph)
+    single = workload in ("7b", "tiny", "7b-4l") and args.graph == "single"
+    cfg = state["cfg"]                      # per-rank shape
+    if comm is not None:
+        ex.set_communicator(comm.address)
+    stream = torch.cuda.ExternalStream(ex.cuda_stream())
+    # tensor-parallel ranks must feed identical tokens; replicas draw their own
+    token0 = np.random.default_rng(0 if tp else rank).integers(0, cfg.vocab, (cfg.batch,)).astype(np.int64)
+    K, W = steps, max(warmup, 3)
+    if int(state["lens0"].max()) + W + K + 8 > cfg.max_seq:
+        raise SystemExit("bench.py: steps exceed the KV cache capacity of this benchmark configuration")
+
+    # launches per step, counted on the eager first pass
+    reset_state(ex, index, state, token0)
+    _barrier(torch, dist, world)
+    l0 = lib.rg_b200_launch_count()
+    ex.run()
+    ex.sync()
+    launches_per_step = int(lib.rg_b200_launch_count() - l0)
+
+    # ---- device-resident loop: `repeats` blocks of K steps, every block restarted from the same state ----
+    for _ in range(W):
+        ex.run()
+    ex.sync()
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    def block():
+        for _ in range(K):
+            ex.run()
+    ms_blocks, windows = timed_blocks(torch, dist, world, stream, sampler, repeats, lambda: reset_state(ex, index, state, token0), block)
+    last_tokens = ex.get_output(index["next"]).ravel().tolist()[:8]
+    logits_finite = bool(np.isfinite(ex.get_output(index["logits"]).astype(np.float32)).all())
+    if not logits_finite:
+        raise SystemExit("bench.py: non-finite logits after the timed loop; the number would be meaningless")
+
+    # ---- end-to-end loop: tokens from pinned host memory each step, sampled tokens read back ----
+    pin_in = torch.from_numpy(token0.copy()).pin_memory()
+    pin_out = torch.zeros(ex.get_output(index["next"]).size, dtype=torch.int64).pin_memory()
+    nbytes_in, nbytes_out = cfg.batch * 8, pin_out.numel() * 8
+
+    def e2e_block(n):
+        for _ in range(n):
+            ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes_in)
+            ex.run()
+            ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes_out)   # synchronises
+            pin_in.copy_(pin_out.view(cfg.batch, -1)[:, 0])
+    reset_state(ex, index, state, token0)
+    e2e_block(3)
+    e2e_ms_blocks = []
+    for _ in range(repeats):
+        reset_state(ex, index, state, token0)
+        pin_in.copy_(torch.from_numpy(token0))
+        _barrier(torch, dist, world)
+        t0 = time.perf_counter()
+        e2e_block(K)
+        torch.cuda.synchronize()
+        e2e_ms_blocks.append((time.perf_counter() - t0) * 1000.0)
+    clocks, samples = sampler.stop()
+    _barrier(torch, dist, world)
+    e2e_ms_blocks = _max_over_ranks(torch, dist, world, e2e_ms_blocks)
+    lin = None
+    if rank == 0:
+        lin = time_linear_kernel(ex, index, cfg, torch, stream) if workload in ("7b", "tiny", "7b-4l") else time_skinny_gemm(ex, index, cfg, torch, stream)
+    comm_ok = comm.status() == capi.OK if comm is not None else True
+    err_state = lib.rg_b200_error_state()
+    del ex
+    torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
-    del ex
-    if world > 1:
-        dist.destroy_process_group()
+    if comm is not None:
+        comm.destroy()
+    if rank != 0:
+        return None
+
+    peak, peak_kind = measured_peak()
+    replicas = 1 if tp else world
+    ms_step, rep = block_summary(ms_blocks, windows, K, samples)
+    value = cfg.batch * replicas / (ms_step * 1e-3)
+    e2e_ms_step = statistics.median(e2e_ms_blocks) / K
+    kv_sum = float(state["lens0"].sum()) + cfg.batch * (1 + (K - 1) / 2.0)        # mean total cached tokens per step
+    step_bytes = cfg.weight_bytes_per_step + cfg.kv_bytes_per_token * kv_sum           # per GPU
+    kernel = "linear_stream_kernel" if workload in ("7b", "tiny", "7b-4l") else "gemm_tc_kernel (activations on the N side)"
+    roof = {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
+            "traffic": None, "kernel": kernel, "peak_source": peak_kind + " HBM copy bandwidth",
+            "avg_launch_us": lin["avg_launch_us"], "launches_timed": lin["launches"],
+            "algorithmic_bytes_per_launch": lin["bytes_per_pass"] / lin["launches"]}
+    if single:
+        # the step IS one launch of the dominant kernel: its duration is the CUDA-event time of a timed block / K
+        step_gbs = step_bytes / (ms_step * 1e-3) / 1e9
+        ratio = ncu_traffic_ratio("decode_mega_7b_4layers_ncu")       # DRAM bytes per algorithmic byte, 4-layer capture; grows with the layer count
+        roof = {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
+                "traffic": step_bytes * ratio if ratio else None,
+                "kernel": "decode_mega_kernel (one launch per token)", "peak_source": peak_kind + " HBM copy bandwidth",
+                "avg_launch_us": 1000.0 * ms_step, "launches_timed": K * repeats, "algorithmic_bytes_per_launch": step_bytes,
+                "linear_stream_kernel_alone_gbs": lin["gbs"]}
+    elif workload == "7b":
+        ratio = ncu_traffic_ratio("linear_gate_up")
+        roof["traffic"] = ratio * roof["algorithmic_bytes_per_launch"] if ratio else None
+    line = {
+        "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic",
+        "config": {"workload": workload_name(workload), "layers": cfg.layers, "hidden": cfg.hidden, "batch": cfg.batch,
+                   "logits_finite": logits_finite, "kv_len_start": int(state["lens0"].mean()),
+                   "l2": "inputs larger than L2 (all weights streamed once per step)",
+                   "parallelism": (f"tp{world}" if tp else ("one independent replica per GPU" if world > 1 else "single GPU")),
+                   "last_tokens": last_tokens, "bounded_waits_ok": bool(comm_ok and err_state == 0)},
+        "e2e": {"value": cfg.batch * replicas / (e2e_ms_step * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": nbytes_out},
+        "gpu_launches": launches_per_step * K * repeats,
+        "launches_per_step": launches_per_step,
+        "clocks": clocks,
+        "roofline": roof,
+        "roofline_step": {"algorithmic_bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                          "frac_of_measured": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+                          "frac_of_nominal_8tbs": step_bytes / (ms_step * 1e-3) / 1e9 / 8000.0},
+    }
+    line.update(rep)
+    line["config"]["graph"] = args.graph if workload in ("7b", "tiny", "7b-4l") else "batched"
+    if tp:
+        line["tp_parity"] = parity
+        line["all_reduce_us"] = ar_us
+    if with_cpu_baseline and workload in ("7b", "tiny", "7b-4l"):
+        line["cpu_baseline"] = cpu_baseline(cfg, kv_len)
+    return line
+
+
+def _brief(line, keys=("metric", "value", "unit", "ms_per_step", "steps", "warmup", "repeats", "repeat_ms_per_step", "repeat_spread", "repeat_sm_mhz",
+                       "dtype", "config", "e2e", "launches_per_step", "clocks", "roofline", "roofline_step", "tp_parity", "all_reduce_us")):
+    return {k: line[k] for k in keys if k in line}
 
 
 def run_b200(args):
@@ -742,152 +1047,30 @@ def run_b200(args):
     lib = capi.load()
     if args.case == "all_reduce":
         return run_all_reduce_case(args, torch, dist, rank, world)
+    R = max(1, args.repeats)
     if args.workload == "7b-prefill":
-        return run_prefill(args, torch, dist, lib, rank, world, local)
-    tp = args.workload == "70b-tp"
-    full_cfg, kv_len = workload_config(args.workload, world)
-    comm = None
-    if tp and world > 1:
-        def exchange(handle):
-            out = [None] * world
-            dist.all_gather_object(out, handle)
-            return out
-        comm = capi.Comm(world, rank, full_cfg.batch * full_cfg.hidden * 2, exchange=exchange)
-    ex, index, state = build_executor(full_cfg, kv_len, torch, args.workload, world, rank, args.graph)
-    single = args.workload in ("7b", "tiny", "7b-4l") and args.graph == "single"
-    cfg = state["cfg"]                      # per-rank shape
-    if comm is not None:
-        ex.set_communicator(comm.address)
-    stream = torch.cuda.ExternalStream(ex.cuda_stream())
-    # tensor-parallel ranks must feed identical tokens; replicas draw their own
-    token0 = np.random.default_rng(0 if tp else rank).integers(0, cfg.vocab, (cfg.batch,)).astype(np.int64)
-    K, W = args.steps, max(args.warmup, 3)
-    assert int(state["lens0"].max()) + 2 * (W + K) + 8 <= cfg.max_seq, "steps exceed the KV cache capacity of this benchmark configuration"
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # launches per step, counted on the eager first pass
-    reset_state(ex, index, state, token0)
-    barrier()
-    l0 = lib.rg_b200_launch_count()
-    ex.run()
-    ex.sync()
-    launches_per_step = int(lib.rg_b200_launch_count() - l0)
-
-    # ---- device-resident loop ----
-    for _ in range(W):
-        ex.run()
-    ex.sync()
-    reset_state(ex, index, state, token0)
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(K):
-        ex.run()
-    e1.record(stream)
-    stream.synchronize()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    last_tokens = ex.get_output(index["next"]).ravel().tolist()[:8]
-    logits_finite = bool(np.isfinite(ex.get_output(index["logits"]).astype(np.float32)).all())
-    if not logits_finite:
-        raise SystemExit("bench.py: non-finite logits after the timed loop; the number would be meaningless")
-
-    # ---- end-to-end loop: tokens from pinned host memory each step, sampled tokens read back ----
-    reset_state(ex, index, state, token0)
-    pin_in = torch.from_numpy(token0.copy()).pin_memory()
-    pin_out = torch.zeros(ex.get_output(index["next"]).size, dtype=torch.int64).pin_memory()
-    nbytes_in, nbytes_out = cfg.batch * 8, pin_out.numel() * 8
-    for _ in range(3):
-        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes_in)
-        ex.run()
-        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes_out)
-        pin_in.copy_(pin_out.view(cfg.batch, -1)[:, 0])
-    reset_state(ex, index, state, token0)
-    pin_in.copy_(torch.from_numpy(token0))
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        ex.set_input_async(index["token"], pin_in.data_ptr(), nbytes_in)
-        ex.run()
-        ex.get_output_into(index["next"], pin_out.data_ptr(), nbytes_out)   # synchronises
-        pin_in.copy_(pin_out.view(cfg.batch, -1)[:, 0])
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    clocks = sampler.stop()
-    barrier()
-
-    # max over ranks
-    if world > 1:
-        t = torch.tensor([ms, e2e_s * 1000.0], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+        line = measure_prefill(args, torch, dist, lib, rank, world, local, args.steps, args.warmup, R)
     else:
-        e2e_ms = e2e_s * 1000.0
-    lin = None
+        line = measure_decode(args, torch, dist, lib, rank, world, local, args.workload, args.steps, args.warmup, R, not args.no_cpu_baseline)
+    # The default run also covers the other configurations, attached to the same JSON line: at one GPU the batch-32 decode,
+    # the bf16 prefill and the 10-layer slice of the 70B-shaped model; at N > 1 the 70B-shaped model tensor-parallel over the
+    # N GPUs (`value` stays the replica measurement).
+    if args.workload == "7b" and not args.only_headline:
+        extra = {}
+        if world == 1:
+            extra["7b-b32"] = measure_decode(args, torch, dist, lib, rank, world, local, "7b-b32", 16, 3, 3, False)
+            extra["7b-prefill"] = measure_prefill(args, torch, dist, lib, rank, world, local, 3, 3, 3)
+        tpl = measure_decode(args, torch, dist, lib, rank, world, local, "70b-tp", 16, 3, 3, False)
+        if rank == 0:
+            if extra:
+                line["workloads"] = {k: _brief(v) for k, v in extra.items()}
+            line["tensor_parallel"] = _brief(tpl)
+            line["tensor_parallel"]["tokens_per_s"] = tpl["value"]
+            line["gpu_launches"] += sum(v["gpu_launches"] for v in extra.values()) + tpl["gpu_launches"]
     if rank == 0:
-        lin = time_linear_kernel(ex, index, cfg, torch, stream) if args.workload in ("7b", "tiny", "7b-4l") else time_skinny_gemm(ex, index, cfg, torch, stream)
-    comm_ok = comm.status() == capi.OK if comm is not None else True
-    err_state = lib.rg_b200_error_state()
-
-    if rank == 0:
-        peak, peak_kind = measured_peak()
-        replicas = 1 if tp else world
-        tokens = K * cfg.batch * replicas
-        value = tokens / (ms * 1e-3)
-        kv_sum = float(state["lens0"].sum()) + cfg.batch * (1 + (K - 1) / 2.0)        # mean total cached tokens per step
-        step_bytes = cfg.weight_bytes_per_step + cfg.kv_bytes_per_token * kv_sum           # per GPU
-        kernel = "linear_stream_kernel" if args.workload in ("7b", "tiny", "7b-4l") else "gemm_tc_kernel (activations on the N side)"
-        roof = {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
-                "traffic": None, "kernel": kernel, "peak_source": peak_kind + " HBM copy bandwidth",
-                "avg_launch_us": lin["avg_launch_us"], "launches_timed": lin["launches"],
-                "algorithmic_bytes_per_launch": lin["bytes_per_pass"] / lin["launches"]}
-        if single:
-            # the step IS one launch of the dominant kernel: its duration is the CUDA-event time of the timed region / K
-            step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak, "traffic": None,
-                    "kernel": "decode_mega_kernel (one launch per token)", "peak_source": peak_kind + " HBM copy bandwidth",
-                    "avg_launch_us": 1000.0 * ms / K, "launches_timed": K, "algorithmic_bytes_per_launch": step_bytes,
-                    "linear_stream_kernel_alone_gbs": lin["gbs"]}
-            # ncu (profiles/decode_mega_7b_4layers_ncu.md): DRAM bytes read+written = 1.0022 x algorithmic on a 4-layer
-            # capture; traffic grows in proportion to the layer count
-            roof["traffic"] = step_bytes * (2.015606e9 + 4.392448e6) / 2.0155e9
-        line = {
-            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
-            "dtype": "fp16", "data": "synthetic",
-            "config": {"workload": workload_name(args.workload), "layers": cfg.layers, "hidden": cfg.hidden, "batch": cfg.batch,
-                       "logits_finite": logits_finite, "kv_len_start": int(state["lens0"].mean()),
-                       "l2": "inputs larger than L2 (all weights streamed once per step)",
-                       "parallelism": (f"tp{world}" if tp else ("one independent replica per GPU" if world > 1 else "single GPU")),
-                       "last_tokens": last_tokens, "bounded_waits_ok": bool(comm_ok and err_state == 0)},
-            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": nbytes_out},
-            "gpu_launches": launches_per_step * K,
-            "launches_per_step": launches_per_step,
-            "clocks": clocks,
-            "roofline": roof,
-            "roofline_step": {"algorithmic_bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
-                              "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak,
-                              "frac_of_nominal_8tbs": step_bytes / (ms / K * 1e-3) / 1e9 / 8000.0},
-        }
-        line["config"]["graph"] = args.graph if args.workload in ("7b", "tiny", "7b-4l") else "batched"
-        if args.workload == "7b" and not single:
-            line["roofline"]["traffic"] = 180404736 * (lin["bytes_per_pass"] / lin["launches"]) / 180355072  # ncu: dram bytes = 1.0003 x algorithmic (profiles/linear_gate_up.md)
-        if not args.no_cpu_baseline and args.workload in ("7b", "tiny", "7b-4l"):
-            line["cpu_baseline"] = cpu_baseline(cfg, kv_len)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
-    del ex
-    if comm is not None:
-        comm.destroy()
-    if world > 1:
         dist.destroy_process_group()
 
 

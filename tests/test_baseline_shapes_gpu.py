@@ -1,0 +1,199 @@
+"""Parity at the shapes the benchmark runs (BASELINE configurations 2, 3 and 4), each against the numpy oracle:
+  * b200::DecodeStep (the single persistent kernel of the headline number) at the Llama-7B shape, KV 2048 -> 2052,
+    and at a grouped-query shape with the 70B head ratio (64 query heads on 8 KV heads);
+  * the batched decode graph at batch 32 with a paged cache, lengths drawn as the benchmark draws them, top-k-50
+    sampling;
+  * the prefill graph in bf16 with 2048-token sequences.
+Two layers of each shape are enough to exercise every work split that depends on the shape; the oracle runs them in
+a few seconds per step.  Tolerance on fp16 / bf16 logits: max-abs 2e-2, relative 1e-2; chosen tokens bit-exact against
+the arg-max / sampler of the oracle applied to the GPU's own logits."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle_np as onp
+from refactorgraph_b200 import capi
+from refactorgraph_b200.graph_builder import BF16
+from refactorgraph_b200.llama import (LlamaConfig, decode_step_graph_batched, decode_step_graph_single_kernel, prefill_graph,
+                                      seeded_weights, weight_inputs)
+
+from _decode_oracle import KvHistory, oracle_decode, oracle_decode_step_rounded
+
+pytestmark = pytest.mark.gpu
+
+r16 = lambda a: np.asarray(a, np.float32).astype(np.float16).astype(np.float32)
+
+
+def _bf16(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("shape", [
+    dict(layers=2, hidden=4096, heads=32, kv_heads=32, head_dim=128, ffn=11008, vocab=32000, past=2048),   # Llama-7B
+    dict(layers=1, hidden=8192, heads=64, kv_heads=8, head_dim=128, ffn=11008, vocab=32000, past=1000),    # 70B head ratio
+], ids=["7b", "gqa64x8"])
+def test_single_kernel_decode_step_at_benchmark_shape(shape):
+    shape = dict(shape)
+    past0 = shape.pop("past")
+    steps = 4
+    cfg = LlamaConfig(max_seq=past0 + 64, batch=1, **shape)
+    w16 = seeded_weights(cfg, 0, np.float16)                       # N(0, 0.02), as the benchmark draws them
+    w = {k: v.astype(np.float32) for k, v in w16.items()}
+    rng = np.random.default_rng(1)
+    cache = lambda: rng.standard_normal((1, cfg.kv_heads, cfg.max_seq, cfg.head_dim), dtype=np.float32).astype(np.float16)
+    kc, vc = [cache() for _ in range(cfg.layers)], [cache() for _ in range(cfg.layers)]
+    token = rng.integers(0, cfg.vocab, (1,)).astype(np.int64)
+    past = np.array([past0], np.int64)
+    want_tok, want_logits = oracle_decode(cfg, w, kc, vc, token, past, steps)
+    g, index = decode_step_graph_single_kernel(cfg)
+    ex = g.compiler().compile("cuda", "flat", [])
+    assert ex.node_count() == 1
+    for name, _ in weight_inputs(cfg):
+        ex.set_input(index[name], w16[name])
+    for l in range(cfg.layers):
+        ex.set_input(index[f"l{l}.k_cache"], kc[l])
+        ex.set_input(index[f"l{l}.v_cache"], vc[l])
+    feed = token
+    for s in range(steps):
+        # the oracle's token is fed every step, so that a legitimate arg-max flip on a near-tie cannot send the two
+        # trajectories apart; the kernel's own state update is checked separately below
+        ex.set_input(index["token"], feed)
+        ex.set_input(index["pos"], past + s)
+        ex.run()
+        assert capi.load().rg_b200_error_state() == 0
+        logits = ex.get_output(index["logits"]).astype(np.float32)
+        np.testing.assert_allclose(logits, want_logits[s], atol=2e-2, rtol=1e-2)
+        tok = ex.get_output(index["next"])
+        np.testing.assert_array_equal(tok, onp.topk(logits, 1)[1][0])           # arg-max of its own logits, bit-exact
+        top2 = np.sort(want_logits[s][0])[-2:]
+        if top2[1] - top2[0] > 4e-2:
+            np.testing.assert_array_equal(tok, want_tok[s])
+        np.testing.assert_allclose(ex.get_output(index["probs"]), onp.topk_softmax(logits, 1)[0][0], rtol=1e-4)
+        feed = want_tok[s]
+    # device-resident state: the step left its own choice and the next position behind
+    ex.run()
+    np.testing.assert_array_equal(ex.get_output(index["next"]), onp.topk(ex.get_output(index["logits"]).astype(np.float32), 1)[1][0])
+
+
+def test_batch32_paged_sampling_decode_at_benchmark_shape():
+    """BASELINE configuration 3 on two layers: batch 32, 16-token pages, per-sequence lengths integers(512, 4097) from
+    seed 0, top-k 50 sampling at temperature 1."""
+    cfg = LlamaConfig(layers=2, max_seq=4096 + 128, batch=32)
+    B, page, D, nKV = cfg.batch, 16, cfg.head_dim, cfg.kv_heads
+    lens0 = np.random.default_rng(0).integers(512, 4097, (B,)).astype(np.int64)
+    max_blocks = cfg.max_seq // page
+    n_blocks = B * max_blocks
+    table = np.random.default_rng(1).permutation(n_blocks).reshape(B, max_blocks).astype(np.int32)
+    w16 = seeded_weights(cfg, 0, np.float16)
+    w = {k: v.astype(np.float32) for k, v in w16.items()}
+    rng = np.random.default_rng(2)
+    seed, steps = 1234, 2
+    g, index = decode_step_graph_batched(cfg, paged=True, page=page, max_blocks=max_blocks, n_blocks=n_blocks, top_k=50, sample=True,
+                                         temperature=1.0, seed=seed)
+    ex = g.compiler().compile("cuda", "flat", [])
+    for name, _ in weight_inputs(cfg):
+        ex.set_input(index[name], w16[name])
+    # Cached K/V ~ N(0,1): sequence b reads a window of one shared random strip, shifted by 8 b tokens (the values only
+    # have to be known to both sides; the strip keeps the host footprint at tens of MB instead of 4.4 GB)
+    kh = [[None] * B for _ in range(cfg.layers)]
+    vh = [[None] * B for _ in range(cfg.layers)]
+    for l in range(cfg.layers):
+        for nm, hist in (("k_cache", kh), ("v_cache", vh)):
+            strip = rng.standard_normal((nKV, cfg.max_seq + 8 * B, D), dtype=np.float32).astype(np.float16)
+            pages = np.zeros((n_blocks, nKV, page, D), np.float16)
+            for b in range(B):
+                win = strip[:, 8 * b: 8 * b + cfg.max_seq]
+                hist[l][b] = KvHistory(win, lens0[b])
+                nb = (int(lens0[b]) + page - 1) // page
+                pages[table[b, :nb]] = win[:, :nb * page].reshape(nKV, nb, page, D).transpose(1, 0, 2, 3)
+            ex.set_input(index[f"l{l}.{nm}"], pages)
+            del pages
+    ex.set_input(index["block_table"], table)
+    token = rng.integers(0, cfg.vocab, (B,)).astype(np.int64)
+    ex.set_input(index["step"], np.zeros(1, np.int64))
+    for s in range(steps):
+        pos = lens0 + s
+        ex.set_input(index["token"], token)
+        ex.set_input(index["pos"], pos)
+        ex.set_input(index["lens"], pos + 1)
+        ex.run()
+        want = oracle_decode_step_rounded(cfg, w, kh, vh, token, pos, r16)
+        logits = ex.get_output(index["logits"]).astype(np.float32)
+        np.testing.assert_allclose(logits, want, atol=2e-2, rtol=1e-2)
+        tok = ex.get_output(index["next"]).ravel()
+        ref = onp.topk_sample(logits, 50, 1.0, seed, s)                     # the oracle's sampler on the GPU's own logits
+        assert (tok == ref).mean() >= 31 / 32                                # an fp32 exp rounding may move one boundary draw
+        top = onp.topk(logits, 50)[1]
+        assert all(tok[r] in top[r] for r in range(B))
+        token = tok.astype(np.int64)
+    assert capi.load().rg_b200_error_state() == 0
+
+
+def test_bf16_prefill_2048_tokens_at_benchmark_shape():
+    """BASELINE configuration 4 on two layers and two sequences of 2048 tokens, bf16: last-token logits and the K/V rows
+    the prefill wrote, against the oracle with every intermediate rounded where the GPU graph stores it."""
+    B, S = 2, 2048
+    cfg = LlamaConfig(layers=2, max_seq=S, batch=B, dtype=BF16)
+    D, nH, nKV, F = cfg.head_dim, cfg.heads, cfg.kv_heads, cfg.ffn
+    rb = lambda a: _bf16(a).float().numpy()
+    w32 = seeded_weights(cfg, 0, np.float32)
+    w = {k: rb(v) for k, v in w32.items()}
+    rng = np.random.default_rng(11)
+    ids = rng.integers(0, cfg.vocab, (B, S)).astype(np.int64)
+    pos = np.tile(np.arange(S, dtype=np.int64), B)
+    mm = lambda x, wt: (torch.from_numpy(x).double() @ torch.from_numpy(wt).double().T).numpy()   # fp64 on all host cores
+    x = w["embed"][ids.ravel()]
+    k_want = v_want = None
+    for l in range(cfg.layers):
+        n1 = rb(onp.rms_norm(x, w[f"l{l}.norm1"], cfg.eps))
+        qkv = mm(n1, w[f"l{l}.wqkv"])                                        # the rotation happens on the fp32 accumulator
+        q = rb(onp.rope(qkv[:, : nH * D].reshape(-1, nH, D), pos))
+        k = rb(onp.rope(qkv[:, nH * D: (nH + nKV) * D].reshape(-1, nKV, D), pos))
+        v = rb(qkv[:, (nH + nKV) * D:].reshape(-1, nKV, D))
+        if l == cfg.layers - 1:
+            k_want, v_want = k, v
+        a = np.empty((B * S, nH * D), np.float32)
+        for b in range(B):                                                   # head by head: [S, S] scores in fp64
+            for h in range(nH):
+                qs = torch.from_numpy(q[b * S:(b + 1) * S, h]).double()
+                ks = torch.from_numpy(k[b * S:(b + 1) * S, h // (nH // nKV)]).double()
+                vs = torch.from_numpy(v[b * S:(b + 1) * S, h // (nH // nKV)]).double()
+                sc = (qs @ ks.T) / np.sqrt(D)
+                sc = sc.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
+                a[b * S:(b + 1) * S, h * D:(h + 1) * D] = (torch.softmax(sc, -1) @ vs).float().numpy()
+        a = rb(a)
+        h_ = rb(mm(a, w[f"l{l}.wo"]) + x)
+        n2 = rb(onp.rms_norm(h_, w[f"l{l}.norm2"], cfg.eps))
+        gu = mm(n2, w[f"l{l}.wgu"])                                          # SiLU gate on the fp32 accumulators
+        u = rb(onp.silu(gu[:, :F]) * gu[:, F:])
+        x = rb(mm(u, w[f"l{l}.wd"]) + h_)
+    last = (np.arange(B, dtype=np.int64) + 1) * S - 1
+    xf = rb(onp.rms_norm(x[last], w["norm_f"], cfg.eps))
+    want_logits = mm(xf, w["lm_head"])
+    # GPU
+    g, index = prefill_graph(cfg, S)
+    ex = g.compiler().compile("cuda", "flat", [])
+    for name, _ in weight_inputs(cfg):
+        t = _bf16(w[name]).cuda()
+        ex.set_input_blob(index[name], t.data_ptr(), t.numel() * 2)
+        del t
+    ex.set_input(index["ids"], ids.ravel())
+    ex.set_input(index["positions"], pos)
+    ex.set_input(index["last"], last)
+    ex.run()
+    raw = ex.get_output(index["logits"])                                   # bf16 travels as raw 16-bit words
+    logits = torch.from_numpy(raw.view(np.int16)).view(torch.bfloat16).float().numpy()
+    np.testing.assert_allclose(logits, want_logits, atol=2e-2, rtol=1e-2)
+    np.testing.assert_array_equal(ex.get_output(index["next"]).ravel(), onp.topk(logits, 1)[1][:, 0])
+    # the last layer's caches hold the rotated keys and the values of every token (device-to-device copy out of the
+    # executor's input edge through the library's own transpose kernel with the identity permutation)
+    kc = torch.empty(B, nKV, S, D, dtype=torch.bfloat16, device="cuda")
+    tp = capi.TransposeParams()
+    tp.elem_bytes, tp.rank = 2, 2
+    tp.in_shape[:] = [B * nKV * S, D, 1, 1]
+    tp.perm[:] = [0, 1, 0, 0]
+    capi.call("transpose", tp, [ex.input_address(index[f"l{cfg.layers - 1}.k_cache"])], [kc.data_ptr()], stream=ex.cuda_stream())
+    ex.sync()
+    got_k = kc.float().cpu().numpy().transpose(0, 2, 1, 3).reshape(B * S, nKV, D)
+    np.testing.assert_allclose(got_k, k_want, atol=2e-2, rtol=1e-2)
+    assert capi.load().rg_b200_error_state() == 0

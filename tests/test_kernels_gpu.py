@@ -32,9 +32,13 @@ def rnd16(a, dtype):
 
 # ---- RMSNorm ---------------------------------------------------------------------------------------------------
 def test_rms_norm_reference_vectors():
-    x = np.arange(24, dtype=np.float32).reshape(2, 3, 4) + 1  # the reference KAT shifted off the all-zero row
+    # src/04kernel/test/kernels/rms_normalization/test_cpu.cpp:21-38, literally: x = 0..23 as [2,3,4], w = 1..4, eps = 0
+    x = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
     w = np.arange(1, 5, dtype=np.float32)
-    np.testing.assert_allclose(ops.rms_norm(ops.dev(x), ops.dev(w), 0.0).cpu().numpy(), oracle.port_rms_norm(x, w, 0.0), rtol=1e-6)
+    expect = np.stack([row * np.float32(1.0 / np.sqrt(np.float32((row * row).sum() / 4))) * w for row in x.reshape(6, 4)]).reshape(2, 3, 4)
+    got = ops.rms_norm(ops.dev(x), ops.dev(w), 0.0).cpu().numpy()
+    np.testing.assert_allclose(got, expect, rtol=4e-7 * 4)           # EXPECT_FLOAT_EQ is 4 ULP
+    np.testing.assert_allclose(got, oracle.port_rms_norm(x, w, 0.0), rtol=1e-6)
     x = np.full((2, 3, 4096), 2, np.float32)
     w = np.full(4096, 3, np.float32)
     np.testing.assert_allclose(ops.rms_norm(ops.dev(x), ops.dev(w), 0.0).cpu().numpy(), 3.0, rtol=1e-6)

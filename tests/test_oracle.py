@@ -23,11 +23,10 @@ def test_rms_norm_reference_kat():
         row = x.reshape(6, 4)[i]
         rms = 1.0 / np.sqrt(np.float32((row * row).sum() / 4))
         expect.reshape(6, 4)[i] = row * rms * w
-    with np.errstate(divide="ignore", invalid="ignore"):
-        got_np = onp.rms_norm(x, w, 0.0)
+    got_np = onp.rms_norm(x, w, 0.0)
     got_c = oracle.port_rms_norm(x, w, 0.0)
-    np.testing.assert_allclose(got_np.reshape(6, 4)[1:], expect.reshape(6, 4)[1:], rtol=4e-7)
-    np.testing.assert_allclose(got_c.reshape(6, 4)[1:], expect.reshape(6, 4)[1:], rtol=4e-7)
+    np.testing.assert_allclose(got_np, expect, rtol=4e-7)      # all six rows (row 0 = [0,1,2,3] has a non-zero mean square)
+    np.testing.assert_allclose(got_c, expect, rtol=4e-7)
 
 
 def test_rms_norm_cuda_test_vector():
