@@ -27,7 +27,7 @@ constexpr uint32_t MG_STAGE_BYTES = 32768;
 constexpr int MG_KCH = 6;          // k <= 6 * 256 * 8 = 12288
 constexpr int MG_MAX_LAYERS = 96;
 constexpr int MG_TILE = 64;        // tokens per attention unit
-constexpr int MG_PART_UNITS = 96;  // max units of one phase per CTA
+constexpr int MG_PART_UNITS = 128; // max units of one phase per CTA (checked on the host for every phase of the shape)
 constexpr int MG_MAX_REC = 8;
 // Measured and removed: asking L2 to fetch further ahead than the ring (cp.async.bulk.prefetch.L2 by the producer, 8 or 14
 // units ahead: step +45 %; prefetch.global.L2 by a consumer warp while a grid barrier completes, 2..16 units: +6..50 %).
@@ -103,8 +103,27 @@ struct Phase {
     uint32_t layer;
 };
 
-__device__ __forceinline__ uint32_t pow2_floor_d(uint32_t v) {
-    return v ? 1u << (31 - __clz(v)) : 0u;
+__host__ __device__ inline uint32_t pow2_floor_d(uint32_t v) {
+    uint32_t p = 0;
+    for (uint32_t b = 1; b && b <= v; b <<= 1) p = b;
+    return p;
+}
+// Rows per segment (g) and units of a linear phase with `n` rows of `k` columns; one definition for the kernel's schedule and
+// for the host-side check that no CTA gets more units of a phase than its shared-memory partial-sum table holds.
+__host__ __device__ inline uint32_t mega_phase_units(int type, uint32_t n, uint32_t k, uint32_t segs, uint32_t D, uint32_t F, uint32_t &g_out) {
+    uint32_t g = pow2_floor_d(MG_STAGE_BYTES / (k * 2u * segs));
+    if (g * segs > 4) g = 4 / segs;
+    uint32_t units;
+    if (type == 0 /* PH_QKV */) {
+        while (g > 1 && (D / 2) % g != 0) g >>= 1;
+        units = n / (2 * g);
+    } else if (type == 3 /* PH_GU */) {
+        units = (F + g - 1) / g;
+    } else {
+        units = (n + g - 1) / g;
+    }
+    g_out = g;
+    return units;
 }
 // Phase p of the step: 5 per layer, then the LM head.  `T` = attention tiles over the cached tokens [0, pos).
 __device__ inline Phase phase_of(const MegaArgs &a, uint32_t p, uint32_t T) {
@@ -122,17 +141,7 @@ __device__ inline Phase phase_of(const MegaArgs &a, uint32_t p, uint32_t T) {
         case PH_DOWN: ph.W = static_cast<const uint8_t *>(L.wd), ph.n = a.H, ph.k = a.F, ph.segs = 1; break;
         default: ph.W = static_cast<const uint8_t *>(a.lm_head), ph.n = a.V, ph.k = a.H, ph.segs = 1; break;
     }
-    uint32_t g = pow2_floor_d(MG_STAGE_BYTES / (ph.k * 2u * ph.segs));
-    if (g * ph.segs > 4) g = 4 / ph.segs;
-    if (ph.type == PH_QKV) {
-        while (g > 1 && (a.D / 2) % g != 0) g >>= 1;
-        ph.units = ph.n / (2 * g);
-    } else if (ph.type == PH_GU) {
-        ph.units = (a.F + g - 1) / g;
-    } else {
-        ph.units = (ph.n + g - 1) / g;
-    }
-    ph.g = g;
+    ph.units = mega_phase_units(ph.type, ph.n, ph.k, ph.segs, a.D, a.F, ph.g);
     return ph;
 }
 // first row of segment s of unit u and how many of its g rows exist
@@ -890,10 +899,17 @@ int rg_b200_decode_step(const rg_decode_step_params *p, void *ws, const void *co
     const int rc = mega_validate(p);
     if (rc != RG_OK) return rc;
     const uint32_t G = static_cast<uint32_t>(sm_count());
-    // per-CTA bounds of the phase tables
-    const uint32_t g4 = 4;
-    const uint32_t max_units = std::max({(p->vocab + g4 - 1) / g4, p->ffn, (p->n_heads + 2 * p->n_kv_heads) * p->head_dim / 2, p->hidden});
-    if ((max_units + G - 1) / G + 1 > MG_PART_UNITS) return RG_ERR_SHAPE;
+    // no CTA may get more units of any phase than its partial-sum table holds: the same unit arithmetic as the kernel's
+    {
+        const uint32_t qd = p->n_heads * p->head_dim, D = p->head_dim, F = p->ffn, H = p->hidden;
+        const uint32_t shapes[5][4] = {{PH_QKV, (p->n_heads + 2 * p->n_kv_heads) * D, H, 2}, {PH_O, H, qd, 1}, {PH_GU, 2 * F, H, 2}, {PH_DOWN, H, F, 1},
+                                       {PH_LM, p->vocab, H, 1}};
+        for (auto const &sh : shapes) {
+            uint32_t g = 0;
+            const uint32_t units = mega_phase_units(static_cast<int>(sh[0]), sh[1], sh[2], sh[3], D, F, g);
+            if (g == 0 || (units + G - 1) / G > MG_PART_UNITS) return RG_ERR_SHAPE;
+        }
+    }
     if (p->n_heads > G) return RG_ERR_SHAPE;// the attention phase gives every head 1..8 CTAs
     MegaArgs a = {};
     // inputs: token, pos, embed, norm_f, lm_head, then per layer norm1, wqkv, wo, norm2, wgu, wd, k_cache, v_cache

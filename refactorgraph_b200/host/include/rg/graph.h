@@ -26,6 +26,7 @@ namespace refactor::computation {
         virtual kernel::CollectorBox candidateKernels(Target) const = 0;
         // output tensor descriptors from input descriptors (the reference keeps this in its frontend operators)
         virtual std::vector<Arc<Tensor>> infer(TensorRefs inputs) const = 0;
+        virtual std::unique_ptr<Operator> clone() const = 0;
     };
     using OpBox = std::unique_ptr<Operator>;
 
@@ -48,6 +49,8 @@ namespace refactor::runtime {
             void *blob;// own device allocation (constants, global inputs/outputs), else nullptr -> stack
             size_t stackOffset, bytes;
             std::string name;
+            DataType dataType = DataType::F32;// descriptor of the tensor behind the edge (what Executor::trace dumps)
+            std::vector<dim_t> shape;
         };
 
         Stream(Resources res, size_t stackBytes, std::vector<NodeSlot> nodes, std::vector<EdgeSlot> edges,
@@ -73,6 +76,10 @@ namespace refactor::runtime {
         Resources &resources() { return _resources; }
         size_t nodeCount() const { return _nodes.size(); }
         std::string_view nodeName(size_t i) const { return _nodes[i].name; }
+        NodeSlot const &node(size_t i) const { return _nodes[i]; }
+        EdgeSlot const &edge(size_t i) const { return _edges[i]; }
+        int device() const { return _device; }
+        void bind() const;// makes the stream's GPU the calling thread's current device
 
     private:
         void *address(size_t edge) const;
@@ -85,6 +92,7 @@ namespace refactor::runtime {
         std::vector<size_t> _globalInputs, _globalOutputs;
         void *_graphExec;
         bool _useGraph, _warm;
+        int _device;// the GPU that was current when the stream was lowered
     };
 }// namespace refactor::runtime
 
@@ -137,6 +145,15 @@ namespace refactor::computation {
         std::vector<size_t> globalInputs, globalOutputs;
 
         void inferShapes();
+        // Kernel fusion on the operator graph (the counterpart of the rewriting the reference does before it lowers,
+        // src/05computation/src/graph.cc:17-77 with layoutPermute as its one transformation): norm + product, product +
+        // residual add, product + SiLU gate, product + QKV split / rotation / cache append, all-reduce + residual add; with
+        // `wholeStep`, a batch-1 greedy decode step that has been fused completely becomes one DecodeStep node.
+        // Needs inferShapes() first.  Returns the number of rewrites applied.
+        size_t fuse(bool wholeStep);
         kernel::Graph lower(Target target) const;
+        // graph.info-style text: one line per node (name, operator, input and output edge names) and per edge (name, type,
+        // shape), and the bytes of all constant edges in edge order (src/09python_ffi/src/compiler.cc:140-169)
+        std::pair<std::string, std::vector<uint8_t>> serialize() const;
     };
 }// namespace refactor::computation

@@ -67,6 +67,7 @@ namespace refactor::kernel {
         std::vector<runtime::Stream::EdgeSlot> es;
         for (size_t i = 0; i < edges.size(); ++i) {
             runtime::Stream::EdgeSlot slot{nullptr, offset[i], edges[i].tensor ? edges[i].tensor->bytesSize() : 0, edges[i].name};
+            if (edges[i].tensor) slot.dataType = edges[i].tensor->dataType, slot.shape = edges[i].tensor->shape;
             if (own[i] && slot.bytes) {
                 if (cudaMalloc(&slot.blob, slot.bytes) != cudaSuccess) RUNTIME_ERROR("cudaMalloc failed for edge " + edges[i].name);
                 if (edges[i].tensor->data) {
@@ -89,14 +90,21 @@ namespace refactor::runtime {
                    std::vector<size_t> globalInputs, std::vector<size_t> globalOutputs)
         : _resources(std::move(res)), _stack(nullptr), _stackBytes(stackBytes), _nodes(std::move(nodes)),
           _edges(std::move(edges)), _globalInputs(std::move(globalInputs)), _globalOutputs(std::move(globalOutputs)),
-          _graphExec(nullptr), _useGraph(true), _warm(false) {
+          _graphExec(nullptr), _useGraph(true), _warm(false), _device(0) {
+        cudaGetDevice(&_device);
         if (_stackBytes) {
             if (cudaMalloc(&_stack, _stackBytes) != cudaSuccess) RUNTIME_ERROR("cudaMalloc failed for the activation stack");
             cudaMemset(_stack, 0, _stackBytes);// workspaces with arrival counters start at zero
         }
         cudaDeviceSynchronize();
     }
+    void Stream::bind() const {
+        int cur = -1;
+        if (cudaGetDevice(&cur) != cudaSuccess || cur != _device)
+            if (cudaSetDevice(_device) != cudaSuccess) RUNTIME_ERROR("cudaSetDevice failed");
+    }
     Stream::~Stream() {
+        cudaSetDevice(_device);
         cudaDeviceSynchronize();
         if (_graphExec) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(_graphExec));
         for (auto &e : _edges)
@@ -111,18 +119,21 @@ namespace refactor::runtime {
     void *Stream::outputAddress(count_t i) const { return address(_globalOutputs.at(i)); }
 
     void Stream::setData(count_t i, void const *host, size_t bytes) {
+        bind();
         auto &e = _edges[_globalInputs.at(i)];
         ASSERT(bytes == e.bytes, "setData: size of input " + e.name + " does not match its tensor");
         if (cudaMemcpyAsync(e.blob, host, bytes, cudaMemcpyHostToDevice, streamOf(_resources)) != cudaSuccess)
             RUNTIME_ERROR("setData: copy failed");
     }
     void Stream::setDataDevice(count_t i, void const *device, size_t bytes) {
+        bind();
         auto &e = _edges[_globalInputs.at(i)];
         ASSERT(bytes == e.bytes, "setDataDevice: size of input " + e.name + " does not match its tensor");
         if (cudaMemcpyAsync(e.blob, device, bytes, cudaMemcpyDeviceToDevice, streamOf(_resources)) != cudaSuccess)
             RUNTIME_ERROR("setDataDevice: copy failed");
     }
     bool Stream::copyData(count_t i, void *host, size_t bytes) const {
+        bind();
         auto const &e = _edges[_globalOutputs.at(i)];
         if (bytes != e.bytes) return false;
         auto st = streamOf(const_cast<Resources &>(_resources));
@@ -130,10 +141,12 @@ namespace refactor::runtime {
         return cudaStreamSynchronize(st) == cudaSuccess;
     }
     void Stream::sync() const {
+        bind();
         if (cudaStreamSynchronize(streamOf(const_cast<Resources &>(_resources))) != cudaSuccess) RUNTIME_ERROR("stream synchronize failed");
     }
 
     void Stream::deviceSync() const {
+        bind();
         if (cudaDeviceSynchronize() != cudaSuccess) RUNTIME_ERROR("device synchronize failed");
     }
 
@@ -152,6 +165,7 @@ namespace refactor::runtime {
     // capture, instantiated as a CUDA graph.  Later calls: one cudaGraphLaunch.  All device addresses are fixed at
     // lower time and setData copies into existing blobs, so the captured graph stays valid.
     void Stream::run() {
+        bind();
         auto st = streamOf(_resources);
         if (!_useGraph || !_warm) {
             runEager();
@@ -180,6 +194,7 @@ namespace refactor::runtime {
 
     // src/03runtime/src/stream.cc:71-86: per-node wall time, optionally synchronising after each node
     std::vector<std::chrono::nanoseconds> Stream::bench(bool sync_) {
+        bind();
         std::vector<std::chrono::nanoseconds> ans;
         std::vector<void const *> in;
         std::vector<void *> out;
@@ -200,6 +215,7 @@ namespace refactor::runtime {
 
     // src/03runtime/src/stream.cc:88-98: callback after every node with its input/output device addresses
     void Stream::trace(std::function<void(count_t, void const *const *, void const *const *)> cb) {
+        bind();
         std::vector<void const *> in, outc;
         std::vector<void *> out;
         auto st = streamOf(_resources);

@@ -10,7 +10,7 @@ from refactorgraph_b200.graph_builder import FP16
 from refactorgraph_b200.llama import LlamaConfig, decode_step_graph_batched, seeded_weights, weight_inputs
 
 import _ops as ops
-from _decode_oracle import oracle_decode
+from _decode_oracle import KvHistory, oracle_decode, oracle_decode_step_rounded
 
 pytestmark = pytest.mark.gpu
 
@@ -60,7 +60,10 @@ def test_batched_decode_graph(paged):
     vc = [rng.standard_normal((B, cfg.kv_heads, cfg.max_seq, cfg.head_dim)).astype(np.float16) for _ in range(cfg.layers)]
     token = rng.integers(0, cfg.vocab, (B,)).astype(np.int64)
     steps = 3
-    want_tok, want_logits = oracle_decode(cfg, w, kc, vc, token, past, steps)
+    # the oracle rounds every intermediate where this graph stores it (normalised activations, products, rotated q / k, ...)
+    r16 = lambda a: np.asarray(a, np.float32).astype(np.float16).astype(np.float32)
+    kh = [[KvHistory(kc[l][b], past[b]) for b in range(B)] for l in range(cfg.layers)]
+    vh = [[KvHistory(vc[l][b], past[b]) for b in range(B)] for l in range(cfg.layers)]
     max_blocks = cfg.max_seq // page
     n_blocks = B * max_blocks
     table = rng.permutation(n_blocks).reshape(B, max_blocks).astype(np.int32)
@@ -81,19 +84,20 @@ def test_batched_decode_graph(paged):
             ex.set_input(index[f"l{l}.v_cache"], vc[l])
     if paged:
         ex.set_input(index["block_table"], table)
-    ex.set_input(index["token"], token)
-    ex.set_input(index["pos"], past)
-    ex.set_input(index["lens"], past + 1)
+    tok = token
     for s in range(steps):
+        # the GPU's own token is fed to both sides, so a legitimate arg-max flip on a near-tie cannot part the trajectories
+        ex.set_input(index["token"], tok)
+        ex.set_input(index["pos"], past + s)
+        ex.set_input(index["lens"], past + s + 1)
         ex.run()
+        want = oracle_decode_step_rounded(cfg, w, kh, vh, tok, past + s, r16)
         logits = ex.get_output(index["logits"]).astype(np.float32)
-        np.testing.assert_allclose(logits, want_logits[s], atol=3e-2, rtol=2e-2)
-        tok = ex.get_output(index["next"])[:, 0]
-        # fp16 near-ties may flip an argmax; the token chosen must be (near-)maximal in the oracle's logits
-        gap = want_logits[s].max(axis=1) - want_logits[s][np.arange(B), tok]
-        assert (gap <= 3e-2).all()
-        if not (tok == want_tok[s]).all():
-            break  # trajectories diverged legitimately on a tie
+        np.testing.assert_allclose(logits, want, atol=2e-2, rtol=1e-2)
+        tok = ex.get_output(index["next"])[:, 0].copy()
+        np.testing.assert_array_equal(tok, onp.topk(logits, 1)[1][:, 0])           # arg-max of its own logits, bit-exact
+        gap = want.max(axis=1) - want[np.arange(B), tok]
+        assert (gap <= 2e-2).all()                                                   # and (near-)maximal in the oracle's
     assert capi.load().rg_b200_error_state() == 0
 
 
@@ -111,7 +115,11 @@ def test_all_reduce_world_one_and_limits():
     comm.all_reduce(capi.FP16, 0, h.numel(), h.data_ptr(), yh.data_ptr())
     assert torch.equal(yh, h)
     assert comm.all_reduce(capi.F32, 0, 1 << 20, x.data_ptr(), y.data_ptr(), check=False) == capi.ERR_LIMIT
-    assert comm.all_reduce(capi.I64, 0, 8, x.data_ptr(), y.data_ptr(), check=False) == capi.ERR_DTYPE
+    assert comm.all_reduce(capi.BOOL, 0, 8, x.data_ptr(), y.data_ptr(), check=False) == capi.ERR_DTYPE
+    i64 = torch.arange(-5, 1000, dtype=torch.int64, device="cuda")                                # integer types pass through a group of one
+    yi = torch.zeros_like(i64)
+    comm.all_reduce(capi.I64, 0, i64.numel(), i64.data_ptr(), yi.data_ptr())
+    assert torch.equal(yi, i64)
     assert comm.status() == capi.OK
     comm.destroy()
 
@@ -128,10 +136,20 @@ def test_all_reduce_missing_peer_reports_timeout_instead_of_hanging():
     y = torch.full_like(x, -1.0)
     comm.all_reduce(capi.F32, 0, x.numel(), x.data_ptr(), y.data_ptr())
     assert comm.status() == capi.ERR_TIMEOUT
+    assert capi.load().rg_b200_error_state() & 8             # bit 3: a communicator on this device gave up a wait
     assert torch.equal(y, torch.full_like(x, -1.0))          # output left untouched
     z = x + 1                                                   # the context is still alive
     assert float(z.sum()) == 512.0
+    # the communicator is out of step with its peers for good: a second call is refused on the host ...
+    assert comm.all_reduce(capi.F32, 0, x.numel(), x.data_ptr(), y.data_ptr(), check=False) == capi.ERR_TIMEOUT
+    assert torch.equal(y, torch.full_like(x, -1.0)) and comm.status() == capi.ERR_TIMEOUT
     comm.destroy()
+    assert capi.load().rg_b200_error_state() == 0            # ... and the error follows the communicator, not the library
+    # a communicator that is recreated works again (a group of one here: no second GPU is needed to show it)
+    fresh = capi.Comm(1, 0, 1 << 12)
+    fresh.all_reduce(capi.F32, 0, x.numel(), x.data_ptr(), y.data_ptr())
+    assert torch.equal(y, x) and fresh.status() == capi.OK
+    fresh.destroy()
 
 
 @pytest.mark.parametrize("np_dtype", [np.float16])
