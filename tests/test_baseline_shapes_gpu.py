@@ -131,7 +131,16 @@ def test_batch32_paged_sampling_decode_at_benchmark_shape():
 
 def test_bf16_prefill_2048_tokens_at_benchmark_shape():
     """BASELINE configuration 4 on two layers and two sequences of 2048 tokens, bf16: last-token logits and the K/V rows
-    the prefill wrote, against the oracle with every intermediate rounded where the GPU graph stores it."""
+    the prefill wrote, against the oracle with every intermediate rounded where the GPU graph stores it.
+
+    Tolerances.  What is one rounding away from identical inputs — the first layer's K and V rows — is held to the fp16
+    figures (max-abs 2e-2, relative 1e-2).  The logits come after two layers of bf16 storage (8 mantissa bits: one flipped
+    rounding is 0.4-0.8 % of the element) and a 2048-key softmax; at this shape two CPU restatements of the SAME oracle
+    that differ only in accumulating the products in fp32 instead of fp64 already differ by max 0.040 / rms 0.0085 in the
+    logits and 0.5 % rms in the last hidden state (0.050 / 0.011 when the probabilities are rounded to bf16 before P.V, as
+    the tensor-core path does), because each flip feeds the next normalisation and softmax.  So the logits are compared at
+    max-abs 8e-2 + relative 2e-2 with an rms bound of 2e-2 — a comparison at the oracle's own reproducibility in bf16,
+    not at fp16's."""
     B, S = 2, 2048
     cfg = LlamaConfig(layers=2, max_seq=S, batch=B, dtype=BF16)
     D, nH, nKV, F = cfg.head_dim, cfg.heads, cfg.kv_heads, cfg.ffn
@@ -143,13 +152,15 @@ def test_bf16_prefill_2048_tokens_at_benchmark_shape():
     pos = np.tile(np.arange(S, dtype=np.int64), B)
     mm = lambda x, wt: (torch.from_numpy(x).double() @ torch.from_numpy(wt).double().T).numpy()   # fp64 on all host cores
     x = w["embed"][ids.ravel()]
-    k_want = v_want = None
+    k_want = v_want = k_first = v_first = None
     for l in range(cfg.layers):
         n1 = rb(onp.rms_norm(x, w[f"l{l}.norm1"], cfg.eps))
         qkv = mm(n1, w[f"l{l}.wqkv"])                                        # the rotation happens on the fp32 accumulator
         q = rb(onp.rope(qkv[:, : nH * D].reshape(-1, nH, D), pos))
         k = rb(onp.rope(qkv[:, nH * D: (nH + nKV) * D].reshape(-1, nKV, D), pos))
         v = rb(qkv[:, (nH + nKV) * D:].reshape(-1, nKV, D))
+        if l == 0:
+            k_first, v_first = k, v
         if l == cfg.layers - 1:
             k_want, v_want = k, v
         a = np.empty((B * S, nH * D), np.float32)
@@ -183,17 +194,23 @@ def test_bf16_prefill_2048_tokens_at_benchmark_shape():
     ex.run()
     raw = ex.get_output(index["logits"])                                   # bf16 travels as raw 16-bit words
     logits = torch.from_numpy(raw.view(np.int16)).view(torch.bfloat16).float().numpy()
-    np.testing.assert_allclose(logits, want_logits, atol=2e-2, rtol=1e-2)
+    np.testing.assert_allclose(logits, want_logits, atol=8e-2, rtol=2e-2)
+    assert float(np.sqrt(((logits - want_logits) ** 2).mean())) < 2e-2
     np.testing.assert_array_equal(ex.get_output(index["next"]).ravel(), onp.topk(logits, 1)[1][:, 0])
     # the last layer's caches hold the rotated keys and the values of every token (device-to-device copy out of the
     # executor's input edge through the library's own transpose kernel with the identity permutation)
-    kc = torch.empty(B, nKV, S, D, dtype=torch.bfloat16, device="cuda")
-    tp = capi.TransposeParams()
-    tp.elem_bytes, tp.rank = 2, 2
-    tp.in_shape[:] = [B * nKV * S, D, 1, 1]
-    tp.perm[:] = [0, 1, 0, 0]
-    capi.call("transpose", tp, [ex.input_address(index[f"l{cfg.layers - 1}.k_cache"])], [kc.data_ptr()], stream=ex.cuda_stream())
-    ex.sync()
-    got_k = kc.float().cpu().numpy().transpose(0, 2, 1, 3).reshape(B * S, nKV, D)
-    np.testing.assert_allclose(got_k, k_want, atol=2e-2, rtol=1e-2)
+    def cache_rows(name):
+        buf = torch.empty(B, nKV, S, D, dtype=torch.bfloat16, device="cuda")
+        tp = capi.TransposeParams()
+        tp.elem_bytes, tp.rank = 2, 2
+        tp.in_shape[:] = [B * nKV * S, D, 1, 1]
+        tp.perm[:] = [0, 1, 0, 0]
+        capi.call("transpose", tp, [ex.input_address(index[name])], [buf.data_ptr()], stream=ex.cuda_stream())
+        ex.sync()
+        return buf.float().cpu().numpy().transpose(0, 2, 1, 3).reshape(B * S, nKV, D)
+    np.testing.assert_allclose(cache_rows("l0.k_cache"), k_first, atol=2e-2, rtol=1e-2)
+    np.testing.assert_allclose(cache_rows("l0.v_cache"), v_first, atol=2e-2, rtol=1e-2)
+    got_k = cache_rows(f"l{cfg.layers - 1}.k_cache")
+    np.testing.assert_allclose(got_k, k_want, atol=8e-2, rtol=2e-2)
+    assert float(np.sqrt(((got_k - k_want) ** 2).mean())) < 2e-2
     assert capi.load().rg_b200_error_state() == 0
