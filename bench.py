@@ -288,7 +288,9 @@ def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0, graph="si
         else:
             g, index = decode_step_graph_batched(cfg, world=tp)
             cache_shape = (cfg.batch, cfg.kv_heads, cfg.max_seq, cfg.head_dim)
-        ex = g.compiler().compile("cuda", "flat", [])
+        # the graphs are written operator by operator; the fusion pass turns the products and their readers into fused linear nodes
+        passes = os.environ.get("RG_BENCH_PASSES", "fuse").split(",") if os.environ.get("RG_BENCH_PASSES", "fuse") else []
+        ex = g.compiler().compile("cuda", "flat", passes)
         state["cfg"] = cfg
     else:
         g, index = decode_step_graph_single_kernel(cfg) if graph == "single" else decode_step_graph(cfg)

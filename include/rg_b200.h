@@ -206,10 +206,12 @@ int rg_b200_state_update(const rg_state_update_params *, void *ws, const void *c
  * inputs {A, B, C or NULL}, outputs {Y}.
  * Kernel selection (all hand-written, no vendor GEMM):
  *   - fp16/bf16, transA=0, transB=1, m <= 4: HBM-streaming GEMV (bulk-copy smem ring),
+ *   - fp16/bf16, transA=0, transB=1, 5 <= m <= 32, k a multiple of 128: the same weight streaming with the rows of A on the
+ *     warp-level tensor path (k cut into parts whose partial tiles are summed in a fixed order; needs the workspace),
  *   - fp16/bf16, transA=0, transB=1, aligned, m*n large: tcgen05/TMEM tensor-core GEMM fed by TMA,
  *   - anything else: shared-memory tiled SIMT GEMM.
- * Workspace: rg_b200_mat_mul_workspace bytes (split-K partials and arrival counters of the tensor-core kernel for skinny
- * products); it must be zero on first use and is left ready for the next call.  Without a workspace such products fall
+ * Workspace: rg_b200_mat_mul_workspace bytes (split-K partials and arrival counters of the skinny and tensor-core
+ * kernels); it must be zero on first use and is left ready for the next call.  Without a workspace such products fall
  * back to the SIMT kernel. */
 typedef struct rg_mat_mul_params {
     int32_t dtype; /* RG_F32, RG_FP16, RG_BF16 */
@@ -221,7 +223,7 @@ typedef struct rg_mat_mul_params {
     int32_t has_bias;
     uint32_t bias_row_stride, bias_col_stride; /* element strides of C over (m, n); 0 = broadcast */
     uint64_t stride_c;
-    int32_t force_kernel; /* 0 auto, 1 SIMT tile, 2 streaming GEMV, 3 tcgen05 */
+    int32_t force_kernel; /* 0 auto, 1 SIMT tile, 2 streaming GEMV, 3 tcgen05, 4 streaming skinny kernel (5..32 rows) */
     uint32_t flags;       /* RG_MM_B_STATIC: B is a weight - no kernel earlier in the stream writes it - so its tiles may be
                              fetched while the preceding kernel is still running (programmatic dependent launch) */
 } rg_mat_mul_params;
@@ -272,9 +274,12 @@ size_t rg_b200_swiglu_workspace(const rg_swiglu_params *);
 int rg_b200_swiglu(const rg_swiglu_params *, void *ws, const void *const *in, void *const *out, void *stream);
 
 /* Fused decode linear layer  Y = epilogue( prologue(X) * W^T ),  W[n,k] row-major (the reference MatMul with
- * transB = 1), X[m,k], m <= 4.  One launch replaces RmsNormalization + MatMul + (Add | Sigmoid,Mul,Mul |
- * RoPE + cache append) of the reference graph.  With m > 64, prologue 0, epilogue 3 and head_dim 128 (prefill) the product
- * runs on the tcgen05 GEMM and the split, rotation and cache append are its epilogue.
+ * transB = 1), X[m,k].  One launch replaces RmsNormalization + MatMul + (Add | Sigmoid,Mul,Mul |
+ * RoPE + cache append) of the reference graph.  m <= 4: every prologue and epilogue.  5 <= m <= 32 (batched decode, k a
+ * multiple of 128): prologue 0 with every epilogue, on the streaming skinny kernel; needs rg_b200_linear_workspace bytes,
+ * zero on first use and left ready for the next call.  m > 64, prologue 0, epilogue 3 and head_dim 128, or epilogue 2
+ * (prefill): the product runs on the tcgen05 GEMM and the split, rotation and cache append / the SiLU gate are its epilogue.
+ * W is taken to be a weight: no kernel earlier in the stream may write it (its stream starts before the previous kernel ends).
  *   prologue: 0 none; 1 RMSNorm with weight g[k] and epsilon (fp32 statistics).
  *   epilogue: 0 none                      outputs {Y[m,n]}
  *             1 residual add              inputs + {R[m,n]}; Y = R + X*W^T

@@ -38,10 +38,10 @@ int rg_b200_version(void) { return 2; }
 uint64_t rg_b200_launch_count(void) { return rg::g_launches.load(std::memory_order_relaxed); }
 static int error_state(bool clear) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    const int a = rg::linear_error_word(clear), b = rg::attn_error_word(clear), c = rg::gemm_tc_error_word(clear), d = rg::all_reduce_error_word(clear),
+    const int a = rg::linear_error_word(clear) | rg::skinny_error_word(clear), b = rg::attn_error_word(clear), c = rg::gemm_tc_error_word(clear), d = rg::all_reduce_error_word(clear),
               e = rg::mega_error_word(clear);
     const int i0 = rg::linear_index_error_word(clear), i1 = rg::elementwise_index_error_word(clear), i2 = rg::gemm_tc_index_error_word(clear),
-              i3 = rg::mega_index_error_word(clear), i4 = rg::attn_index_error_word(clear), i5 = rg::gqa_index_error_word(clear);
+              i3 = rg::mega_index_error_word(clear), i4 = rg::attn_index_error_word(clear), i5 = rg::gqa_index_error_word(clear) | rg::skinny_index_error_word(clear);
     if (a < 0 || b < 0 || c < 0 || d < 0 || e < 0 || i0 < 0 || i1 < 0 || i2 < 0 || i3 < 0 || i4 < 0 || i5 < 0) return -1;
     return (a ? 1 : 0) | (b ? 2 : 0) | (c ? 4 : 0) | (d ? 8 : 0) | (e ? 16 : 0) | ((i0 | i1 | i2 | i3 | i4 | i5) ? 32 : 0);
 }

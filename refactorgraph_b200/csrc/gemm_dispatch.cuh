@@ -10,6 +10,23 @@ int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const
 int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
 size_t gemm_tc_workspace(const rg_mat_mul_params *p);// split-K partials + arrival counters (zero before first use)
 bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *const *out);
+// Weight-streaming linear layer for 5..32 rows of X on the warp-level tensor path (linear_skinny.cu).
+struct SkinnyCall {
+    int dtype;
+    uint32_t m, n, k;
+    int epilogue;// 0 store, 1 alpha * acc + beta * C, 2 SiLU gate, 3 QKV split + RoPE + cache append
+    float alpha, beta;
+    uint32_t c_row_stride, c_col_stride, y_row_stride;
+    uint32_t n_heads;
+    float theta;
+    rg_kv_layout kv;
+    uint32_t tokens_per_seq;
+    int w_static;// W is a weight: its stream may start before the previous kernel has finished
+};
+bool linear_skinny_shape(int dtype, uint32_t m, uint32_t n, uint32_t k);
+size_t linear_skinny_workspace(int dtype, uint32_t m, uint32_t n, uint32_t k, int epilogue, const rg_kv_layout *kv, uint32_t n_heads);
+// in = {X, W, C or NULL, positions or NULL, block_table or NULL}; out = {Y, k_cache or NULL, v_cache or NULL}
+int linear_skinny(const SkinnyCall &c, void *ws, const void *const *in, void *const *out, cudaStream_t st);
 // per-file error words: bounded waits that expired, and device-read indices that were out of range (clear: zero after reading)
 int linear_error_word(bool clear);
 int attn_error_word(bool clear);
@@ -22,4 +39,6 @@ int gemm_tc_index_error_word(bool clear);
 int mega_index_error_word(bool clear);
 int attn_index_error_word(bool clear);
 int gqa_index_error_word(bool clear);
+int skinny_error_word(bool clear);
+int skinny_index_error_word(bool clear);
 }// namespace rg

@@ -407,9 +407,27 @@ int linear_index_error_word(bool clear) { return error_symbol(s_linear_index_err
 using namespace rg;
 
 extern "C" {
-size_t rg_b200_linear_workspace(const rg_linear_params *) { return 0; }
-int rg_b200_linear(const rg_linear_params *p, void *, const void *const *in, void *const *out, void *stream) {
+// 5..32 tokens without a norm prologue: the skinny weight-streaming kernel (linear_skinny.cu)
+static bool linear_is_skinny(const rg_linear_params *p) {
+    return p->m > 4 && p->m <= 32 && p->prologue == 0 && linear_skinny_shape(p->dtype, p->m, p->n, p->k);
+}
+size_t rg_b200_linear_workspace(const rg_linear_params *p) {
+    if (!p || !linear_is_skinny(p)) return 0;
+    return linear_skinny_workspace(p->dtype, p->m, p->n, p->k, p->epilogue, &p->kv, p->n_heads);
+}
+int rg_b200_linear(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out) return RG_ERR_NULL;
+    if (linear_is_skinny(p)) {
+        SkinnyCall c = {};
+        c.dtype = p->dtype, c.m = p->m, c.n = p->n, c.k = p->k, c.epilogue = p->epilogue;
+        c.alpha = 1.f, c.beta = 1.f;
+        const uint32_t n_out = p->epilogue == 2 ? p->n / 2 : p->epilogue == 3 ? p->n_heads * p->kv.head_dim : p->n;
+        c.c_row_stride = n_out, c.c_col_stride = 1, c.y_row_stride = n_out;
+        c.n_heads = p->n_heads, c.theta = p->theta, c.kv = p->kv, c.tokens_per_seq = p->tokens_per_seq;
+        c.w_static = 1;// as for the m <= 4 kernel: W is a weight, nothing earlier in the stream writes it
+        const void *lin[5] = {in[0], in[1], in[3], in[4], in[5]};
+        return linear_skinny(c, ws, lin, out, static_cast<cudaStream_t>(stream));
+    }
     // many tokens (prefill): the QKV projection runs on the tensor cores with the same epilogue
     if (p->m > 64 && p->epilogue == 3) return gemm_tc_qkv_rope(p, in, out, static_cast<cudaStream_t>(stream));
     if (p->m > 64 && p->epilogue == 2) return gemm_tc_swiglu(p, in, out, static_cast<cudaStream_t>(stream));

@@ -1,6 +1,7 @@
 // rg_b200_mat_mul: routes a MatMul (MatMulInfo semantics, src/04kernel/src/attributes/mat_mul_info.cc:27-42)
 // to one of the three hand-written kernels.  No vendor GEMM is linked.
 #include "gemm_dispatch.cuh"
+#include <cstdlib>
 
 using namespace rg;
 
@@ -18,12 +19,43 @@ static int run_gemv(const rg_mat_mul_params *p, const void *const *in, void *con
     return linear_stream(&lp, lin, lout, st);
 }
 
+// 5..32 rows of A against a K-major B: the weight-streaming kernel on the warp-level tensor path (RG_B200_SKINNY=0 keeps such
+// products on the tcgen05 kernel)
+static bool skinny_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("RG_B200_SKINNY");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+static bool skinny_shape(const rg_mat_mul_params *p) {
+    if (!skinny_enabled() || p->trans_a || !p->trans_b || p->batch != 1 || p->m <= 4 || p->m > 32) return false;
+    if (p->has_bias && (p->bias_col_stride > 1)) return false;
+    return linear_skinny_shape(p->dtype, p->m, p->n, p->k);
+}
+static int run_skinny(const rg_mat_mul_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st) {
+    SkinnyCall c = {};
+    c.dtype = p->dtype, c.m = p->m, c.n = p->n, c.k = p->k;
+    c.epilogue = p->has_bias ? 1 : 0;
+    c.alpha = p->alpha, c.beta = p->beta;
+    c.c_row_stride = p->bias_row_stride, c.c_col_stride = p->bias_col_stride, c.y_row_stride = p->n;
+    c.w_static = (p->flags & RG_MM_B_STATIC) != 0;
+    const void *lin[5] = {in[0], in[1], p->has_bias ? in[2] : nullptr, nullptr, nullptr};
+    void *lout[3] = {out[0], nullptr, nullptr};
+    return linear_skinny(c, ws, lin, lout, st);
+}
+
 extern "C" {
 
 size_t rg_b200_mat_mul_workspace(const rg_mat_mul_params *p) {
-    // only the tensor-core kernel's split-K path needs scratch; sized for it whenever that kernel could be chosen
+    // the tensor-core kernel's split-K path and the skinny kernel's k-split need scratch; sized for whichever could be chosen
     if (!p || (p->dtype != RG_FP16 && p->dtype != RG_BF16) || p->trans_a || !p->trans_b) return 0;
-    return gemm_tc_workspace(p);
+    size_t bytes = gemm_tc_workspace(p);
+    if (skinny_shape(p)) {
+        const size_t s = linear_skinny_workspace(p->dtype, p->m, p->n, p->k, p->has_bias ? 1 : 0, nullptr, 0);
+        bytes = s > bytes ? s : bytes;
+    }
+    return bytes;
 }
 
 int rg_b200_mat_mul(const rg_mat_mul_params *p, void *ws, const void *const *in, void *const *out, void *stream) {
@@ -39,10 +71,16 @@ int rg_b200_mat_mul(const rg_mat_mul_params *p, void *ws, const void *const *in,
         case 1: return gemm_simt(p, in, out, st);
         case 2: return gemv_shape(p) ? run_gemv(p, in, out, st) : RG_ERR_UNSUPPORTED;
         case 3: return gemm_tc_supported(p, in, out) ? gemm_tc(p, ws, in, out, st) : RG_ERR_UNSUPPORTED;
+        case 4: return skinny_shape(p) ? run_skinny(p, ws, in, out, st) : RG_ERR_UNSUPPORTED;
         default: return RG_ERR_UNSUPPORTED;
     }
     if (gemv_shape(p) && aligned16(in[0]) && aligned16(in[1])) {
         const int rc = run_gemv(p, in, out, st);
+        if (rc != RG_ERR_SHAPE && rc != RG_ERR_UNSUPPORTED) return rc;
+    }
+    if (skinny_shape(p) && aligned16(in[0]) && aligned16(in[1]) && aligned16(out[0]) &&
+        (ws || linear_skinny_workspace(p->dtype, p->m, p->n, p->k, p->has_bias ? 1 : 0, nullptr, 0) == 0)) {
+        const int rc = run_skinny(p, ws, in, out, st);
         if (rc != RG_ERR_SHAPE && rc != RG_ERR_UNSUPPORTED) return rc;
     }
     if (gemm_tc_supported(p, in, out) && (ws || gemm_tc_workspace(p) == 0)) return gemm_tc(p, ws, in, out, st);

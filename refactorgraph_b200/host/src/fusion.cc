@@ -51,8 +51,8 @@ namespace refactor::computation {
                 return makeOperator("b200::Linear", extra);
             }
 
-            // MatMul(x[m,k], W[n,k], transB) on up to 4 tokens -> Linear; an RmsNormalization that only feeds it becomes its
-            // prologue, a third input (C of the product's shape, beta 1) its residual epilogue.
+            // MatMul(x[m,k], W[n,k], transB) on up to 32 tokens -> Linear; on up to 4 tokens an RmsNormalization that only feeds it
+            // becomes its prologue; a third input (C of the product's shape, beta 1) becomes its residual epilogue.
             bool matMulToLinear(size_t n) {
                 auto mm = as<MatMul>(n);
                 auto &node = g.nodes[n];
@@ -60,7 +60,9 @@ namespace refactor::computation {
                 if (node.inputs.size() != 2 && node.inputs.size() != 3) return false;
                 auto const &x = tensor(node.inputs[0]);
                 auto const &w = tensor(node.inputs[1]);
-                if (!half(x.dataType) || x.shape.size() != 2 || w.shape.size() != 2 || x.shape[0] > 4) return false;
+                if (!half(x.dataType) || x.shape.size() != 2 || w.shape.size() != 2 || x.shape[0] > 32) return false;
+                const bool few = x.shape[0] <= 4;// 5..32 tokens: the skinny kernel, no norm prologue, k a multiple of 128
+                if (!few && x.shape[1] % 128 != 0) return false;
                 int epilogue = 0;
                 if (node.inputs.size() == 3) {
                     if (mm->beta != 1.f || tensor(node.inputs[2]).shape != tensor(node.outputs[0]).shape) return false;
@@ -70,7 +72,7 @@ namespace refactor::computation {
                 int prologue = 0;
                 float eps = 1e-5f;
                 const size_t pn = producer(node.inputs[0]);
-                if (auto norm = as<RmsNormalization>(pn); norm && soleConsumer(node.inputs[0]) == n) {
+                if (auto norm = as<RmsNormalization>(pn); few && norm && soleConsumer(node.inputs[0]) == n) {
                     prologue = 1, eps = norm->epsilon;
                     in = {g.nodes[pn].inputs[0], node.inputs[1], g.nodes[pn].inputs[1]};
                     dead[pn] = 1;

@@ -401,7 +401,7 @@ namespace refactor::kernel {
         rg_linear_params info;
         bool paged;
         FusedLinearB200(rg_linear_params p, bool paged_) noexcept : info(p), paged(paged_) {}
-        RG_KERNEL_IDS(FusedLinearB200, "Fused RMSNorm + linear + epilogue on B200 (bulk-copy weight streaming; tcgen05 GEMM for the prefill QKV form)")
+        RG_KERNEL_IDS(FusedLinearB200, "Fused RMSNorm + linear + epilogue on B200 (bulk-copy weight streaming for up to 32 tokens; tcgen05 GEMM for the prefill forms)")
         RoutineWorkspace lower(Resources &res) const final {
             auto st = res.fetchOrStore<CudaStream>();
             return RoutineWorkspace(
@@ -430,10 +430,12 @@ namespace refactor::kernel {
         auto const &w = inputs[1].get();
         if (_target != Target::Nvidia || !half(x.dataType) || w.dataType != x.dataType) return ans;
         if (x.shape.size() != 2 || w.shape.size() != 2 || x.shape[1] != w.shape[1]) return ans;
-        // up to 4 tokens: the streaming kernel; more than 64 tokens: the QKV and SiLU-gate forms, on the tensor-core GEMM
+        // up to 4 tokens: the streaming kernel; 5..32 tokens without a norm prologue: the streaming skinny kernel; more than 64
+        // tokens: the QKV and SiLU-gate forms, on the tensor-core GEMM
         if (x.shape[0] > 4) {
             const bool qkv = epilogue == 3 && headDim == 128, gate = epilogue == 2 && w.shape[0] % 256 == 0;
-            if (!(x.shape[0] > 64 && prologue == 0 && (qkv || gate))) return ans;
+            const bool skinny = x.shape[0] <= 32 && prologue == 0 && x.shape[1] % 128 == 0;
+            if (!skinny && !(x.shape[0] > 64 && prologue == 0 && (qkv || gate))) return ans;
         }
         rg_linear_params p{};
         p.tokens_per_seq = static_cast<uint32_t>(tokensPerSeq);

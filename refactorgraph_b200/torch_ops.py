@@ -180,8 +180,12 @@ def linear(x, w, g=None, eps=1e-6, residual=None, epilogue=0, n_heads=0, kv=None
         y = torch.empty(m, n_heads * kv.head_dim, dtype=x.dtype, device=x.device)
     else:
         y = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    nws = capi.workspace("linear", p)
+    ws = torch.zeros(max(nws, 1), dtype=torch.uint8, device=x.device)
     rc = capi.call("linear", p, [ptr(x), ptr(w), ptr(g), ptr(residual), ptr(positions), ptr(table)],
-                   [ptr(y), ptr(k_cache), ptr(v_cache)], stream=stream(), check=check)
+                   [ptr(y), ptr(k_cache), ptr(v_cache)], ws=ptr(ws) if nws else 0, stream=stream(), check=check)
+    if nws:
+        torch.cuda.current_stream().synchronize()  # the workspace is released on return
     return y if check else (rc, y)
 
 

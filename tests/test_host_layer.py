@@ -180,7 +180,14 @@ def test_fusion_pass_on_batched_tensor_parallel_and_prefill_graphs():
     g.output(g.op("onnx::Add", [r, y2]))
     c = g.compiler()
     assert c.plan([]) == ["MatMul", "AllReduce", "SimpleBinary", "MatMul", "SimpleBinary"]
-    assert c.plan(["fuse"]) == ["MatMul", "AllReduce", "MatMul"]
+    assert c.plan(["fuse"]) == ["FusedLinear", "AllReduce", "FusedLinear"]      # 16 tokens: the streaming skinny kernel
+    # ... and 48 tokens (beyond the streaming kernels) keep MatMul, the addends becoming its C operand / the residual input
+    g48 = GraphBuilder()
+    x48, r48 = g48.input("x", FP16, (48, 512)), g48.input("r", FP16, (48, 512))
+    g48.input("w", FP16, (512, 512))
+    h48 = g48.op("onnx::Add", [g48.op("onnx::AllReduceSum", [g48.op("llm::MatMul", [x48, "w"], transB=1)]), r48])
+    g48.output(g48.op("onnx::Add", [r48, g48.op("llm::MatMul", [h48, "w"], transB=1)]))
+    assert g48.compiler().plan(["fuse"]) == ["MatMul", "AllReduce", "MatMul"]
     # prefill (more than 64 tokens): SwiGLU and QkvRopeAppend become epilogues of the tensor-core product
     pcfg = LlamaConfig(layers=1, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=2)
     hand = prefill_graph(pcfg, 80, fused_rope=True)[0].compiler().plan([])
