@@ -592,6 +592,20 @@ static bool make_map(CUtensorMap *map, const void *base, int is_bf16, uint64_t r
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A K-major matrix W[rows, k] seen as (64 columns, rows, k / 64 column blocks): one request then loads a box of box_rows rows
+// x box_blocks column blocks, stored [block][row][128 bytes] with the 128-byte swizzle (the streaming skinny kernel's unit).
+bool tma_encode_rows_by_blocks(void *map, const void *base, int is_bf16, uint64_t rows, uint64_t k, uint32_t box_rows, uint32_t box_blocks) {
+    EncodeFn fn = encode_fn();
+    if (!fn || k % 64 != 0) return false;
+    const cuuint64_t dims[3] = {64, rows, k / 64};
+    const cuuint64_t strides[2] = {k * 2, 128};
+    const cuuint32_t box[3] = {64, box_rows, box_blocks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(static_cast<CUtensorMap *>(map), is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+              const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *const *out) {
     if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return false;
     if (p->trans_a || !p->trans_b) return false;

@@ -7,29 +7,46 @@
 //
 //  * k is cut into `ksplit` parts so that a warp's share of X fits in registers as A fragments (64 registers): the eight
 //    consumer warps take the eight 16-column steps of every 128-column block, a part has at most 16 blocks (8 for 32 rows).
-//  * a unit = (block of R = 8 or 16 weight rows, part): R bulk copies of one row segment each into a stage whose rows
-//    are padded by 16 bytes, which makes the B-fragment loads (lane = row g, column pair t) conflict-free.
-//  * per unit every warp holds a 16 x 8 (x MT x NT) partial tile; the warps' tiles are summed through shared memory in
-//    warp order, and four epilogue warps — decoupled from the consumers by a ring of tile slots — finish the unit:
-//    with ksplit > 1 the tile goes to a scratch area and the last part to arrive sums all parts in part order
+//  * a unit = (block of R = 8 or 16 weight rows, part) = 32 KiB.  W is described to the TMA unit as a 3-D tensor
+//    (64 columns, rows, k / 64 column blocks), so ONE tiled copy brings a unit's box [column block][row][128 bytes] (two copies
+//    when the epilogue pairs rows from two places); per-row bulk copies of 2-4 KiB ran into the copy unit's request rate
+//    (~9 M requests/s per SM) long before HBM.  The 128-byte swizzle puts the eight rows a B-fragment load touches on
+//    eight different bank groups.
+//  * per unit every warp holds a 16 x 8 (x MT x NT) partial tile, which it parks in a ring of shared-memory buffers and
+//    moves on — the consumer warps never meet at a barrier; four epilogue warps sum the eight tiles of a unit in warp
+//    order and finish it: with ksplit > 1 the tile goes to a scratch area and the last part to arrive sums all parts in part order
 //    (self-resetting counters), then the epilogue runs: plain store, alpha/beta with a C operand, SiLU gate on paired
 //    gate / up rows, or QKV split + rotary embedding + KV-cache append on paired (i, i + D/2) rows.
 //  * every wait is bounded; a wait that runs out is recorded and all threads leave through the same barriers.
 // Summation order is fixed (k steps, then warps, then parts), so results do not depend on timing.
+//
+// Where it is used.  On B200 the warp-level mma.sync path runs at about an eighth of the tcgen05 rate, and with 16 rows of X
+// this kernel needs ~60 % of that for the multiply-adds alone: cycle counters in the consumer warps show ~870 cycles per 32 KiB
+// unit inside the mma loop and ~120 waiting for data, i.e. the tensor path, not HBM, bounds it (3.8-4.4 TB/s on 134 MB of
+// weights, where the tcgen05 kernel streams 5.0).  It wins where the tcgen05 kernel's 128-row tiles are too few to fill the
+// GPU without a deep split (1280 x 8192 weights, one rank's QKV projection at tensor-parallel 8: 13.0 us against 18.3 us) and
+// it carries the RoPE / cache-append and SiLU epilogues for 5..32 rows, so the dispatch (mat_mul.cu, host fusion pass) sends
+// it the products with few rows of W and a long k, and leaves the rest on tcgen05.  Also measured and dropped: per-row 1-D
+// bulk copies instead of the tiled box (same speed), a CTA-wide barrier per unit for the cross-warp sum (same speed),
+// an L2 prefetch cursor eight units ahead of the ring (8-15 % slower), five instead of six stages (same speed).
 #include "gemm_dispatch.cuh"
+#include <cuda.h>
+#include <cstdlib>
 
 namespace rg {
+
+bool tma_encode_rows_by_blocks(void *map, const void *base, int is_bf16, uint64_t rows, uint64_t k, uint32_t box_rows, uint32_t box_blocks);// gemm_tc.cu
 
 constexpr int SK_NW = 8;                              // consumer warps
 constexpr int SK_EW = 4;                              // epilogue warps
 constexpr int SK_CONSUMERS = SK_NW * 32;
 constexpr int SK_THREADS = (SK_NW + SK_EW + 1) * 32;  // + producer warp
-constexpr int SK_STAGES = 5;
-constexpr int SK_SLOTS = 8;
-constexpr uint32_t SK_STAGE_BYTES = 33024;            // 16 rows x (2048 + 16) >= 8 rows x (4096 + 16)
+constexpr int SK_STAGES = 6;
+constexpr uint32_t SK_STAGE_BYTES = 33 * 1024;        // a 32 KiB box, or two 16 KiB boxes the second of which starts 512 bytes later (see sk_sub_offset)
 
 static __device__ int s_skinny_error;      // a bounded wait ran out
-static __device__ int s_skinny_index_error;// a cache-append position or block-table entry was out of range (store skipped)
+static __device__ int s_skinny_index_error;
+static __device__ unsigned long long s_skinny_prof[64];// TEMP diagnostics: per consumer warp of CTA 0: wait-full, mma, slot-wait cycles, units// a cache-append position or block-table entry was out of range (store skipped)
 
 struct SkinnyArgs {
     const void *W, *X, *C;
@@ -50,15 +67,27 @@ struct SkinnyArgs {
     int w_static;
 };
 
-__device__ __forceinline__ void sk_consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(SK_CONSUMERS) : "memory"); }
+// 3-D tiled copy (128-byte swizzle) into this CTA's shared memory with an L2 eviction hint, completion counted on `bar`
+__device__ __forceinline__ void sk_tma_load(void *dst, const CUtensorMap *map, uint32_t row, uint32_t block, uint64_t *bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(0u), "r"(row), "r"(block), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+// Where the 128-byte swizzle puts a byte whose unswizzled offset from a 1024-byte aligned base is `off`: bits 4-6 ^= bits 7-9.
+__device__ __forceinline__ uint32_t sk_swz(uint32_t off) { return off ^ ((off >> 3) & 0x70u); }
+// Stage offset of the second half of a paired unit.  With 4-row halves both halves' rows would fall on the same four swizzle
+// phases; starting the second box 512 bytes (four 128-byte lines) later shifts its phases by four.
+template<int R> __device__ __forceinline__ constexpr uint32_t sk_sub_offset() { return 16384u + (R == 8 ? 512u : 0u); }
 
 // global row of W behind row j of row block rb, or 0xffffffff when the block has no such row
 template<int R>
 __device__ __forceinline__ uint32_t sk_unit_row(const SkinnyArgs &a, uint32_t rb, uint32_t j) {
     constexpr uint32_t half = R / 2;
-    if (a.epilogue == 2) {
+    if (a.epilogue == 2) {// rows past the gate (up) half are never stored: the copy may fetch whatever lies there
         const uint32_t F = a.n / 2, r = rb * half + (j % half);
-        return r < F ? (j < half ? r : F + r) : 0xffffffffu;
+        return j < half ? r : F + r;
     }
     if (a.epilogue == 3) {
         const uint32_t D = a.kv.head_dim, per_head = (D / 2) / half;
@@ -90,21 +119,22 @@ __device__ __forceinline__ void sk_store2(T *base, uint64_t off, float v0, float
 }
 
 template<class T, int MT, int NT>
-__global__ void __launch_bounds__(SK_THREADS, 1) linear_skinny_kernel(const SkinnyArgs a) {
+__global__ void __launch_bounds__(SK_THREADS, 1) linear_skinny_kernel(const __grid_constant__ CUtensorMap map_full,
+                                                                      const __grid_constant__ CUtensorMap map_half, const SkinnyArgs a) {
     constexpr int R = 8 * NT;                 // weight rows per unit
     constexpr int BMAX = 16 / MT;             // 128-column blocks per part
-    constexpr uint32_t PITCH = BMAX * 256 + 16;
     constexpr int TILE = MT * NT * 128;       // floats of a unit's output tile, in C-fragment order
-    static_assert(R * PITCH <= SK_STAGE_BYTES, "stage too small");
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t *ring = smem;
-    float *pbuf = reinterpret_cast<float *>(smem + SK_STAGES * SK_STAGE_BYTES);// [2][SK_NW][TILE]
-    float *slots = pbuf + 2 * SK_NW * TILE;                                       // [SK_SLOTS][TILE]
-    uint64_t *full = reinterpret_cast<uint64_t *>(slots + SK_SLOTS * TILE);
+    constexpr int NBUF = MT * NT >= 4 ? 1 : 4; // partial-tile buffers in flight (16 KiB of shared memory either way)
+    constexpr int EWU = NBUF < SK_EW ? NBUF : SK_EW;// epilogue warps in use: a buffer always belongs to the same warp
+    static_assert(2 * BMAX * R * 128 == 32768, "a unit is a 32 KiB box");
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t *ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);// the swizzle is a function of address bits 7-9
+    float *pbuf = reinterpret_cast<float *>(ring + SK_STAGES * SK_STAGE_BYTES);// [NBUF][SK_NW][TILE]
+    uint64_t *full = reinterpret_cast<uint64_t *>(pbuf + NBUF * SK_NW * TILE);
     uint64_t *empty = full + SK_STAGES;
-    uint64_t *slot_full = empty + SK_STAGES;
-    uint64_t *slot_empty = slot_full + SK_SLOTS;
-    volatile int *failed = reinterpret_cast<volatile int *>(slot_empty + SK_SLOTS);
+    uint64_t *slot_full = empty + SK_STAGES;  // [NBUF] all eight warps have parked their tile of the unit
+    uint64_t *slot_empty = slot_full + 8;     // [NBUF] the epilogue warp has taken the tiles
+    volatile int *failed = reinterpret_cast<volatile int *>(slot_empty + 8);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3u;
     const uint32_t u0 = static_cast<uint32_t>(static_cast<uint64_t>(a.units) * blockIdx.x / gridDim.x);
@@ -116,7 +146,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) linear_skinny_kernel(const Skin
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], SK_NW);
         }
-        for (int s = 0; s < SK_SLOTS; ++s) {
+        for (int s = 0; s < NBUF; ++s) {
             mbar_init(&slot_full[s], SK_NW);
             mbar_init(&slot_empty[s], 1);
         }
@@ -127,29 +157,28 @@ __global__ void __launch_bounds__(SK_THREADS, 1) linear_skinny_kernel(const Skin
     pdl_launch_dependents();
 
     if (warp == SK_NW + SK_EW) {
-        // ---------------- producer: one thread streams this CTA's units through the ring ----------------
+        // ---------------- producer: one thread, one or two tiled copies per unit ----------------
         if (lane == 0) {
             if (!a.w_static) pdl_wait();
             const uint64_t policy = l2_policy_evict_first();
-            const uint8_t *W = static_cast<const uint8_t *>(a.W);
-            const uint64_t row_bytes = static_cast<uint64_t>(a.k) * 2u;
+            const bool paired = a.epilogue >= 2;
+            uint32_t p = u0 / a.nrb, rb = u0 % a.nrb;
             for (uint32_t i = 0; i < nu; ++i) {
                 const uint32_t s = i % SK_STAGES, ph = (i / SK_STAGES) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u)) {
                     atomicExch(&s_skinny_error, 2);
                     break;
                 }
-                const uint32_t u = u0 + i, p = u / a.nrb, rb = u % a.nrb;
-                const uint32_t kb0 = a.kblocks * p / a.ksplit, kb1 = a.kblocks * (p + 1) / a.ksplit;
-                const uint32_t seg = (kb1 - kb0) * 256u;
-                uint32_t live = 0;
-                for (uint32_t j = 0; j < R; ++j) live += sk_unit_row<R>(a, rb, j) != 0xffffffffu;
-                mbar_arrive_expect_tx(&full[s], live * seg);
+                const uint32_t kb0 = a.kblocks * p / a.ksplit;
                 uint8_t *st = ring + s * SK_STAGE_BYTES;
-                for (uint32_t j = 0; j < R; ++j) {
-                    const uint32_t row = sk_unit_row<R>(a, rb, j);
-                    if (row != 0xffffffffu) bulk_g2s_hint(st + j * PITCH, W + row * row_bytes + kb0 * 256u, seg, &full[s], policy);
+                mbar_arrive_expect_tx(&full[s], 32768u);// the box is always complete: rows or column blocks outside W arrive as zeros
+                if (!paired) {
+                    sk_tma_load(st, &map_full, rb * R, 2 * kb0, &full[s], policy);
+                } else {
+                    sk_tma_load(st, &map_half, sk_unit_row<R>(a, rb, 0) & 0x7fffffffu, 2 * kb0, &full[s], policy);
+                    sk_tma_load(st + sk_sub_offset<R>(), &map_half, sk_unit_row<R>(a, rb, R / 2) & 0x7fffffffu, 2 * kb0, &full[s], policy);
                 }
+                if (++rb == a.nrb) rb = 0, ++p;
             }
         }
         return;
@@ -159,18 +188,29 @@ __global__ void __launch_bounds__(SK_THREADS, 1) linear_skinny_kernel(const Skin
         // ---------------- epilogue warps: warp e finishes the units i = e, e + 4, ... ----------------
         pdl_wait();
         const uint32_t e = warp - SK_NW;
+        if (e >= EWU) return;
         T *Y = static_cast<T *>(a.Y);
         const T *C = static_cast<const T *>(a.C);
-        for (uint32_t i = e; i < nu; i += SK_EW) {
-            const uint32_t sl = i % SK_SLOTS;
-            if (!mbar_wait(&slot_full[sl], (i / SK_SLOTS) & 1u)) {
+        for (uint32_t i = e; i < nu; i += EWU) {
+            const uint32_t sl = i % NBUF;
+            if (!mbar_wait(&slot_full[sl], (i / NBUF) & 1u)) {
                 atomicExch(&s_skinny_error, 3);
                 return;
             }
             if (*failed) return;
+            // the eight warps' tiles, summed in warp order
             float4 v[MT * NT];
 #pragma unroll
-            for (int q = 0; q < MT * NT; ++q) v[q] = *reinterpret_cast<const float4 *>(slots + sl * TILE + q * 128 + lane * 4);
+            for (int q = 0; q < MT * NT; ++q) {
+                const float *src = pbuf + static_cast<size_t>(sl) * SK_NW * TILE + q * 128 + lane * 4;
+                float4 sum = *reinterpret_cast<const float4 *>(src);
+#pragma unroll
+                for (int w = 1; w < SK_NW; ++w) {
+                    const float4 x4 = *reinterpret_cast<const float4 *>(src + w * TILE);
+                    sum.x += x4.x, sum.y += x4.y, sum.z += x4.z, sum.w += x4.w;
+                }
+                v[q] = sum;
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&slot_empty[sl]);
             const uint32_t u = u0 + i, p = u / a.nrb, rb = u % a.nrb;
@@ -305,8 +345,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) linear_skinny_kernel(const Skin
     const uint32_t *Xw = static_cast<const uint32_t *>(a.X);
     uint32_t xf[BMAX][MT][4];
     uint32_t cur_part = 0xffffffffu, nb = 0;
+    uint32_t p = u0 / a.nrb, rbc = u0 % a.nrb;
     for (uint32_t i = 0; i < nu; ++i) {
-        const uint32_t u = u0 + i, p = u / a.nrb;
+        if (i && ++rbc == a.nrb) rbc = 0, ++p;
         if (p != cur_part) {
             cur_part = p;
             const uint32_t kb0 = a.kblocks * p / a.ksplit;
@@ -326,59 +367,101 @@ __global__ void __launch_bounds__(SK_THREADS, 1) linear_skinny_kernel(const Skin
                 }
         }
         const uint32_t s = i % SK_STAGES, ph = (i / SK_STAGES) & 1u;
-        const bool got = mbar_wait(&full[s], ph);
+        const bool got = __all_sync(0xffffffffu, mbar_wait(&full[s], ph) ? 1 : 0) != 0;// uniform for the warp
         if (!got) *failed = 1;
-        float acc[MT][NT][4];
+        // CH independent accumulator chains per output tile (k blocks b, b + CH, ...): a chain of dependent mma.sync instructions
+        // runs at the instruction's latency, not at its issue rate
+        constexpr int CH = MT * NT >= 4 ? 1 : 4;
+        float accc[CH][MT][NT][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+        for (int c = 0; c < CH; ++c)
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int r = 0; r < 4; ++r) acc[mt][nt][r] = 0.f;
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) accc[c][mt][nt][r] = 0.f;
         if (got) {
-            const uint8_t *st = ring + s * SK_STAGE_BYTES + warp * 32u + t * 4u;
+            // row g of n-tile nt, columns b * 128 + warp * 16 + 2t (+8): column block 2b + warp / 4, byte (warp % 4) * 32 + 4t (+16)
+            // of its 128-byte line; a box holds [column block][row][128 bytes], swizzled
+            const uint8_t *st = ring + s * SK_STAGE_BYTES;
+            const bool paired = a.epilogue >= 2;
+            uint32_t rowoff[NT], rows_in_box[NT];
 #pragma unroll
-            for (int b = 0; b < BMAX; ++b) {
-                if (static_cast<uint32_t>(b) < nb) {
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t j = nt * 8 + g;
+                if (!paired) rowoff[nt] = j * 128u, rows_in_box[nt] = R;
+                else
+                    rowoff[nt] = (j >= R / 2 ? sk_sub_offset<R>() : 0u) + (j % (R / 2)) * 128u, rows_in_box[nt] = R / 2;
+            }
+            const uint32_t inline_off = (warp & 3u) * 32u + t * 4u;
+            // all B fragments of the unit are loaded before the first mma, so that the shared-memory latency is paid once per
+            // unit and not once per k block; a full part takes the branch-free path
+            uint32_t bf[BMAX][NT][2];
+            if (nb == BMAX) {
+#pragma unroll
+                for (int b = 0; b < BMAX; ++b)
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
-                        const uint8_t *wp = st + (nt * 8 + g) * PITCH + b * 256;
-                        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(wp), b1 = *reinterpret_cast<const uint32_t *>(wp + 16);
+                        const uint32_t off = rowoff[nt] + (2u * b + (warp >> 2)) * rows_in_box[nt] * 128u + inline_off;
+                        bf[b][nt][0] = *reinterpret_cast<const uint32_t *>(st + sk_swz(off));
+                        bf[b][nt][1] = *reinterpret_cast<const uint32_t *>(st + sk_swz(off + 16u));
+                    }
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) mma16816<T>(acc[mt][nt], xf[b][mt], b0, b1);
+                for (int b = 0; b < BMAX; ++b)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) mma16816<T>(accc[b % CH][mt][nt], xf[b][mt], bf[b][nt][0], bf[b][nt][1]);
+            } else {
+#pragma unroll
+                for (int b = 0; b < BMAX; ++b) {
+                    if (static_cast<uint32_t>(b) < nb) {
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const uint32_t off = rowoff[nt] + (2u * b + (warp >> 2)) * rows_in_box[nt] * 128u + inline_off;
+                            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(st + sk_swz(off));
+                            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(st + sk_swz(off + 16u));
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) mma16816<T>(accc[b % CH][mt][nt], xf[b][mt], b0, b1);
+                        }
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
         }
-        // this warp's partial tile -> pbuf[i & 1][warp]
-        float *pb = pbuf + ((i & 1u) * SK_NW + warp) * TILE;
+        float acc[MT][NT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float v = accc[0][mt][nt][r];
+#pragma unroll
+                    for (int c = 1; c < CH; ++c) v += accc[c][mt][nt][r];
+                    acc[mt][nt][r] = v;
+                }
+        if (!got) break;// this warp gives up; the others run into their own bounded waits
+        // park this warp's partial tile in the unit's buffer and move on
+        const uint32_t sl = i % NBUF;
+        int oks = 1;
+        if (lane == 0) oks = mbar_wait(&slot_empty[sl], ((i / NBUF) & 1u) ^ 1u) ? 1 : 0;
+        if (!__shfl_sync(0xffffffffu, oks, 0)) {
+            *failed = 1;
+            break;
+        }
+        float *pb = pbuf + (static_cast<size_t>(sl) * SK_NW + warp) * TILE;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
                 *reinterpret_cast<float4 *>(pb + (mt * NT + nt) * 128 + lane * 4) = make_float4(acc[mt][nt][0], acc[mt][nt][1], acc[mt][nt][2], acc[mt][nt][3]);
-        sk_consumer_bar();
-        if (*failed) break;
-        // sum the eight warps' tiles in warp order into the unit's slot
-        const uint32_t sl = i % SK_SLOTS;
-        if (!mbar_wait(&slot_empty[sl], ((i / SK_SLOTS) & 1u) ^ 1u)) {
-            *failed = 1;
-            atomicExch(&s_skinny_error, 1);
-        } else {
-            for (uint32_t o = tid; o < TILE; o += SK_CONSUMERS) {
-                const float *src = pbuf + (i & 1u) * SK_NW * TILE + o;
-                float sum = src[0];
-#pragma unroll
-                for (int w = 1; w < SK_NW; ++w) sum += src[w * TILE];
-                slots[sl * TILE + o] = sum;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&slot_full[sl]);
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&slot_full[sl]);
     }
-    if (*failed && tid == 0) atomicExch(&s_skinny_error, 1);
+    if (*failed && lane == 0) atomicExch(&s_skinny_error, 1);
 }
 
 int skinny_error_word(bool clear) { return error_symbol(s_skinny_error, clear); }
@@ -416,7 +499,7 @@ static int skinny_plan(int dtype, uint32_t m, uint32_t n, uint32_t k, int epilog
     pl.tile = pl.mt * pl.nt * 128;
     pl.cnt_bytes = pl.ksplit > 1 ? (static_cast<size_t>(pl.nrb) * 4 + 255) / 256 * 256 : 0;
     pl.part_bytes = pl.ksplit > 1 ? static_cast<size_t>(pl.nrb) * pl.ksplit * pl.tile * 4 : 0;
-    pl.smem = SK_STAGES * SK_STAGE_BYTES + (2 * SK_NW + SK_SLOTS) * pl.tile * 4 + (2 * SK_STAGES + 2 * SK_SLOTS) * 8 + 16;
+    pl.smem = SK_STAGES * SK_STAGE_BYTES + 4 * SK_NW * 128 * 4 + (2 * SK_STAGES + 16) * 8 + 16 + 1024;// + room to align the ring to 1 KiB
     return RG_OK;
 }
 
@@ -431,12 +514,18 @@ size_t linear_skinny_workspace(int dtype, uint32_t m, uint32_t n, uint32_t k, in
 }
 
 template<class T>
-static int skinny_launch(const SkinnyArgs &a, const SkinnyPlan &pl, cudaStream_t st) {
-    void (*kern)(const SkinnyArgs) = pl.mt == 1 ? linear_skinny_kernel<T, 1, 1> : linear_skinny_kernel<T, 2, 2>;
+static int skinny_launch(const SkinnyArgs &a, const SkinnyPlan &pl, int is_bf16, cudaStream_t st) {
+    // one unit = box of R rows (or two boxes of R / 2 rows) x 32 / MT column blocks of 64
+    CUtensorMap full, half;
+    const uint32_t blocks = 32 / pl.mt;
+    if (!tma_encode_rows_by_blocks(&full, a.W, is_bf16, a.n, a.k, pl.R, blocks) ||
+        !tma_encode_rows_by_blocks(&half, a.W, is_bf16, a.n, a.k, pl.R / 2, blocks))
+        return RG_ERR_UNSUPPORTED;
+    void (*kern)(const CUtensorMap, const CUtensorMap, const SkinnyArgs) = pl.mt == 1 ? linear_skinny_kernel<T, 1, 1> : linear_skinny_kernel<T, 2, 2>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem)));
     unsigned grid = static_cast<unsigned>(sm_count());
     if (grid > pl.units) grid = pl.units;
-    RG_CHECK_CUDA(launch_pdl(kern, dim3(grid), dim3(SK_THREADS), pl.smem, st, a));
+    RG_CHECK_CUDA(launch_pdl(kern, dim3(grid), dim3(SK_THREADS), pl.smem, st, full, half, a));
     count_launch();
     return RG_OK;
 }
@@ -466,7 +555,7 @@ int linear_skinny(const SkinnyCall &c, void *ws, const void *const *in, void *co
     a.kv = c.kv, a.tokens_per_seq = c.tokens_per_seq;
     a.ksplit = pl.ksplit, a.kblocks = pl.kblocks, a.nrb = pl.nrb, a.units = pl.units;
     a.w_static = c.w_static;
-    return c.dtype == RG_FP16 ? skinny_launch<__half>(a, pl, st) : skinny_launch<__nv_bfloat16>(a, pl, st);
+    return c.dtype == RG_FP16 ? skinny_launch<__half>(a, pl, 0, st) : skinny_launch<__nv_bfloat16>(a, pl, 1, st);
 }
 
 }// namespace rg

@@ -51,8 +51,9 @@ namespace refactor::computation {
                 return makeOperator("b200::Linear", extra);
             }
 
-            // MatMul(x[m,k], W[n,k], transB) on up to 32 tokens -> Linear; on up to 4 tokens an RmsNormalization that only feeds it
-            // becomes its prologue; a third input (C of the product's shape, beta 1) becomes its residual epilogue.
+            // MatMul(x[m,k], W[n,k], transB) on up to 4 tokens (or up to 16 with few rows of W) -> Linear; on up to 4 tokens an
+            // RmsNormalization that only feeds it becomes its prologue; a third input (C of the product's shape, beta 1) becomes its
+            // residual epilogue.
             bool matMulToLinear(size_t n) {
                 auto mm = as<MatMul>(n);
                 auto &node = g.nodes[n];
@@ -60,9 +61,11 @@ namespace refactor::computation {
                 if (node.inputs.size() != 2 && node.inputs.size() != 3) return false;
                 auto const &x = tensor(node.inputs[0]);
                 auto const &w = tensor(node.inputs[1]);
-                if (!half(x.dataType) || x.shape.size() != 2 || w.shape.size() != 2 || x.shape[0] > 32) return false;
-                const bool few = x.shape[0] <= 4;// 5..32 tokens: the skinny kernel, no norm prologue, k a multiple of 128
-                if (!few && x.shape[1] % 128 != 0) return false;
+                if (!half(x.dataType) || x.shape.size() != 2 || w.shape.size() != 2 || x.shape[0] > 16) return false;
+                const bool few = x.shape[0] <= 4;
+                // 5..16 tokens: the streaming skinny kernel (no norm prologue), for the shape it is faster on than the tensor-core
+                // GEMM: few rows of W and a long k (one rank's QKV projection of a tensor-parallel step)
+                if (!few && !(x.shape[0] <= 16 && x.shape[1] % 128 == 0 && x.shape[1] >= 4096 && w.shape[0] <= 2560)) return false;
                 int epilogue = 0;
                 if (node.inputs.size() == 3) {
                     if (mm->beta != 1.f || tensor(node.inputs[2]).shape != tensor(node.outputs[0]).shape) return false;

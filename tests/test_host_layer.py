@@ -180,14 +180,13 @@ def test_fusion_pass_on_batched_tensor_parallel_and_prefill_graphs():
     g.output(g.op("onnx::Add", [r, y2]))
     c = g.compiler()
     assert c.plan([]) == ["MatMul", "AllReduce", "SimpleBinary", "MatMul", "SimpleBinary"]
-    assert c.plan(["fuse"]) == ["FusedLinear", "AllReduce", "FusedLinear"]      # 16 tokens: the streaming skinny kernel
-    # ... and 48 tokens (beyond the streaming kernels) keep MatMul, the addends becoming its C operand / the residual input
-    g48 = GraphBuilder()
-    x48, r48 = g48.input("x", FP16, (48, 512)), g48.input("r", FP16, (48, 512))
-    g48.input("w", FP16, (512, 512))
-    h48 = g48.op("onnx::Add", [g48.op("onnx::AllReduceSum", [g48.op("llm::MatMul", [x48, "w"], transB=1)]), r48])
-    g48.output(g48.op("onnx::Add", [r48, g48.op("llm::MatMul", [h48, "w"], transB=1)]))
-    assert g48.compiler().plan(["fuse"]) == ["MatMul", "AllReduce", "MatMul"]
+    assert c.plan(["fuse"]) == ["MatMul", "AllReduce", "MatMul"]                 # the addends become the C operand / the residual input
+    # 16 tokens against few weight rows with a long k (one rank's QKV projection): the streaming skinny kernel takes the
+    # product together with the RoPE / cache-append reader
+    cq = LlamaConfig(layers=1, hidden=8192, heads=8, kv_heads=1, head_dim=128, ffn=3584, vocab=2000, max_seq=256, batch=16)
+    pq = decode_step_graph_batched(cq, world=8)[0].compiler().plan(["fuse"])
+    assert pq[:3] == ["Gather", "RmsNormalization", "FusedLinear"] and pq.count("QkvRopeAppend") == 0
+    assert pq.count("MatMul") == 3 and pq.count("FusedLinear") == 2        # O, gate/up, down stay on tcgen05; the 2000-row LM head qualifies too
     # prefill (more than 64 tokens): SwiGLU and QkvRopeAppend become epilogues of the tensor-core product
     pcfg = LlamaConfig(layers=1, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=2)
     hand = prefill_graph(pcfg, 80, fused_rope=True)[0].compiler().plan([])
