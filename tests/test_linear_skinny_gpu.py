@@ -33,14 +33,17 @@ def test_plain_and_residual_products(m, n, k, dtype):
     tol = dict(atol=2e-2, rtol=1e-2) if dtype == torch.float16 else dict(atol=4e-2, rtol=2e-2)   # outputs of magnitude ~1-4 stored in bf16
     close(ops.linear(xd, wd), want, **tol)
     close(ops.linear(xd, wd, residual=rd, epilogue=1), want + r, **tol)
-    # the MatMul entry point routes these shapes to the same kernel (forced and automatic choice give the same bytes)
+    # the MatMul entry point can be told to use this kernel (force 4); left alone it picks it for up to 16 rows against few
+    # weight rows with a long k, where it is the faster one, and the tensor-core kernel otherwise
     y_auto = ops.mat_mul(xd, wd, trans_b=True)
     y_forced = ops.mat_mul(xd, wd, trans_b=True, force=4)
-    assert torch.equal(y_auto, y_forced)
     close(y_auto, want, **tol)
-    close(ops.mat_mul(xd, wd, c=rd, trans_b=True, alpha=0.5, beta=2.0), 0.5 * want + 2.0 * r, **tol)
+    close(y_forced, want, **tol)
+    if m <= 16 and n <= 2560 and k >= 4096:
+        assert torch.equal(y_auto, y_forced)
+    close(ops.mat_mul(xd, wd, c=rd, trans_b=True, alpha=0.5, beta=2.0, force=4), 0.5 * want + 2.0 * r, **tol)
     bias = r16(rng.standard_normal(n), dtype)
-    close(ops.mat_mul(xd, wd, c=ops.dev(bias, dtype), trans_b=True), want + bias, **tol)           # row-broadcast bias
+    close(ops.mat_mul(xd, wd, c=ops.dev(bias, dtype), trans_b=True, force=4), want + bias, **tol)  # row-broadcast bias
     assert capi.load().rg_b200_error_state() == 0
 
 
