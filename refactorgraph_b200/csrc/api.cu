@@ -38,7 +38,7 @@ int rg_b200_version(void) { return 2; }
 uint64_t rg_b200_launch_count(void) { return rg::g_launches.load(std::memory_order_relaxed); }
 static int error_state(bool clear) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    const int a = rg::linear_error_word(clear) | rg::skinny_error_word(clear), b = rg::attn_error_word(clear), c = rg::gemm_tc_error_word(clear), d = rg::all_reduce_error_word(clear),
+    const int a = rg::linear_error_word(clear) | rg::skinny_error_word(clear), b = rg::attn_error_word(clear) | rg::attn_tc_error_word(clear), c = rg::gemm_tc_error_word(clear), d = rg::all_reduce_error_word(clear),
               e = rg::mega_error_word(clear);
     const int i0 = rg::linear_index_error_word(clear), i1 = rg::elementwise_index_error_word(clear), i2 = rg::gemm_tc_index_error_word(clear),
               i3 = rg::mega_index_error_word(clear), i4 = rg::attn_index_error_word(clear), i5 = rg::gqa_index_error_word(clear) | rg::skinny_index_error_word(clear);

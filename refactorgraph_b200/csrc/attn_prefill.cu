@@ -237,6 +237,10 @@ int attn_prefill_launch(int dtype, const PrefillArgs &a, uint32_t batch, cudaStr
     return launch_status();
 }
 
+// the tcgen05 / TMEM kernel (attn_prefill_tc.cu)
+bool attn_prefill_tc_applies(const rg_attn_prefill_params *p, const void *const *in);
+int attn_prefill_tc_launch(const rg_attn_prefill_params *p, const void *const *in, void *const *out, cudaStream_t st);
+
 // reference layout [N, heads, S, D] for q / o and [N, kv_heads, kv_tokens, D] for k / v
 int attn_prefill_ref_layout(int dtype, const void *q, const void *K, const void *V, void *o, const int64_t *past, uint32_t batch,
                             uint32_t n_heads, uint32_t n_kv, uint32_t S, uint32_t kv_tokens, cudaStream_t st) {
@@ -248,6 +252,15 @@ int attn_prefill_ref_layout(int dtype, const void *q, const void *K, const void 
     a.v_sn = a.k_sn, a.v_sh = a.k_sh, a.v_st = PF_D;
     a.n_heads = n_heads, a.n_kv = n_kv, a.S = S, a.kv_cap = kv_tokens;
     a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(PF_D));
+    {
+        rg_attn_prefill_params p = {};
+        p.dtype = dtype, p.batch = batch, p.n_heads = n_heads, p.n_kv_heads = n_kv, p.seq_len = S, p.head_dim = PF_D, p.kv_capacity = kv_tokens;
+        const int64_t strides[12] = {a.q_sn, a.q_sh, a.q_st, a.k_sn, a.k_sh, a.k_st, a.v_sn, a.v_sh, a.v_st, a.o_sn, a.o_sh, a.o_st};
+        for (int i = 0; i < 12; ++i) p.strides[i] = strides[i];
+        const void *in[4] = {q, K, V, past};
+        void *out[1] = {o};
+        if (attn_prefill_tc_applies(&p, in) && aligned16(o)) return attn_prefill_tc_launch(&p, in, out, st);
+    }
     return attn_prefill_launch(dtype, a, batch, st);
 }
 
@@ -268,6 +281,8 @@ int rg_b200_attn_prefill(const rg_attn_prefill_params *p, void *, const void *co
     const int64_t *s = p->strides;
     for (int i = 0; i < 12; ++i)
         if (s[i] % 8 != 0) return RG_ERR_ALIGN;// 16-byte rows
+    // 128 query rows and more, from position 0: the tcgen05 kernel; the warp-level kernel serves the rest
+    if (attn_prefill_tc_applies(p, in) && aligned16(out[0])) return attn_prefill_tc_launch(p, in, out, static_cast<cudaStream_t>(stream));
     PrefillArgs a = {};
     a.q = in[0], a.k = in[1], a.v = in[2], a.past = static_cast<const int64_t *>(in[3]), a.o = out[0];
     a.q_sn = s[0], a.q_sh = s[1], a.q_st = s[2];

@@ -1,0 +1,381 @@
+// Causal flash attention for prefill on the fifth-generation tensor cores (head_dim 128, fp16 / bf16).
+// Semantics: src/08-01llm/README.md:29-63 (causal multi-head self-attention, query head h uses KV head h / (heads / kv_heads),
+// scores scaled by 1/sqrt(head_dim), softmax and accumulation in fp32).
+//
+// One CTA = 128 query rows of one (sequence, head) and walks the 128-key tiles at or below its causal diagonal:
+//   warp 4 (one thread)  TMA producer: Q once, then K and V tiles (two d-halves of [128 rows x 64 columns], 128-byte swizzle)
+//                        into double-buffered shared-memory stages, completion on mbarriers;
+//   warp 5 (one thread)  issues tcgen05.mma: S = Q K^T (both operands K-major, 8 instructions of M128 N128 K16) into one of two
+//                        128-column accumulators in tensor memory, and O_tile = P V (A = P from shared memory, K-major; B = V as
+//                        it lies in the cache, i.e. MN-major, 8 instructions) into a third; S of the NEXT tile is issued
+//                        before the wait for P, so it runs while the softmax warps work;
+//   warps 0-3            one query row per thread: tcgen05.ld of the row's scores, online softmax in fp32 with exp2, P written
+//                        to shared memory in the swizzled K-major layout the second product reads, O_tile read back with
+//                        tcgen05.ld and folded into the row's 128 fp32 accumulators (rescaled when the running maximum moves).
+// Keeping O in registers instead of in tensor memory avoids a read-modify-write of the accumulator whenever the maximum
+// changes; the price is one tcgen05.ld of 128 columns per tile, which is cheap next to the 128 exponentials per row.
+// Every wait is bounded; on expiry the kernel records an error word, releases its tensor memory and leaves.
+#include "tcgen05.cuh"
+#include <cstdlib>
+
+namespace rg {
+
+constexpr int AT_BM = 128, AT_BN = 128, AT_D = 128, AT_THREADS = 192;
+constexpr uint32_t AT_TILE_BYTES = 128 * 128 * 2;// one [128 x 128] 16-bit tile = two [128 x 64] swizzled halves
+
+static __device__ int s_attn_tc_error;
+
+struct AttnTcArgs {
+    void *o;
+    int64_t o_sn, o_sh, o_st;
+    uint32_t n_heads, n_kv, S, kv_len;
+    float scale_log2e;
+    int is_bf16;
+    uint32_t v_lbo, v_sbo;// descriptor offsets of the MN-major V operand (bytes)
+};
+
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t z, uint32_t w, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+        : "memory");
+}
+// Shared-memory descriptor with explicit leading / stride byte offsets, 128-byte swizzle (see smem_desc_sw128 for the fields)
+__device__ __forceinline__ uint64_t smem_desc_sw128_ex(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+// A bounded wait whose outcome is the same for every lane of the warp (the .sync.aligned tensor-memory instructions behind
+// it must be executed by the whole warp or by none of it)
+__device__ __forceinline__ bool at_warp_wait(uint64_t *bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
+}
+template<class T> __device__ __forceinline__ uint32_t at_pack2(float lo, float hi);
+template<> __device__ __forceinline__ uint32_t at_pack2<__half>(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+template<> __device__ __forceinline__ uint32_t at_pack2<__nv_bfloat16>(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+template<class T>
+__global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                                                        const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t *sQ = smem;                          // 32 KiB
+    uint8_t *sK = sQ + AT_TILE_BYTES;            // 2 x 32 KiB
+    uint8_t *sV = sK + 2 * AT_TILE_BYTES;        // 2 x 32 KiB
+    uint8_t *sP = sV + 2 * AT_TILE_BYTES;        // 32 KiB
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sP + AT_TILE_BYTES);
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
+    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 14, *o_empty = bars + 15;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heavy query tiles (far from the start of the sequence) first
+    const uint32_t q_tiles = gridDim.x, qt = q_tiles - 1 - blockIdx.x, h = blockIdx.y, n = blockIdx.z;
+    const uint32_t kvh = h / (a.n_heads / a.n_kv), q0 = qt * AT_BM;
+    // keys any row of this tile may see: [0, q0 + 128) cut at kv_len
+    uint32_t last_key = q0 + AT_BM < a.kv_len ? q0 + AT_BM : a.kv_len;
+    const uint32_t ntiles = (last_key + AT_BN - 1) / AT_BN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1), mbar_init(&s_empty[s], 4);
+        }
+        mbar_init(p_full, 4), mbar_init(o_full, 1), mbar_init(o_empty, 4);
+        *failed = 0;
+        fence_mbar_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, 512);// S x 2, O_tile: 384 columns, rounded up to the next power of two
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();// q, k and v come from the previous kernels of the stream
+
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, AT_TILE_BYTES);
+            tma_load_4d(sQ, &map_q, 0, q0, h, n, q_full);
+            tma_load_4d(sQ + AT_TILE_BYTES / 2, &map_q, 64, q0, h, n, q_full);
+            for (uint32_t j = 0; j < ntiles; ++j) {
+                const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+                if (!mbar_wait(&k_empty[s], ph ^ 1u)) {
+                    *failed = 1;
+                    break;
+                }
+                mbar_arrive_expect_tx(&k_full[s], AT_TILE_BYTES);
+                tma_load_4d(sK + s * AT_TILE_BYTES, &map_k, 0, j * AT_BN, kvh, n, &k_full[s]);
+                tma_load_4d(sK + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_k, 64, j * AT_BN, kvh, n, &k_full[s]);
+                if (!mbar_wait(&v_empty[s], ph ^ 1u)) {
+                    *failed = 1;
+                    break;
+                }
+                mbar_arrive_expect_tx(&v_full[s], AT_TILE_BYTES);
+                tma_load_4d(sV + s * AT_TILE_BYTES, &map_v, 0, j * AT_BN, kvh, n, &v_full[s]);
+                tma_load_4d(sV + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_v, 64, j * AT_BN, kvh, n, &v_full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            const uint32_t idesc_s = instr_desc(a.is_bf16, AT_BM, AT_BN);
+            const uint32_t idesc_o = instr_desc(a.is_bf16, AT_BM, AT_D) | (1u << 16);// B (= V) is MN-major
+            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            bool ok = mbar_wait(q_full, 0);
+            // S_j = Q K_j^T into accumulator j & 1
+            auto issue_s = [&](uint32_t j) {
+                const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+                if (!mbar_wait(&k_full[s], ph) || !mbar_wait(&s_empty[s], ph ^ 1u)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sK + s * AT_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = (kk >> 2) * (AT_TILE_BYTES / 2) + (kk & 3) * 32;
+                    tc_mma_f16(tmem_base + s * AT_BN, smem_desc_sw128(q_addr + off), smem_desc_sw128(k_addr + off), idesc_s, kk ? 1u : 0u);
+                }
+                tc_commit(&k_empty[s]);
+                tc_commit(&s_full[s]);
+                return true;
+            };
+            if (ok && ntiles) ok = issue_s(0);
+            for (uint32_t j = 0; ok && j < ntiles; ++j) {
+                if (j + 1 < ntiles) ok = issue_s(j + 1);
+                if (!ok) break;
+                const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+                // O_tile = P_j V_j once P is in shared memory, V has landed and the previous O_tile has been read
+                if (!mbar_wait(p_full, j & 1u) || !mbar_wait(&v_full[s], ph) || !mbar_wait(o_empty, (j & 1u) ^ 1u)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(sV + s * AT_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    // A = P: keys 16 kk .. 16 kk + 15 of the row -> half kk / 4, 32 bytes per step inside the swizzle atom
+                    const uint64_t ad = smem_desc_sw128(p_addr + (kk >> 2) * (AT_TILE_BYTES / 2) + (kk & 3) * 32);
+                    // B = V: 16 keys = 16 lines of 128 bytes further down the [key][64 d] half
+                    const uint64_t bd = smem_desc_sw128_ex(v_addr + kk * 2048, a.v_lbo, a.v_sbo);
+                    tc_mma_f16(tmem_base + 2 * AT_BN, ad, bd, idesc_o, kk ? 1u : 0u);
+                }
+                tc_commit(&v_empty[s]);
+                tc_commit(o_full);
+            }
+            if (!ok) *failed = 2;
+        }
+    } else {
+        // ---- softmax / output warps: thread = query row 32 * warp + lane = tensor-memory lane ----
+        const uint32_t row = warp * 32 + lane, qrow = q0 + row;
+        const uint32_t lane_addr = (warp * 32u) << 16;
+        float m_run = -INFINITY, l_run = 0.f;
+        float acc[AT_D];
+#pragma unroll
+        for (int d = 0; d < AT_D; ++d) acc[d] = 0.f;
+        bool ok = true;
+        for (uint32_t j = 0; j < ntiles && ok; ++j) {
+            const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+            if (!at_warp_wait(&s_full[s], ph)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t s_addr = tmem_base + s * AT_BN + lane_addr, key0 = j * AT_BN;
+            // keys this row may see in this tile: key <= qrow and key < kv_len
+            const uint32_t lim = qrow + 1 < a.kv_len ? qrow + 1 : a.kv_len;// first key NOT visible
+            const bool need_mask = key0 + AT_BN > lim;
+            // pass 1: row maximum
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(s_addr + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float v = __uint_as_float(r[e]);
+                    mx = fmaxf(mx, (!need_mask || key0 + c0 + e < lim) ? v : -INFINITY);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * a.scale_log2e);
+            // the previous tile's product: P free again, O_tile ready
+            if (j > 0) {
+                if (!at_warp_wait(o_full, (j - 1) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + 2 * AT_BN + lane_addr + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_empty);
+            }
+#pragma unroll
+            for (int d = 0; d < AT_D; ++d) acc[d] *= alpha;
+            l_run *= alpha;
+            m_run = m_new;
+            // pass 2: p = exp2((s - m) * scale), written as 16-bit into the swizzled K-major P tile
+            const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * a.scale_log2e;
+            float lsum = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(s_addr + c0, r);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float p0 = exp2f(fmaf(__uint_as_float(r[e]), a.scale_log2e, mneg));
+                    float p1 = exp2f(fmaf(__uint_as_float(r[e + 1]), a.scale_log2e, mneg));
+                    if (need_mask) {
+                        if (key0 + c0 + e >= lim) p0 = 0.f;
+                        if (key0 + c0 + e + 1 >= lim) p1 = 0.f;
+                    }
+                    packed[e / 2] = at_pack2<T>(p0, p1);
+                    // the row sum uses the rounded values, the ones the second product multiplies
+                    const float2 back = unpack2<T>(packed[e / 2]);
+                    lsum += back.x + back.y;
+                }
+                // 32 keys = four 16-byte chunks of this row's 128-byte line in half c0 / 64
+                uint8_t *line = sP + (c0 >> 6) * (AT_TILE_BYTES / 2) + row * 128u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t chunk = ((c0 & 63) >> 3) + q;
+                    *reinterpret_cast<uint4 *>(line + ((chunk ^ (row & 7u)) << 4)) =
+                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            l_run += lsum;
+            tc_fence_before();
+            fence_proxy_async();// the tensor core reads P through the async proxy
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&s_empty[s]);
+                mbar_arrive(p_full);
+            }
+        }
+        if (ok && ntiles) {
+            if (!at_warp_wait(o_full, (ntiles - 1) & 1u)) ok = false;
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + 2 * AT_BN + lane_addr + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
+                }
+                tc_fence_before();
+            }
+        }
+        if (!ok) *failed = 3;
+        if (ok && qrow < a.S) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T *dst = static_cast<T *>(a.o) + n * a.o_sn + h * a.o_sh + static_cast<int64_t>(qrow) * a.o_st;
+#pragma unroll
+            for (int d = 0; d < AT_D; d += 8) {
+                uint4 v;
+                v.x = at_pack2<T>(acc[d] * inv, acc[d + 1] * inv), v.y = at_pack2<T>(acc[d + 2] * inv, acc[d + 3] * inv);
+                v.z = at_pack2<T>(acc[d + 4] * inv, acc[d + 5] * inv), v.w = at_pack2<T>(acc[d + 6] * inv, acc[d + 7] * inv);
+                *reinterpret_cast<uint4 *>(dst + d) = v;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *failed) atomicExch(&s_attn_tc_error, *failed);
+}
+
+int attn_tc_error_word(bool clear) { return error_symbol(s_attn_tc_error, clear); }
+
+// (64 columns of d, tokens, heads, sequences) with the caller's element strides; box = 64 x 128 tokens, 128-byte swizzle
+static bool make_map_4d(CUtensorMap *map, const void *base, int is_bf16, uint64_t tokens, uint64_t heads, uint64_t seqs, int64_t st, int64_t sh,
+                        int64_t sn) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {128, tokens, heads, seqs};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(sn) * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// True when the tcgen05 kernel can serve the request: prefill from position 0 (no device-side past), enough rows for a tile,
+// strides a tensor map can express.  RG_B200_ATTN_TC=0 keeps every request on the warp-level kernel.
+bool attn_prefill_tc_applies(const rg_attn_prefill_params *p, const void *const *in) {
+    static const bool on = [] {
+        const char *e = std::getenv("RG_B200_ATTN_TC");
+        return !(e && e[0] == '0');
+    }();
+    if (!on || in[3] != nullptr || p->head_dim != AT_D || p->seq_len < 128) return false;
+    if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return false;
+    for (int i = 0; i < 12; ++i)
+        if (p->strides[i] <= 0 || p->strides[i] % 8 != 0) return false;
+    return encode_fn() != nullptr;
+}
+
+int attn_prefill_tc_launch(const rg_attn_prefill_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+    const int64_t *s = p->strides;
+    const int is_bf16 = p->dtype == RG_BF16;
+    const uint32_t kv_len = p->seq_len < p->kv_capacity ? p->seq_len : p->kv_capacity;
+    CUtensorMap mq, mk, mv;
+    // rows past kv_len are outside the K / V maps, so they arrive as zeros instead of whatever the cache holds there
+    if (!make_map_4d(&mq, in[0], is_bf16, p->seq_len, p->n_heads, p->batch, s[2], s[1], s[0]) ||
+        !make_map_4d(&mk, in[1], is_bf16, kv_len, p->n_kv_heads, p->batch, s[5], s[4], s[3]) ||
+        !make_map_4d(&mv, in[2], is_bf16, kv_len, p->n_kv_heads, p->batch, s[8], s[7], s[6]))
+        return RG_ERR_UNSUPPORTED;
+    AttnTcArgs a = {};
+    a.o = out[0];
+    a.o_sn = s[9], a.o_sh = s[10], a.o_st = s[11];
+    a.n_heads = p->n_heads, a.n_kv = p->n_kv_heads, a.S = p->seq_len, a.kv_len = kv_len;
+    a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(AT_D));
+    a.is_bf16 = is_bf16;
+    // MN-major operand: the next 64 columns of d are the other half tile (16 KiB further), the next 8 keys 1 KiB further
+    static const uint32_t lbo = std::getenv("RG_B200_ATTN_V_LBO") ? static_cast<uint32_t>(atoi(std::getenv("RG_B200_ATTN_V_LBO"))) : AT_TILE_BYTES / 2;
+    static const uint32_t sbo = std::getenv("RG_B200_ATTN_V_SBO") ? static_cast<uint32_t>(atoi(std::getenv("RG_B200_ATTN_V_SBO"))) : 1024u;
+    a.v_lbo = lbo, a.v_sbo = sbo;
+    const size_t smem = 6 * AT_TILE_BYTES + 256 + 1024;
+    dim3 grid((p->seq_len + AT_BM - 1) / AT_BM, p->n_heads, p->batch);
+    if (is_bf16) {
+        RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        RG_CHECK_CUDA(launch_pdl(attn_prefill_tc_kernel<__nv_bfloat16>, grid, dim3(AT_THREADS), smem, st, mq, mk, mv, a));
+    } else {
+        RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        RG_CHECK_CUDA(launch_pdl(attn_prefill_tc_kernel<__half>, grid, dim3(AT_THREADS), smem, st, mq, mk, mv, a));
+    }
+    count_launch();
+    return RG_OK;
+}
+
+}// namespace rg

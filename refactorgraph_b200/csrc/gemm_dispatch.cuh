@@ -40,5 +40,6 @@ int mega_index_error_word(bool clear);
 int attn_index_error_word(bool clear);
 int gqa_index_error_word(bool clear);
 int skinny_error_word(bool clear);
+int attn_tc_error_word(bool clear);
 int skinny_index_error_word(bool clear);
 }// namespace rg
