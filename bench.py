@@ -58,7 +58,8 @@ def parse_args():
                     help="7b / tiny workloads: 'single' = the whole step as one persistent kernel (b200::DecodeStep); "
                          "'fused' = five fused launches per layer replayed as a CUDA graph")
     ap.add_argument("--case", default=None, choices=["linear_gate_up", "linear_down", "linear_qkv", "attn_decode", "attn_decode_b32", "attn_decode_gqa", "attn_decode_gqa_tp2", "topk", "gemm_qkv", "gemm_down", "gemm_gate_up",
-                             "gemm_skinny16", "gemm_skinny32", "gemm_tp8", "all_reduce", "decode_step_timeline"],
+                             "gemm_skinny16", "gemm_skinny32", "gemm_tp8", "all_reduce", "decode_step_timeline",
+                             "rms_norm", "softmax", "gather", "attn_prefill", "skinny_qkv_tp8", "topk_sample"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
     ap.add_argument("--launches", type=int, default=6)
     return ap.parse_args()
@@ -583,6 +584,79 @@ def run_case(args):
         def launch(i):
             kc, vc = caches[i % len(caches)]
             capi.call("attn_decode", p, [q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), 0], [o.data_ptr()], ws=wsb.data_ptr(), stream=sid)
+    elif args.case == "rms_norm":
+        # the prefill shape: 8192 tokens x 4096, bf16 (64 MiB in, 64 MiB out per launch; two buffers > L2)
+        from refactorgraph_b200 import torch_ops as tops
+        rows, dim = 8192, H
+        xs = [torch.randn(rows, dim, device=dev).to(torch.bfloat16) for _ in range(3)]
+        w = torch.ones(dim, dtype=torch.bfloat16, device=dev)
+        y = torch.empty_like(xs[0])
+        p = capi.RmsNormParams(capi.BF16, rows, dim, 1e-6, 0)
+        bytes_per = 2 * rows * dim * 2
+
+        def launch(i):
+            capi.call("rms_norm", p, [xs[i % 3].data_ptr(), w.data_ptr()], [y.data_ptr()], stream=sid)
+    elif args.case == "softmax":
+        # attention-score shaped: [4 * 32 * 2048 rows, 2048] would be 1 GiB; a quarter of it (one sequence), fp16
+        rows, n = 32 * 2048, 2048
+        xs = [torch.randn(rows, n, device=dev).to(dt) for _ in range(2)]
+        y = torch.empty_like(xs[0])
+        p = capi.SoftmaxParams(capi.FP16, rows, n, 1)
+        bytes_per = 2 * rows * n * 2
+
+        def launch(i):
+            capi.call("softmax", p, [xs[i % 2].data_ptr()], [y.data_ptr()], stream=sid)
+    elif args.case == "gather":
+        # embedding lookup of a prefill: 8192 token ids into a [32000, 4096] fp16 table
+        table = torch.randn(V, H, device=dev).to(dt)
+        ids = [torch.randint(0, V, (8192,), device=dev) for _ in range(4)]
+        y = torch.empty(8192, H, dtype=dt, device=dev)
+        p = capi.GatherParams(1, V, 8192, H * 2, capi.I64)
+        bytes_per = 2 * 8192 * H * 2
+
+        def launch(i):
+            capi.call("gather", p, [table.data_ptr(), ids[i % 4].data_ptr()], [y.data_ptr()], stream=sid)
+    elif args.case == "attn_prefill":
+        # the attention launch of the prefill workload: [4, 32 heads, 2048 tokens, 128], bf16, causal; flops = 4 S^2 D / 2 per head
+        bf, S = torch.bfloat16, 2048
+        NB = int(os.environ.get("RG_BENCH_ATTN_SEQS", "4"))   # sequences per launch (the prefill workload has 4)
+        qkv = [tuple(torch.randn(NB, nH, S, D, device=dev).to(bf) for _ in range(3)) for _ in range(2)]
+        o = torch.empty(NB, nH, S, D, dtype=bf, device=dev)
+        p = capi.AttentionParams(capi.BF16, NB, nH, nH, S, D, S, 0)
+        bytes_per = 4 * NB * nH * S * D * 2
+        flops_per = NB * nH * 4.0 * D * (S * (S + 1) / 2.0)
+
+        def launch(i):
+            q, k, v = qkv[i % 2]
+            capi.call("attention", p, [q.data_ptr(), k.data_ptr(), v.data_ptr(), 0, 0, 0], [o.data_ptr(), 0, 0], stream=sid)
+    elif args.case == "skinny_qkv_tp8":
+        # one rank's QKV projection at tensor-parallel 8 (16 tokens, 1280 x 8192 weights) with the RoPE + cache-append epilogue
+        m, nq, nkv, k, MS = 16, 8, 1, 8192, 4096 + 128
+        n = (nq + 2 * nkv) * D
+        ws_ = [(0.02 * torch.randn(n, k, device=dev)).to(dt) for _ in range(8)]
+        x = torch.randn(m, k, device=dev).to(dt)
+        y = torch.empty(m, nq * D, dtype=dt, device=dev)
+        kc = torch.zeros(m, nkv, MS, D, dtype=dt, device=dev)
+        vc = torch.zeros_like(kc)
+        pos = torch.full((m,), 4096, device=dev, dtype=torch.int64)
+        p = capi.LinearParams()
+        p.dtype, p.m, p.n, p.k, p.prologue, p.epilogue, p.n_heads, p.theta = capi.FP16, m, n, k, 0, 3, nq, 10000.0
+        p.kv = capi.KvLayout(nkv, D, MS, 0, 0, 0)
+        wsb = torch.zeros(max(capi.workspace("linear", p), 1), dtype=torch.uint8, device=dev)
+        bytes_per = n * k * 2
+
+        def launch(i):
+            capi.call("linear", p, [x.data_ptr(), ws_[i % 8].data_ptr(), 0, 0, pos.data_ptr(), 0], [y.data_ptr(), kc.data_ptr(), vc.data_ptr()],
+                      ws=wsb.data_ptr(), stream=sid)
+    elif args.case == "topk_sample":
+        xs = [torch.randn(32, V, device=dev).to(dt) for _ in range(nbuf)]
+        tok = torch.empty(32, dtype=torch.int64, device=dev)
+        stp = torch.zeros(1, dtype=torch.int64, device=dev)
+        p = capi.TopkSampleParams(capi.FP16, 32, V, 50, 1.0, 0)
+        bytes_per = 32 * V * 2
+
+        def launch(i):
+            capi.call("topk_sample", p, [xs[i % nbuf].data_ptr(), stp.data_ptr()], [tok.data_ptr()], stream=sid)
     else:
         xs = [torch.randn(1, V, device=dev).to(dt) for _ in range(nbuf)]
         vals = torch.empty(1, 1, dtype=torch.float32, device=dev)
@@ -604,7 +678,7 @@ def run_case(args):
     us = 1000.0 * e0.elapsed_time(e1) / args.launches
     out = {"case": args.case, "launches": args.launches, "us_per_launch": us, "algorithmic_bytes_per_launch": bytes_per,
            "gbs": bytes_per / us / 1e3}
-    if args.case.startswith("gemm"):
+    if args.case.startswith("gemm") or args.case == "attn_prefill":
         out["tflops"] = flops_per / us / 1e6
     print(json.dumps(out), flush=True)
 

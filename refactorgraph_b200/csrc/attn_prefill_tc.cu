@@ -9,18 +9,27 @@
 //                        128-column accumulators in tensor memory, and O_tile = P V (A = P from shared memory, K-major; B = V as
 //                        it lies in the cache, i.e. MN-major, 8 instructions) into a third; S of the NEXT tile is issued
 //                        before the wait for P, so it runs while the softmax warps work;
-//   warps 0-3            one query row per thread: tcgen05.ld of the row's scores, online softmax in fp32 with exp2, P written
-//                        to shared memory in the swizzled K-major layout the second product reads, O_tile read back with
-//                        tcgen05.ld and folded into the row's 128 fp32 accumulators (rescaled when the running maximum moves).
+//   warps 0-7            two threads per query row (warps w and w + 4 share tensor-memory lane quarter w, one takes key / d columns
+//                        0-63, the other 64-127): tcgen05.ld of the scores, online softmax in fp32 with ex2.approx, P written to
+//                        shared memory in the swizzled K-major layout the second product reads, O_tile read back with tcgen05.ld
+//                        and added to the thread's 64 fp32 accumulators.  The two threads of a row swap their half-row maxima
+//                        through shared memory once per tile.  The running maximum is only moved (and the accumulators rescaled)
+//                        when a row's maximum grows by more than 2^8 in the exponent's units — probabilities then stay below 256,
+//                        exact in fp32 and far inside the 16-bit range — so most tiles skip the rescaling altogether.
 // Keeping O in registers instead of in tensor memory avoids a read-modify-write of the accumulator whenever the maximum
-// changes; the price is one tcgen05.ld of 128 columns per tile, which is cheap next to the 128 exponentials per row.
+// changes; the price is one tcgen05.ld of the tile per key tile.
+// Measured on [4, 32, 2048, 128] bf16: 275 us = 499 TFLOP/s (the warp-level mma.sync kernel: 565 us = 243 TFLOP/s); one row per
+// thread (four softmax warps, one per scheduler) gave 306 TFLOP/s on one sequence against 392 with two threads per row.  Cycle
+// counters in a softmax warp, per key tile: ~1480 in the exponential pass (the special-function unit's 16 results per clock
+// bound it at 1024), ~330 reading the scores for the maximum, ~200 in the pair exchange, ~190 adding O_tile, and ~800 waiting
+// for the tensor core (the single P buffer makes tile j's second product and tile j + 1's exponentials take turns).
 // Every wait is bounded; on expiry the kernel records an error word, releases its tensor memory and leaves.
 #include "tcgen05.cuh"
 #include <cstdlib>
 
 namespace rg {
 
-constexpr int AT_BM = 128, AT_BN = 128, AT_D = 128, AT_THREADS = 192;
+constexpr int AT_BM = 128, AT_BN = 128, AT_D = 128, AT_SW = 8, AT_THREADS = (AT_SW + 2) * 32;
 constexpr uint32_t AT_TILE_BYTES = 128 * 128 * 2;// one [128 x 128] 16-bit tile = two [128 x 64] swizzled halves
 
 static __device__ int s_attn_tc_error;
@@ -80,6 +89,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
     uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 14, *o_empty = bars + 15;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
     volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *xch = reinterpret_cast<float *>(bars + 18);// [2 tiles in flight][2 halves][128 rows]: half-row maxima
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy query tiles (far from the start of the sequence) first
@@ -94,13 +104,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1), mbar_init(&s_empty[s], 4);
+            mbar_init(&s_full[s], 1), mbar_init(&s_empty[s], AT_SW);
         }
-        mbar_init(p_full, 4), mbar_init(o_full, 1), mbar_init(o_empty, 4);
+        mbar_init(p_full, AT_SW), mbar_init(o_full, 1), mbar_init(o_empty, AT_SW);
         *failed = 0;
         fence_mbar_init();
     }
-    if (warp == 5) {
+    if (warp == AT_SW + 1) {
         tmem_alloc(tmem_slot, 512);// S x 2, O_tile: 384 columns, rounded up to the next power of two
         tmem_relinquish();
     }
@@ -111,7 +121,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
     pdl_launch_dependents();
     pdl_wait();// q, k and v come from the previous kernels of the stream
 
-    if (warp == 4) {
+    if (warp == AT_SW) {
         if (lane == 0) {
             mbar_arrive_expect_tx(q_full, AT_TILE_BYTES);
             tma_load_4d(sQ, &map_q, 0, q0, h, n, q_full);
@@ -134,7 +144,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                 tma_load_4d(sV + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_v, 64, j * AT_BN, kvh, n, &v_full[s]);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == AT_SW + 1) {
         if (lane == 0) {
             const uint32_t idesc_s = instr_desc(a.is_bf16, AT_BM, AT_BN);
             const uint32_t idesc_o = instr_desc(a.is_bf16, AT_BM, AT_D) | (1u << 16);// B (= V) is MN-major
@@ -181,90 +191,102 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
             if (!ok) *failed = 2;
         }
     } else {
-        // ---- softmax / output warps: thread = query row 32 * warp + lane = tensor-memory lane ----
-        const uint32_t row = warp * 32 + lane, qrow = q0 + row;
-        const uint32_t lane_addr = (warp * 32u) << 16;
-        float m_run = -INFINITY, l_run = 0.f;
-        float acc[AT_D];
+        // ---- softmax / output warps: lane quarter = warp % 4, column half = warp / 4 ----
+        const uint32_t quarter = warp & 3u, half = warp >> 2, row = quarter * 32 + lane, qrow = q0 + row;
+        const uint32_t lane_addr = (quarter * 32u) << 16, col0 = half * 64u;
+        const float c = a.scale_log2e, thr = 8.0f / c;
+        float m_used = -INFINITY, l_run = 0.f;
+        float acc[64];
 #pragma unroll
-        for (int d = 0; d < AT_D; ++d) acc[d] = 0.f;
+        for (int d = 0; d < 64; ++d) acc[d] = 0.f;
         bool ok = true;
-        for (uint32_t j = 0; j < ntiles && ok; ++j) {
-            const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
-            if (!at_warp_wait(&s_full[s], ph)) {
-                ok = false;
-                break;
-            }
+        auto add_o_tile = [&]() {// acc += this thread's 64 columns of O_tile
             tc_fence_after();
-            const uint32_t s_addr = tmem_base + s * AT_BN + lane_addr, key0 = j * AT_BN;
-            // keys this row may see in this tile: key <= qrow and key < kv_len
-            const uint32_t lim = qrow + 1 < a.kv_len ? qrow + 1 : a.kv_len;// first key NOT visible
-            const bool need_mask = key0 + AT_BN > lim;
-            // pass 1: row maximum
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + 2 * AT_BN + lane_addr + col0 + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
+            }
+            tc_fence_before();
+        };
+        // A wait that runs out is recorded in `failed`; the two warps of a lane quarter leave the loop together, right after
+        // the barrier they share, so neither is left waiting for the other.
+        for (uint32_t j = 0; j < ntiles; ++j) {
+            const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+            if (ok && !at_warp_wait(&s_full[s], ph)) ok = false, *failed = 3;
+            tc_fence_after();
+            const uint32_t s_addr = tmem_base + s * AT_BN + lane_addr + col0, key0 = j * AT_BN + col0;
+            // first key this row may NOT see; only the tiles on the diagonal or at the end of the sequence need the mask
+            const uint32_t lim = qrow + 1 < a.kv_len ? qrow + 1 : a.kv_len;
+            const uint32_t warp_lim = q0 + quarter * 32 + 1 < a.kv_len ? q0 + quarter * 32 + 1 : a.kv_len;// smallest lim in the warp
+            const bool masked = key0 + 64 > warp_lim;// warp-uniform
+            // pass 1: maximum of this thread's 64 scores, then of the whole row
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld_32x32(s_addr + c0, r);
                 tmem_ld_wait();
+                if (masked) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float v = __uint_as_float(r[e]);
-                    mx = fmaxf(mx, (!need_mask || key0 + c0 + e < lim) ? v : -INFINITY);
+                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, key0 + c0 + e < lim ? __uint_as_float(r[e]) : -INFINITY);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
                 }
             }
-            const float m_new = fmaxf(m_run, mx);
-            const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * a.scale_log2e);
+            float *xr = xch + (j & 1u) * 256;
+            xr[half * 128 + row] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");// the two warps of this lane quarter
+            if (*failed) break;
+            mx = fmaxf(mx, xr[(half ^ 1u) * 128 + row]);
             // the previous tile's product: P free again, O_tile ready
             if (j > 0) {
                 if (!at_warp_wait(o_full, (j - 1) & 1u)) {
-                    ok = false;
-                    break;
+                    ok = false, *failed = 3;
+                    continue;// the partner learns of it at the next shared barrier (or at the one behind the loop)
                 }
-                tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < AT_D; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + 2 * AT_BN + lane_addr + c0, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
-                }
-                tc_fence_before();
+                add_o_tile();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(o_empty);
             }
+            // move the reference maximum only when some row of the warp needs it (both warps of a row see the same maxima)
+            if (__any_sync(0xffffffffu, mx > m_used + thr)) {
+                const float m_new = fmaxf(m_used, mx);
+                const float alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * c);
 #pragma unroll
-            for (int d = 0; d < AT_D; ++d) acc[d] *= alpha;
-            l_run *= alpha;
-            m_run = m_new;
-            // pass 2: p = exp2((s - m) * scale), written as 16-bit into the swizzled K-major P tile
-            const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * a.scale_log2e;
+                for (int d = 0; d < 64; ++d) acc[d] *= alpha;
+                l_run *= alpha;
+                m_used = m_new;
+            }
+            // pass 2: p = 2^((s - m) * scale), written as 16-bit into this thread's 128-byte line of P half `half`
+            const float mneg = (m_used == -INFINITY) ? 0.f : -m_used * c;
             float lsum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+            uint8_t *line = sP + half * (AT_TILE_BYTES / 2) + row * 128u;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld_32x32(s_addr + c0, r);
                 tmem_ld_wait();
                 uint32_t packed[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float p0 = exp2f(fmaf(__uint_as_float(r[e]), a.scale_log2e, mneg));
-                    float p1 = exp2f(fmaf(__uint_as_float(r[e + 1]), a.scale_log2e, mneg));
-                    if (need_mask) {
+                    float p0, p1;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(r[e]), c, mneg)));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(r[e + 1]), c, mneg)));
+                    if (masked) {
                         if (key0 + c0 + e >= lim) p0 = 0.f;
                         if (key0 + c0 + e + 1 >= lim) p1 = 0.f;
                     }
+                    lsum += p0 + p1;
                     packed[e / 2] = at_pack2<T>(p0, p1);
-                    // the row sum uses the rounded values, the ones the second product multiplies
-                    const float2 back = unpack2<T>(packed[e / 2]);
-                    lsum += back.x + back.y;
                 }
-                // 32 keys = four 16-byte chunks of this row's 128-byte line in half c0 / 64
-                uint8_t *line = sP + (c0 >> 6) * (AT_TILE_BYTES / 2) + row * 128u;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    const uint32_t chunk = ((c0 & 63) >> 3) + q;
+                    const uint32_t chunk = (c0 >> 3) + q;
                     *reinterpret_cast<uint4 *>(line + ((chunk ^ (row & 7u)) << 4)) =
                         make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
@@ -278,27 +300,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                 mbar_arrive(p_full);
             }
         }
+        if (*failed) ok = false;
         if (ok && ntiles) {
-            if (!at_warp_wait(o_full, (ntiles - 1) & 1u)) ok = false;
-            if (ok) {
-                tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < AT_D; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + 2 * AT_BN + lane_addr + c0, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
-                }
-                tc_fence_before();
-            }
+            if (!at_warp_wait(o_full, (ntiles - 1) & 1u)) ok = false, *failed = 3;
+            if (ok) add_o_tile();
         }
-        if (!ok) *failed = 3;
+        // the row's denominator is the sum of its two threads' partial sums (same reference maximum in both)
+        float *xl = xch + 512;
+        xl[half * 128 + row] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
+        const float l_tot = l_run + xl[(half ^ 1u) * 128 + row];
         if (ok && qrow < a.S) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            T *dst = static_cast<T *>(a.o) + n * a.o_sn + h * a.o_sh + static_cast<int64_t>(qrow) * a.o_st;
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            T *dst = static_cast<T *>(a.o) + n * a.o_sn + h * a.o_sh + static_cast<int64_t>(qrow) * a.o_st + col0;
 #pragma unroll
-            for (int d = 0; d < AT_D; d += 8) {
+            for (int d = 0; d < 64; d += 8) {
                 uint4 v;
                 v.x = at_pack2<T>(acc[d] * inv, acc[d + 1] * inv), v.y = at_pack2<T>(acc[d + 2] * inv, acc[d + 3] * inv);
                 v.z = at_pack2<T>(acc[d + 4] * inv, acc[d + 5] * inv), v.w = at_pack2<T>(acc[d + 6] * inv, acc[d + 7] * inv);
@@ -308,7 +324,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == AT_SW + 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -365,7 +381,7 @@ int attn_prefill_tc_launch(const rg_attn_prefill_params *p, const void *const *i
     static const uint32_t lbo = std::getenv("RG_B200_ATTN_V_LBO") ? static_cast<uint32_t>(atoi(std::getenv("RG_B200_ATTN_V_LBO"))) : AT_TILE_BYTES / 2;
     static const uint32_t sbo = std::getenv("RG_B200_ATTN_V_SBO") ? static_cast<uint32_t>(atoi(std::getenv("RG_B200_ATTN_V_SBO"))) : 1024u;
     a.v_lbo = lbo, a.v_sbo = sbo;
-    const size_t smem = 6 * AT_TILE_BYTES + 256 + 1024;
+    const size_t smem = 6 * AT_TILE_BYTES + 18 * 8 + 3 * 256 * 4 + 1024;
     dim3 grid((p->seq_len + AT_BM - 1) / AT_BM, p->n_heads, p->batch);
     if (is_bf16) {
         RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
