@@ -62,6 +62,9 @@ def parse_args():
                              "rms_norm", "softmax", "gather", "attn_prefill", "skinny_qkv_tp8", "topk_sample"],
                     help="time one kernel alone at its 7B decode shape (small footprint; the case ncu captures run)")
     ap.add_argument("--launches", type=int, default=6)
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="with --workload 70b-tp on one GPU: run one rank's share of an N-way tensor-parallel step (all 80 layers, "
+                         "the all-reduce left out). A diagnostic for launch lists; its line is marked and is not a benchmark value")
     return ap.parse_args()
 
 
@@ -265,7 +268,7 @@ class ClockSampler:
         return min(samples, key=lambda tm: abs(tm[0] - mid))[1]
 
 
-def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0, graph="single"):
+def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0, graph="single", shard_of=0):
     """Compiles the decode-step graph of the workload and fills weights and caches with seeded values generated on
     the device.  Returns (executor, index, state) where state holds what reset_state needs."""
     from refactorgraph_b200.llama import (decode_step_graph, decode_step_graph_batched, decode_step_graph_single_kernel, shard_config,
@@ -276,7 +279,7 @@ def build_executor(cfg, kv_len, torch, workload="7b", world=1, rank=0, graph="si
     state = {"lens0": np.full(cfg.batch, kv_len, np.int64), "paged": False}
     if workload in ("7b-b32", "70b-tp"):
         tp = world if workload == "70b-tp" else 1
-        cfg = shard_config(cfg, tp)
+        cfg = shard_config(cfg, shard_of if (shard_of and tp == 1) else tp)
         page = 16
         if workload == "7b-b32":
             lens0 = np.random.default_rng(0).integers(512, 4097, (cfg.batch,)).astype(np.int64)
@@ -963,7 +966,8 @@ def measure_decode(args, torch, dist, lib, rank, world, local, workload, steps, 
     `7b` at world > 1 = one independent replica per GPU; `70b-tp` = one model sharded over the ranks."""
     from refactorgraph_b200 import capi
     tp = workload == "70b-tp"
-    full_cfg, kv_len = workload_config(workload, world)
+    shard_of = getattr(args, "shard_of", 0) if (tp and world == 1) else 0
+    full_cfg, kv_len = workload_config(workload, max(world, shard_of))
     comm, parity, ar_us = None, None, None
     if tp and world > 1:
         def exchange(handle):
@@ -973,7 +977,7 @@ def measure_decode(args, torch, dist, lib, rank, world, local, workload, steps, 
         comm = capi.Comm(world, rank, full_cfg.batch * full_cfg.hidden * 2, exchange=exchange)
         parity = tp_parity_check(torch, dist, lib, comm, rank, world)
         ar_us = time_all_reduce(torch, dist, comm, rank, world, full_cfg.batch * full_cfg.hidden)
-    ex, index, state = build_executor(full_cfg, kv_len, torch, workload, world, rank, args.graph)
+    ex, index, state = build_executor(full_cfg, kv_len, torch, workload, world, rank, args.graph, shard_of)
     single = workload in ("7b", "tiny", "7b-4l") and args.graph == "single"
     cfg = state["cfg"]                      # per-rank shape
     if comm is not None:
@@ -1095,6 +1099,9 @@ def measure_decode(args, torch, dist, lib, rank, world, local, workload, steps, 
     if tp:
         line["tp_parity"] = parity
         line["all_reduce_us"] = ar_us
+    if shard_of:
+        line["diagnostic"] = f"one rank's share of a tp{shard_of} step on one GPU, all-reduce left out: not a benchmark value"
+        line["config"]["parallelism"] = f"shard 0 of tp{shard_of}, no exchange"
     if with_cpu_baseline and workload in ("7b", "tiny", "7b-4l"):
         line["cpu_baseline"] = cpu_baseline(cfg, kv_len)
     return line

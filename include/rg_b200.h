@@ -435,6 +435,20 @@ typedef struct rg_all_reduce_params {
 } rg_all_reduce_params;
 int rg_b200_all_reduce(rg_comm *, const rg_all_reduce_params *, const void *const *in, void *const *out, void *stream);
 
+/* AllReduce(Sum) + residual + RmsNormalization in one launch: the three operators that follow a row-parallel product of a
+ * tensor-parallel decoder layer (AllReduceNccl, nccl_kernel.cu:9-19; BinaryCuda Add; RmsNormalizationCuda,
+ * src/04kernel/src/kernels/rms_normalization/cuda_kernel.cc:24-131).  inputs {x [rows, dim], residual [rows, dim] or NULL,
+ * w [dim]}, outputs {y = sum over ranks of x (+ residual), n = y * rsqrt(mean(y^2) + epsilon) * w}; RG_FP16 / RG_BF16;
+ * dim a multiple of 8 and at most 16384 (a row is held in the registers of one CTA); rows * dim * 2 <= the capacity given
+ * at create.  y and n carry the same bits as rg_b200_all_reduce followed by rg_b200_rms_norm.  Counts as one call of the
+ * communicator's sequence; waits and failure behave as for rg_b200_all_reduce. */
+typedef struct rg_all_reduce_norm_params {
+    int32_t dtype;
+    uint32_t rows, dim;
+    float epsilon;
+} rg_all_reduce_norm_params;
+int rg_b200_all_reduce_norm(rg_comm *, const rg_all_reduce_norm_params *, const void *const *in, void *const *out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -124,6 +124,10 @@ class AllReduceParams(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("op", C.c_int32), ("count", C.c_uint64)]
 
 
+class AllReduceNormParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("rows", C.c_uint32), ("dim", C.c_uint32), ("epsilon", C.c_float)]
+
+
 # name -> params struct, for every op with the (params, ws, in, out, stream) calling shape
 OPS = {
     "rms_norm": RmsNormParams, "softmax": SoftmaxParams, "topk": TopkParams, "topk_sample": TopkSampleParams,
@@ -136,7 +140,7 @@ OPS = {
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_error_clear", "rg_b200_attn_decode_static",
             "rg_b200_attn_decode_static_capacity", "rg_b200_decode_step_timeline", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_bytes", "rg_b200_comm_connect_ptrs",
             "rg_b200_comm_set_wait_ns",
-            "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce"]
+            "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce", "rg_b200_all_reduce_norm"]
            + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])
 
 _lib = None
@@ -176,6 +180,8 @@ def load() -> C.CDLL:
         lib.rg_b200_comm_destroy.argtypes = [C.c_void_p]
         lib.rg_b200_all_reduce.argtypes = [C.c_void_p, C.POINTER(AllReduceParams), C.POINTER(C.c_void_p),
                                            C.POINTER(C.c_void_p), C.c_void_p]
+        lib.rg_b200_all_reduce_norm.argtypes = [C.c_void_p, C.POINTER(AllReduceNormParams), C.POINTER(C.c_void_p),
+                                                C.POINTER(C.c_void_p), C.c_void_p]
         _lib = lib
     return _lib
 
@@ -256,6 +262,15 @@ class Comm:
         rc = load().rg_b200_all_reduce(self._ptr, C.byref(p), _ptrs([x, residual]), _ptrs([y]), stream or None)
         if check and rc != OK:
             raise RgError("all_reduce", rc)
+        return rc
+
+    def all_reduce_norm(self, dtype: int, rows: int, dim: int, eps: float, x: int, w: int, y: int, n: int, residual: int = 0,
+                        stream: int = 0, check: bool = True) -> int:
+        """y = sum over ranks of x (+ residual), n = rmsnorm(y) * w, in one launch."""
+        p = AllReduceNormParams(dtype, rows, dim, eps)
+        rc = load().rg_b200_all_reduce_norm(self._ptr, C.byref(p), _ptrs([x, residual, w]), _ptrs([y, n]), stream or None)
+        if check and rc != OK:
+            raise RgError("all_reduce_norm", rc)
         return rc
 
     def status(self) -> int:

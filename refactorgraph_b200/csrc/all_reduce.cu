@@ -324,6 +324,165 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const A
 }
 
 
+// ---------------------------------------------------------------------------------------------------------------------
+// AllReduce(Sum) + residual + RmsNormalization in one launch: what follows the row-parallel products (O and down) of a
+// tensor-parallel decoder layer.  y = sum over ranks of x (+ res), n = y * rsqrt(mean(y^2) + eps) * w.  One CTA per row with
+// the thread / chunk assignment and the summation order of rms_norm_vec_kernel, so y and n carry the same bits as the
+// all-reduce kernel followed by the normalisation kernel.  The exchange is the one above: flag-in-data lines, one-shot up to
+// 4 ranks, owner-reduces-and-broadcasts beyond; a thread sends everything it has to send before it waits for anything.
+struct ArNormArgs {
+    ArArgs a;
+    const void *w;
+    void *n;
+    uint32_t dim;
+    float eps;
+};
+
+// polls the 32-byte line at src until its four flags match; false when the wait expired
+__device__ __forceinline__ bool ar_poll_line(const uint8_t *src, uint32_t flag, uint64_t t0, uint64_t wait_ns, uint4 &out) {
+    for (uint32_t spin = 1;; ++spin) {
+        const uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 16);
+        if (lo.y == flag && lo.w == flag && hi.y == flag && hi.w == flag) {
+            out = make_uint4(lo.x, lo.z, hi.x, hi.z);
+            return true;
+        }
+        if ((spin & 63u) == 0 && global_timer_ns() - t0 > wait_ns) return false;
+    }
+}
+__device__ __forceinline__ void ar_push_line(uint8_t *dst, const uint4 &v, uint32_t flag) {
+    st_volatile_v4(dst, v.x, flag, v.y, flag);
+    st_volatile_v4(dst + 16, v.z, flag, v.w, flag);
+}
+
+template<class T, int CH, bool TWO>
+__global__ void __launch_bounds__(AR_THREADS) all_reduce_norm_kernel(const ArNormArgs p) {
+    pdl_enter();
+    constexpr int N = 16 / sizeof(T);
+    const ArArgs &a = p.a;
+    ArHeader *hdr = reinterpret_cast<ArHeader *>(a.mine);
+    __shared__ unsigned long long s_seq;
+    __shared__ int s_status;
+    __shared__ float red[33];
+    if (threadIdx.x == 0) {
+        const unsigned long long sq = *reinterpret_cast<volatile unsigned long long *>(&hdr->seq);
+        s_seq = sq;
+        s_status = *reinterpret_cast<volatile int *>(&hdr->status);// one read per CTA: the CTA leaves as a whole or not at all
+        if (atomicAdd(&hdr->done, 1u) == gridDim.x - 1) {
+            hdr->done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned long long *>(&hdr->seq) = sq + 1;
+        }
+    }
+    __syncthreads();
+    if (s_status != 0) return;// out of step with the peers: no-op, as the plain kernels
+    const unsigned long long seq = s_seq;
+    const unsigned q = static_cast<unsigned>(seq & 1ull);
+    const uint32_t flag = ar_flag(seq);
+    const uint32_t chunks = p.dim / N;
+    const uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * chunks;// first chunk of this CTA's row
+    const T *x = static_cast<const T *>(a.x);
+    const T *res = static_cast<const T *>(a.res);
+    T *y = static_cast<T *>(a.y);
+    const size_t my_off = ar_slot_off(a, q, a.rank);
+    const size_t b_off = ar_slot_off(a, 2, 0) + static_cast<size_t>(q) * (2 * a.capacity);
+    const uint64_t t0 = global_timer_ns();
+
+    // 1. send: to every peer (one-shot) or to the owner of the 32-chunk run (two-shot)
+    uint4 mine[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            const uint64_t gc = row0 + c;
+            mine[i] = *reinterpret_cast<const uint4 *>(x + gc * N);
+            if constexpr (TWO) {
+                const int owner = static_cast<int>((gc / 32) % static_cast<uint64_t>(a.world));
+                if (owner != a.rank) ar_push_line(a.peer[owner] + my_off + gc * 32, mine[i], flag);
+            } else {
+#pragma unroll
+                for (int r = 0; r < AR_MAX_RANKS; ++r)
+                    if (r < a.world && r != a.rank) ar_push_line(a.peer[r] + my_off + gc * 32, mine[i], flag);
+            }
+        }
+    }
+    // 2. owned chunks (all of them, one-shot): gather the peers' lines, combine in rank order, add the residual
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            const uint64_t gc = row0 + c;
+            const bool own = !TWO || static_cast<int>((gc / 32) % static_cast<uint64_t>(a.world)) == a.rank;
+            if (own) {
+                uint4 raw[AR_MAX_RANKS];
+#pragma unroll
+                for (int r = 0; r < AR_MAX_RANKS; ++r) {
+                    raw[r] = mine[i];
+                    if (r < a.world && r != a.rank && ok) ok = ar_poll_line(a.mine + ar_slot_off(a, q, r) + gc * 32, flag, t0, a.wait_ns, raw[r]);
+                }
+                mine[i] = ar_reduce_chunk<T>(raw, a.world, 0, res, gc * N, a.count);
+                if constexpr (TWO) {
+                    if (ok) {
+#pragma unroll
+                        for (int r = 0; r < AR_MAX_RANKS; ++r)
+                            if (r < a.world && r != a.rank) ar_push_line(a.peer[r] + b_off + gc * 32, mine[i], flag);
+                    }
+                }
+            }
+        }
+    }
+    // 3. two-shot: the finished values of the chunks other ranks own
+    if constexpr (TWO) {
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            if (c < chunks) {
+                const uint64_t gc = row0 + c;
+                if (static_cast<int>((gc / 32) % static_cast<uint64_t>(a.world)) != a.rank && ok)
+                    ok = ar_poll_line(a.mine + b_off + gc * 32, flag, t0, a.wait_ns, mine[i]);
+            }
+        }
+    }
+    if (__syncthreads_or(!ok)) {
+        if (threadIdx.x == 0) hdr->status = 1;// outputs untouched; the host sees the status word
+        return;
+    }
+    // 4. y, then the normalisation of the rounded y exactly as rms_norm_vec_kernel computes it
+    float v[CH][N];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            *reinterpret_cast<uint4 *>(y + (row0 + c) * N) = mine[i];
+            Vec16<T> t;
+            t.raw = mine[i];
+            t.unpack(v[i]);
+#pragma unroll
+            for (int j = 0; j < N; ++j) ss += v[i][j] * v[i][j];
+        }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / static_cast<float>(p.dim) + p.eps);
+    const T *w = static_cast<const T *>(p.w);
+    T *n = static_cast<T *>(p.n);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            Vec16<T> g, o;
+            float gw[N], out[N];
+            g.load(w + c * N);
+            g.unpack(gw);
+#pragma unroll
+            for (int j = 0; j < N; ++j) out[j] = v[i][j] * rstd * gw[j];
+            o.pack(out);
+            o.store(n + (row0 + c) * N);
+        }
+    }
+}
+
+
 }// namespace rg
 
 using namespace rg;
@@ -524,6 +683,59 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
         default: RG_AR(double); break;
     }
 #undef RG_AR
+    if (e != cudaSuccess) return RG_ERR_CUDA;
+    count_launch();
+    return launch_status();
+}
+
+int rg_b200_all_reduce_norm(rg_comm *c, const rg_all_reduce_norm_params *p, const void *const *in, void *const *out, void *stream) {
+    if (!c || !p || !in || !out || !in[0] || !in[2] || !out[0] || !out[1]) return RG_ERR_NULL;
+    if (!c->connected) return RG_ERR_UNSUPPORTED;
+    if (c->failed) return RG_ERR_TIMEOUT;
+    if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return RG_ERR_DTYPE;
+    if (p->rows == 0 || p->dim == 0) return RG_OK;
+    // the row lives in registers: 16-byte chunks, at most 8 per thread of a 256-thread CTA
+    if (p->dim % 8 != 0 || p->dim > 8u * 8u * AR_THREADS || p->rows > 65535u) return RG_ERR_SHAPE;
+    const size_t bytes = static_cast<size_t>(p->rows) * p->dim * 2;
+    if (bytes > c->capacity) return RG_ERR_LIMIT;
+    for (int i = 0; i < 3; ++i)
+        if (in[i] && !aligned16(in[i])) return RG_ERR_ALIGN;
+    if (!aligned16(out[0]) || !aligned16(out[1])) return RG_ERR_ALIGN;
+    ArNormArgs a = {};
+    a.a.mine = c->mine;
+    for (int r = 0; r < c->world; ++r) a.a.peer[r] = c->peers[r];
+    a.a.x = in[0], a.a.res = in[1], a.a.y = out[0];
+    a.a.count = static_cast<uint64_t>(p->rows) * p->dim, a.a.capacity = c->capacity;
+    a.a.world = c->world, a.a.rank = c->rank, a.a.op = 0;
+    a.a.wait_ns = c->wait_ns;
+    a.w = in[2], a.n = out[1], a.dim = p->dim, a.eps = p->epsilon;
+    // chunks per thread and CTA size exactly as the RmsNormalization launcher picks them (same bits as the two-kernel form)
+    const uint32_t chunks = p->dim / 8;
+    uint32_t ch = (chunks + 255) / 256;
+    ch = ch <= 1 ? 1 : ch <= 2 ? 2 : ch <= 4 ? 4 : 8;
+    uint32_t threads = ((chunks + ch - 1) / ch + 31) / 32 * 32;
+    if (threads > 256) threads = 256;
+    if (threads < 32) threads = 32;
+    static const int algo_env = std::getenv("RG_B200_AR_ALGO") ? atoi(std::getenv("RG_B200_AR_ALGO")) : 0;
+    const bool two = c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world > 4));
+    auto st = static_cast<cudaStream_t>(stream);
+    const dim3 g(p->rows), b(threads);
+    cudaError_t e = cudaSuccess;
+#define RG_ARN2(T, CH) e = two ? launch_pdl(all_reduce_norm_kernel<T, CH, true>, g, b, 0, st, a) : launch_pdl(all_reduce_norm_kernel<T, CH, false>, g, b, 0, st, a)
+#define RG_ARN(T)                                                                                                      \
+    switch (ch) {                                                                                                      \
+        case 1: RG_ARN2(T, 1); break;                                                                                  \
+        case 2: RG_ARN2(T, 2); break;                                                                                  \
+        case 4: RG_ARN2(T, 4); break;                                                                                  \
+        default: RG_ARN2(T, 8); break;                                                                                 \
+    }
+    if (p->dtype == RG_FP16) {
+        RG_ARN(__half)
+    } else {
+        RG_ARN(__nv_bfloat16)
+    }
+#undef RG_ARN
+#undef RG_ARN2
     if (e != cudaSuccess) return RG_ERR_CUDA;
     count_launch();
     return launch_status();

@@ -78,18 +78,23 @@ template<> __device__ __forceinline__ uint32_t at_pack2<__nv_bfloat16>(float lo,
 template<class T>
 __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    // Seven 32 KiB tiles leave no room for alignment slack below the 227 KiB a CTA may have: the swizzled tiles need the dynamic
+    // shared memory to start on a 1 KiB boundary, which is checked below (it does when the kernel has no static shared memory).
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sQ = smem;                          // 32 KiB
     uint8_t *sK = sQ + AT_TILE_BYTES;            // 2 x 32 KiB
     uint8_t *sV = sK + 2 * AT_TILE_BYTES;        // 2 x 32 KiB
-    uint8_t *sP = sV + 2 * AT_TILE_BYTES;        // 32 KiB
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sP + AT_TILE_BYTES);
+    uint8_t *sP = sV + 2 * AT_TILE_BYTES;        // 2 x 32 KiB
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sP + 2 * AT_TILE_BYTES);
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
-    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 14, *o_empty = bars + 15;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 15, *o_empty = bars + 17;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 19);
     volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *xch = reinterpret_cast<float *>(bars + 18);// [2 tiles in flight][2 halves][128 rows]: half-row maxima
+    float *xch = reinterpret_cast<float *>(bars + 20);// [2 tiles in flight][2 halves][128 rows]: half-row maxima, then the row sums
+    if (smem_u32(smem) & 1023u) {// uniform over the CTA; nothing has been set up yet
+        if (threadIdx.x == 0) atomicExch(&s_attn_tc_error, 5);
+        return;
+    }
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy query tiles (far from the start of the sequence) first
@@ -105,13 +110,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
             mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1), mbar_init(&s_empty[s], AT_SW);
+            mbar_init(&p_full[s], AT_SW), mbar_init(&o_full[s], 1), mbar_init(&o_empty[s], AT_SW);
         }
-        mbar_init(p_full, AT_SW), mbar_init(o_full, 1), mbar_init(o_empty, AT_SW);
         *failed = 0;
         fence_mbar_init();
     }
     if (warp == AT_SW + 1) {
-        tmem_alloc(tmem_slot, 512);// S x 2, O_tile: 384 columns, rounded up to the next power of two
+        tmem_alloc(tmem_slot, 512);// S x 2, O_tile x 2
         tmem_relinquish();
     }
     tc_fence_before();
@@ -170,8 +175,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                 if (j + 1 < ntiles) ok = issue_s(j + 1);
                 if (!ok) break;
                 const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
-                // O_tile = P_j V_j once P is in shared memory, V has landed and the previous O_tile has been read
-                if (!mbar_wait(p_full, j & 1u) || !mbar_wait(&v_full[s], ph) || !mbar_wait(o_empty, (j & 1u) ^ 1u)) {
+                // O_tile[j & 1] = P_j V_j once P_j is in shared memory, V_j has landed and O_tile of tile j - 2 has been read
+                if (!mbar_wait(&p_full[s], ph) || !mbar_wait(&v_full[s], ph) || !mbar_wait(&o_empty[s], ph ^ 1u)) {
                     ok = false;
                     break;
                 }
@@ -180,13 +185,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     // A = P: keys 16 kk .. 16 kk + 15 of the row -> half kk / 4, 32 bytes per step inside the swizzle atom
-                    const uint64_t ad = smem_desc_sw128(p_addr + (kk >> 2) * (AT_TILE_BYTES / 2) + (kk & 3) * 32);
+                    const uint64_t ad = smem_desc_sw128(p_addr + s * AT_TILE_BYTES + (kk >> 2) * (AT_TILE_BYTES / 2) + (kk & 3) * 32);
                     // B = V: 16 keys = 16 lines of 128 bytes further down the [key][64 d] half
                     const uint64_t bd = smem_desc_sw128_ex(v_addr + kk * 2048, a.v_lbo, a.v_sbo);
-                    tc_mma_f16(tmem_base + 2 * AT_BN, ad, bd, idesc_o, kk ? 1u : 0u);
+                    tc_mma_f16(tmem_base + (2 + s) * AT_BN, ad, bd, idesc_o, kk ? 1u : 0u);
                 }
                 tc_commit(&v_empty[s]);
-                tc_commit(o_full);
+                tc_commit(&o_full[s]);
             }
             if (!ok) *failed = 2;
         }
@@ -200,18 +205,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
 #pragma unroll
         for (int d = 0; d < 64; ++d) acc[d] = 0.f;
         bool ok = true;
-        auto add_o_tile = [&]() {// acc += this thread's 64 columns of O_tile
+        // acc += f * (this thread's 64 columns of O_tile buffer b); f carries a rescaling that happened after the tile's
+        // probabilities were computed and before the tile is added
+        auto add_o_tile = [&](uint32_t b, float f) {
             tc_fence_after();
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + 2 * AT_BN + lane_addr + col0 + c0, r);
+                tmem_ld_32x32(tmem_base + (2 + b) * AT_BN + lane_addr + col0 + c0, r);
                 tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
+                for (int e = 0; e < 32; ++e) acc[c0 + e] = fmaf(__uint_as_float(r[e]), f, acc[c0 + e]);
             }
             tc_fence_before();
         };
+        float pend = 1.f;// factor applied to the accumulators at the previous tile: the product still in flight needs it too
         // A wait that runs out is recorded in `failed`; the two warps of a lane quarter leave the loop together, right after
         // the barrier they share, so neither is left waiting for the other.
         for (uint32_t j = 0; j < ntiles; ++j) {
@@ -243,17 +251,19 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
             asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");// the two warps of this lane quarter
             if (*failed) break;
             mx = fmaxf(mx, xr[(half ^ 1u) * 128 + row]);
-            // the previous tile's product: P free again, O_tile ready
-            if (j > 0) {
-                if (!at_warp_wait(o_full, (j - 1) & 1u)) {
+            // the product of tile j - 2 (the one before last: tile j - 1's may still be running): its P buffer is free again,
+            // its O_tile ready
+            if (j > 1) {
+                if (!at_warp_wait(&o_full[s], ((j - 2) >> 1) & 1u)) {
                     ok = false, *failed = 3;
                     continue;// the partner learns of it at the next shared barrier (or at the one behind the loop)
                 }
-                add_o_tile();
+                add_o_tile(s, pend);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(o_empty);
+                if (lane == 0) mbar_arrive(&o_empty[s]);
             }
             // move the reference maximum only when some row of the warp needs it (both warps of a row see the same maxima)
+            pend = 1.f;
             if (__any_sync(0xffffffffu, mx > m_used + thr)) {
                 const float m_new = fmaxf(m_used, mx);
                 const float alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * c);
@@ -261,11 +271,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                 for (int d = 0; d < 64; ++d) acc[d] *= alpha;
                 l_run *= alpha;
                 m_used = m_new;
+                pend = alpha;
             }
             // pass 2: p = 2^((s - m) * scale), written as 16-bit into this thread's 128-byte line of P half `half`
             const float mneg = (m_used == -INFINITY) ? 0.f : -m_used * c;
             float lsum = 0.f;
-            uint8_t *line = sP + half * (AT_TILE_BYTES / 2) + row * 128u;
+            uint8_t *line = sP + s * AT_TILE_BYTES + half * (AT_TILE_BYTES / 2) + row * 128u;
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t r[32];
@@ -297,16 +308,24 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&s_empty[s]);
-                mbar_arrive(p_full);
+                mbar_arrive(&p_full[s]);
             }
         }
         if (*failed) ok = false;
-        if (ok && ntiles) {
-            if (!at_warp_wait(o_full, (ntiles - 1) & 1u)) ok = false, *failed = 3;
-            if (ok) add_o_tile();
+        // the last two products
+        if (ok && ntiles > 1) {
+            const uint32_t t = ntiles - 2;
+            if (!at_warp_wait(&o_full[t & 1u], (t >> 1) & 1u)) ok = false, *failed = 3;
+            if (ok) add_o_tile(t & 1u, pend);
         }
-        // the row's denominator is the sum of its two threads' partial sums (same reference maximum in both)
-        float *xl = xch + 512;
+        if (ok && ntiles) {
+            const uint32_t t = ntiles - 1;
+            if (!at_warp_wait(&o_full[t & 1u], (t >> 1) & 1u)) ok = false, *failed = 3;
+            if (ok) add_o_tile(t & 1u, 1.f);
+        }
+        // the row's denominator is the sum of its two threads' partial sums (same reference maximum in both); the slot is the
+        // one the tile before last used for its maxima, which both threads have read
+        float *xl = xch + (ntiles & 1u) * 256;
         xl[half * 128 + row] = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
         const float l_tot = l_run + xl[(half ^ 1u) * 128 + row];
@@ -381,7 +400,7 @@ int attn_prefill_tc_launch(const rg_attn_prefill_params *p, const void *const *i
     static const uint32_t lbo = std::getenv("RG_B200_ATTN_V_LBO") ? static_cast<uint32_t>(atoi(std::getenv("RG_B200_ATTN_V_LBO"))) : AT_TILE_BYTES / 2;
     static const uint32_t sbo = std::getenv("RG_B200_ATTN_V_SBO") ? static_cast<uint32_t>(atoi(std::getenv("RG_B200_ATTN_V_SBO"))) : 1024u;
     a.v_lbo = lbo, a.v_sbo = sbo;
-    const size_t smem = 6 * AT_TILE_BYTES + 18 * 8 + 3 * 256 * 4 + 1024;
+    const size_t smem = 7 * AT_TILE_BYTES + 20 * 8 + 2 * 256 * 4;
     dim3 grid((p->seq_len + AT_BM - 1) / AT_BM, p->n_heads, p->batch);
     if (is_bf16) {
         RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

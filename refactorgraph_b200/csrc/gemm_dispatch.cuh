@@ -7,6 +7,10 @@ int linear_stream(const rg_linear_params *p, const void *const *in, void *const 
 // tcgen05/TMEM GEMM: Y[m,n] = alpha * A[m,k] * B[n,k]^T (+ beta*C), fp16/bf16, fp32 accumulation in TMEM.
 int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st);
 int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
+// SiLU gate on 5..64 tokens: weights on the instruction's M side, k-split plan of the skinny product (workspace as reported)
+bool gemm_tc_swiglu_small_shape(const rg_linear_params *p);
+size_t gemm_tc_swiglu_small_workspace(const rg_linear_params *p);
+int gemm_tc_swiglu_small(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st);
 int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
 size_t gemm_tc_workspace(const rg_mat_mul_params *p);// split-K partials + arrival counters (zero before first use)
 bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *const *out);

@@ -17,6 +17,7 @@
 #include "gemm_dispatch.cuh"
 #include "tcgen05.cuh"
 #include <cstdlib>
+#include <type_traits>
 #include <cuda.h>
 
 namespace rg {
@@ -162,6 +163,16 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     tma_load_2d(dst, &tmap_b, kb * TC_BK, nt * BN, bar);
                 }
             };
+            // A tile of row tile mt: 128 consecutive rows of A, or (SiLU-gate form with the weights on the A side) 64 gate rows
+            // and their 64 up rows: two boxes of a 64-row tensor map, one behind the other
+            auto load_a = [&](uint8_t *dst, uint32_t kb, uint32_t mt, uint64_t *bar) {
+                if (BN <= 64 && a.swiglu) {
+                    tma_load_2d(dst, &tmap_a, kb * TC_BK, mt * 64, bar);
+                    tma_load_2d(dst + 64 * TC_BK * 2, &tmap_a, kb * TC_BK, a.swiglu + mt * 64, bar);
+                } else {
+                    tma_load_2d(dst, &tmap_a, kb * TC_BK, mt * TC_BM, bar);
+                }
+            };
             TcWalk walk;
             walk.init(a, tiles, kblocks);
             TcSeg sg;
@@ -174,7 +185,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     for (uint32_t kb = sg.kb0; kb < sg.kb1 && pre < STAGES; ++kb, ++pre) {
                         mbar_arrive_expect_tx(&full[pre], STAGE_BYTES);
                         uint8_t *st = smem + pre * STAGE_BYTES;
-                        if (a.early == 1) tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[pre]);
+                        if (a.early == 1) load_a(st, kb, mt, &full[pre]);
                         else
                             load_b(st + A_BYTES, kb, nt, &full[pre]);
                     }
@@ -191,7 +202,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     if (it < pre) {// stage armed and half filled above
                         if (a.early == 1) load_b(st + A_BYTES, kb, nt, &full[s]);
                         else
-                            tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[s]);
+                            load_a(st, kb, mt, &full[s]);
                         continue;
                     }
                     if (!mbar_wait(&empty[s], ph ^ 1u)) {
@@ -200,7 +211,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                         break;
                     }
                     mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(st, &tmap_a, kb * TC_BK, mt * TC_BM, &full[s]);
+                    load_a(st, kb, mt, &full[s]);
                     load_b(st + A_BYTES, kb, nt, &full[s]);
                 }
             }
@@ -247,6 +258,32 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         const T *C = static_cast<const T *>(a.C);
         const bool c_rowmajor = C && a.c_col_stride == 1 && (a.c_row_stride % 8) == 0;
         __shared__ int s_last;
+        // SiLU gate with the weights on the A side: tile rows [0, 64) are gate rows, [64, 128) their up rows; the up half hands
+        // its values to the gate half through this buffer
+        constexpr int UPW = BN <= 64 ? BN : 1;
+        __shared__ float s_up[BN <= 64 ? 64 : 1][UPW + 1];
+        // v[0..W) = this thread's row, columns c_first ..; every one of the 128 epilogue threads calls it
+        auto swiglu_rows = [&](const float *v, auto width, uint32_t mt, uint32_t c_first) {
+            constexpr int W = decltype(width)::value;
+            const uint32_t trow = warp * 32 + lane, f = a.swiglu;
+            if (trow >= 64) {
+#pragma unroll
+                for (int j = 0; j < W; ++j) s_up[trow - 64][j] = v[j];
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (trow < 64) {
+                const uint32_t feat = mt * 64 + trow;
+#pragma unroll
+                for (int j = 0; j < W; ++j) {
+                    const uint32_t tok = c_first + j;
+                    if (feat < f && tok < a.n) {
+                        const float g = a.alpha * v[j], u = a.alpha * s_up[trow][j];
+                        Y[static_cast<uint64_t>(tok) * f + feat] = Num<T>::from_f(g / (1.f + expf(-g)) * u);
+                    }
+                }
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+        };
         uint32_t local = 0;
         TcWalk walk;
         walk.init(a, tiles, kblocks);
@@ -289,7 +326,21 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 const uint32_t row = m0 + trow;
                 const float *base = a.partial + static_cast<size_t>(tile) * a.splits * (TC_BM * BN) + static_cast<size_t>(trow) * BN;
                 if constexpr (BN <= 64) {// split-K is only planned for the skinny (swapped) shapes
-                    if (row < a.m) {
+                    if (a.swiglu) {
+                        float acc[BN];
+#pragma unroll
+                        for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+#pragma unroll 2
+                        for (uint32_t sidx = 0; sidx < sg.ncontrib; ++sidx) {
+                            const float4 *src = reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN));
+                            float4 v[BN / 4];
+#pragma unroll
+                            for (int c = 0; c < BN / 4; ++c) v[c] = __ldcg(src + c);
+#pragma unroll
+                            for (int c = 0; c < BN / 4; ++c) acc[4 * c] += v[c].x, acc[4 * c + 1] += v[c].y, acc[4 * c + 2] += v[c].z, acc[4 * c + 3] += v[c].w;
+                        }
+                        swiglu_rows(acc, std::integral_constant<int, BN>{}, mt, n0);
+                    } else if (row < a.m) {
                         // this thread's row of every split: the BN/4 loads of one split are independent, so the sum
                         // costs one L2 round trip per split (fixed split order => deterministic)
                         float4 acc[BN / 4];
@@ -324,6 +375,24 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 continue;
             }
             const uint32_t row = m0 + warp * 32 + lane;
+            if constexpr (BN <= 64) {
+                if (a.swiglu) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + buf * BN + ((warp * 32u) << 16) + c0, r);
+                        tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        swiglu_rows(v, std::integral_constant<int, 32>{}, mt, n0 + c0);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    continue;
+                }
+            }
             if constexpr (BN == 256) {
                 if (a.swiglu) {
                     // accumulator columns [0, 128) = gate, [128, 256) = up of output columns n0/2 .. n0/2 + 127
@@ -599,11 +668,17 @@ size_t gemm_tc_workspace(const rg_mat_mul_params *p) {
     return pl.counter_bytes + pl.partial_bytes;
 }
 
+// Measured on one rank's share of a tensor-parallel-8 decode step (16 tokens, 80 layers, one GPU, no exchange; 9.55 ms):
+// 5 stages for the up-to-32-token products, so that a CTA of the next kernel fits beside one of this kernel and fetches its
+// first weight tiles early: 10.55 ms; 10 stages: 9.57 ms; asking L2 for 16 / 48 further weight tiles of the CTA's run before the
+// dependency wait (cp.async.bulk.prefetch.tensor): 9.62 / 9.69 ms.  None is kept.
 template<class T, int BN, int STAGES>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
     constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<T, BN, STAGES>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    // the whole shared-memory carve-out, so that a CTA of the next kernel can sit beside one of this kernel when both fit
+    RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(cudaSharedmemCarveoutMaxShared)));
     const uint32_t items = ((a.n + BN - 1) / BN) * ((a.m + TC_BM - 1) / TC_BM) * a.splits;
     const uint32_t sms = static_cast<uint32_t>(sm_count());
     const uint32_t grid = a.streamk ? a.streamk : (items < sms ? items : sms);
@@ -682,6 +757,45 @@ int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *con
 
 // Y[m, n/2] = silu(X Wg^T) * (X Wu^T), W = [gate rows ; up rows] (rg_b200_linear, epilogue 2, more than 64 tokens): one B tile
 // pairs 128 gate rows with their 128 up rows, so both halves of an output column meet in one accumulator.
+// Up to 64 tokens: the weights go on the instruction's M side (a tile = 64 gate rows + their 64 up rows), the tokens on its N
+// side, with the k-split / stream-K plan of the plain skinny product; the up half of a tile hands its sums to the gate half.
+static rg_mat_mul_params swiglu_small_as_mat_mul(const rg_linear_params *p) {
+    rg_mat_mul_params mp = {};
+    mp.dtype = p->dtype, mp.m = p->m, mp.n = p->n, mp.k = p->k, mp.batch = 1;
+    mp.trans_b = 1, mp.alpha = 1.f, mp.flags = RG_MM_B_STATIC;
+    return mp;
+}
+bool gemm_tc_swiglu_small_shape(const rg_linear_params *p) {
+    return (p->dtype == RG_FP16 || p->dtype == RG_BF16) && p->epilogue == 2 && p->prologue == 0 && p->m > 4 && p->m <= 64 &&
+           p->n % 128 == 0 && p->n >= 128 && p->k % 8 == 0 && p->k >= 64 && encode_fn() != nullptr;
+}
+size_t gemm_tc_swiglu_small_workspace(const rg_linear_params *p) {
+    const rg_mat_mul_params mp = swiglu_small_as_mat_mul(p);
+    return gemm_tc_workspace(&mp);
+}
+int gemm_tc_swiglu_small(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st) {
+    if (!gemm_tc_swiglu_small_shape(p)) return RG_ERR_SHAPE;
+    if (!in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
+    if (!aligned16(in[0]) || !aligned16(in[1]) || !aligned16(out[0])) return RG_ERR_ALIGN;
+    const rg_mat_mul_params mp = swiglu_small_as_mat_mul(p);
+    const TcPlan pl = tc_plan(&mp);
+    if (!pl.swap) return RG_ERR_SHAPE;
+    if (pl.splits > 1 && !ws) return RG_ERR_NULL;
+    const int is_bf16 = p->dtype == RG_BF16;
+    TcArgs a = {};
+    a.alpha = 1.f, a.beta = 0.f, a.is_bf16 = is_bf16, a.k = p->k;
+    a.m = p->n, a.n = p->m;// kernel rows = weight rows (gate and up interleaved by tile), kernel columns = tokens
+    a.splits = pl.splits, a.streamk = pl.streamk_grid;
+    a.counter = static_cast<unsigned *>(ws);
+    a.partial = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + pl.counter_bytes);
+    a.early = 1, a.swiglu = p->n / 2;
+    a.Y = out[0], a.y_row_stride = 1, a.y_col_stride = p->n / 2;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, in[1], is_bf16, p->n, p->k, p->k, 64) || !make_map(&mb, in[0], is_bf16, p->m, p->k, p->k, pl.bn)) return RG_ERR_CUDA;
+    if (pl.bn == 32) return is_bf16 ? tc_launch<__nv_bfloat16, 32, 8>(ma, mb, a, st) : tc_launch<__half, 32, 8>(ma, mb, a, st);
+    return is_bf16 ? tc_launch<__nv_bfloat16, 64, 8>(ma, mb, a, st) : tc_launch<__half, 64, 8>(ma, mb, a, st);
+}
+
 int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st) {
     if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return RG_ERR_DTYPE;
     const uint32_t f = p->n / 2;

@@ -39,14 +39,12 @@ bool tma_encode_rows_by_blocks(void *map, const void *base, int is_bf16, uint64_
 
 constexpr int SK_NW = 8;                              // consumer warps
 constexpr int SK_EW = 4;                              // epilogue warps
-constexpr int SK_CONSUMERS = SK_NW * 32;
 constexpr int SK_THREADS = (SK_NW + SK_EW + 1) * 32;  // + producer warp
 constexpr int SK_STAGES = 6;
 constexpr uint32_t SK_STAGE_BYTES = 33 * 1024;        // a 32 KiB box, or two 16 KiB boxes the second of which starts 512 bytes later (see sk_sub_offset)
 
 static __device__ int s_skinny_error;      // a bounded wait ran out
-static __device__ int s_skinny_index_error;
-static __device__ unsigned long long s_skinny_prof[64];// TEMP diagnostics: per consumer warp of CTA 0: wait-full, mma, slot-wait cycles, units// a cache-append position or block-table entry was out of range (store skipped)
+static __device__ int s_skinny_index_error;// a cache-append position or block-table entry was out of range (store skipped)
 
 struct SkinnyArgs {
     const void *W, *X, *C;

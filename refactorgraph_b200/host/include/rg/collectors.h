@@ -114,6 +114,8 @@ namespace refactor::kernel {
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
     // x[rows, 2f] -> silu(x[:, :f]) * x[:, f:]
+    // AllReduce(Sum) + residual + RmsNormalization: x[rows, dim], (residual[rows, dim],) w[dim] -> y = sum(x) (+ residual), n = rmsnorm(y) * w
+    RG_COLLECTOR(AllReduceNormCollector, float, epsilon);
     struct SwigluCollector final : public InfoCollector {
         explicit SwigluCollector(Target target) noexcept : InfoCollector(target) {}
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;

@@ -121,17 +121,22 @@ namespace refactor::computation {
 
             // Products on more than 64 tokens run on the tensor cores; their SiLU-gate and QKV split / rotation / append
             // readers become the GEMM's epilogue (the forms the kernel library has: head_dim 128, gate rows a multiple of 128).
+            // On 5..64 tokens the SiLU gate has such an epilogue too.
             bool gemmEpilogue(size_t n) {
                 auto mm = as<MatMul>(n);
                 auto &node = g.nodes[n];
                 if (!mm || mm->transA || !mm->transB || mm->alpha != 1.f || node.inputs.size() != 2) return false;
                 auto const &x = tensor(node.inputs[0]);
                 auto const &w = tensor(node.inputs[1]);
-                if (!half(x.dataType) || x.shape.size() != 2 || w.shape.size() != 2 || x.shape[0] <= 64) return false;
+                if (!half(x.dataType) || x.shape.size() != 2 || w.shape.size() != 2 || x.shape[0] <= 4) return false;
                 const size_t y = node.outputs[0], c = soleConsumer(y);
                 if (c == NONE) return false;
                 auto &next = g.nodes[c];
-                if (as<Swiglu>(c) && w.shape[0] % 256 == 0) {
+                if (x.shape[0] <= 64) {
+                    // 5..64 tokens: only the SiLU gate has a tensor-core epilogue (weights on the M side, gate rows in 64s)
+                    if (!as<Swiglu>(c) || w.shape[0] % 128 != 0 || x.shape[1] % 8 != 0 || x.shape[1] < 64) return false;
+                    node.op = linear(0, 2, 1e-5f);
+                } else if (as<Swiglu>(c) && w.shape[0] % 256 == 0) {
                     node.op = linear(0, 2, 1e-5f);
                 } else if (auto qa = as<QkvRopeAppend>(c); qa && next.inputs[0] == y && qa->headDim == 128) {
                     auto const &kc = tensor(next.inputs[next.inputs.size() - 2]);
@@ -168,6 +173,31 @@ namespace refactor::computation {
                 node.outputs = next.outputs;
                 dead[c] = 1;
                 return true;
+            }
+
+            // AllReduceSum (with or without an absorbed residual) one of whose readers is an RmsNormalization of rows that fit one
+            // CTA's registers: one node with two outputs, the sum (still read by the next residual) and its normalisation.
+            bool allReduceNorm(size_t n) {
+                auto ar = as<AllReduce>(n);
+                auto &node = g.nodes[n];
+                if (!ar || ar->type != AllReduceType::Sum || node.inputs.empty() || node.inputs.size() > 2) return false;
+                const size_t y = node.outputs[0];
+                auto const &ty = tensor(y);
+                if (!half(ty.dataType) || ty.shape.empty() || ty.shape.back() % 8 != 0 || ty.shape.back() > 16384) return false;
+                for (auto c : consumers(y)) {
+                    auto norm = as<RmsNormalization>(c);
+                    auto &next = g.nodes[c];
+                    if (!norm || next.inputs.size() != 2 || next.inputs[0] != y || next.inputs[1] == y) continue;
+                    if (tensor(next.inputs[1]).elementsSize() != ty.shape.back() || tensor(next.inputs[1]).dataType != ty.dataType) continue;
+                    Attributes a;
+                    a["epsilon"] = static_cast<double>(norm->epsilon);
+                    node.op = makeOperator("b200::AllReduceNorm", a);
+                    node.inputs.push_back(next.inputs[1]);
+                    node.outputs = {y, next.outputs[0]};
+                    dead[c] = 1;
+                    return true;
+                }
+                return false;
             }
 
             // follows identity operators (Reshape) from edge e to the node that really reads it
@@ -356,6 +386,9 @@ namespace refactor::computation {
                 if (rw.matMulToLinear(n) || rw.linearEpilogue(n) || rw.gemmEpilogue(n) || rw.absorbAdd(n)) changed = true, ++rw.rewrites;
             }
         }
+        // after the residual adds have been absorbed: all-reduce + normalisation pairs
+        for (size_t n = 0; n < nodes.size(); ++n)
+            if (!rw.dead[n] && rw.allReduceNorm(n)) ++rw.rewrites;
         if (wholeStep && rw.wholeStep()) ++rw.rewrites;
         rw.compact();
         rw.sortTopologically();

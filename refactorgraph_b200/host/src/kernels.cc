@@ -430,12 +430,14 @@ namespace refactor::kernel {
         auto const &w = inputs[1].get();
         if (_target != Target::Nvidia || !half(x.dataType) || w.dataType != x.dataType) return ans;
         if (x.shape.size() != 2 || w.shape.size() != 2 || x.shape[1] != w.shape[1]) return ans;
-        // up to 4 tokens: the streaming kernel; 5..32 tokens without a norm prologue: the streaming skinny kernel; more than 64
-        // tokens: the QKV and SiLU-gate forms, on the tensor-core GEMM
+        // up to 4 tokens: the streaming kernel; 5..32 tokens without a norm prologue: the streaming skinny kernel; 5..64 tokens
+        // with the SiLU gate, and more than 64 tokens with the QKV or SiLU-gate form: the tensor-core GEMM
         if (x.shape[0] > 4) {
             const bool qkv = epilogue == 3 && headDim == 128, gate = epilogue == 2 && w.shape[0] % 256 == 0;
             const bool skinny = x.shape[0] <= 32 && prologue == 0 && x.shape[1] % 128 == 0;
-            if (!skinny && !(x.shape[0] > 64 && prologue == 0 && (qkv || gate))) return ans;
+            // 5..64 tokens, SiLU gate: the tensor-core GEMM with the weights on the instruction's M side (gate rows in 64s)
+            const bool gateSmall = x.shape[0] <= 64 && prologue == 0 && epilogue == 2 && w.shape[0] % 128 == 0 && x.shape[1] % 8 == 0 && x.shape[1] >= 64;
+            if (!skinny && !gateSmall && !(x.shape[0] > 64 && prologue == 0 && (qkv || gate))) return ans;
         }
         rg_linear_params p{};
         p.tokens_per_seq = static_cast<uint32_t>(tokensPerSeq);
@@ -674,6 +676,37 @@ namespace refactor::kernel {
         p.op = static_cast<int>(type);
         p.count = x.elementsSize();
         ans.emplace_back(std::make_unique<AllReduceB200>(p, inputs.size() > 1));
+        return ans;
+    }
+
+    // ---- AllReduce(Sum) + residual + RmsNormalization in one launch (what the fusion pass makes of the three operators) ----
+    struct AllReduceNormB200 final : public Kernel {
+        rg_all_reduce_norm_params info;
+        bool hasResidual;
+        AllReduceNormB200(rg_all_reduce_norm_params p, bool r) noexcept : info(p), hasResidual(r) {}
+        RG_KERNEL_IDS(AllReduceNormB200, "AllReduce + residual + RMS normalization over NVLink peer memory on B200 (one launch, one CTA per row)")
+        RoutineWorkspace lower(Resources &res) const final {
+            auto st = res.fetchOrStore<CudaStream>();
+            return RoutineWorkspace([info = info, r = hasResidual, st](Resources &res, void *, void const *const *in, void *const *out) {
+                auto comm = res.fetch<CommResource>();
+                if (!comm) RUNTIME_ERROR("AllReduceNorm: no communicator in Resources");
+                void const *in_[3] = {in[0], r ? in[1] : nullptr, r ? in[2] : in[1]};
+                check(rg_b200_all_reduce_norm(comm->comm, &info, in_, out, st->stream), "rg_b200_all_reduce_norm");
+            });
+        }
+    };
+    std::vector<KernelBox> AllReduceNormCollector::filter(TensorRefs inputs, TensorRefs outputs) const {
+        std::vector<KernelBox> ans;
+        auto const &x = inputs[0].get();
+        if (_target != Target::Nvidia || (x.dataType != RG_FP16 && x.dataType != RG_BF16) || x.shape.empty()) return ans;
+        if (outputs.size() != 2 || inputs.size() < 2 || inputs.size() > 3) return ans;
+        rg_all_reduce_norm_params p{};
+        p.dtype = x.dataType;
+        p.dim = x.shape.back();
+        p.rows = p.dim ? static_cast<uint32_t>(x.elementsSize() / p.dim) : 0;
+        p.epsilon = epsilon;
+        if (p.dim % 8 != 0 || p.dim > 16384 || inputs.back().get().elementsSize() != p.dim) return ans;
+        ans.emplace_back(std::make_unique<AllReduceNormB200>(p, inputs.size() == 3));
         return ans;
     }
 

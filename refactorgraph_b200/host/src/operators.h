@@ -117,6 +117,16 @@ namespace refactor::computation {
         CollectorBox candidateKernels(Target t) const final { return std::make_unique<AllReduceCollector>(t, type); }
         std::vector<Arc<Tensor>> infer(TensorRefs in) const final { return one(in[0].get().dataType, in[0].get().shape); }
     };
+    struct AllReduceNorm final : Operator {
+        float epsilon;
+        explicit AllReduceNorm(float e) : epsilon(e) {}
+        RG_OP(AllReduceNorm, "AllReduceNorm")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<AllReduceNormCollector>(t, epsilon); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            ASSERT(in.size() == 2 || in.size() == 3, "AllReduceNorm takes x, an optional residual and the norm weight");
+            return {Tensor::share(in[0].get().dataType, in[0].get().shape), Tensor::share(in[0].get().dataType, in[0].get().shape)};
+        }
+    };
     struct Gather final : Operator {
         int64_t axis;
         explicit Gather(int64_t a) : axis(a) {}

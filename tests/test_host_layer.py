@@ -186,7 +186,10 @@ def test_fusion_pass_on_batched_tensor_parallel_and_prefill_graphs():
     cq = LlamaConfig(layers=1, hidden=8192, heads=8, kv_heads=1, head_dim=128, ffn=3584, vocab=2000, max_seq=256, batch=16)
     pq = decode_step_graph_batched(cq, world=8)[0].compiler().plan(["fuse"])
     assert pq[:3] == ["Gather", "RmsNormalization", "FusedLinear"] and pq.count("QkvRopeAppend") == 0
-    assert pq.count("MatMul") == 3 and pq.count("FusedLinear") == 2        # O, gate/up, down stay on tcgen05; the 2000-row LM head qualifies too
+    # O and down stay plain tensor-core products; gate/up takes its SiLU gate as the epilogue; the 2000-row LM head qualifies for
+    # the skinny kernel too; every all-reduce of the layer is followed by a normalisation (the layer's second, or the final one)
+    assert pq == ["Gather", "RmsNormalization", "FusedLinear", "AttentionDecode", "MatMul", "AllReduceNorm", "FusedLinear", "MatMul",
+                  "AllReduceNorm", "FusedLinear", "TopK", "StateUpdate", "StateUpdate", "StateUpdate"], pq
     # prefill (more than 64 tokens): SwiGLU and QkvRopeAppend become epilogues of the tensor-core product
     pcfg = LlamaConfig(layers=1, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=2)
     hand = prefill_graph(pcfg, 80, fused_rope=True)[0].compiler().plan([])

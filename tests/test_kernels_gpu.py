@@ -385,6 +385,24 @@ def test_linear_silu_gate_many_tokens(dtype, m, f, k):
     assert capi.load().rg_b200_error_state() == 0
 
 
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("m,f,k", [(16, 3584, 8192), (5, 64, 64), (33, 448, 1024), (64, 1024, 512), (16, 11008, 4096), (32, 192, 8200)])
+def test_linear_silu_gate_few_tokens_on_tensor_cores(dtype, m, f, k):
+    """5..64 tokens: the weights sit on the M side of the tcgen05 instruction (a tile = 64 gate rows + their 64 up rows), the
+    k range is split over CTAs; the up half of a tile hands its sums to the gate half.  Twice in a row: the arrival counters
+    of the split must be back at zero."""
+    rng = np.random.default_rng(m + f + k)
+    x = rnd16(rng.standard_normal((m, k)).astype(np.float32), dtype)
+    w = rnd16((0.03 * rng.standard_normal((2 * f, k))).astype(np.float32), dtype)
+    xd, wd = ops.dev(x, dtype), ops.dev(w, dtype)
+    want = onp.linear_fused(x, w, epilogue=2)
+    for _ in range(2):
+        y = ops.linear(xd, wd, epilogue=2)
+        assert tuple(y.shape) == (m, f)
+        close_half(y, want)
+    assert capi.load().rg_b200_error_state() == 0
+
+
 def test_linear_rejects_what_it_cannot_do():
     x = torch.zeros(33, 4096, dtype=torch.float16, device="cuda")
     w = torch.zeros(64, 4096, dtype=torch.float16, device="cuda")

@@ -85,6 +85,26 @@ def _worker(rank, world, port, q, algo):
                             2: np.minimum(a, b), 3: np.maximum(a, b), 4: (a * b).astype(ndt)}[op]
             ok = ok and np.array_equal(ys.cpu().numpy().view(ndt)[:n], want.astype(ndt))
         res["int_ops"] = ok
+        # (2c) all-reduce + residual + RMSNorm in one launch: the same bits as the all-reduce followed by the norm kernel
+        import _ops as ops
+        ok = True
+        for it, (dt, rows, dim, with_res) in enumerate([(torch.float16, 16, 8192, True), (torch.bfloat16, 5, 512, True), (torch.float16, 3, 4096, False),
+                                                        (torch.bfloat16, 16, 1024, True), (torch.float16, 2, 16384, True), (torch.float16, 7, 136, False)] * 2):
+            gens = [torch.Generator().manual_seed(5000 + 10 * it + r) for r in range(world)]
+            parts = [torch.randn(rows, dim, generator=g).to(dt) for g in gens]
+            gw = torch.Generator().manual_seed(77 + it)
+            res_t = torch.randn(rows, dim, generator=gw).to(dt).cuda() if with_res else None
+            wn = (1.0 + 0.1 * torch.randn(dim, generator=gw)).to(dt).cuda()
+            xs = parts[rank].cuda()
+            code = capi.FP16 if dt == torch.float16 else capi.BF16
+            y0 = torch.empty_like(xs)
+            comm.all_reduce(code, 0, rows * dim, xs.data_ptr(), y0.data_ptr(), residual=res_t.data_ptr() if with_res else 0)
+            n0 = ops.rms_norm(y0, wn, 1e-5)
+            y1, n1 = torch.zeros_like(xs), torch.zeros_like(xs)
+            comm.all_reduce_norm(code, rows, dim, 1e-5, xs.data_ptr(), wn.data_ptr(), y1.data_ptr(), n1.data_ptr(), residual=res_t.data_ptr() if with_res else 0)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(y0.view(torch.int16), y1.view(torch.int16)) and torch.equal(n0.view(torch.int16), n1.view(torch.int16))
+        res["ar_norm"] = ok
         # (3) tensor-parallel decode step vs the unsharded oracle
         cfg = LlamaConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=16)
         rng = np.random.default_rng(3)
@@ -124,6 +144,25 @@ def _worker(rank, world, port, q, algo):
             dist.all_gather_object(gathered, logits.tobytes())
             good = good and gathered[0] == gathered[1]      # bit-identical logits on both ranks
         res["tp"] = bool(good)
+        # (3b) the same graph through the fusion pass: all-reduce + RMSNorm pairs become one node each; same tolerance, ranks agree
+        exf = g.compiler().compile("cuda", "flat", ["fuse"])
+        exf.set_communicator(comm.address)
+        for name, _ in weight_inputs(sc):
+            exf.set_input(index[name], np.ascontiguousarray(ws[name]))
+        for l in range(cfg.layers):
+            exf.set_input(index[f"l{l}.k_cache"], np.ascontiguousarray(kc[l][:, rank * kr:(rank + 1) * kr]))
+            exf.set_input(index[f"l{l}.v_cache"], np.ascontiguousarray(vc[l][:, rank * kr:(rank + 1) * kr]))
+        exf.set_input(index["token"], token)
+        exf.set_input(index["pos"], past)
+        exf.set_input(index["lens"], past + 1)
+        dist.barrier()
+        exf.run()
+        lf = exf.get_output(index["logits"]).astype(np.float32)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, lf.tobytes())
+        res["tp_fused"] = bool(np.allclose(lf, want_logits[0], atol=2e-2, rtol=1e-2) and gathered[0] == gathered[1])
+        dist.barrier()
+        del exf
         res["status"] = comm.status() == capi.OK
         dist.barrier()
         del ex
@@ -149,4 +188,4 @@ def test_two_ranks_all_reduce_and_tensor_parallel_decode(algo):
         p.join(timeout=120)
     for r in range(2):
         assert "error" not in results[r], results[r].get("error")
-        assert results[r] == {"kat": True, "ops": True, "int_ops": True, "tp": True, "status": True}, results[r]
+        assert results[r] == {"kat": True, "ops": True, "int_ops": True, "ar_norm": True, "tp": True, "tp_fused": True, "status": True}, results[r]
