@@ -354,6 +354,26 @@ __device__ __forceinline__ void ar_push_line(uint8_t *dst, const uint4 &v, uint3
     st_volatile_v4(dst + 16, v.z, flag, v.w, flag);
 }
 
+// polls the lines src[k] whose bit is set in `need` until each carries the flag; the loads of one round are independent, so a
+// round costs one trip to L2 whatever the number of lines.  out[k] is written for the lines asked for only.
+template<int NL>
+__device__ __forceinline__ bool ar_poll_many(const uint8_t *const (&src)[NL], uint32_t need, uint32_t flag, uint64_t t0, uint64_t wait_ns, uint4 (&out)[NL]) {
+    for (uint32_t spin = 1; need; ++spin) {
+        uint4 lo[NL], hi[NL];
+#pragma unroll
+        for (int k = 0; k < NL; ++k)
+            if (need >> k & 1u) lo[k] = ld_volatile_v4(src[k]), hi[k] = ld_volatile_v4(src[k] + 16);
+#pragma unroll
+        for (int k = 0; k < NL; ++k)
+            if ((need >> k & 1u) && lo[k].y == flag && lo[k].w == flag && hi[k].y == flag && hi[k].w == flag) {
+                out[k] = make_uint4(lo[k].x, lo[k].z, hi[k].x, hi[k].z);
+                need &= ~(1u << k);
+            }
+        if (need && (spin & 63u) == 0 && global_timer_ns() - t0 > wait_ns) return false;
+    }
+    return true;
+}
+
 template<class T, int CH, bool TWO>
 __global__ void __launch_bounds__(AR_THREADS) all_reduce_norm_kernel(const ArNormArgs p) {
     pdl_enter();
@@ -405,23 +425,64 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_norm_kernel(const ArNor
             }
         }
     }
-    // 2. owned chunks (all of them, one-shot): gather the peers' lines, combine in rank order, add the residual
+    // 2. owned chunks (all of them, one-shot): gather the peers' lines, combine in rank order, add the residual.  All the lines
+    // a thread waits for are polled together, so the wait costs one round trip to L2 and not one per line.
     bool ok = true;
+    if constexpr (!TWO) {
+        constexpr int PEERS = 3;         // one-shot serves up to 4 ranks
+        constexpr int G = CH < 4 ? CH : 4;// chunks polled together (more would not fit the register file)
 #pragma unroll
-    for (int i = 0; i < CH; ++i) {
-        const uint32_t c = threadIdx.x + i * blockDim.x;
-        if (c < chunks) {
-            const uint64_t gc = row0 + c;
-            const bool own = !TWO || static_cast<int>((gc / 32) % static_cast<uint64_t>(a.world)) == a.rank;
-            if (own) {
-                uint4 raw[AR_MAX_RANKS];
+        for (int i0 = 0; i0 < CH; i0 += G) {
+            const uint8_t *src[G * PEERS];
+            uint4 got[G * PEERS];
+            uint32_t need = 0;
 #pragma unroll
-                for (int r = 0; r < AR_MAX_RANKS; ++r) {
-                    raw[r] = mine[i];
-                    if (r < a.world && r != a.rank && ok) ok = ar_poll_line(a.mine + ar_slot_off(a, q, r) + gc * 32, flag, t0, a.wait_ns, raw[r]);
+            for (int i = 0; i < G; ++i) {
+                const uint32_t c = threadIdx.x + (i0 + i) * blockDim.x;
+#pragma unroll
+                for (int k = 0; k < PEERS; ++k) {
+                    const int r = k < a.rank ? k : k + 1;// the k-th rank that is not this one
+                    src[i * PEERS + k] = a.mine + ar_slot_off(a, q, r < a.world ? r : 0) + (row0 + c) * 32;
+                    if (c < chunks && r < a.world) need |= 1u << (i * PEERS + k);
                 }
-                mine[i] = ar_reduce_chunk<T>(raw, a.world, 0, res, gc * N, a.count);
-                if constexpr (TWO) {
+            }
+            if (ok) ok = ar_poll_many<G * PEERS>(src, need, flag, t0, a.wait_ns, got);
+#pragma unroll
+            for (int i = 0; i < G; ++i) {
+                const uint32_t c = threadIdx.x + (i0 + i) * blockDim.x;
+                if (c < chunks) {
+                    uint4 raw[AR_MAX_RANKS];
+#pragma unroll
+                    for (int r = 0; r < AR_MAX_RANKS; ++r) raw[r] = mine[i0 + i];
+#pragma unroll
+                    for (int k = 0; k < PEERS; ++k) {
+                        const int r = k < a.rank ? k : k + 1;
+#pragma unroll
+                        for (int rr = 0; rr < 4; ++rr)
+                            if (rr == r && r < a.world) raw[rr] = got[i * PEERS + k];
+                    }
+                    mine[i0 + i] = ar_reduce_chunk<T>(raw, a.world, 0, res, (row0 + c) * N, a.count);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            if (c < chunks) {
+                const uint64_t gc = row0 + c;
+                if (static_cast<int>((gc / 32) % static_cast<uint64_t>(a.world)) == a.rank) {
+                    const uint8_t *src[AR_MAX_RANKS];
+                    uint4 raw[AR_MAX_RANKS];
+                    uint32_t need = 0;
+#pragma unroll
+                    for (int r = 0; r < AR_MAX_RANKS; ++r) {
+                        raw[r] = mine[i];
+                        src[r] = a.mine + ar_slot_off(a, q, r < a.world ? r : 0) + gc * 32;
+                        if (r < a.world && r != a.rank) need |= 1u << r;
+                    }
+                    if (ok) ok = ar_poll_many<AR_MAX_RANKS>(src, need, flag, t0, a.wait_ns, raw);
+                    mine[i] = ar_reduce_chunk<T>(raw, a.world, 0, res, gc * N, a.count);
                     if (ok) {
 #pragma unroll
                         for (int r = 0; r < AR_MAX_RANKS; ++r)
@@ -430,18 +491,17 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_norm_kernel(const ArNor
                 }
             }
         }
-    }
-    // 3. two-shot: the finished values of the chunks other ranks own
-    if constexpr (TWO) {
+        // 3. the finished values of the chunks other ranks own
+        const uint8_t *src[CH];
+        uint32_t need = 0;
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
             const uint32_t c = threadIdx.x + i * blockDim.x;
-            if (c < chunks) {
-                const uint64_t gc = row0 + c;
-                if (static_cast<int>((gc / 32) % static_cast<uint64_t>(a.world)) != a.rank && ok)
-                    ok = ar_poll_line(a.mine + b_off + gc * 32, flag, t0, a.wait_ns, mine[i]);
-            }
+            const uint64_t gc = row0 + c;
+            src[i] = a.mine + b_off + gc * 32;
+            if (c < chunks && static_cast<int>((gc / 32) % static_cast<uint64_t>(a.world)) != a.rank) need |= 1u << i;
         }
+        if (ok) ok = ar_poll_many<CH>(src, need, flag, t0, a.wait_ns, mine);
     }
     if (__syncthreads_or(!ok)) {
         if (threadIdx.x == 0) hdr->status = 1;// outputs untouched; the host sees the status word

@@ -7,6 +7,7 @@
 // operators the kernels implement, so that `compile("cuda", allocator, ["fuse"])` of the plain graph runs the same
 // launches as a graph whose author emitted the fused operators by hand.
 #include "operators.h"
+#include <cstdlib>
 #include <functional>
 
 namespace refactor::computation {
@@ -43,6 +44,15 @@ namespace refactor::computation {
             }
             template<class Op> Op *as(size_t n) const { return n == NONE ? nullptr : dynamic_cast<Op *>(g.nodes[n].op.get()); }
             static bool half(DataType t) { return t == DataType::FP16 || t == DataType::BF16; }
+            // NAME=0 in the environment switches one rewrite off, NAME=1 an optional one on (A/B timing of a fused kernel against its parts)
+            static bool envOff(char const *name) {
+                char const *e = std::getenv(name);
+                return e && e[0] == '0';
+            }
+            static bool envOn(char const *name) {
+                char const *e = std::getenv(name);
+                return e && e[0] == '1';
+            }
 
             static OpBox linear(int prologue, int epilogue, float epsilon, Attributes extra = {}) {
                 extra["prologue"] = static_cast<int64_t>(prologue);
@@ -134,6 +144,7 @@ namespace refactor::computation {
                 auto &next = g.nodes[c];
                 if (x.shape[0] <= 64) {
                     // 5..64 tokens: only the SiLU gate has a tensor-core epilogue (weights on the M side, gate rows in 64s)
+                    if (envOff("RG_B200_FUSE_GATE_SMALL")) return false;
                     if (!as<Swiglu>(c) || w.shape[0] % 128 != 0 || x.shape[1] % 8 != 0 || x.shape[1] < 64) return false;
                     node.op = linear(0, 2, 1e-5f);
                 } else if (as<Swiglu>(c) && w.shape[0] % 256 == 0) {
@@ -178,6 +189,10 @@ namespace refactor::computation {
             // AllReduceSum (with or without an absorbed residual) one of whose readers is an RmsNormalization of rows that fit one
             // CTA's registers: one node with two outputs, the sum (still read by the next residual) and its normalisation.
             bool allReduceNorm(size_t n) {
+                // Off unless RG_B200_FUSE_AR_NORM=1: on two GPUs the one-launch form measured 1.3 % slower per decode step than the
+                // all-reduce (64 CTAs pushing) followed by the normalisation kernel (which starts early under programmatic
+                // dependent launch): one CTA per row means 16 SMs issue all the NVLink stores.
+                if (!envOn("RG_B200_FUSE_AR_NORM")) return false;
                 auto ar = as<AllReduce>(n);
                 auto &node = g.nodes[n];
                 if (!ar || ar->type != AllReduceType::Sum || node.inputs.empty() || node.inputs.size() > 2) return false;

@@ -1,4 +1,6 @@
 """Host layer without a GPU: graph assembly, shape inference and the reference's error behaviour."""
+import os
+
 import numpy as np
 import pytest
 
@@ -187,9 +189,17 @@ def test_fusion_pass_on_batched_tensor_parallel_and_prefill_graphs():
     pq = decode_step_graph_batched(cq, world=8)[0].compiler().plan(["fuse"])
     assert pq[:3] == ["Gather", "RmsNormalization", "FusedLinear"] and pq.count("QkvRopeAppend") == 0
     # O and down stay plain tensor-core products; gate/up takes its SiLU gate as the epilogue; the 2000-row LM head qualifies for
-    # the skinny kernel too; every all-reduce of the layer is followed by a normalisation (the layer's second, or the final one)
-    assert pq == ["Gather", "RmsNormalization", "FusedLinear", "AttentionDecode", "MatMul", "AllReduceNorm", "FusedLinear", "MatMul",
-                  "AllReduceNorm", "FusedLinear", "TopK", "StateUpdate", "StateUpdate", "StateUpdate"], pq
+    # the skinny kernel too
+    assert pq == ["Gather", "RmsNormalization", "FusedLinear", "AttentionDecode", "MatMul", "AllReduce", "RmsNormalization", "FusedLinear",
+                  "MatMul", "AllReduce", "RmsNormalization", "FusedLinear", "TopK", "StateUpdate", "StateUpdate", "StateUpdate"], pq
+    # opt-in: every all-reduce of the layer is followed by a normalisation (the layer's second, or the final one): one launch each
+    os.environ["RG_B200_FUSE_AR_NORM"] = "1"
+    try:
+        pn = decode_step_graph_batched(cq, world=8)[0].compiler().plan(["fuse"])
+    finally:
+        del os.environ["RG_B200_FUSE_AR_NORM"]
+    assert pn == ["Gather", "RmsNormalization", "FusedLinear", "AttentionDecode", "MatMul", "AllReduceNorm", "FusedLinear", "MatMul",
+                  "AllReduceNorm", "FusedLinear", "TopK", "StateUpdate", "StateUpdate", "StateUpdate"], pn
     # prefill (more than 64 tokens): SwiGLU and QkvRopeAppend become epilogues of the tensor-core product
     pcfg = LlamaConfig(layers=1, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=2)
     hand = prefill_graph(pcfg, 80, fused_rope=True)[0].compiler().plan([])

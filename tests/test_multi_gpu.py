@@ -144,7 +144,9 @@ def _worker(rank, world, port, q, algo):
             dist.all_gather_object(gathered, logits.tobytes())
             good = good and gathered[0] == gathered[1]      # bit-identical logits on both ranks
         res["tp"] = bool(good)
-        # (3b) the same graph through the fusion pass: all-reduce + RMSNorm pairs become one node each; same tolerance, ranks agree
+        # (3b) the same graph through the fusion pass with the opt-in all-reduce + RMSNorm node; same tolerance, ranks agree
+        os.environ["RG_B200_FUSE_AR_NORM"] = "1"
+        assert g.compiler().plan(["fuse"]).count("AllReduceNorm") == 2 * cfg.layers
         exf = g.compiler().compile("cuda", "flat", ["fuse"])
         exf.set_communicator(comm.address)
         for name, _ in weight_inputs(sc):
