@@ -1159,6 +1159,12 @@ def run_b200(args):
 
 def main():
     args = parse_args()
+    # Libraries print to descriptor 1 too (NCCL's version banner with NCCL_DEBUG=VERSION): they get stderr, and the JSON line
+    # goes to the real stdout through sys.stdout.
+    sys.stdout.flush()
+    real = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real, "w", buffering=1)
     if args.case and args.case != "all_reduce":   # all_reduce needs the process group: run_b200 dispatches it
         run_case(args)
     elif args.impl == "reference":

@@ -41,7 +41,28 @@ struct AttnTcArgs {
     float scale_log2e;
     int is_bf16;
     uint32_t v_lbo, v_sbo;// descriptor offsets of the MN-major V operand (bytes)
+    uint32_t q_tiles, batch;
 };
+
+// Work item i of the launch: query tile qt of (sequence n, head h), heaviest tiles (far from the start of the sequence) first.
+// CTA c takes one item of every band of G consecutive items, walking the bands back and forth (item c of even bands, G - 1 - c of
+// odd ones), so that the weights it collects add up to within ~1 % of every other CTA's.
+__device__ __forceinline__ uint32_t at_item_of(uint32_t band, uint32_t n_items) {// >= n_items: this CTA has none in this band
+    return band * gridDim.x + ((band & 1u) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+}
+struct AtItem {
+    uint32_t q0, h, n, kvh, ntiles;
+};
+__device__ __forceinline__ AtItem at_item(const AttnTcArgs &a, uint32_t i) {
+    const uint32_t hn = a.n_heads * a.batch, qt = a.q_tiles - 1 - i / hn, r = i % hn;
+    AtItem it;
+    it.q0 = qt * AT_BM, it.h = r % a.n_heads, it.n = r / a.n_heads;
+    it.kvh = it.h / (a.n_heads / a.n_kv);
+    // keys any row of this tile may see: [0, q0 + 128) cut at kv_len
+    const uint32_t last_key = it.q0 + AT_BM < a.kv_len ? it.q0 + AT_BM : a.kv_len;
+    it.ntiles = (last_key + AT_BN - 1) / AT_BN;
+    return it;
+}
 
 __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t z, uint32_t w, uint64_t *bar) {
     asm volatile(
@@ -65,6 +86,23 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_ex(uint32_t smem_addr, uint3
 __device__ __forceinline__ bool at_warp_wait(uint64_t *bar, uint32_t parity) {
     return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
 }
+// Barrier of the 64 threads that share named barrier `id` which also ORs a predicate over them: both warps of a lane quarter
+// get the same answer, so they take the same way out when a wait has failed (a plain flag read could differ between them and
+// leave one warp at a barrier the other never reaches).
+__device__ __forceinline__ bool at_pair_sync_or(uint32_t id, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 q, %2, 0;\n"
+        "bar.red.or.pred p, %1, 64, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r)
+        : "r"(id), "r"(pred ? 1u : 0u)
+        : "memory");
+    return r != 0;
+}
 template<class T> __device__ __forceinline__ uint32_t at_pack2(float lo, float hi);
 template<> __device__ __forceinline__ uint32_t at_pack2<__half>(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
@@ -87,25 +125,20 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
     uint8_t *sP = sV + 2 * AT_TILE_BYTES;        // 2 x 32 KiB
     uint64_t *bars = reinterpret_cast<uint64_t *>(sP + 2 * AT_TILE_BYTES);
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
-    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 15, *o_empty = bars + 17;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 19);
+    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_full = bars + 15, *o_empty = bars + 17, *q_empty = bars + 19;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 20);
     volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *xch = reinterpret_cast<float *>(bars + 20);// [2 tiles in flight][2 halves][128 rows]: half-row maxima, then the row sums
+    float *xch = reinterpret_cast<float *>(bars + 21);// [2 tiles in flight][2 halves][128 rows]: half-row maxima, then the row sums
     if (smem_u32(smem) & 1023u) {// uniform over the CTA; nothing has been set up yet
         if (threadIdx.x == 0) atomicExch(&s_attn_tc_error, 5);
         return;
     }
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heavy query tiles (far from the start of the sequence) first
-    const uint32_t q_tiles = gridDim.x, qt = q_tiles - 1 - blockIdx.x, h = blockIdx.y, n = blockIdx.z;
-    const uint32_t kvh = h / (a.n_heads / a.n_kv), q0 = qt * AT_BM;
-    // keys any row of this tile may see: [0, q0 + 128) cut at kv_len
-    uint32_t last_key = q0 + AT_BM < a.kv_len ? q0 + AT_BM : a.kv_len;
-    const uint32_t ntiles = (last_key + AT_BN - 1) / AT_BN;
+    const uint32_t n_items = a.q_tiles * a.n_heads * a.batch;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        mbar_init(q_full, 1), mbar_init(q_empty, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
@@ -128,25 +161,38 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
 
     if (warp == AT_SW) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, AT_TILE_BYTES);
-            tma_load_4d(sQ, &map_q, 0, q0, h, n, q_full);
-            tma_load_4d(sQ + AT_TILE_BYTES / 2, &map_q, 64, q0, h, n, q_full);
-            for (uint32_t j = 0; j < ntiles; ++j) {
-                const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
-                if (!mbar_wait(&k_empty[s], ph ^ 1u)) {
+            // t counts key tiles over all items of this CTA: stage t & 1, phase (t >> 1) & 1, whatever the item
+            uint32_t t = 0, done = 0;
+            for (uint32_t band = 0; band * gridDim.x < n_items && !*failed; ++band) {
+                const uint32_t i = at_item_of(band, n_items);
+                if (i >= n_items) continue;
+                const AtItem w = at_item(a, i);
+                // Q is single-buffered: the previous item's last S product must have read it
+                if (done && !mbar_wait(q_empty, (done - 1) & 1u)) {
                     *failed = 1;
                     break;
                 }
-                mbar_arrive_expect_tx(&k_full[s], AT_TILE_BYTES);
-                tma_load_4d(sK + s * AT_TILE_BYTES, &map_k, 0, j * AT_BN, kvh, n, &k_full[s]);
-                tma_load_4d(sK + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_k, 64, j * AT_BN, kvh, n, &k_full[s]);
-                if (!mbar_wait(&v_empty[s], ph ^ 1u)) {
-                    *failed = 1;
-                    break;
+                mbar_arrive_expect_tx(q_full, AT_TILE_BYTES);
+                tma_load_4d(sQ, &map_q, 0, w.q0, w.h, w.n, q_full);
+                tma_load_4d(sQ + AT_TILE_BYTES / 2, &map_q, 64, w.q0, w.h, w.n, q_full);
+                for (uint32_t j = 0; j < w.ntiles; ++j, ++t) {
+                    const uint32_t s = t & 1u, ph = (t >> 1) & 1u;
+                    if (!mbar_wait(&k_empty[s], ph ^ 1u)) {
+                        *failed = 1;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&k_full[s], AT_TILE_BYTES);
+                    tma_load_4d(sK + s * AT_TILE_BYTES, &map_k, 0, j * AT_BN, w.kvh, w.n, &k_full[s]);
+                    tma_load_4d(sK + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_k, 64, j * AT_BN, w.kvh, w.n, &k_full[s]);
+                    if (!mbar_wait(&v_empty[s], ph ^ 1u)) {
+                        *failed = 1;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&v_full[s], AT_TILE_BYTES);
+                    tma_load_4d(sV + s * AT_TILE_BYTES, &map_v, 0, j * AT_BN, w.kvh, w.n, &v_full[s]);
+                    tma_load_4d(sV + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_v, 64, j * AT_BN, w.kvh, w.n, &v_full[s]);
                 }
-                mbar_arrive_expect_tx(&v_full[s], AT_TILE_BYTES);
-                tma_load_4d(sV + s * AT_TILE_BYTES, &map_v, 0, j * AT_BN, kvh, n, &v_full[s]);
-                tma_load_4d(sV + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_v, 64, j * AT_BN, kvh, n, &v_full[s]);
+                ++done;
             }
         }
     } else if (warp == AT_SW + 1) {
@@ -154,10 +200,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
             const uint32_t idesc_s = instr_desc(a.is_bf16, AT_BM, AT_BN);
             const uint32_t idesc_o = instr_desc(a.is_bf16, AT_BM, AT_D) | (1u << 16);// B (= V) is MN-major
             const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-            bool ok = mbar_wait(q_full, 0);
-            // S_j = Q K_j^T into accumulator j & 1
-            auto issue_s = [&](uint32_t j) {
-                const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+            bool ok = true;
+            // S of key tile t (counted over all items of this CTA) = Q K^T into accumulator t & 1
+            auto issue_s = [&](uint32_t t) {
+                const uint32_t s = t & 1u, ph = (t >> 1) & 1u;
                 if (!mbar_wait(&k_full[s], ph) || !mbar_wait(&s_empty[s], ph ^ 1u)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(sK + s * AT_TILE_BYTES);
@@ -170,11 +216,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                 tc_commit(&s_full[s]);
                 return true;
             };
-            if (ok && ntiles) ok = issue_s(0);
-            for (uint32_t j = 0; ok && j < ntiles; ++j) {
-                if (j + 1 < ntiles) ok = issue_s(j + 1);
+            uint32_t t = 0, done = 0;
+            for (uint32_t band = 0; ok && band * gridDim.x < n_items; ++band) {
+              const uint32_t i = at_item_of(band, n_items);
+              if (i >= n_items) continue;
+              const uint32_t ntiles = at_item(a, i).ntiles;
+              ok = mbar_wait(q_full, done & 1u);
+              if (ok) ok = issue_s(t);
+              if (ok && ntiles == 1) tc_commit(q_empty);
+              for (uint32_t j = 0; ok && j < ntiles; ++j, ++t) {
+                if (j + 1 < ntiles) {
+                    ok = issue_s(t + 1);
+                    if (ok && j + 2 == ntiles) tc_commit(q_empty);// the item's last S: Q may be replaced once it has run
+                }
                 if (!ok) break;
-                const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+                const uint32_t s = t & 1u, ph = (t >> 1) & 1u;
                 // O_tile[j & 1] = P_j V_j once P_j is in shared memory, V_j has landed and O_tile of tile j - 2 has been read
                 if (!mbar_wait(&p_full[s], ph) || !mbar_wait(&v_full[s], ph) || !mbar_wait(&o_empty[s], ph ^ 1u)) {
                     ok = false;
@@ -192,19 +248,20 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                 }
                 tc_commit(&v_empty[s]);
                 tc_commit(&o_full[s]);
+              }
+              ++done;
             }
             if (!ok) *failed = 2;
         }
     } else {
         // ---- softmax / output warps: lane quarter = warp % 4, column half = warp / 4 ----
-        const uint32_t quarter = warp & 3u, half = warp >> 2, row = quarter * 32 + lane, qrow = q0 + row;
+        const uint32_t quarter = warp & 3u, half = warp >> 2, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32u) << 16, col0 = half * 64u;
         const float c = a.scale_log2e, thr = 8.0f / c;
-        float m_used = -INFINITY, l_run = 0.f;
+        float m_used, l_run;
         float acc[64];
-#pragma unroll
-        for (int d = 0; d < 64; ++d) acc[d] = 0.f;
         bool ok = true;
+        uint32_t t = 0;// key tiles over all items of this CTA: buffers and barrier phases follow it
         // acc += f * (this thread's 64 columns of O_tile buffer b); f carries a rescaling that happened after the tile's
         // probabilities were computed and before the tile is added
         auto add_o_tile = [&](uint32_t b, float f) {
@@ -220,10 +277,18 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
             tc_fence_before();
         };
         float pend = 1.f;// factor applied to the accumulators at the previous tile: the product still in flight needs it too
+        for (uint32_t band = 0; band * gridDim.x < n_items; ++band) {
+        const uint32_t item = at_item_of(band, n_items);
+        if (item >= n_items) continue;
+        const AtItem w = at_item(a, item);
+        const uint32_t ntiles = w.ntiles, q0 = w.q0, qrow = q0 + row;
+        m_used = -INFINITY, l_run = 0.f, pend = 1.f;
+#pragma unroll
+        for (int d = 0; d < 64; ++d) acc[d] = 0.f;
         // A wait that runs out is recorded in `failed`; the two warps of a lane quarter leave the loop together, right after
         // the barrier they share, so neither is left waiting for the other.
-        for (uint32_t j = 0; j < ntiles; ++j) {
-            const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+        for (uint32_t j = 0; j < ntiles; ++j, ++t) {
+            const uint32_t s = t & 1u, ph = (t >> 1) & 1u;
             if (ok && !at_warp_wait(&s_full[s], ph)) ok = false, *failed = 3;
             tc_fence_after();
             const uint32_t s_addr = tmem_base + s * AT_BN + lane_addr + col0, key0 = j * AT_BN + col0;
@@ -246,15 +311,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                     for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
                 }
             }
-            float *xr = xch + (j & 1u) * 256;
+            float *xr = xch + s * 256;
             xr[half * 128 + row] = mx;
-            asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");// the two warps of this lane quarter
-            if (*failed) break;
+            if (at_pair_sync_or(1u + quarter, *failed != 0)) break;// the two warps of this lane quarter, leaving together
             mx = fmaxf(mx, xr[(half ^ 1u) * 128 + row]);
             // the product of tile j - 2 (the one before last: tile j - 1's may still be running): its P buffer is free again,
             // its O_tile ready
             if (j > 1) {
-                if (!at_warp_wait(&o_full[s], ((j - 2) >> 1) & 1u)) {
+                if (!at_warp_wait(&o_full[s], ((t - 2) >> 1) & 1u)) {
                     ok = false, *failed = 3;
                     continue;// the partner learns of it at the next shared barrier (or at the one behind the loop)
                 }
@@ -312,26 +376,37 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
             }
         }
         if (*failed) ok = false;
-        // the last two products
+        // the item's last two products (t is now one past its last tile); the buffers go back to the tensor-core thread
         if (ok && ntiles > 1) {
-            const uint32_t t = ntiles - 2;
-            if (!at_warp_wait(&o_full[t & 1u], (t >> 1) & 1u)) ok = false, *failed = 3;
-            if (ok) add_o_tile(t & 1u, pend);
+            const uint32_t u = t - 2;
+            if (!at_warp_wait(&o_full[u & 1u], (u >> 1) & 1u)) ok = false, *failed = 3;
+            if (ok) {
+                add_o_tile(u & 1u, pend);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&o_empty[u & 1u]);
+            }
         }
         if (ok && ntiles) {
-            const uint32_t t = ntiles - 1;
-            if (!at_warp_wait(&o_full[t & 1u], (t >> 1) & 1u)) ok = false, *failed = 3;
-            if (ok) add_o_tile(t & 1u, 1.f);
+            const uint32_t u = t - 1;
+            if (!at_warp_wait(&o_full[u & 1u], (u >> 1) & 1u)) ok = false, *failed = 3;
+            if (ok) {
+                add_o_tile(u & 1u, 1.f);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&o_empty[u & 1u]);
+            }
         }
         // the row's denominator is the sum of its two threads' partial sums (same reference maximum in both); the slot is the
         // one the tile before last used for its maxima, which both threads have read
-        float *xl = xch + (ntiles & 1u) * 256;
+        float *xl = xch + (t & 1u) * 256;
         xl[half * 128 + row] = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
         const float l_tot = l_run + xl[(half ^ 1u) * 128 + row];
+        // the next item's first tile writes its maxima into the same slot: both threads must have read the sums first; the two
+        // warps also agree here on whether to go on
+        const bool stop = at_pair_sync_or(1u + quarter, !ok || *failed != 0);
         if (ok && qrow < a.S) {
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            T *dst = static_cast<T *>(a.o) + n * a.o_sn + h * a.o_sh + static_cast<int64_t>(qrow) * a.o_st + col0;
+            T *dst = static_cast<T *>(a.o) + w.n * a.o_sn + w.h * a.o_sh + static_cast<int64_t>(qrow) * a.o_st + col0;
 #pragma unroll
             for (int d = 0; d < 64; d += 8) {
                 uint4 v;
@@ -340,6 +415,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
                 *reinterpret_cast<uint4 *>(dst + d) = v;
             }
         }
+        if (stop) break;
+        }// items
     }
     tc_fence_before();
     __syncthreads();
@@ -401,7 +478,13 @@ int attn_prefill_tc_launch(const rg_attn_prefill_params *p, const void *const *i
     static const uint32_t sbo = std::getenv("RG_B200_ATTN_V_SBO") ? static_cast<uint32_t>(atoi(std::getenv("RG_B200_ATTN_V_SBO"))) : 1024u;
     a.v_lbo = lbo, a.v_sbo = sbo;
     const size_t smem = 7 * AT_TILE_BYTES + 20 * 8 + 2 * 256 * 4;
-    dim3 grid((p->seq_len + AT_BM - 1) / AT_BM, p->n_heads, p->batch);
+    a.q_tiles = (p->seq_len + AT_BM - 1) / AT_BM, a.batch = p->batch;
+    // persistent CTAs, one per SM (the shared memory of a CTA fills the SM): the next item's Q, K and V are fetched while the
+    // softmax warps finish the current one, and tensor memory and barriers are set up once
+    const uint64_t items = static_cast<uint64_t>(a.q_tiles) * p->n_heads * p->batch;
+    if (items > 0xffffffffull) return RG_ERR_SHAPE;
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
     if (is_bf16) {
         RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         RG_CHECK_CUDA(launch_pdl(attn_prefill_tc_kernel<__nv_bfloat16>, grid, dim3(AT_THREADS), smem, st, mq, mk, mv, a));
