@@ -18,11 +18,16 @@
 //                        exact in fp32 and far inside the 16-bit range — so most tiles skip the rescaling altogether.
 // Keeping O in registers instead of in tensor memory avoids a read-modify-write of the accumulator whenever the maximum
 // changes; the price is one tcgen05.ld of the tile per key tile.
-// Measured on [4, 32, 2048, 128] bf16: 275 us = 499 TFLOP/s (the warp-level mma.sync kernel: 565 us = 243 TFLOP/s); one row per
-// thread (four softmax warps, one per scheduler) gave 306 TFLOP/s on one sequence against 392 with two threads per row.  Cycle
-// counters in a softmax warp, per key tile: ~1480 in the exponential pass (the special-function unit's 16 results per clock
-// bound it at 1024), ~330 reading the scores for the maximum, ~200 in the pair exchange, ~190 adding O_tile, and ~800 waiting
-// for the tensor core (the single P buffer makes tile j's second product and tile j + 1's exponentials take turns).
+// Measured on [4, 32, 2048, 128] bf16: 237.5 us = 579 TFLOP/s (the warp-level mma.sync kernel: 565 us = 243 TFLOP/s).  The steps:
+// one row per thread (four softmax warps) 306 TFLOP/s on one sequence, two threads per row 392 (499 on four sequences); P and
+// O_tile double-buffered, so that tile j's second product runs under tile j + 1's exponentials (the accumulators take O_tile
+// two tiles late, times whatever rescaling happened in between): 523; persistent CTAs, one per SM, that fetch the next item's
+// Q / K / V under the current item's tail and set tensor memory and barriers up once: 563; items dealt back and forth over the
+// CTAs instead of round-robin (the heaviest CTA carries 119 key tiles instead of 125, the mean is 117.6): 579.  Keeping a
+// thread's 64 scores in registers between the maximum pass and the exponential pass (one tcgen05.ld round instead of two) spills
+// at the 168 registers a 320-thread CTA gets and measured 532.  Cycle counters in a softmax warp, per key tile, before the
+// double buffering: ~1480 in the exponential pass (the special-function unit's 16 results per clock bound it at 1024), ~330
+// reading the scores for the maximum, ~200 in the pair exchange, ~190 adding O_tile, ~800 waiting for the tensor core.
 // Every wait is bounded; on expiry the kernel records an error word, releases its tensor memory and leaves.
 #include "tcgen05.cuh"
 #include <cstdlib>
