@@ -25,7 +25,9 @@
 // Q / K / V under the current item's tail and set tensor memory and barriers up once: 563; items dealt back and forth over the
 // CTAs instead of round-robin (the heaviest CTA carries 119 key tiles instead of 125, the mean is 117.6): 579.  Keeping a
 // thread's 64 scores in registers between the maximum pass and the exponential pass (one tcgen05.ld round instead of two) spills
-// at the 168 registers a 320-thread CTA gets and measured 532.  Cycle counters in a softmax warp, per key tile, before the
+// at the 168 registers a 320-thread CTA gets and measured 532.  A head-major item order (all query tiles of a head in flight
+// together, so that K / V come from L2: ncu shows 3.2 x the algorithmic bytes in DRAM traffic, 41 % of DRAM peak) measured 568:
+// the loads are not what the kernel waits for.  Cycle counters in a softmax warp, per key tile, before the
 // double buffering: ~1480 in the exponential pass (the special-function unit's 16 results per clock bound it at 1024), ~330
 // reading the scores for the maximum, ~200 in the pair exchange, ~190 adding O_tile, ~800 waiting for the tensor core.
 // Every wait is bounded; on expiry the kernel records an error word, releases its tensor memory and leaves.
