@@ -12,6 +12,12 @@
 //     logits + running arg-max) and meet the other CTAs at a grid barrier (monotonic counter, bounded spin).
 //   * attention over the cached tokens [0, pos) is split over (head, 64-token tile) units; the token produced in
 //     this step is folded in when the partial records are merged, so its K/V rows never have to be prefetched.
+// Measured and not kept: replacing three of a layer's five grid barriers (after O, gate/up and down) by readiness carried
+// in the data — every element of h, u and x a 32-bit word {value, 16-bit tag}, the next phase's consumers polling the words
+// they need (with a 150 ns back-off) instead of barrier + load.  Correct (all parity tests green), but 3.08-3.09 ms per step
+// against 3.01: the per-phase stamps show the wait moves from the barrier into the activation load (what a barrier costs is
+// mostly the arrival skew of the CTAs, which a poll has to sit out just the same), the two remaining barriers absorb the
+// accumulated skew, and 38 000 polling threads slow the attention and down phases' streams.
 // Semantics equal the multi-kernel graph: Gather, [Linear(norm,QKV,RoPE,append), AttentionDecode, Linear(O,+res),
 // Linear(norm,gate/up,SiLU), Linear(down,+res)] x L, Linear(norm, LM head), TopK(k=1, softmax), state updates.
 #include "gemm_dispatch.cuh"
