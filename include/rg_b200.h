@@ -435,6 +435,23 @@ typedef struct rg_all_reduce_params {
 } rg_all_reduce_params;
 int rg_b200_all_reduce(rg_comm *, const rg_all_reduce_params *, const void *const *in, void *const *out, void *stream);
 
+/* Row-parallel product + all-reduce as two halves that meet in peer memory, replacing MatMulCublas followed by AllReduceNccl
+ * (src/04kernel/src/kernels/mat_mul/cublas_kernel.cu:48-55, src/04kernel/src/kernels/all_reduce/nccl_kernel.cu:9-19) where a
+ * tensor-parallel layer multiplies by its slice of Wo / Wdown and sums the partial results over the ranks:
+ *   rg_b200_mat_mul_push  — the tcgen05 product of up to 64 tokens (A [m, k] activations, B [n, k] weights, transB, no C, batch 1,
+ *     n a multiple of 8, fp16 / bf16) whose epilogue does not write Y: every finished pair of 16-bit values goes, with the flag
+ *     of the communicator's call in flight, straight into this rank's input slot on every peer (one-shot) or on the rank that
+ *     owns the run of chunks (two-shot), by ordinary 8-byte stores over NVLink.  inputs {A, B}; workspace as
+ *     rg_b200_mat_mul_workspace of the same parameters.  RG_ERR_UNSUPPORTED for any other shape (call rg_b200_mat_mul and
+ *     rg_b200_all_reduce instead), RG_ERR_LIMIT when m * n * 2 exceeds the communicator's capacity.
+ *   rg_b200_all_reduce_recv — the receiving half: the all-reduce kernel without its send phase (this rank's own input is read
+ *     from its slot like a peer's).  inputs {residual or NULL}, outputs {y}; count * element size a multiple of 16.  It is the
+ *     call that advances the communicator's sequence, so every rg_b200_mat_mul_push must be followed by exactly one
+ *     rg_b200_all_reduce_recv of the same element count on the same stream, on every rank.
+ * The result carries the same bits as the tcgen05 product (rg_b200_mat_mul, force_kernel 3) followed by rg_b200_all_reduce. */
+int rg_b200_mat_mul_push(rg_comm *, const rg_mat_mul_params *, void *ws, const void *const *in, void *stream);
+int rg_b200_all_reduce_recv(rg_comm *, const rg_all_reduce_params *, const void *const *in, void *const *out, void *stream);
+
 /* AllReduce(Sum) + residual + RmsNormalization in one launch: the three operators that follow a row-parallel product of a
  * tensor-parallel decoder layer (AllReduceNccl, nccl_kernel.cu:9-19; BinaryCuda Add; RmsNormalizationCuda,
  * src/04kernel/src/kernels/rms_normalization/cuda_kernel.cc:24-131).  inputs {x [rows, dim], residual [rows, dim] or NULL,

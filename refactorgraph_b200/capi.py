@@ -140,7 +140,7 @@ OPS = {
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_error_clear", "rg_b200_attn_decode_static",
             "rg_b200_attn_decode_static_capacity", "rg_b200_decode_step_timeline", "rg_b200_comm_create", "rg_b200_comm_base", "rg_b200_comm_bytes", "rg_b200_comm_connect_ptrs",
             "rg_b200_comm_set_wait_ns",
-            "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce", "rg_b200_all_reduce_norm"]
+            "rg_b200_comm_connect", "rg_b200_comm_status", "rg_b200_comm_destroy", "rg_b200_all_reduce", "rg_b200_all_reduce_norm", "rg_b200_all_reduce_recv", "rg_b200_mat_mul_push"]
            + [f"rg_b200_{n}" for n in OPS] + [f"rg_b200_{n}_workspace" for n in OPS])
 
 _lib = None
@@ -180,6 +180,8 @@ def load() -> C.CDLL:
         lib.rg_b200_comm_destroy.argtypes = [C.c_void_p]
         lib.rg_b200_all_reduce.argtypes = [C.c_void_p, C.POINTER(AllReduceParams), C.POINTER(C.c_void_p),
                                            C.POINTER(C.c_void_p), C.c_void_p]
+        lib.rg_b200_all_reduce_recv.argtypes = [C.c_void_p, C.POINTER(AllReduceParams), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p]
+        lib.rg_b200_mat_mul_push.argtypes = [C.c_void_p, C.POINTER(MatMulParams), C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p]
         lib.rg_b200_all_reduce_norm.argtypes = [C.c_void_p, C.POINTER(AllReduceNormParams), C.POINTER(C.c_void_p),
                                                 C.POINTER(C.c_void_p), C.c_void_p]
         _lib = lib
@@ -262,6 +264,21 @@ class Comm:
         rc = load().rg_b200_all_reduce(self._ptr, C.byref(p), _ptrs([x, residual]), _ptrs([y]), stream or None)
         if check and rc != OK:
             raise RgError("all_reduce", rc)
+        return rc
+
+    def mat_mul_push(self, p, a: int, b: int, ws: int = 0, stream: int = 0, check: bool = True) -> int:
+        """Row-parallel product whose epilogue writes this rank's all-reduce input into the peers' slots (p: MatMulParams)."""
+        rc = load().rg_b200_mat_mul_push(self._ptr, C.byref(p), ws or None, _ptrs([a, b]), stream or None)
+        if check and rc != OK:
+            raise RgError("mat_mul_push", rc)
+        return rc
+
+    def all_reduce_recv(self, dtype: int, count: int, y: int, residual: int = 0, stream: int = 0, check: bool = True) -> int:
+        """Receiving half of an all-reduce (Sum) whose input a mat_mul_push has already delivered."""
+        p = AllReduceParams(dtype, 0, count)
+        rc = load().rg_b200_all_reduce_recv(self._ptr, C.byref(p), _ptrs([residual]), _ptrs([y]), stream or None)
+        if check and rc != OK:
+            raise RgError("all_reduce_recv", rc)
         return rc
 
     def all_reduce_norm(self, dtype: int, rows: int, dim: int, eps: float, x: int, w: int, y: int, n: int, residual: int = 0,

@@ -13,6 +13,7 @@
 // loads) 26 / 49 us on 2 / 8 GPUs; push with a system fence and one flag per CTA 20 / 26 us.
 // No TMA and no multicast instructions touch peer memory.
 #include "gemm_dispatch.cuh"
+#include "ar_slots.cuh"
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -20,20 +21,12 @@
 
 namespace rg {
 
-constexpr int AR_MAX_RANKS = 8;
 constexpr int AR_THREADS = 256;
-constexpr size_t AR_HEADER_BYTES = 4096;
-
-struct ArHeader {
-    unsigned long long seq;// number of the call in flight (starts at 1)
-    unsigned int done;     // CTAs of the current call that have read seq
-    int status;            // 0 ok; 1 = a wait on a peer flag expired
-};
 
 struct ArArgs {
     uint8_t *mine;
     uint8_t *peer[AR_MAX_RANKS];// peer[rank] = mine
-    const void *x, *res;
+    const void *x, *res;// x == nullptr: this rank's input is already in its slots (written by a product's epilogue): receive only
     void *y;
     uint64_t count;
     size_t capacity;
@@ -118,12 +111,7 @@ __device__ __forceinline__ uint4 ar_reduce_chunk(const uint4 (&raw)[8], int worl
 
 // byte offset of the slot that holds rank `src`'s input of a call with parity q, inside any rank's allocation; a slot is
 // 2 * capacity bytes because every 4 data bytes travel with a 4-byte flag
-__device__ __forceinline__ size_t ar_slot_off(const ArArgs &a, unsigned q, int src) {
-    return AR_HEADER_BYTES + (static_cast<size_t>(q) * a.world + src) * (2 * a.capacity);
-}
-// Flag of call number seq: never 0 (slots start zeroed, so memory no call has written can never look complete) and
-// different from the flag two calls earlier, which is what a slot of the same parity may still hold.
-__device__ __forceinline__ uint32_t ar_flag(unsigned long long seq) { return static_cast<uint32_t>(seq % 0xffffffffull) + 1u; }
+__device__ __forceinline__ size_t ar_slot_off(const ArArgs &a, unsigned q, int src) { return ar_slot_offset(a.capacity, a.world, q, src); }
 __device__ __forceinline__ void st_volatile_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -166,27 +154,30 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_kernel(const ArArgs a) 
     for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks; c += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
         // 1. push chunk c of my input, every 32-bit word paired with the call's flag, into slot [q][rank] of every peer
         uint4 mine4 = make_uint4(0u, 0u, 0u, 0u);
-        if (c < full_chunks) {
-            mine4 = *reinterpret_cast<const uint4 *>(x + c * N);
-        } else {
-            T *tail = reinterpret_cast<T *>(&mine4);
-            for (uint64_t e = c * N; e < a.count; ++e) tail[e - c * N] = x[e];
-        }
+        if (x) {
+            if (c < full_chunks) {
+                mine4 = *reinterpret_cast<const uint4 *>(x + c * N);
+            } else {
+                T *tail = reinterpret_cast<T *>(&mine4);
+                for (uint64_t e = c * N; e < a.count; ++e) tail[e - c * N] = x[e];
+            }
 #pragma unroll
-        for (int r = 0; r < AR_MAX_RANKS; ++r) {
-            if (r < a.world && r != a.rank) {
-                uint8_t *dst = a.peer[r] + my_off + c * 32;
-                st_volatile_v4(dst, mine4.x, flag, mine4.y, flag);
-                st_volatile_v4(dst + 16, mine4.z, flag, mine4.w, flag);
+            for (int r = 0; r < AR_MAX_RANKS; ++r) {
+                if (r < a.world && r != a.rank) {
+                    uint8_t *dst = a.peer[r] + my_off + c * 32;
+                    st_volatile_v4(dst, mine4.x, flag, mine4.y, flag);
+                    st_volatile_v4(dst + 16, mine4.z, flag, mine4.w, flag);
+                }
             }
         }
         // 2. the same chunk of every peer lands in my allocation: poll local memory until all four flags of a line match
+        // (receive-only: this rank's own chunk is read from its own slot the same way)
         uint4 raw[AR_MAX_RANKS];
         bool ok = true;
 #pragma unroll
         for (int r = 0; r < AR_MAX_RANKS; ++r) {
             raw[r] = mine4;
-            if (r < a.world && r != a.rank && ok) {
+            if (r < a.world && (r != a.rank || !x) && ok) {
                 const uint8_t *src = a.mine + ar_slot_off(a, q, r) + c * 32;
                 for (uint32_t spin = 1;; ++spin) {
                     const uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 16);
@@ -254,18 +245,22 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const A
     for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks; c += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
         const int owner = static_cast<int>((c / 32) % static_cast<uint64_t>(a.world));
         uint4 mine4 = make_uint4(0u, 0u, 0u, 0u);
-        if (c < full_chunks) {
-            mine4 = *reinterpret_cast<const uint4 *>(x + c * N);
-        } else {
-            T *tail = reinterpret_cast<T *>(&mine4);
-            for (uint64_t e = c * N; e < a.count; ++e) tail[e - c * N] = x[e];
+        if (x) {
+            if (c < full_chunks) {
+                mine4 = *reinterpret_cast<const uint4 *>(x + c * N);
+            } else {
+                T *tail = reinterpret_cast<T *>(&mine4);
+                for (uint64_t e = c * N; e < a.count; ++e) tail[e - c * N] = x[e];
+            }
         }
         uint4 out4;
         bool ok = true;
         if (owner != a.rank) {
-            uint8_t *dst = a.peer[owner] + my_off + c * 32;
-            st_volatile_v4(dst, mine4.x, flag, mine4.y, flag);
-            st_volatile_v4(dst + 16, mine4.z, flag, mine4.w, flag);
+            if (x) {
+                uint8_t *dst = a.peer[owner] + my_off + c * 32;
+                st_volatile_v4(dst, mine4.x, flag, mine4.y, flag);
+                st_volatile_v4(dst + 16, mine4.z, flag, mine4.w, flag);
+            }
             const uint8_t *src = a.mine + b_off + c * 32;
             for (uint32_t spin = 1;; ++spin) {
                 const uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 16);
@@ -283,7 +278,7 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const A
 #pragma unroll
             for (int r = 0; r < AR_MAX_RANKS; ++r) {
                 raw[r] = mine4;
-                if (r < a.world && r != a.rank && ok) {
+                if (r < a.world && (r != a.rank || !x) && ok) {
                     const uint8_t *src = a.mine + ar_slot_off(a, q, r) + c * 32;
                     for (uint32_t spin = 1;; ++spin) {
                         const uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 16);
@@ -695,8 +690,14 @@ int rg_b200_comm_destroy(rg_comm *c) {
     return RG_OK;
 }
 
-int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *const *in, void *const *out, void *stream) {
-    if (!c || !p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+// every rank must take the same variant: it depends on the group size and on RG_B200_AR_ALGO (1 one-shot, 2 two-shot) only
+static bool comm_two_shot(const rg_comm *c) {
+    static const int algo_env = std::getenv("RG_B200_AR_ALGO") ? atoi(std::getenv("RG_B200_AR_ALGO")) : 0;
+    return c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world > 4));
+}
+
+// x == nullptr: receive only (this rank's input already lies in its slots)
+static int all_reduce_launch(rg_comm *c, const rg_all_reduce_params *p, const void *x, const void *res, void *y, void *stream) {
     if (!c->connected) return RG_ERR_UNSUPPORTED;
     if (p->op < 0 || p->op > 4) return RG_ERR_UNSUPPORTED;
     if (c->failed) return RG_ERR_TIMEOUT;// out of step with its peers since a wait expired: destroy and recreate
@@ -709,13 +710,14 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
         default: return RG_ERR_DTYPE;
     }
     if (p->count == 0) return RG_OK;
+    if (!x && (p->count * es) % 16 != 0) return RG_ERR_SHAPE;// an epilogue writes whole 16-byte chunks
     const size_t bytes = (p->count * es + 15) / 16 * 16;
     if (bytes > c->capacity) return RG_ERR_LIMIT;
-    if (!aligned16(in[0]) || !aligned16(out[0])) return RG_ERR_ALIGN;
+    if ((x && !aligned16(x)) || !aligned16(y)) return RG_ERR_ALIGN;
     ArArgs a = {};
     a.mine = c->mine;
     for (int r = 0; r < c->world; ++r) a.peer[r] = c->peers[r];
-    a.x = in[0], a.res = in[1], a.y = out[0];
+    a.x = x, a.res = res, a.y = y;
     a.count = p->count, a.capacity = c->capacity;
     a.world = c->world, a.rank = c->rank, a.op = p->op;
     a.wait_ns = c->wait_ns;
@@ -725,9 +727,7 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
     if (grid < 1) grid = 1;
     if (grid > 128) grid = 128;
     auto st = static_cast<cudaStream_t>(stream);
-    // every rank must take the same variant: it depends on the group size and on RG_B200_AR_ALGO (1 one-shot, 2 two-shot) only
-    static const int algo_env = std::getenv("RG_B200_AR_ALGO") ? atoi(std::getenv("RG_B200_AR_ALGO")) : 0;
-    const bool two_shot = c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world > 4));
+    const bool two_shot = comm_two_shot(c);
     const dim3 g(static_cast<unsigned>(grid)), b(AR_THREADS);
     cudaError_t e;
 #define RG_AR(T) e = two_shot ? launch_pdl(all_reduce_two_shot_kernel<T>, g, b, 0, st, a) : launch_pdl(all_reduce_kernel<T>, g, b, 0, st, a)
@@ -746,6 +746,29 @@ int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *co
     if (e != cudaSuccess) return RG_ERR_CUDA;
     count_launch();
     return launch_status();
+}
+
+int rg_b200_all_reduce(rg_comm *c, const rg_all_reduce_params *p, const void *const *in, void *const *out, void *stream) {
+    if (!c || !p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+    return all_reduce_launch(c, p, in[0], in[1], out[0], stream);
+}
+
+int rg_b200_all_reduce_recv(rg_comm *c, const rg_all_reduce_params *p, const void *const *in, void *const *out, void *stream) {
+    if (!c || !p || !out || !out[0]) return RG_ERR_NULL;
+    return all_reduce_launch(c, p, nullptr, in ? in[0] : nullptr, out[0], stream);
+}
+
+int rg_b200_mat_mul_push(rg_comm *c, const rg_mat_mul_params *p, void *ws, const void *const *in, void *stream) {
+    if (!c || !p || !in || !in[0] || !in[1]) return RG_ERR_NULL;
+    if (!c->connected) return RG_ERR_UNSUPPORTED;
+    if (c->failed) return RG_ERR_TIMEOUT;
+    if (static_cast<size_t>(p->m) * p->n * 2 > c->capacity) return RG_ERR_LIMIT;
+    ArPeers peers = {};
+    peers.mine = c->mine;
+    for (int r = 0; r < c->world; ++r) peers.peer[r] = c->peers[r];
+    peers.capacity = c->capacity, peers.world = c->world, peers.rank = c->rank;
+    peers.two_shot = comm_two_shot(c) ? 1 : 0;
+    return gemm_tc_push(p, ws, in, peers, static_cast<cudaStream_t>(stream));
 }
 
 int rg_b200_all_reduce_norm(rg_comm *c, const rg_all_reduce_norm_params *p, const void *const *in, void *const *out, void *stream) {
@@ -776,8 +799,7 @@ int rg_b200_all_reduce_norm(rg_comm *c, const rg_all_reduce_norm_params *p, cons
     uint32_t threads = ((chunks + ch - 1) / ch + 31) / 32 * 32;
     if (threads > 256) threads = 256;
     if (threads < 32) threads = 32;
-    static const int algo_env = std::getenv("RG_B200_AR_ALGO") ? atoi(std::getenv("RG_B200_AR_ALGO")) : 0;
-    const bool two = c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world > 4));
+    const bool two = comm_two_shot(c);
     auto st = static_cast<cudaStream_t>(stream);
     const dim3 g(p->rows), b(threads);
     cudaError_t e = cudaSuccess;

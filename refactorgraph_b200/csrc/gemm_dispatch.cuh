@@ -2,6 +2,7 @@
 #pragma once
 #include "common.cuh"
 namespace rg {
+struct ArPeers;
 int gemm_simt(const rg_mat_mul_params *p, const void *const *in, void *const *out, cudaStream_t st);
 int linear_stream(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
 // tcgen05/TMEM GEMM: Y[m,n] = alpha * A[m,k] * B[n,k]^T (+ beta*C), fp16/bf16, fp32 accumulation in TMEM.
@@ -13,6 +14,9 @@ size_t gemm_tc_swiglu_small_workspace(const rg_linear_params *p);
 int gemm_tc_swiglu_small(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st);
 int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
 size_t gemm_tc_workspace(const rg_mat_mul_params *p);// split-K partials + arrival counters (zero before first use)
+// The product of up to 64 tokens whose 16-bit result goes, paired with the flag of the communicator's call in flight, into this
+// rank's all-reduce slots on the peers instead of into Y (in = {A, B}); RG_ERR_UNSUPPORTED for any other shape
+int gemm_tc_push(const rg_mat_mul_params *p, void *ws, const void *const *in, const ArPeers &peers, cudaStream_t st);
 bool gemm_tc_supported(const rg_mat_mul_params *p, const void *const *in, void *const *out);
 // Weight-streaming linear layer for 5..32 rows of X on the warp-level tensor path (linear_skinny.cu).
 struct SkinnyCall {

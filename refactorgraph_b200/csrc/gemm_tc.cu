@@ -16,6 +16,7 @@
 // an error word, still frees its tensor memory and exits.
 #include "gemm_dispatch.cuh"
 #include "tcgen05.cuh"
+#include "ar_slots.cuh"
 #include <cstdlib>
 #include <type_traits>
 #include <cuda.h>
@@ -51,7 +52,34 @@ struct TcArgs {
     const int32_t *table;
     void *q_out, *kc, *vc;
     rg_kv_layout kv;
+    // push != 0 (weights on the M side only): the finished 16-bit values do not go to Y; paired with the flag of the all-reduce
+    // call in flight they are stored into this rank's input slot in the allocation of every rank (1, one-shot) or of the rank
+    // that owns the run of chunks (2, two-shot), over NVLink with ordinary 8-byte stores — the row-parallel product and the send
+    // half of the all-reduce are one kernel
+    uint32_t push;
+    ArPeers ar;
 };
+
+// Row `feat` of the kernel's output (an output feature; a.m of them) for token `tok`: even lanes take the value of the next
+// lane (feature feat + 1: both lie in one 16-byte chunk of the token's row) and store {two 16-bit values, flag}.  Called by all
+// 32 lanes of a warp; `live` = this lane's row exists.
+template<class T>
+__device__ __forceinline__ void tc_push_value(const TcArgs &a, uint32_t flag, unsigned q, uint32_t feat, uint32_t tok, float v, bool live, uint32_t lane) {
+    const float vn = __shfl_down_sync(0xffffffffu, v, 1);
+    if ((lane & 1u) || !live) return;
+    const T lo = Num<T>::from_f(v), hi = Num<T>::from_f(vn);
+    const uint32_t data = static_cast<uint32_t>(*reinterpret_cast<const uint16_t *>(&lo)) | (static_cast<uint32_t>(*reinterpret_cast<const uint16_t *>(&hi)) << 16);
+    const uint64_t e = static_cast<uint64_t>(tok) * a.m + feat, chunk = e >> 3;
+    const size_t off = ar_slot_offset(a.ar.capacity, a.ar.world, q, a.ar.rank) + chunk * 32 + ((e & 7u) >> 1) * 8;
+    if (a.push == 2) {
+        const int owner = static_cast<int>((chunk / 32) % static_cast<uint64_t>(a.ar.world));
+        asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(a.ar.peer[owner] + off), "r"(data), "r"(flag) : "memory");
+    } else {
+#pragma unroll
+        for (int r = 0; r < AR_MAX_RANKS; ++r)
+            if (r < a.ar.world) asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(a.ar.peer[r] + off), "r"(data), "r"(flag) : "memory");
+    }
+}
 
 // Tile order: groups of TC_GROUP_M row tiles are walked column by column, so the CTAs running at the same time share
 // a few A row-panels and B column-panels in L2 instead of streaming all of B once per row tile.
@@ -258,6 +286,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         const T *C = static_cast<const T *>(a.C);
         const bool c_rowmajor = C && a.c_col_stride == 1 && (a.c_row_stride % 8) == 0;
         __shared__ int s_last;
+        // the all-reduce call this product feeds: its number stays put until the receiving kernel behind this one has run
+        uint32_t ar_flag_v = 0;
+        unsigned ar_q = 0;
+        if (a.push) {
+            const unsigned long long seq = *reinterpret_cast<const volatile unsigned long long *>(a.ar.mine);
+            ar_flag_v = ar_flag(seq), ar_q = static_cast<unsigned>(seq & 1ull);
+        }
         // SiLU gate with the weights on the A side: tile rows [0, 64) are gate rows, [64, 128) their up rows; the up half hands
         // its values to the gate half through this buffer
         constexpr int UPW = BN <= 64 ? BN : 1;
@@ -340,6 +375,24 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                             for (int c = 0; c < BN / 4; ++c) acc[4 * c] += v[c].x, acc[4 * c + 1] += v[c].y, acc[4 * c + 2] += v[c].z, acc[4 * c + 3] += v[c].w;
                         }
                         swiglu_rows(acc, std::integral_constant<int, BN>{}, mt, n0);
+                    } else if (a.push) {
+                        float acc[BN];
+#pragma unroll
+                        for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+                        if (row < a.m) {
+#pragma unroll 2
+                            for (uint32_t sidx = 0; sidx < sg.ncontrib; ++sidx) {
+                                const float4 *src = reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN));
+                                float4 v[BN / 4];
+#pragma unroll
+                                for (int c = 0; c < BN / 4; ++c) v[c] = __ldcg(src + c);
+#pragma unroll
+                                for (int c = 0; c < BN / 4; ++c) acc[4 * c] += v[c].x, acc[4 * c + 1] += v[c].y, acc[4 * c + 2] += v[c].z, acc[4 * c + 3] += v[c].w;
+                            }
+                        }
+#pragma unroll
+                        for (int c = 0; c < BN; ++c)
+                            if (n0 + c < a.n) tc_push_value<T>(a, ar_flag_v, ar_q, row, n0 + c, a.alpha * acc[c], row < a.m, lane);
                     } else if (row < a.m) {
                         // this thread's row of every split: the BN/4 loads of one split are independent, so the sum
                         // costs one L2 round trip per split (fixed split order => deterministic)
@@ -376,6 +429,21 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             }
             const uint32_t row = m0 + warp * 32 + lane;
             if constexpr (BN <= 64) {
+                if (a.push) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + buf * BN + ((warp * 32u) << 16) + c0, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c0 + j < a.n) tc_push_value<T>(a, ar_flag_v, ar_q, row, n0 + c0 + j, a.alpha * __uint_as_float(r[j]), row < a.m, lane);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    continue;
+                }
                 if (a.swiglu) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -795,6 +863,31 @@ int gemm_tc_swiglu_small(const rg_linear_params *p, void *ws, const void *const 
     a.Y = out[0], a.y_row_stride = 1, a.y_col_stride = p->n / 2;
     CUtensorMap ma, mb;
     if (!make_map(&ma, in[1], is_bf16, p->n, p->k, p->k, 64) || !make_map(&mb, in[0], is_bf16, p->m, p->k, p->k, pl.bn)) return RG_ERR_CUDA;
+    if (pl.bn == 32) return is_bf16 ? tc_launch<__nv_bfloat16, 32, 8>(ma, mb, a, st) : tc_launch<__half, 32, 8>(ma, mb, a, st);
+    return is_bf16 ? tc_launch<__nv_bfloat16, 64, 8>(ma, mb, a, st) : tc_launch<__half, 64, 8>(ma, mb, a, st);
+}
+
+// Row-parallel product feeding an all-reduce: the plain skinny product (weights on the M side) whose epilogue stores into the
+// communicator's slots.  m <= 64 tokens, n a multiple of 8, no C operand.
+int gemm_tc_push(const rg_mat_mul_params *p, void *ws, const void *const *in, const ArPeers &peers, cudaStream_t st) {
+    if (p->dtype != RG_FP16 && p->dtype != RG_BF16) return RG_ERR_UNSUPPORTED;
+    if (p->trans_a || !p->trans_b || p->batch != 1 || p->has_bias || p->m == 0 || p->m > 64 || p->n < 128 || p->n % 8 != 0 || p->k % 8 != 0 || p->k < 64)
+        return RG_ERR_UNSUPPORTED;
+    if (!aligned16(in[0]) || !aligned16(in[1]) || !encode_fn()) return RG_ERR_UNSUPPORTED;
+    const TcPlan pl = tc_plan(p);
+    if (!pl.swap) return RG_ERR_UNSUPPORTED;
+    if (pl.splits > 1 && !ws) return RG_ERR_NULL;
+    const int is_bf16 = p->dtype == RG_BF16;
+    TcArgs a = {};
+    a.alpha = p->alpha, a.beta = 0.f, a.is_bf16 = is_bf16, a.k = p->k;
+    a.m = p->n, a.n = p->m;// kernel rows = output features, kernel columns = tokens
+    a.splits = pl.splits, a.streamk = pl.streamk_grid;
+    a.counter = static_cast<unsigned *>(ws);
+    a.partial = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + pl.counter_bytes);
+    a.early = (p->flags & RG_MM_B_STATIC) ? 1u : 0u;
+    a.push = peers.two_shot ? 2u : 1u, a.ar = peers;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, in[1], is_bf16, p->n, p->k, p->k, TC_BM) || !make_map(&mb, in[0], is_bf16, p->m, p->k, p->k, pl.bn)) return RG_ERR_CUDA;
     if (pl.bn == 32) return is_bf16 ? tc_launch<__nv_bfloat16, 32, 8>(ma, mb, a, st) : tc_launch<__half, 32, 8>(ma, mb, a, st);
     return is_bf16 ? tc_launch<__nv_bfloat16, 64, 8>(ma, mb, a, st) : tc_launch<__half, 64, 8>(ma, mb, a, st);
 }

@@ -114,6 +114,9 @@ namespace refactor::kernel {
         std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
     };
     // x[rows, 2f] -> silu(x[:, :f]) * x[:, f:]
+    // Row-parallel product + AllReduce(Sum) (+ residual): x[m, k], w[n, k] (, residual[m, n]) -> y[m, n]; the product's epilogue is
+    // the sending half of the all-reduce
+    RG_COLLECTOR(MatMulAllReduceCollector, float, alpha);
     // AllReduce(Sum) + residual + RmsNormalization: x[rows, dim], (residual[rows, dim],) w[dim] -> y = sum(x) (+ residual), n = rmsnorm(y) * w
     RG_COLLECTOR(AllReduceNormCollector, float, epsilon);
     struct SwigluCollector final : public InfoCollector {

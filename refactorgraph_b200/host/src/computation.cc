@@ -50,6 +50,7 @@ namespace refactor::computation {
             return std::make_unique<AttentionDecode>(static_cast<dim_t>(getInt(a, "max_len", 0)), static_cast<dim_t>(getInt(a, "page_size", 0)));
         if (is({"b200::QkvRopeAppend"})) return std::make_unique<QkvRopeAppend>(a);
         if (is({"b200::SwiGLU"})) return std::make_unique<Swiglu>();
+        if (is({"b200::MatMulAllReduce"})) return std::make_unique<MatMulAllReduce>(static_cast<float>(getFloat(a, "alpha", 1.0)));
         if (is({"b200::AllReduceNorm"})) return std::make_unique<AllReduceNorm>(static_cast<float>(getFloat(a, "epsilon", 1e-5)));
         if (is({"b200::AttentionPrefill"}))
             return std::make_unique<AttentionPrefill>(static_cast<dim_t>(getInt(a, "n_heads", 0)), static_cast<dim_t>(getInt(a, "seq_len", 0)));

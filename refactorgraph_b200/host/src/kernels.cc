@@ -679,6 +679,47 @@ namespace refactor::kernel {
         return ans;
     }
 
+    // ---- Row-parallel product whose epilogue is the sending half of the all-reduce, then the receiving half ---------------
+    struct MatMulAllReduceB200 final : public Kernel {
+        rg_mat_mul_params mm;
+        rg_all_reduce_params ar;
+        bool hasResidual;
+        MatMulAllReduceB200(rg_mat_mul_params m, rg_all_reduce_params a, bool r) noexcept : mm(m), ar(a), hasResidual(r) {}
+        RG_KERNEL_IDS(MatMulAllReduceB200, "tcgen05 product that stores into the peers' all-reduce slots over NVLink, then the receiving half of the all-reduce, on B200")
+        RoutineWorkspace lower(Resources &res) const final {
+            auto st = res.fetchOrStore<CudaStream>();
+            return RoutineWorkspace(
+                [mm = mm, ar = ar, r = hasResidual, st](Resources &res, void *ws, void const *const *in, void *const *out) {
+                    auto comm = res.fetch<CommResource>();
+                    if (!comm) RUNTIME_ERROR("MatMulAllReduce: no communicator in Resources");
+                    void const *in_[2] = {in[0], in[1]};
+                    check(rg_b200_mat_mul_push(comm->comm, &mm, ws, in_, st->stream), "rg_b200_mat_mul_push");
+                    void const *res_[1] = {r ? in[2] : nullptr};
+                    check(rg_b200_all_reduce_recv(comm->comm, &ar, res_, out, st->stream), "rg_b200_all_reduce_recv");
+                },
+                rg_b200_mat_mul_workspace(&mm));
+        }
+    };
+    std::vector<KernelBox> MatMulAllReduceCollector::filter(TensorRefs inputs, TensorRefs outputs) const {
+        std::vector<KernelBox> ans;
+        if (_target != Target::Nvidia || inputs.size() < 2 || inputs.size() > 3 || outputs.size() != 1) return ans;
+        auto const &x = inputs[0].get();
+        auto const &w = inputs[1].get();
+        if ((x.dataType != RG_FP16 && x.dataType != RG_BF16) || w.dataType != x.dataType) return ans;
+        if (x.shape.size() != 2 || w.shape.size() != 2 || x.shape[1] != w.shape[1]) return ans;
+        // what rg_b200_mat_mul_push takes: up to 64 tokens, whole 16-byte chunks per output row
+        if (x.shape[0] == 0 || x.shape[0] > 64 || w.shape[0] < 128 || w.shape[0] % 8 != 0 || x.shape[1] % 8 != 0 || x.shape[1] < 64) return ans;
+        rg_mat_mul_params mm{};
+        mm.dtype = x.dataType;
+        mm.m = x.shape[0], mm.n = w.shape[0], mm.k = x.shape[1];
+        mm.trans_b = 1, mm.alpha = alpha, mm.beta = 0.f, mm.batch = 1;
+        mm.flags = RG_MM_B_STATIC;// the weight operand is a graph input or constant: nothing in the stream writes it
+        rg_all_reduce_params ar{};
+        ar.dtype = x.dataType, ar.op = 0, ar.count = static_cast<uint64_t>(mm.m) * mm.n;
+        ans.emplace_back(std::make_unique<MatMulAllReduceB200>(mm, ar, inputs.size() == 3));
+        return ans;
+    }
+
     // ---- AllReduce(Sum) + residual + RmsNormalization in one launch (what the fusion pass makes of the three operators) ----
     struct AllReduceNormB200 final : public Kernel {
         rg_all_reduce_norm_params info;

@@ -117,6 +117,17 @@ namespace refactor::computation {
         CollectorBox candidateKernels(Target t) const final { return std::make_unique<AllReduceCollector>(t, type); }
         std::vector<Arc<Tensor>> infer(TensorRefs in) const final { return one(in[0].get().dataType, in[0].get().shape); }
     };
+    struct MatMulAllReduce final : Operator {
+        float alpha;
+        explicit MatMulAllReduce(float a) : alpha(a) {}
+        RG_OP(MatMulAllReduce, "MatMulAllReduce")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<MatMulAllReduceCollector>(t, alpha); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            ASSERT((in.size() == 2 || in.size() == 3) && in[0].get().shape.size() == 2 && in[1].get().shape.size() == 2,
+                   "MatMulAllReduce takes x[m, k], w[n, k] and an optional residual");
+            return one(in[0].get().dataType, Shape{in[0].get().shape[0], in[1].get().shape[0]});
+        }
+    };
     struct AllReduceNorm final : Operator {
         float epsilon;
         explicit AllReduceNorm(float e) : epsilon(e) {}

@@ -182,7 +182,14 @@ def test_fusion_pass_on_batched_tensor_parallel_and_prefill_graphs():
     g.output(g.op("onnx::Add", [r, y2]))
     c = g.compiler()
     assert c.plan([]) == ["MatMul", "AllReduce", "SimpleBinary", "MatMul", "SimpleBinary"]
-    assert c.plan(["fuse"]) == ["MatMul", "AllReduce", "MatMul"]                 # the addends become the C operand / the residual input
+    # the addends become the C operand / the residual input
+    assert c.plan(["fuse"]) == ["MatMul", "AllReduce", "MatMul"]
+    # opt-in: the product in front of the all-reduce becomes its sending half
+    os.environ["RG_B200_FUSE_MM_AR"] = "1"
+    try:
+        assert c.plan(["fuse"]) == ["MatMulAllReduce", "MatMul"]
+    finally:
+        del os.environ["RG_B200_FUSE_MM_AR"]
     # 16 tokens against few weight rows with a long k (one rank's QKV projection): the streaming skinny kernel takes the
     # product together with the RoPE / cache-append reader
     cq = LlamaConfig(layers=1, hidden=8192, heads=8, kv_heads=1, head_dim=128, ffn=3584, vocab=2000, max_seq=256, batch=16)
@@ -192,6 +199,14 @@ def test_fusion_pass_on_batched_tensor_parallel_and_prefill_graphs():
     # the skinny kernel too
     assert pq == ["Gather", "RmsNormalization", "FusedLinear", "AttentionDecode", "MatMul", "AllReduce", "RmsNormalization", "FusedLinear",
                   "MatMul", "AllReduce", "RmsNormalization", "FusedLinear", "TopK", "StateUpdate", "StateUpdate", "StateUpdate"], pq
+    # opt-in: O and down become products that write into the peers' all-reduce slots, with the receiving half behind them
+    os.environ["RG_B200_FUSE_MM_AR"] = "1"
+    try:
+        pm = decode_step_graph_batched(cq, world=8)[0].compiler().plan(["fuse"])
+    finally:
+        del os.environ["RG_B200_FUSE_MM_AR"]
+    assert pm == ["Gather", "RmsNormalization", "FusedLinear", "AttentionDecode", "MatMulAllReduce", "RmsNormalization", "FusedLinear",
+                  "MatMulAllReduce", "RmsNormalization", "FusedLinear", "TopK", "StateUpdate", "StateUpdate", "StateUpdate"], pm
     # opt-in: every all-reduce of the layer is followed by a normalisation (the layer's second, or the final one): one launch each
     os.environ["RG_B200_FUSE_AR_NORM"] = "1"
     try:

@@ -105,6 +105,34 @@ def _worker(rank, world, port, q, algo):
             torch.cuda.synchronize()
             ok = ok and torch.equal(y0.view(torch.int16), y1.view(torch.int16)) and torch.equal(n0.view(torch.int16), n1.view(torch.int16))
         res["ar_norm"] = ok
+        # (2d) row-parallel product whose epilogue is the sending half of the all-reduce + the receiving half: the same bits as
+        # the tcgen05 product followed by the all-reduce (unsplit, k-split and stream-K plans; with and without residual)
+        ok = True
+        for it, (dt, m, n, k, with_res) in enumerate([(torch.float16, 16, 8192, 1024, True), (torch.float16, 16, 8192, 3584, True), (torch.bfloat16, 32, 4096, 4096, False),
+                                                      (torch.float16, 64, 1024, 512, True), (torch.bfloat16, 5, 136, 64, False), (torch.float16, 16, 4096, 11008, True)] * 2):
+            gx = torch.Generator().manual_seed(9000 + 10 * it + rank)
+            xs = torch.randn(m, k, generator=gx).to(dt).cuda()
+            wt = (0.05 * torch.randn(n, k, generator=gx)).to(dt).cuda()
+            gr = torch.Generator().manual_seed(9500 + it)
+            res_t = torch.randn(m, n, generator=gr).to(dt).cuda() if with_res else None
+            code = capi.FP16 if dt == torch.float16 else capi.BF16
+            p = capi.MatMulParams()
+            p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y, p.force_kernel = code, m, n, k, 1, 1.0, 0.0, 1, m * n, 3
+            nws = capi.workspace("mat_mul", p)
+            wsb = torch.zeros(max(nws, 1), dtype=torch.uint8, device="cuda")
+            y_part = torch.empty(m, n, dtype=dt, device="cuda")
+            rc = capi.call("mat_mul", p, [xs.data_ptr(), wt.data_ptr(), 0], [y_part.data_ptr()], ws=wsb.data_ptr() if nws else 0, check=False)
+            if rc != capi.OK:       # a shape the tcgen05 kernel does not take has no fused form either
+                continue
+            y0 = torch.empty_like(y_part)
+            comm.all_reduce(code, 0, m * n, y_part.data_ptr(), y0.data_ptr(), residual=res_t.data_ptr() if with_res else 0)
+            y1 = torch.zeros_like(y_part)
+            p.force_kernel = 0
+            comm.mat_mul_push(p, xs.data_ptr(), wt.data_ptr(), ws=wsb.data_ptr() if nws else 0)
+            comm.all_reduce_recv(code, m * n, y1.data_ptr(), residual=res_t.data_ptr() if with_res else 0)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(y0.view(torch.int16), y1.view(torch.int16))
+        res["mm_push"] = ok
         # (3) tensor-parallel decode step vs the unsharded oracle
         cfg = LlamaConfig(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, max_seq=128, batch=16)
         rng = np.random.default_rng(3)
@@ -144,9 +172,11 @@ def _worker(rank, world, port, q, algo):
             dist.all_gather_object(gathered, logits.tobytes())
             good = good and gathered[0] == gathered[1]      # bit-identical logits on both ranks
         res["tp"] = bool(good)
-        # (3b) the same graph through the fusion pass with the opt-in all-reduce + RMSNorm node; same tolerance, ranks agree
-        os.environ["RG_B200_FUSE_AR_NORM"] = "1"
-        assert g.compiler().plan(["fuse"]).count("AllReduceNorm") == 2 * cfg.layers
+        # (3b) the same graph through the fusion pass with an opt-in fused node (all-reduce + RMSNorm, or product + all-reduce,
+        # by the all-reduce variant under test, so both get a run); same tolerance, ranks agree
+        knob, node = ("RG_B200_FUSE_AR_NORM", "AllReduceNorm") if algo == "1" else ("RG_B200_FUSE_MM_AR", "MatMulAllReduce")
+        os.environ[knob] = "1"
+        assert g.compiler().plan(["fuse"]).count(node) == 2 * cfg.layers
         exf = g.compiler().compile("cuda", "flat", ["fuse"])
         exf.set_communicator(comm.address)
         for name, _ in weight_inputs(sc):
@@ -190,4 +220,4 @@ def test_two_ranks_all_reduce_and_tensor_parallel_decode(algo):
         p.join(timeout=120)
     for r in range(2):
         assert "error" not in results[r], results[r].get("error")
-        assert results[r] == {"kat": True, "ops": True, "int_ops": True, "ar_norm": True, "tp": True, "tp_fused": True, "status": True}, results[r]
+        assert results[r] == {"kat": True, "ops": True, "int_ops": True, "ar_norm": True, "mm_push": True, "tp": True, "tp_fused": True, "status": True}, results[r]
