@@ -1,4 +1,4 @@
-// The adapters a RefactorGraph maintainer adds to bind the B200 kernel library, written against
+// The adapters a RefactorGraph maintainer adds to bind the B200 kernel library (one per operator), written against
 // the REFERENCE's own headers: kernel/kernel.h, kernel/tensor.h, kernel/collectors/*.h, kernel/attributes/*.h,
 // runtime/resource.h.  tests/test_reference_headers_compile.py compiles this file with g++ -fsyntax-only against a reference
 // checkout (include directories src/00common .. src/04kernel plus the two shims under oracle/shim), which is the proof that

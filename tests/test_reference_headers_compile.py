@@ -1,4 +1,4 @@
-"""The adapters of INTEGRATION.md compile against the reference's OWN headers (not this repository's mirror of them).
+"""The adapters a reference maintainer would add to bind this kernel library compile against the reference's OWN headers (not this repository's mirror of them).
 
 tests/ref_adapters/b200_adapters.cc holds three adapters — RmsNormalization (plain operator), MatMul (attribute struct,
 workspace, the weight-is-static hint) and AllReduce (a handle kept in runtime::Resources) — and the collector lines that
