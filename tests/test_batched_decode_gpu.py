@@ -124,6 +124,63 @@ def test_all_reduce_world_one_and_limits():
     comm.destroy()
 
 
+def test_fused_all_reduce_forms_on_a_group_of_one():
+    """AllReduce + residual + RMSNorm in one launch, and the product whose epilogue is the sending half of the all-reduce, on
+    a communicator of one rank (no second GPU needed): values against the separate kernels, and the shapes they refuse."""
+    comm = capi.Comm(1, 0, 1 << 20)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for dt, code in ((torch.float16, capi.FP16), (torch.bfloat16, capi.BF16)):
+        x = torch.randn(16, 1024, device="cuda", generator=g).to(dt)
+        r = torch.randn(16, 1024, device="cuda", generator=g).to(dt)
+        w = (1 + 0.1 * torch.randn(1024, device="cuda", generator=g)).to(dt)
+        y0 = torch.empty_like(x)
+        comm.all_reduce(code, 0, x.numel(), x.data_ptr(), y0.data_ptr(), residual=r.data_ptr())
+        n0 = ops.rms_norm(y0, w, 1e-5)
+        y1, n1 = torch.zeros_like(x), torch.zeros_like(x)
+        comm.all_reduce_norm(code, 16, 1024, 1e-5, x.data_ptr(), w.data_ptr(), y1.data_ptr(), n1.data_ptr(), residual=r.data_ptr())
+        torch.cuda.synchronize()
+        assert torch.equal(y0.view(torch.int16), y1.view(torch.int16)) and torch.equal(n0.view(torch.int16), n1.view(torch.int16))
+        # product + all-reduce: 16 tokens x [512, 1024] weights, residual added by the receiving half
+        a = torch.randn(16, 1024, device="cuda", generator=g).to(dt)
+        wt = (0.05 * torch.randn(512, 1024, device="cuda", generator=g)).to(dt)
+        res = torch.randn(16, 512, device="cuda", generator=g).to(dt)
+        p = capi.MatMulParams()
+        p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.beta, p.batch, p.stride_y, p.force_kernel = code, 16, 512, 1024, 1, 1.0, 0.0, 1, 16 * 512, 3
+        nws = capi.workspace("mat_mul", p)
+        ws = torch.zeros(max(nws, 1), dtype=torch.uint8, device="cuda")
+        part = torch.empty(16, 512, dtype=dt, device="cuda")
+        capi.call("mat_mul", p, [a.data_ptr(), wt.data_ptr(), 0], [part.data_ptr()], ws=ws.data_ptr() if nws else 0)
+        z0 = torch.empty_like(part)
+        comm.all_reduce(code, 0, part.numel(), part.data_ptr(), z0.data_ptr(), residual=res.data_ptr())
+        p.force_kernel = 0
+        z1 = torch.zeros_like(part)
+        comm.mat_mul_push(p, a.data_ptr(), wt.data_ptr(), ws=ws.data_ptr() if nws else 0)
+        comm.all_reduce_recv(code, part.numel(), z1.data_ptr(), residual=res.data_ptr())
+        torch.cuda.synchronize()
+        assert torch.equal(z0.view(torch.int16), z1.view(torch.int16))
+        want = (a.float() @ wt.float().T).to(dt).float() + res.float()
+        assert torch.allclose(z1.float(), want, atol=2e-2, rtol=1e-2)
+    # refusals: nothing is launched
+    x = torch.zeros(4, 1024, dtype=torch.float16, device="cuda")
+    assert comm.all_reduce_norm(capi.F32, 4, 1024, 1e-5, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_DTYPE
+    assert comm.all_reduce_norm(capi.FP16, 4, 1028, 1e-5, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_SHAPE
+    assert comm.all_reduce_norm(capi.FP16, 4, 32768, 1e-5, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_SHAPE
+    assert comm.all_reduce_norm(capi.FP16, 1 << 12, 1024, 1e-5, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_LIMIT
+    assert comm.all_reduce_norm(capi.FP16, 0, 1024, 1e-5, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), check=False) == capi.OK
+    p = capi.MatMulParams()
+    p.dtype, p.m, p.n, p.k, p.trans_b, p.alpha, p.batch = capi.FP16, 65, 512, 1024, 1, 1.0, 1
+    assert comm.mat_mul_push(p, x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_UNSUPPORTED      # more than 64 tokens
+    p.m, p.n = 16, 516
+    assert comm.mat_mul_push(p, x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_UNSUPPORTED      # rows of Y not whole 16-byte chunks
+    p.n, p.dtype = 512, capi.F32
+    assert comm.mat_mul_push(p, x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_UNSUPPORTED
+    p.dtype, p.m, p.n = capi.FP16, 64, 1 << 14
+    assert comm.mat_mul_push(p, x.data_ptr(), x.data_ptr(), check=False) == capi.ERR_LIMIT            # 2 MiB of results, 1 MiB of slots
+    assert comm.all_reduce_recv(capi.FP16, 1004, x.data_ptr(), check=False) == capi.ERR_SHAPE            # not whole 16-byte chunks
+    assert comm.status() == capi.OK and capi.load().rg_b200_error_state() == 0
+    comm.destroy()
+
+
 def test_all_reduce_missing_peer_reports_timeout_instead_of_hanging():
     """Failure detection without faulting a GPU: rank 0 of a 2-rank group whose peer never raises its flag (a zeroed
     buffer stands in for the peer).  The device-side wait is bounded (20 ms here); the kernel returns, the status
