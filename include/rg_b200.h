@@ -42,8 +42,8 @@ typedef enum rg_status {
 
 /* Data type codes = the reference's DataType enum (src/00common/include/common/data_type.h:14-35). */
 typedef enum rg_dtype {
-    RG_F32 = 1, RG_U8 = 2, RG_I8 = 3, RG_I32 = 6, RG_I64 = 7, RG_BOOL = 9,
-    RG_FP16 = 10, RG_F64 = 11, RG_U32 = 12, RG_BF16 = 16
+    RG_F32 = 1, RG_U8 = 2, RG_I8 = 3, RG_U16 = 4, RG_I16 = 5, RG_I32 = 6, RG_I64 = 7, RG_BOOL = 9,
+    RG_FP16 = 10, RG_F64 = 11, RG_U32 = 12, RG_U64 = 13, RG_BF16 = 16
 } rg_dtype;
 
 const char *rg_b200_status_string(int status);
@@ -173,6 +173,59 @@ typedef struct rg_transpose_params {
 } rg_transpose_params;
 size_t rg_b200_transpose_workspace(const rg_transpose_params *);
 int rg_b200_transpose(const rg_transpose_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Byte-exact data movement around the arithmetic.  Shapes are in elements of elem_bytes (1, 2, 4, 8 or 16).
+ *
+ * Concat / Split along one axis, the tensors seen as [outer, axis_len, inner].  Replace ConcatCuda and SplitCuda
+ * (src/04kernel/src/kernels/concat/cuda_kernel.cc, src/04kernel/src/kernels/split/cuda_kernel.cc; SplitInfo,
+ * src/04kernel/src/attributes/split_info.cc:6-28).  concat: inputs {part 0 .. part n_parts - 1}, outputs {whole};
+ * split: inputs {whole}, outputs {part 0 ..}.  Parts of length 0 are allowed (their pointer is not read). */
+#define RG_CONCAT_MAX_PARTS 32
+typedef struct rg_concat_params {
+    uint32_t elem_bytes;
+    uint32_t n_parts;
+    uint32_t outer, inner;
+    uint32_t axis_len[RG_CONCAT_MAX_PARTS];
+} rg_concat_params;
+size_t rg_b200_concat_workspace(const rg_concat_params *);
+int rg_b200_concat(const rg_concat_params *, void *ws, const void *const *in, void *const *out, void *stream);
+size_t rg_b200_split_workspace(const rg_concat_params *);
+int rg_b200_split(const rg_concat_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Slice: y[i0, i1, ..] = x[start0 + i0 * step0, ..], 0 <= i_d < length_d; steps may be negative (the Dimensions {start, step,
+ * length} of the reference's SliceCollector, src/04kernel/include/kernel/attributes/slice_info.h:8-13; replaces SliceCuda).  Every
+ * addressed index must lie inside the input (RG_ERR_SHAPE otherwise: nothing is launched).  rank <= 6.  inputs {x}, outputs {y}. */
+#define RG_MOVE_MAX_RANK 6
+typedef struct rg_slice_params {
+    uint32_t elem_bytes;
+    uint32_t rank;
+    uint32_t in_shape[RG_MOVE_MAX_RANK];
+    int64_t start[RG_MOVE_MAX_RANK], step[RG_MOVE_MAX_RANK];
+    uint32_t length[RG_MOVE_MAX_RANK];
+} rg_slice_params;
+size_t rg_b200_slice_workspace(const rg_slice_params *);
+int rg_b200_slice(const rg_slice_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Expand: broadcast x to out_shape; in_shape has the same rank (the caller pads it with leading 1s) and every dimension equals
+ * the output's or is 1.  Replaces ExpandCuda (src/04kernel/src/kernels/expand/cuda_kernel.cc).  inputs {x}, outputs {y}. */
+typedef struct rg_expand_params {
+    uint32_t elem_bytes;
+    uint32_t rank;
+    uint32_t in_shape[RG_MOVE_MAX_RANK], out_shape[RG_MOVE_MAX_RANK];
+} rg_expand_params;
+size_t rg_b200_expand_workspace(const rg_expand_params *);
+int rg_b200_expand(const rg_expand_params *, void *ws, const void *const *in, void *const *out, void *stream);
+
+/* Cast between RG_F32, RG_F64, RG_FP16, RG_BF16, RG_I8, RG_U8, RG_I16, RG_U16, RG_I32, RG_U32, RG_I64, RG_U64 and RG_BOOL (one byte
+ * holding 0 or 1).  Replaces CastCuda (src/04kernel/src/kernels/cast/cuda_kernel.cc).  static_cast semantics: float -> integer
+ * truncates toward zero, anything -> bool is `!= 0`; conversions to 16-bit floats round to nearest even.  inputs {x}, outputs {y}. */
+typedef struct rg_cast_params {
+    int32_t from, to;
+    uint64_t n;
+} rg_cast_params;
+size_t rg_b200_cast_workspace(const rg_cast_params *);
+int rg_b200_cast(const rg_cast_params *, void *ws, const void *const *in, void *const *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * RotaryPositionEmbedding (no reference counterpart).  x[tokens, heads, head_dim], rotate-half pairing

@@ -91,6 +91,35 @@ def silu(x):
 # ------------------------------------------------------------------------------------------------
 # Definitions with no reference implementation (parity unpinned).
 
+# ---- data movement: the reference's CPU kernels are block copies driven by ConcatInfo / SplitInfo / SliceInfo / ExpandInfo
+# (src/04kernel/src/kernels/{concat,split,slice,expand}/cpu_kernel.cc), i.e. exactly numpy's concatenate / split / strided
+# indexing / broadcast_to; Cast is `static_cast<U>(a)` per element (src/04kernel/src/kernels/cast/cpu_kernel.cc:36).
+def concat(xs, axis: int) -> np.ndarray:
+    return np.concatenate(xs, axis=axis)
+
+
+def split(x: np.ndarray, sizes, axis: int):
+    return np.split(x, np.cumsum(sizes)[:-1], axis=axis)
+
+
+def slice_(x: np.ndarray, starts, steps, lengths) -> np.ndarray:
+    """y[i0, i1, ..] = x[start0 + i0 * step0, ..] — the {start, step, length} triples of
+    src/04kernel/include/kernel/attributes/slice_info.h:8-13."""
+    idx = tuple(np.asarray(s + st * np.arange(n), np.int64) for s, st, n in zip(starts, steps, lengths))
+    return x[np.ix_(*idx)] if idx else x.copy()
+
+
+def expand(x: np.ndarray, shape) -> np.ndarray:
+    return np.ascontiguousarray(np.broadcast_to(x, shape))
+
+
+def cast(x: np.ndarray, to) -> np.ndarray:
+    """static_cast semantics: float -> integer truncates toward zero, anything -> bool is `!= 0`; float -> half rounds to
+    nearest even (what the reference's CUDA cast computes; its host fp16_t truncates)."""
+    with np.errstate(invalid="ignore", over="ignore"):
+        return x.astype(to)
+
+
 def rope(x: np.ndarray, positions: np.ndarray, theta: float = 10000.0) -> np.ndarray:
     """x[tokens, heads, D]; rotate-half pairing (i, i + D/2); angle = pos * theta^(-2i/D)."""
     T, H, D = x.shape

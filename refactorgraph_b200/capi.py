@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "librg_b200.so")
 OK, ERR_NULL, ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_LIMIT = range(9)
 # rg_dtype (= the reference's DataType codes)
 F32, U8, I8, I32, I64, BOOL, FP16, F64, U32, BF16 = 1, 2, 3, 6, 7, 9, 10, 11, 12, 16
+U16, I16, U64 = 4, 5, 13
 
 
 class RmsNormParams(C.Structure):
@@ -57,6 +58,23 @@ class WhereParams(C.Structure):
 class TransposeParams(C.Structure):
     _fields_ = [("elem_bytes", C.c_uint32), ("rank", C.c_uint32), ("in_shape", C.c_uint32 * 4),
                 ("perm", C.c_uint32 * 4)]
+
+
+class ConcatParams(C.Structure):       # concat and split
+    _fields_ = [("elem_bytes", C.c_uint32), ("n_parts", C.c_uint32), ("outer", C.c_uint32), ("inner", C.c_uint32), ("axis_len", C.c_uint32 * 32)]
+
+
+class SliceParams(C.Structure):
+    _fields_ = [("elem_bytes", C.c_uint32), ("rank", C.c_uint32), ("in_shape", C.c_uint32 * 6), ("start", C.c_int64 * 6), ("step", C.c_int64 * 6),
+                ("length", C.c_uint32 * 6)]
+
+
+class ExpandParams(C.Structure):
+    _fields_ = [("elem_bytes", C.c_uint32), ("rank", C.c_uint32), ("in_shape", C.c_uint32 * 6), ("out_shape", C.c_uint32 * 6)]
+
+
+class CastParams(C.Structure):
+    _fields_ = [("from_", C.c_int32), ("to", C.c_int32), ("n", C.c_uint64)]
 
 
 class RopeParams(C.Structure):
@@ -135,6 +153,7 @@ OPS = {
     "transpose": TransposeParams, "rope": RopeParams, "state_update": StateUpdateParams, "mat_mul": MatMulParams, "linear": LinearParams,
     "attention": AttentionParams, "attn_decode": AttnDecodeParams, "qkv_rope_append": QkvRopeAppendParams,
     "swiglu": SwigluParams, "decode_step": DecodeStepParams, "attn_prefill": AttnPrefillParams,
+    "concat": ConcatParams, "split": ConcatParams, "slice": SliceParams, "expand": ExpandParams, "cast": CastParams,
 }
 # every symbol include/rg_b200.h declares
 SYMBOLS = (["rg_b200_status_string", "rg_b200_version", "rg_b200_launch_count", "rg_b200_error_state", "rg_b200_error_clear", "rg_b200_attn_decode_static",

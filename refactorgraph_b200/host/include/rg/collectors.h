@@ -48,6 +48,24 @@ namespace refactor::kernel {
     RG_COLLECTOR(SimpleUnaryCollector, SimpleUnaryType, type);
     // src/04kernel/include/kernel/collectors/transpose.h
     RG_COLLECTOR(TransposeCollector, std::vector<dim_t>, perm);
+    // src/04kernel/include/kernel/collectors/concat.h, split.h: the axis; part lengths come from the tensors
+    RG_COLLECTOR(ConcatCollector, dim_t, axis);
+    RG_COLLECTOR(SplitCollector, dim_t, axis);
+    // src/04kernel/include/kernel/collectors/slice.h with the Dimensions of src/04kernel/include/kernel/attributes/slice_info.h:8-13
+    struct SliceDim {
+        int64_t start, step, length;
+    };
+    using SliceDimensions = std::vector<SliceDim>;
+    RG_COLLECTOR(SliceCollector, SliceDimensions, dims);
+    // src/04kernel/include/kernel/collectors/cast.h and the expand collector (src/04kernel/src/collectors/expand.cc): no attributes
+    struct CastCollector final : public InfoCollector {
+        explicit CastCollector(Target target) noexcept : InfoCollector(target) {}
+        std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
+    };
+    struct ExpandCollector final : public InfoCollector {
+        explicit ExpandCollector(Target target) noexcept : InfoCollector(target) {}
+        std::vector<KernelBox> filter(TensorRefs inputs, TensorRefs outputs) const final;
+    };
     // src/04kernel/include/kernel/collectors/where.h
     struct WhereCollector final : public InfoCollector {
         explicit WhereCollector(Target target) noexcept : InfoCollector(target) {}

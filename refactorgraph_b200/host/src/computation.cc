@@ -34,6 +34,15 @@ namespace refactor::computation {
             return std::make_unique<Transpose>(std::vector<dim_t>(p.begin(), p.end()));
         }
         if (is({"onnx::Reshape"})) return std::make_unique<Reshape>(getInts(a, "shape"));
+        if (is({"onnx::Concat"})) return std::make_unique<Concat>(getInt(a, "axis", 0));
+        if (is({"onnx::Split"})) return std::make_unique<Split>(getInt(a, "axis", 0), getInts(a, "split"), static_cast<dim_t>(getInt(a, "num_outputs", 0)));
+        if (is({"onnx::Slice"})) return std::make_unique<Slice>(getInts(a, "starts"), getInts(a, "ends"), getInts(a, "axes"), getInts(a, "steps"));
+        if (is({"onnx::Expand"})) return std::make_unique<Expand>(getInts(a, "shape"));
+        if (is({"onnx::Cast"})) {
+            auto to = DataType::parse(static_cast<uint8_t>(getInt(a, "to", 0)));
+            if (!to) RUNTIME_ERROR("onnx::Cast: unknown target type");
+            return std::make_unique<Cast>(*to);
+        }
         if (is({"onnx::Where"})) return std::make_unique<Where>();
         if (is({"onnx::AllReduceSum"})) return std::make_unique<AllReduce>(AllReduceType::Sum);
         if (is({"onnx::AllReduceAvg"})) return std::make_unique<AllReduce>(AllReduceType::Avg);

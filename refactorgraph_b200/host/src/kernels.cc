@@ -64,6 +64,11 @@ namespace refactor::kernel {
     RG_SIMPLE_KERNEL(WhereB200, rg_where_params, rg_b200_where, "Where on B200");
     RG_SIMPLE_KERNEL(TransposeB200, rg_transpose_params, rg_b200_transpose, "Transpose on B200");
     RG_SIMPLE_KERNEL(RopeB200, rg_rope_params, rg_b200_rope, "Rotary position embedding on B200");
+    RG_SIMPLE_KERNEL(ConcatB200, rg_concat_params, rg_b200_concat, "Concat on B200 (strided copy in the widest aligned unit)");
+    RG_SIMPLE_KERNEL(SplitB200, rg_concat_params, rg_b200_split, "Split on B200 (strided copy in the widest aligned unit)");
+    RG_SIMPLE_KERNEL(SliceB200, rg_slice_params, rg_b200_slice, "Slice on B200 (strided copy, negative steps allowed)");
+    RG_SIMPLE_KERNEL(ExpandB200, rg_expand_params, rg_b200_expand, "Expand on B200 (broadcast copy)");
+    RG_SIMPLE_KERNEL(CastB200, rg_cast_params, rg_b200_cast, "Cast on B200");
     RG_SIMPLE_KERNEL(TopKB200, rg_topk_params, rg_b200_topk, "TopK on B200 (radix select in shared memory)");
     RG_SIMPLE_KERNEL(TopKSampleB200, rg_topk_sample_params, rg_b200_topk_sample, "Top-k sampling on B200 (radix select + Philox)");
     RG_SIMPLE_KERNEL(AttentionB200, rg_attention_params, rg_b200_attention, "Causal attention with KV cache on B200");
@@ -213,6 +218,96 @@ namespace refactor::kernel {
         p.rank = static_cast<uint32_t>(x.shape.size());
         for (size_t i = 0; i < x.shape.size(); ++i) p.in_shape[i] = x.shape[i], p.perm[i] = perm[i];
         ans.emplace_back(std::make_unique<TransposeB200>(p));
+        return ans;
+    }
+
+    // ---- Concat / Split / Slice / Expand / Cast: byte-exact movement, any data type ------------------------------------
+    static bool asOuterAxisInner(Shape const &s, dim_t axis, rg_concat_params &p) {
+        if (axis >= s.size()) return false;
+        uint64_t outer = 1, inner = 1;
+        for (size_t i = 0; i < axis; ++i) outer *= s[i];
+        for (size_t i = axis + 1; i < s.size(); ++i) inner *= s[i];
+        if (outer > 0xffffffffull || inner > 0xffffffffull) return false;
+        p.outer = static_cast<uint32_t>(outer), p.inner = static_cast<uint32_t>(inner);
+        return true;
+    }
+    std::vector<KernelBox> ConcatCollector::filter(TensorRefs inputs, TensorRefs outputs) const {
+        std::vector<KernelBox> ans;
+        if (_target != Target::Nvidia || inputs.empty() || inputs.size() > RG_CONCAT_MAX_PARTS || outputs.size() != 1) return ans;
+        rg_concat_params p{};
+        p.elem_bytes = static_cast<uint32_t>(outputs[0].get().dataType.size());
+        p.n_parts = static_cast<uint32_t>(inputs.size());
+        if (!asOuterAxisInner(outputs[0].get().shape, axis, p)) return ans;
+        for (size_t i = 0; i < inputs.size(); ++i) {
+            auto const &t = inputs[i].get();
+            if (t.dataType != outputs[0].get().dataType || t.shape.size() != outputs[0].get().shape.size()) return ans;
+            p.axis_len[i] = t.shape[axis];
+        }
+        ans.emplace_back(std::make_unique<ConcatB200>(p));
+        return ans;
+    }
+    std::vector<KernelBox> SplitCollector::filter(TensorRefs inputs, TensorRefs outputs) const {
+        std::vector<KernelBox> ans;
+        if (_target != Target::Nvidia || inputs.empty() || outputs.empty() || outputs.size() > RG_CONCAT_MAX_PARTS) return ans;
+        rg_concat_params p{};
+        p.elem_bytes = static_cast<uint32_t>(inputs[0].get().dataType.size());
+        p.n_parts = static_cast<uint32_t>(outputs.size());
+        if (!asOuterAxisInner(inputs[0].get().shape, axis, p)) return ans;
+        for (size_t i = 0; i < outputs.size(); ++i) {
+            auto const &t = outputs[i].get();
+            if (t.shape.size() != inputs[0].get().shape.size()) return ans;
+            p.axis_len[i] = t.shape[axis];
+        }
+        ans.emplace_back(std::make_unique<SplitB200>(p));
+        return ans;
+    }
+    std::vector<KernelBox> SliceCollector::filter(TensorRefs inputs, TensorRefs) const {
+        std::vector<KernelBox> ans;
+        auto const &x = inputs[0].get();
+        if (_target != Target::Nvidia || x.shape.size() > RG_MOVE_MAX_RANK || dims.size() != x.shape.size()) return ans;
+        rg_slice_params p{};
+        p.elem_bytes = static_cast<uint32_t>(x.dataType.size());
+        p.rank = static_cast<uint32_t>(x.shape.size());
+        for (size_t i = 0; i < dims.size(); ++i) {
+            if (dims[i].length < 0) return ans;
+            p.in_shape[i] = x.shape[i], p.start[i] = dims[i].start, p.step[i] = dims[i].step, p.length[i] = static_cast<uint32_t>(dims[i].length);
+        }
+        ans.emplace_back(std::make_unique<SliceB200>(p));
+        return ans;
+    }
+    std::vector<KernelBox> ExpandCollector::filter(TensorRefs inputs, TensorRefs outputs) const {
+        std::vector<KernelBox> ans;
+        auto const &x = inputs[0].get();
+        auto const &y = outputs[0].get();
+        if (_target != Target::Nvidia || y.shape.size() > RG_MOVE_MAX_RANK || x.shape.size() > y.shape.size() || x.dataType != y.dataType) return ans;
+        rg_expand_params p{};
+        p.elem_bytes = static_cast<uint32_t>(x.dataType.size());
+        p.rank = static_cast<uint32_t>(y.shape.size());
+        const size_t lead = y.shape.size() - x.shape.size();
+        for (size_t i = 0; i < y.shape.size(); ++i) {
+            p.out_shape[i] = y.shape[i];
+            p.in_shape[i] = i < lead ? 1 : x.shape[i - lead];
+            if (p.in_shape[i] != 1 && p.in_shape[i] != p.out_shape[i]) return ans;
+        }
+        ans.emplace_back(std::make_unique<ExpandB200>(p));
+        return ans;
+    }
+    std::vector<KernelBox> CastCollector::filter(TensorRefs inputs, TensorRefs outputs) const {
+        std::vector<KernelBox> ans;
+        auto const &x = inputs[0].get();
+        auto const &y = outputs[0].get();
+        if (_target != Target::Nvidia || x.elementsSize() != y.elementsSize()) return ans;
+        auto known = [](int t) {
+            switch (t) {
+                case RG_F32: case RG_F64: case RG_FP16: case RG_BF16: case RG_I8: case RG_U8: case RG_I16: case RG_U16: case RG_I32: case RG_U32:
+                case RG_I64: case RG_U64: case RG_BOOL: return true;
+                default: return false;
+            }
+        };
+        if (!known(x.dataType) || !known(y.dataType)) return ans;
+        rg_cast_params p{};
+        p.from = x.dataType, p.to = y.dataType, p.n = x.elementsSize();
+        ans.emplace_back(std::make_unique<CastB200>(p));
         return ans;
     }
 

@@ -182,6 +182,119 @@ namespace refactor::computation {
             return one(in[0].get().dataType, o);
         }
     };
+    // ---- data movement (ONNX semantics; negative axes count from the end) ----
+    inline dim_t normAxis(int64_t axis, size_t rank) {
+        if (axis < 0) axis += static_cast<int64_t>(rank);
+        ASSERT(axis >= 0 && static_cast<size_t>(axis) < rank, "axis out of range");
+        return static_cast<dim_t>(axis);
+    }
+    struct Concat final : Operator {
+        int64_t axis;
+        explicit Concat(int64_t a) : axis(a) {}
+        RG_OP(Concat, "Concat")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<ConcatCollector>(t, resolved); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            ASSERT(!in.empty(), "Concat needs an input");
+            Shape o = in[0].get().shape;
+            resolved = normAxis(axis, o.size());
+            o[resolved] = 0;
+            for (auto const &t : in) {
+                auto const &s = t.get().shape;
+                ASSERT(s.size() == o.size() && t.get().dataType == in[0].get().dataType, "Concat: rank or type mismatch");
+                for (size_t i = 0; i < s.size(); ++i) {
+                    ASSERT(i == resolved || s[i] == o[i], "Concat: shapes differ outside the axis");
+                }
+                o[resolved] += s[resolved];
+            }
+            return one(in[0].get().dataType, o);
+        }
+        mutable dim_t resolved = 0;// axis >= 0, known once the input rank is
+    };
+    struct Split final : Operator {
+        int64_t axis;
+        std::vector<int64_t> sizes;// empty: equal parts, one per output
+        dim_t nOut;
+        Split(int64_t a, std::vector<int64_t> s, dim_t n) : axis(a), sizes(std::move(s)), nOut(n) {}
+        RG_OP(Split, "Split")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<SplitCollector>(t, resolved); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            auto const &x = in[0].get();
+            resolved = normAxis(axis, x.shape.size());
+            std::vector<int64_t> parts = sizes;
+            if (parts.empty()) {
+                ASSERT(nOut > 0 && x.shape[resolved] % nOut == 0, "Split: the axis does not divide into equal parts");
+                parts.assign(nOut, x.shape[resolved] / nOut);
+            }
+            int64_t sum = 0;
+            for (auto v : parts) {
+                ASSERT(v >= 0, "Split: negative part");
+                sum += v;
+            }
+            ASSERT(sum == static_cast<int64_t>(x.shape[resolved]), "Split: parts do not add up to the axis");
+            std::vector<Arc<Tensor>> out;
+            for (auto v : parts) {
+                Shape o = x.shape;
+                o[resolved] = static_cast<dim_t>(v);
+                out.push_back(Tensor::share(x.dataType, o));
+            }
+            return out;
+        }
+        mutable dim_t resolved = 0;
+    };
+    // starts / ends / axes / steps as ONNX Slice defines them (clamped ends, negative indices, negative steps)
+    struct Slice final : Operator {
+        std::vector<int64_t> starts, ends, axes, steps;
+        Slice(std::vector<int64_t> s, std::vector<int64_t> e, std::vector<int64_t> a, std::vector<int64_t> st)
+            : starts(std::move(s)), ends(std::move(e)), axes(std::move(a)), steps(std::move(st)) {}
+        RG_OP(Slice, "Slice")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<SliceCollector>(t, dims); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            auto const &x = in[0].get();
+            const size_t rank = x.shape.size();
+            ASSERT(starts.size() == ends.size() && (axes.empty() || axes.size() == starts.size()) && (steps.empty() || steps.size() == starts.size()),
+                   "Slice: starts, ends, axes and steps must have one entry per sliced axis");
+            dims.assign(rank, SliceDim{0, 1, 0});
+            for (size_t d = 0; d < rank; ++d) dims[d].length = x.shape[d];
+            for (size_t i = 0; i < starts.size(); ++i) {
+                const dim_t d = normAxis(axes.empty() ? static_cast<int64_t>(i) : axes[i], rank);
+                const int64_t n = x.shape[d], step = steps.empty() ? 1 : steps[i];
+                ASSERT(step != 0, "Slice: step 0");
+                int64_t s = starts[i] < 0 ? starts[i] + n : starts[i], e = ends[i] < 0 ? ends[i] + n : ends[i];
+                if (step > 0) {
+                    s = std::min(std::max<int64_t>(s, 0), n), e = std::min(std::max<int64_t>(e, 0), n);
+                    dims[d] = SliceDim{s, step, e > s ? (e - s + step - 1) / step : 0};
+                } else {
+                    s = std::min(std::max<int64_t>(s, -1), n - 1), e = std::min(std::max<int64_t>(e, -1), n - 1);
+                    dims[d] = SliceDim{s, step, s > e ? (s - e - step - 1) / (-step) : 0};
+                }
+            }
+            Shape o(rank);
+            for (size_t d = 0; d < rank; ++d) o[d] = static_cast<dim_t>(dims[d].length);
+            return one(x.dataType, o);
+        }
+        mutable SliceDimensions dims;
+    };
+    struct Cast final : Operator {
+        DataType to;
+        explicit Cast(DataType t) : to(t) {}
+        RG_OP(Cast, "Cast")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<CastCollector>(t); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final { return one(to, in[0].get().shape); }
+    };
+    struct Expand final : Operator {
+        std::vector<int64_t> shape;
+        explicit Expand(std::vector<int64_t> s) : shape(std::move(s)) {}
+        RG_OP(Expand, "Expand")
+        CollectorBox candidateKernels(Target t) const final { return std::make_unique<ExpandCollector>(t); }
+        std::vector<Arc<Tensor>> infer(TensorRefs in) const final {
+            Shape want(shape.size());
+            for (size_t i = 0; i < shape.size(); ++i) {
+                ASSERT(shape[i] >= 0, "Expand: negative dimension");
+                want[i] = static_cast<dim_t>(shape[i]);
+            }
+            return one(in[0].get().dataType, broadcastShape(in[0].get().shape, want));
+        }
+    };
     struct Reshape final : Operator {
         std::vector<int64_t> shape;
         explicit Reshape(std::vector<int64_t> s) : shape(std::move(s)) {}

@@ -122,6 +122,73 @@ def transpose(x, perm):
     return y
 
 
+def _as_3d(shape, axis):
+    axis %= len(shape)
+    return int(np.prod(shape[:axis], dtype=np.int64)), int(shape[axis]), int(np.prod(shape[axis + 1:], dtype=np.int64))
+
+
+def concat(xs, axis):
+    axis %= xs[0].dim()
+    outer, _, inner = _as_3d(xs[0].shape, axis)
+    shape = list(xs[0].shape)
+    shape[axis] = sum(int(x.shape[axis]) for x in xs)
+    y = torch.empty(shape, dtype=xs[0].dtype, device=xs[0].device)
+    p = capi.ConcatParams()
+    p.elem_bytes, p.n_parts, p.outer, p.inner = xs[0].element_size(), len(xs), outer, inner
+    for i, x in enumerate(xs):
+        p.axis_len[i] = int(x.shape[axis])
+    capi.call("concat", p, [ptr(x) if x.numel() else 0 for x in xs], [ptr(y)], stream=stream())
+    return y
+
+
+def split(x, sizes, axis):
+    axis %= x.dim()
+    outer, _, inner = _as_3d(x.shape, axis)
+    ys = []
+    for n in sizes:
+        shape = list(x.shape)
+        shape[axis] = n
+        ys.append(torch.empty(shape, dtype=x.dtype, device=x.device))
+    p = capi.ConcatParams()
+    p.elem_bytes, p.n_parts, p.outer, p.inner = x.element_size(), len(sizes), outer, inner
+    for i, n in enumerate(sizes):
+        p.axis_len[i] = n
+    capi.call("split", p, [ptr(x)], [ptr(y) if y.numel() else 0 for y in ys], stream=stream())
+    return ys
+
+
+def slice_(x, starts, steps, lengths, check=True):
+    y = torch.empty(list(lengths), dtype=x.dtype, device=x.device)
+    p = capi.SliceParams()
+    p.elem_bytes, p.rank = x.element_size(), x.dim()
+    for d in range(x.dim()):
+        p.in_shape[d], p.start[d], p.step[d], p.length[d] = int(x.shape[d]), int(starts[d]), int(steps[d]), int(lengths[d])
+    rc = capi.call("slice", p, [ptr(x)], [ptr(y)], stream=stream(), check=check)
+    return y if check else (rc, y)
+
+
+def expand(x, shape):
+    y = torch.empty(list(shape), dtype=x.dtype, device=x.device)
+    p = capi.ExpandParams()
+    p.elem_bytes, p.rank = x.element_size(), len(shape)
+    ins = [1] * (len(shape) - x.dim()) + list(x.shape)
+    for d in range(len(shape)):
+        p.in_shape[d], p.out_shape[d] = int(ins[d]), int(shape[d])
+    capi.call("expand", p, [ptr(x)], [ptr(y)], stream=stream())
+    return y
+
+
+CAST_CODE = {torch.float32: capi.F32, torch.float64: capi.F64, torch.float16: capi.FP16, torch.bfloat16: capi.BF16, torch.int8: capi.I8,
+             torch.uint8: capi.U8, torch.int16: capi.I16, torch.int32: capi.I32, torch.int64: capi.I64, torch.bool: capi.BOOL}
+
+
+def cast(x, to):
+    y = torch.empty(x.shape, dtype=to, device=x.device)
+    p = capi.CastParams(CAST_CODE[x.dtype], CAST_CODE[to], x.numel())
+    capi.call("cast", p, [ptr(x)], [ptr(y)], stream=stream())
+    return y
+
+
 def rope(x, pos, theta=10000.0):
     y = torch.empty_like(x)
     t, h, d = x.shape

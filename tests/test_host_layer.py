@@ -144,6 +144,41 @@ def test_serialize_writes_graph_info_and_data(tmp_path):
     np.testing.assert_array_equal(np.frombuffer(data[:32], np.float32), np.arange(8, dtype=np.float32))
 
 
+def test_data_movement_operators_infer_onnx_shapes(tmp_path):
+    """Concat / Split / Slice / Expand / Cast with the attributes ONNX gives them: negative axes, a negative-step slice with a
+    negative end, broadcast to a higher rank.  Shapes are read back from the serialised graph."""
+    from refactorgraph_b200.graph_builder import FP16 as F16
+    g = GraphBuilder()
+    a = g.input("a", F32, (2, 3, 8))
+    b = g.input("b", F32, (2, 5, 8))
+    c = g.op("onnx::Concat", [a, b], axis=1, name="cat")
+    s0, s1 = g.op("onnx::Split", [c], n_out=2, axis=-1, split=[6, 2], name="sp")
+    sl = g.op("onnx::Slice", [s0], starts=[7, 1], ends=[-9, 6], axes=[1, 2], steps=[-2, 2], name="sl")
+    e = g.op("onnx::Expand", [s1], shape=[3, 2, 8, 2], name="ex")
+    h = g.op("onnx::Cast", [sl], to=int(F16), name="ca")
+    g.output(h)
+    g.output(e)
+    comp = g.compiler()
+    assert sorted(comp.plan([])) == ["Cast", "Concat", "Expand", "Slice", "Split"]
+    comp.serialize(str(tmp_path / "dump"))
+    info = (tmp_path / "dump" / "graph.info").read_text()
+    for line in ("cat:0\tF32<2x8x8>", "sp:0\tF32<2x8x6>", "sp:1\tF32<2x8x2>", "sl:0\tF32<2x4x3>", "ex:0\tF32<3x2x8x2>", "ca:0\tFP16<2x4x3>"):
+        assert line in info, (line, info)
+    # equal parts when no sizes are given; parts that do not add up are refused
+    g2 = GraphBuilder()
+    x = g2.input("x", F32, (4, 9))
+    parts = g2.op("onnx::Split", [x], n_out=3, axis=1, num_outputs=3, name="eq")
+    for p_ in parts:
+        g2.output(p_)
+    g2.compiler().serialize(str(tmp_path / "dump2"))
+    assert (tmp_path / "dump2" / "graph.info").read_text().count("F32<4x3>") == 3
+    g3 = GraphBuilder()
+    x = g3.input("x", F32, (4, 9))
+    with pytest.raises(RuntimeError):
+        g3.op("onnx::Split", [x], n_out=2, axis=1, split=[4, 4])
+        g3.compiler().plan([])
+
+
 # ---- fusion pass: a decoder written operator by operator becomes the hand-fused graph ------------------------------------
 def test_fusion_pass_reproduces_the_hand_fused_decode_graph():
     from refactorgraph_b200.llama import decode_step_graph_batched, decode_step_graph_single_kernel
