@@ -229,8 +229,14 @@ int rg_b200_split(const rg_concat_params *p, void *, const void *const *in, void
 }
 
 int rg_b200_slice(const rg_slice_params *p, void *, const void *const *in, void *const *out, void *stream) {
-    if (!p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+    if (!p || !in || !out) return RG_ERR_NULL;
     if (p->rank > RG_MOVE_MAX_RANK) return RG_ERR_SHAPE;
+    {// an empty result needs no buffers
+        uint64_t total = 1;
+        for (uint32_t d = 0; d < p->rank; ++d) total *= p->length[d];
+        if (total == 0) return RG_OK;
+    }
+    if (!in[0] || !out[0]) return RG_ERR_NULL;
     int64_t base[RG_MOVE_MAX_RANK], in_stride[RG_MOVE_MAX_RANK], out_stride[RG_MOVE_MAX_RANK];
     int64_t s = 1;
     for (int d = static_cast<int>(p->rank) - 1; d >= 0; --d) base[d] = s, s *= p->in_shape[d];
@@ -249,8 +255,14 @@ int rg_b200_slice(const rg_slice_params *p, void *, const void *const *in, void 
 }
 
 int rg_b200_expand(const rg_expand_params *p, void *, const void *const *in, void *const *out, void *stream) {
-    if (!p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+    if (!p || !in || !out) return RG_ERR_NULL;
     if (p->rank > RG_MOVE_MAX_RANK) return RG_ERR_SHAPE;
+    {
+        uint64_t total = 1;
+        for (uint32_t d = 0; d < p->rank; ++d) total *= p->out_shape[d];
+        if (total == 0) return RG_OK;
+    }
+    if (!in[0] || !out[0]) return RG_ERR_NULL;
     int64_t in_stride[RG_MOVE_MAX_RANK], out_stride[RG_MOVE_MAX_RANK];
     int64_t si = 1, so = 1;
     for (int d = static_cast<int>(p->rank) - 1; d >= 0; --d) {
@@ -263,8 +275,9 @@ int rg_b200_expand(const rg_expand_params *p, void *, const void *const *in, voi
 }
 
 int rg_b200_cast(const rg_cast_params *p, void *, const void *const *in, void *const *out, void *stream) {
-    if (!p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
+    if (!p || !in || !out) return RG_ERR_NULL;
     if (p->n == 0) return RG_OK;
+    if (!in[0] || !out[0]) return RG_ERR_NULL;
     auto st = static_cast<cudaStream_t>(stream);
     switch (p->from) {
         case RG_F32: return cast_from<float>(p->to, in[0], out[0], p->n, st);
