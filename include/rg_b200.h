@@ -133,7 +133,10 @@ int rg_b200_gather(const rg_gather_params *, void *ws, const void *const *in, vo
  * Element-wise binary with multidirectional broadcast, rank <= 4.  Replaces BinaryCudnn / BinaryCuda
  * (src/04kernel/src/kernels/simple_binary/cuda_kernel.cc:42-136).  op uses the reference's
  * SimpleBinaryType values (src/04kernel/include/kernel/collectors/simple_binary.h:8-19): 0 Add, 1 Sub,
- * 2 Mul, 3 Div.  Strides are in elements, 0 on a broadcast axis.  inputs {a, b}, outputs {y}. */
+ * 2 Mul, 3 Div, 4 Pow, 5 And, 6 Or, 7 Xor, 8 Mod, 9 Fmod.  RG_F32 / RG_FP16 / RG_BF16: 0-4 and 9 (evaluated in fp32);
+ * RG_U8 / RG_I8 / RG_I16 / RG_I32 / RG_U32 / RG_I64: 0-4, 8 and 9 (`%` of C++: sign of the dividend; a zero divisor gives 0);
+ * RG_BOOL: 5-7.  Any other pair is RG_ERR_UNSUPPORTED.  Strides are in elements, 0 on a broadcast axis.
+ * inputs {a, b}, outputs {y}. */
 typedef struct rg_binary_params {
     int32_t op, dtype;
     uint32_t shape[4];
@@ -144,8 +147,10 @@ int rg_b200_binary(const rg_binary_params *, void *ws, const void *const *in, vo
 
 /* Element-wise unary.  Replaces ActivationCudnn / SimpleUnaryCuda
  * (src/04kernel/src/kernels/simple_unary/cuda_kernel.cc:96-175).  op uses SimpleUnaryType values
- * (src/04kernel/include/kernel/collectors/simple_unary.h:8-30): 12 Tanh, 13 Relu, 14 Sqrt, 15 Sigmoid,
- * 17 Neg, 20 Exp; 100 = SiLU (x*sigmoid(x), the fused pair the decoder uses).  inputs {x}, outputs {y}. */
+ * (src/04kernel/include/kernel/collectors/simple_unary.h:8-30): 0 Abs, 1 Acos, 2 Acosh, 3 Asin, 4 Asinh, 5 Atan, 6 Atanh, 7 Cos,
+ * 8 Cosh, 9 Sin, 10 Sinh, 11 Tan, 12 Tanh, 13 Relu, 14 Sqrt, 15 Sigmoid, 16 Erf, 17 Neg, 19 HardSwish, 20 Exp on RG_F32 / RG_FP16 /
+ * RG_BF16 (evaluated in fp32); 18 Not on RG_BOOL; 100 = SiLU (x*sigmoid(x), the fused pair the decoder uses).
+ * inputs {x}, outputs {y}. */
 typedef struct rg_unary_params {
     int32_t op, dtype;
     uint64_t n;

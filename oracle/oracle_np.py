@@ -74,7 +74,38 @@ def gather(data: np.ndarray, indices: np.ndarray, axis: int) -> np.ndarray:
 
 # BinaryCpu — src/04kernel/src/kernels/simple_binary/cpu_kernel.cc:33-154 (Add 0, Sub 1, Mul 2, Div 3).
 def binary(op: int, a, b):
-    return {0: np.add, 1: np.subtract, 2: np.multiply, 3: np.divide}[op](a, b)
+    """SimpleBinaryType 0-9 as BinaryCpu computes them (src/04kernel/src/kernels/simple_binary/cpu_kernel.cc:88-150): integer Div and
+    Mod / Fmod are the C++ `/` and `%` (truncation toward zero, sign of the dividend); And / Or / Xor are for bool."""
+    a, b = np.asarray(a), np.asarray(b)
+    if op in (0, 1, 2):
+        with np.errstate(over="ignore"):
+            return {0: np.add, 1: np.subtract, 2: np.multiply}[op](a, b)
+    if op == 3:
+        return np.trunc(np.true_divide(a, b)).astype(a.dtype) if np.issubdtype(a.dtype, np.integer) else np.divide(a, b)
+    if op == 4:
+        return np.power(a.astype(np.float64), b.astype(np.float64)).astype(a.dtype) if np.issubdtype(a.dtype, np.integer) else np.power(a, b)
+    if op in (5, 6, 7):
+        return {5: np.logical_and, 6: np.logical_or, 7: np.logical_xor}[op](a, b)
+    return np.fmod(a, b)      # 8 Mod (integers), 9 Fmod: both follow the sign of the dividend
+
+
+UNARY = {0: np.abs, 1: np.arccos, 2: np.arccosh, 3: np.arcsin, 4: np.arcsinh, 5: np.arctan, 6: np.arctanh, 7: np.cos, 8: np.cosh, 9: np.sin,
+         10: np.sinh, 11: np.tan, 12: np.tanh, 13: lambda x: np.maximum(x, 0), 14: np.sqrt, 15: lambda x: 1 / (1 + np.exp(-x)), 17: np.negative,
+         18: np.logical_not, 20: np.exp}
+
+
+def unary(op: int, x):
+    """SimpleUnaryType values (src/04kernel/include/kernel/collectors/simple_unary.h:8-30) in float64; Erf (16) and HardSwish (19,
+    x * clamp(x / 6 + 0.5, 0, 1): hardswishFun, src/04kernel/src/kernels/simple_unary/cpu_kernel.cc:54-59) spelled out."""
+    if op == 18:
+        return np.logical_not(x)
+    xf = np.asarray(x, np.float64)
+    if op == 16:
+        import math
+        return np.vectorize(math.erf)(xf)
+    if op == 19:
+        return xf * np.clip(xf / 6 + 0.5, 0, 1)
+    return UNARY[op](xf)
 
 
 # SimpleUnaryCpu — src/04kernel/src/kernels/simple_unary/cpu_kernel.cc:42-45 (sigmoid = 1/(1+exp(-x))).

@@ -73,12 +73,40 @@ __device__ __forceinline__ void locate(const Idx4 &ix, uint64_t t, uint64_t &a, 
         c += static_cast<uint64_t>(i) * ix.sc[d];
     }
 }
+// SimpleBinaryType values (src/04kernel/include/kernel/collectors/simple_binary.h:8-19): 0 Add, 1 Sub, 2 Mul, 3 Div, 4 Pow, 5 And,
+// 6 Or, 7 Xor, 8 Mod, 9 Fmod.  Floating types: 0-4 and 9 (std::pow / std::fmod as BinaryCpu computes them,
+// src/04kernel/src/kernels/simple_binary/cpu_kernel.cc:88-150).
 __device__ __forceinline__ float binary_op(int op, float a, float b) {
     switch (op) {
         case 0: return a + b;
         case 1: return a - b;
         case 2: return a * b;
+        case 4: return powf(a, b);
+        case 9: return fmodf(a, b);
         default: return a / b;
+    }
+}
+// Integer types: 0-3, 4 (through double, as std::pow does), 8 / 9 (the C++ `%`: sign of the dividend); a zero divisor gives 0
+// instead of the reference's undefined behaviour.  Bool (one byte): 5 And, 6 Or, 7 Xor.
+template<class T> __device__ __forceinline__ T binary_op_int(int op, T a, T b) {
+    switch (op) {
+        case 0: return static_cast<T>(a + b);
+        case 1: return static_cast<T>(a - b);
+        case 2: return static_cast<T>(a * b);
+        case 3: return b ? static_cast<T>(a / b) : T(0);
+        case 4: return static_cast<T>(pow(static_cast<double>(a), static_cast<double>(b)));
+        case 5: return static_cast<T>((a != 0) && (b != 0));
+        case 6: return static_cast<T>((a != 0) || (b != 0));
+        case 7: return static_cast<T>((a != 0) != (b != 0));
+        default: return b ? static_cast<T>(a % b) : T(0);
+    }
+}
+template<class T>
+__global__ void binary_int_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ y, Idx4 ix, int op, uint64_t total) {
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        uint64_t ia, ib, ic;
+        locate(ix, t, ia, ib, ic);
+        y[t] = binary_op_int<T>(op, a[ia], b[ib]);
     }
 }
 template<class T>
@@ -147,9 +175,39 @@ static int binary_launch(const rg_binary_params *p, const void *const *in, void 
     return launch_status();
 }
 
+template<class T>
+static int binary_int_launch(const rg_binary_params *p, const void *const *in, void *const *out, cudaStream_t st) {
+    uint64_t total = 1;
+    Idx4 ix;
+    for (int d = 0; d < 4; ++d) ix.shape[d] = p->shape[d], ix.sa[d] = p->a_stride[d], ix.sb[d] = p->b_stride[d], ix.sc[d] = 0, total *= p->shape[d];
+    if (total == 0) return RG_OK;
+    binary_int_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(static_cast<const T *>(in[0]), static_cast<const T *>(in[1]), static_cast<T *>(out[0]), ix, p->op, total);
+    count_launch();
+    return launch_status();
+}
+
 // ---- Unary ------------------------------------------------------------------------------------
+// SimpleUnaryType values (src/04kernel/include/kernel/collectors/simple_unary.h:8-30), computed in fp32 as SimpleUnaryCpu does
+// for F32 (src/04kernel/src/kernels/simple_unary/cpu_kernel.cc:42-59, 100-200); HardSwish is x * clamp(x / 6 + 0.5, 0, 1).
 __device__ __forceinline__ float unary_op(int op, float x) {
     switch (op) {
+        case 0: return fabsf(x);
+        case 1: return acosf(x);
+        case 2: return acoshf(x);
+        case 3: return asinf(x);
+        case 4: return asinhf(x);
+        case 5: return atanf(x);
+        case 6: return atanhf(x);
+        case 7: return cosf(x);
+        case 8: return coshf(x);
+        case 9: return sinf(x);
+        case 10: return sinhf(x);
+        case 11: return tanf(x);
+        case 16: return erff(x);
+        case 19: {
+            const float mid = x / 6.f + .5f;
+            return mid <= 0.f ? 0.f : (1.f <= mid ? x : x * mid);
+        }
         case 12: return tanhf(x);
         case 13: return x > 0.f ? x : 0.f;
         case 14: return sqrtf(x);
@@ -164,6 +222,12 @@ __global__ void unary_kernel(const T *__restrict__ x, T *__restrict__ y, int op,
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < n;
          t += static_cast<uint64_t>(gridDim.x) * blockDim.x)
         y[t] = Num<T>::from_f(unary_op(op, Num<T>::to_f(x[t])));
+}
+
+// 18 Not on bool bytes
+__global__ void not_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, uint64_t n) {
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < n; t += static_cast<uint64_t>(gridDim.x) * blockDim.x)
+        y[t] = x[t] ? 0 : 1;
 }
 
 // ---- Transpose ----------------------------------------------------------------------------------
@@ -332,12 +396,20 @@ int rg_b200_gather(const rg_gather_params *p, void *, const void *const *in, voi
 size_t rg_b200_binary_workspace(const rg_binary_params *) { return 0; }
 int rg_b200_binary(const rg_binary_params *p, void *, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out || !in[0] || !in[1] || !out[0]) return RG_ERR_NULL;
-    if (p->op < 0 || p->op > 3) return RG_ERR_UNSUPPORTED;
+    if (p->op < 0 || p->op > 9) return RG_ERR_UNSUPPORTED;
     auto st = static_cast<cudaStream_t>(stream);
+    const bool logic = p->op >= 5 && p->op <= 7;
     switch (p->dtype) {
-        case RG_F32: return binary_launch<float>(p, in, out, st);
-        case RG_FP16: return binary_launch<__half>(p, in, out, st);
-        case RG_BF16: return binary_launch<__nv_bfloat16>(p, in, out, st);
+        case RG_F32: case RG_FP16: case RG_BF16:
+            if (logic || p->op == 8) return RG_ERR_UNSUPPORTED;// And / Or / Xor are for bool, Mod for integers
+            return p->dtype == RG_F32 ? binary_launch<float>(p, in, out, st) : p->dtype == RG_FP16 ? binary_launch<__half>(p, in, out, st) : binary_launch<__nv_bfloat16>(p, in, out, st);
+        case RG_BOOL: return logic ? binary_int_launch<uint8_t>(p, in, out, st) : RG_ERR_UNSUPPORTED;
+        case RG_U8: return logic ? RG_ERR_UNSUPPORTED : binary_int_launch<uint8_t>(p, in, out, st);
+        case RG_I8: return logic ? RG_ERR_UNSUPPORTED : binary_int_launch<int8_t>(p, in, out, st);
+        case RG_I16: return logic ? RG_ERR_UNSUPPORTED : binary_int_launch<int16_t>(p, in, out, st);
+        case RG_I32: return logic ? RG_ERR_UNSUPPORTED : binary_int_launch<int32_t>(p, in, out, st);
+        case RG_U32: return logic ? RG_ERR_UNSUPPORTED : binary_int_launch<uint32_t>(p, in, out, st);
+        case RG_I64: return logic ? RG_ERR_UNSUPPORTED : binary_int_launch<long long>(p, in, out, st);
         default: return RG_ERR_DTYPE;
     }
 }
@@ -345,13 +417,16 @@ int rg_b200_binary(const rg_binary_params *p, void *, const void *const *in, voi
 size_t rg_b200_unary_workspace(const rg_unary_params *) { return 0; }
 int rg_b200_unary(const rg_unary_params *p, void *, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out || !in[0] || !out[0]) return RG_ERR_NULL;
-    switch (p->op) {
-        case 12: case 13: case 14: case 15: case 17: case 20: case 100: break;
-        default: return RG_ERR_UNSUPPORTED;
-    }
+    if (!((p->op >= 0 && p->op <= 20) || p->op == 100)) return RG_ERR_UNSUPPORTED;
     if (p->n == 0) return RG_OK;
     auto st = static_cast<cudaStream_t>(stream);
     const unsigned g = grid_for(p->n, 256);
+    if (p->op == 18) {// Not: bool bytes only
+        if (p->dtype != RG_BOOL) return RG_ERR_DTYPE;
+        not_kernel<<<g, 256, 0, st>>>(static_cast<const uint8_t *>(in[0]), static_cast<uint8_t *>(out[0]), p->n);
+        count_launch();
+        return launch_status();
+    }
     switch (p->dtype) {
         case RG_F32: unary_kernel<float><<<g, 256, 0, st>>>(static_cast<const float *>(in[0]), static_cast<float *>(out[0]), p->op, p->n); break;
         case RG_FP16: unary_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half *>(in[0]), static_cast<__half *>(out[0]), p->op, p->n); break;

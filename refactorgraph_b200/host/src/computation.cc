@@ -22,6 +22,21 @@ namespace refactor::computation {
         if (is({"onnx::Sub"})) return std::make_unique<SimpleBinary>(SimpleBinaryType::Sub);
         if (is({"onnx::Mul"})) return std::make_unique<SimpleBinary>(SimpleBinaryType::Mul);
         if (is({"onnx::Div"})) return std::make_unique<SimpleBinary>(SimpleBinaryType::Div);
+        if (is({"onnx::Pow"})) return std::make_unique<SimpleBinary>(SimpleBinaryType::Pow);
+        if (is({"onnx::And"})) return std::make_unique<SimpleBinary>(SimpleBinaryType::And);
+        if (is({"onnx::Or"})) return std::make_unique<SimpleBinary>(SimpleBinaryType::Or);
+        if (is({"onnx::Xor"})) return std::make_unique<SimpleBinary>(SimpleBinaryType::Xor);
+        if (is({"onnx::Mod"})) return std::make_unique<SimpleBinary>(getInt(a, "fmod", 0) ? SimpleBinaryType::Fmod : SimpleBinaryType::Mod);
+        {
+            static const std::pair<char const *, SimpleUnaryType> UNARY[] = {
+                {"onnx::Abs", SimpleUnaryType::Abs}, {"onnx::Acos", SimpleUnaryType::Acos}, {"onnx::Acosh", SimpleUnaryType::Acosh},
+                {"onnx::Asin", SimpleUnaryType::Asin}, {"onnx::Asinh", SimpleUnaryType::Asinh}, {"onnx::Atan", SimpleUnaryType::Atan},
+                {"onnx::Atanh", SimpleUnaryType::Atanh}, {"onnx::Cos", SimpleUnaryType::Cos}, {"onnx::Cosh", SimpleUnaryType::Cosh},
+                {"onnx::Sin", SimpleUnaryType::Sin}, {"onnx::Sinh", SimpleUnaryType::Sinh}, {"onnx::Tan", SimpleUnaryType::Tan},
+                {"onnx::Erf", SimpleUnaryType::Erf}, {"onnx::Not", SimpleUnaryType::Not}, {"onnx::HardSwish", SimpleUnaryType::HardSwish}};
+            for (auto const &[name, t] : UNARY)
+                if (is({name})) return std::make_unique<SimpleUnary>(t);
+        }
         if (is({"onnx::Sigmoid"})) return std::make_unique<SimpleUnary>(SimpleUnaryType::Sigmoid);
         if (is({"onnx::Tanh"})) return std::make_unique<SimpleUnary>(SimpleUnaryType::Tanh);
         if (is({"onnx::Relu"})) return std::make_unique<SimpleUnary>(SimpleUnaryType::Relu);

@@ -162,8 +162,18 @@ namespace refactor::kernel {
         auto const &a = inputs[0].get();
         auto const &b = inputs[1].get();
         auto const &y = outputs[0].get();
-        if (_target != Target::Nvidia || !halfOrFloat(a.dataType) || a.dataType != b.dataType) return ans;
-        if (static_cast<int>(type) > 3) return ans;
+        if (_target != Target::Nvidia || a.dataType != b.dataType) return ans;
+        {// the (operator, type) pairs the kernel library has: the sets BinaryCpu implements (simple_binary/cpu_kernel.cc:88-150)
+            const bool logic = type == SimpleBinaryType::And || type == SimpleBinaryType::Or || type == SimpleBinaryType::Xor;
+            bool ok;
+            switch (a.dataType) {
+                case DataType::F32: case DataType::FP16: case DataType::BF16: ok = !logic && type != SimpleBinaryType::Mod; break;
+                case DataType::Bool: ok = logic; break;
+                case DataType::U8: case DataType::I8: case DataType::I16: case DataType::I32: case DataType::U32: case DataType::I64: ok = !logic; break;
+                default: ok = false;
+            }
+            if (!ok) return ans;
+        }
         rg_binary_params p{};
         p.op = static_cast<int>(type);
         p.dtype = a.dataType;
@@ -177,13 +187,8 @@ namespace refactor::kernel {
     std::vector<KernelBox> SimpleUnaryCollector::filter(TensorRefs inputs, TensorRefs) const {
         std::vector<KernelBox> ans;
         auto const &x = inputs[0].get();
-        if (_target != Target::Nvidia || !halfOrFloat(x.dataType)) return ans;
-        switch (type) {
-            case SimpleUnaryType::Tanh: case SimpleUnaryType::Relu: case SimpleUnaryType::Sqrt:
-            case SimpleUnaryType::Sigmoid: case SimpleUnaryType::Neg: case SimpleUnaryType::Exp:
-            case SimpleUnaryType::Silu: break;
-            default: return ans;
-        }
+        if (_target != Target::Nvidia) return ans;
+        if (type == SimpleUnaryType::Not ? x.dataType != DataType::Bool : !halfOrFloat(x.dataType)) return ans;
         rg_unary_params p{};
         p.op = static_cast<int>(type);
         p.dtype = x.dataType;

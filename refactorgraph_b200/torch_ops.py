@@ -7,7 +7,7 @@ import torch
 from . import capi
 
 DT = {torch.float32: capi.F32, torch.float16: capi.FP16, torch.bfloat16: capi.BF16,
-      torch.int32: capi.I32, torch.int64: capi.I64}
+      torch.int32: capi.I32, torch.int64: capi.I64, torch.int8: capi.I8, torch.uint8: capi.U8, torch.int16: capi.I16, torch.bool: capi.BOOL}
 
 
 def ptr(t):
@@ -81,7 +81,7 @@ def _pad4(v, fill):
     return [fill] * (4 - len(v)) + list(v)
 
 
-def binary(op, a, b):
+def binary(op, a, b, check=True):
     shape = torch.broadcast_shapes(a.shape, b.shape)
     y = torch.empty(shape, dtype=a.dtype, device=a.device)
     p = capi.BinaryParams()
@@ -89,8 +89,8 @@ def binary(op, a, b):
     p.shape[:] = _pad4(shape, 1)
     p.a_stride[:] = _pad4(_bstrides(a.shape, shape), 0)
     p.b_stride[:] = _pad4(_bstrides(b.shape, shape), 0)
-    capi.call("binary", p, [ptr(a), ptr(b)], [ptr(y)], stream=stream())
-    return y
+    rc = capi.call("binary", p, [ptr(a), ptr(b)], [ptr(y)], stream=stream(), check=check)
+    return y if check else (rc, y)
 
 
 def unary(op, x):

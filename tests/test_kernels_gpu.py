@@ -203,6 +203,50 @@ def test_binary_unary_where_transpose():
     np.testing.assert_array_equal(ops.transpose(ops.dev(t[0, 0]), (1, 0)).cpu().numpy(), t[0, 0].T)
 
 
+UNARY_OPS = {0: (-3, 3), 1: (-1, 1), 2: (1, 6), 3: (-1, 1), 4: (-4, 4), 5: (-6, 6), 6: (-0.95, 0.95), 7: (-6, 6), 8: (-4, 4), 9: (-6, 6), 10: (-4, 4),
+             11: (-1.4, 1.4), 12: (-4, 4), 13: (-3, 3), 14: (0, 9), 15: (-8, 8), 16: (-3, 3), 17: (-3, 3), 19: (-7, 7), 20: (-6, 6)}
+
+
+@pytest.mark.parametrize("op", sorted(UNARY_OPS))
+def test_unary_every_reference_operator(op):
+    """Every SimpleUnaryType of the reference on fp32 (against float64 numpy at 2e-6 relative) and on fp16 (input rounded first,
+    result within the half tolerance); Not on bool."""
+    lo, hi = UNARY_OPS[op]
+    rng = np.random.default_rng(op)
+    x = rng.uniform(lo, hi, 4099).astype(np.float32)
+    np.testing.assert_allclose(ops.unary(op, ops.dev(x)).cpu().numpy(), onp.unary(op, x), rtol=2e-6, atol=2e-6)
+    xh = x.astype(np.float16)
+    close_half(ops.unary(op, torch.from_numpy(xh).cuda()), onp.unary(op, xh.astype(np.float32)))
+
+
+def test_unary_not_and_the_integer_and_bool_binary_operators():
+    rng = np.random.default_rng(3)
+    b1 = torch.from_numpy(rng.integers(0, 2, 1000).astype(np.bool_)).cuda()
+    b2 = torch.from_numpy(rng.integers(0, 2, 1000).astype(np.bool_)).cuda()
+    assert torch.equal(ops.unary(18, b1), ~b1)
+    for op, fn in ((5, torch.logical_and), (6, torch.logical_or), (7, torch.logical_xor)):
+        assert torch.equal(ops.binary(op, b1, b2), fn(b1, b2))
+    for dt in (torch.int32, torch.int64, torch.int8, torch.uint8, torch.int16):
+        lo = 0 if dt == torch.uint8 else -11
+        a = torch.from_numpy(rng.integers(lo, 12, (7, 33))).to(dt).cuda()
+        b = torch.from_numpy(rng.integers(1, 6, (33,))).to(dt).cuda()          # broadcast over the rows; no zero divisor
+        an, bn = a.cpu().numpy(), b.cpu().numpy()
+        for op in (0, 1, 2, 3, 8, 9):
+            got = ops.binary(op, a, b).cpu().numpy()
+            np.testing.assert_array_equal(got, onp.binary(op, an, bn).astype(an.dtype), err_msg=f"{dt} op {op}")
+        small = torch.from_numpy(rng.integers(0, 4, (33,))).to(dt).cuda()
+        two = torch.full((1,), 2, dtype=dt, device="cuda")
+        np.testing.assert_array_equal(ops.binary(4, two, small).cpu().numpy(), (2 ** small.cpu().numpy().astype(np.int64)).astype(an.dtype))
+    # float Pow and Fmod; pairs the library does not have are refused
+    x = torch.from_numpy(rng.uniform(0.5, 3, 2048).astype(np.float32)).cuda()
+    y = torch.from_numpy(rng.uniform(-2, 2, 2048).astype(np.float32)).cuda()
+    np.testing.assert_allclose(ops.binary(4, x, y).cpu().numpy(), np.power(x.cpu().numpy().astype(np.float64), y.cpu().numpy()), rtol=3e-6)
+    np.testing.assert_allclose(ops.binary(9, y, x).cpu().numpy(), np.fmod(y.cpu().numpy(), x.cpu().numpy()), rtol=1e-6, atol=1e-7)
+    assert ops.binary(5, x, y, check=False)[0] == capi.ERR_UNSUPPORTED      # And on floats
+    assert ops.binary(8, x, y, check=False)[0] == capi.ERR_UNSUPPORTED      # Mod on floats (Fmod is)
+    assert ops.binary(0, b1, b2, check=False)[0] == capi.ERR_UNSUPPORTED    # Add on bool
+
+
 # ---- RoPE ------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32] + HALF)
 def test_rope(dtype):
