@@ -137,7 +137,7 @@ struct TcWalk {
 
 // Persistent: CTA c computes tiles c, c + gridDim.x, ...  The accumulator is double-buffered in tensor memory (2 x BN
 // columns), so the epilogue of one tile (tcgen05.ld, conversion, stores) overlaps the MMA main loop of the next.
-template<class T, int BN, int STAGES>
+template<class T, int BN, int STAGES, bool PUSH = false>// PUSH: the epilogue that stores into the all-reduce slots is compiled in
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_b, const TcArgs a) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         // the all-reduce call this product feeds: its number stays put until the receiving kernel behind this one has run
         uint32_t ar_flag_v = 0;
         unsigned ar_q = 0;
-        if (a.push) {
+        if constexpr (PUSH) {
             const unsigned long long seq = *reinterpret_cast<const volatile unsigned long long *>(a.ar.mine);
             ar_flag_v = ar_flag(seq), ar_q = static_cast<unsigned>(seq & 1ull);
         }
@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                             for (int c = 0; c < BN / 4; ++c) acc[4 * c] += v[c].x, acc[4 * c + 1] += v[c].y, acc[4 * c + 2] += v[c].z, acc[4 * c + 3] += v[c].w;
                         }
                         swiglu_rows(acc, std::integral_constant<int, BN>{}, mt, n0);
-                    } else if (a.push) {
+                    } else if (PUSH) {
                         float acc[BN];
 #pragma unroll
                         for (int c = 0; c < BN; ++c) acc[c] = 0.f;
@@ -429,7 +429,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             }
             const uint32_t row = m0 + warp * 32 + lane;
             if constexpr (BN <= 64) {
-                if (a.push) {
+                if constexpr (PUSH) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 32) {
                         uint32_t r[32];
@@ -750,10 +750,10 @@ size_t gemm_tc_workspace(const rg_mat_mul_params *p) {
 // waits for a free stage 41 % of the time.  Leaving the activation-tile loads out altogether (timing only): 41.3 us.  What is
 // left is the fill and drain of the memory pipeline around the dependency on the previous kernel (~10 us per launch): the
 // TMA-only stream has no such dependency, so its launches overlap.
-template<class T, int BN, int STAGES>
+template<class T, int BN, int STAGES, bool PUSH = false>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
     constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
-    auto kern = gemm_tc_kernel<T, BN, STAGES>;
+    auto kern = gemm_tc_kernel<T, BN, STAGES, PUSH>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     // the whole shared-memory carve-out, so that a CTA of the next kernel can sit beside one of this kernel when both fit
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(cudaSharedmemCarveoutMaxShared)));
@@ -895,8 +895,8 @@ int gemm_tc_push(const rg_mat_mul_params *p, void *ws, const void *const *in, co
     a.push = peers.two_shot ? 2u : 1u, a.ar = peers;
     CUtensorMap ma, mb;
     if (!make_map(&ma, in[1], is_bf16, p->n, p->k, p->k, TC_BM) || !make_map(&mb, in[0], is_bf16, p->m, p->k, p->k, pl.bn)) return RG_ERR_CUDA;
-    if (pl.bn == 32) return is_bf16 ? tc_launch<__nv_bfloat16, 32, 8>(ma, mb, a, st) : tc_launch<__half, 32, 8>(ma, mb, a, st);
-    return is_bf16 ? tc_launch<__nv_bfloat16, 64, 8>(ma, mb, a, st) : tc_launch<__half, 64, 8>(ma, mb, a, st);
+    if (pl.bn == 32) return is_bf16 ? tc_launch<__nv_bfloat16, 32, 8, true>(ma, mb, a, st) : tc_launch<__half, 32, 8, true>(ma, mb, a, st);
+    return is_bf16 ? tc_launch<__nv_bfloat16, 64, 8, true>(ma, mb, a, st) : tc_launch<__half, 64, 8, true>(ma, mb, a, st);
 }
 
 int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st) {
