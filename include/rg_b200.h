@@ -460,8 +460,8 @@ int rg_b200_attn_decode_static(const rg_attn_decode_params *, const void *const 
  * One process per GPU.  rg_b200_comm_create allocates this rank's symmetric buffer and returns an opaque
  * 64-byte IPC handle; the caller exchanges handles out of band (any host transport) and calls
  * rg_b200_comm_connect with all ranks' handles.  The reduction is a push over NVLink peer memory with ordinary
- * stores (every 32-bit word travels with the call's 32-bit flag; the receiver polls its own memory): up to 4 ranks every
- * rank sends its whole input to every peer (one-shot); above that each run of chunks has an owner rank that combines
+ * stores (every 32-bit word travels with the call's 32-bit flag; the receiver polls its own memory): up to 3 ranks every
+ * rank sends its whole input to every peer (one-shot); from 4 ranks on each run of chunks has an owner rank that combines
  * and sends the finished values back (two-shot).  Values are combined in rank order, so every rank gets bit-identical
  * results.  No TMA and no multicast instruction touches peer memory.
  * dtype: RG_F32, RG_FP16, RG_BF16 (combined in fp32), RG_F64, RG_U8, RG_I8, RG_I32, RG_U32, RG_I64 (combined in their

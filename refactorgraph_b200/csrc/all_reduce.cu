@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_two_shot_kernel(const A
 // tensor-parallel decoder layer.  y = sum over ranks of x (+ res), n = y * rsqrt(mean(y^2) + eps) * w.  One CTA per row with
 // the thread / chunk assignment and the summation order of rms_norm_vec_kernel, so y and n carry the same bits as the
 // all-reduce kernel followed by the normalisation kernel.  The exchange is the one above: flag-in-data lines, one-shot up to
-// 4 ranks, owner-reduces-and-broadcasts beyond; a thread sends everything it has to send before it waits for anything.
+// 3 ranks, owner-reduces-and-broadcasts beyond; a thread sends everything it has to send before it waits for anything.
 struct ArNormArgs {
     ArArgs a;
     const void *w;
@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(AR_THREADS) all_reduce_norm_kernel(const ArNor
     // a thread waits for are polled together, so the wait costs one round trip to L2 and not one per line.
     bool ok = true;
     if constexpr (!TWO) {
-        constexpr int PEERS = 3;         // one-shot serves up to 4 ranks
+        constexpr int PEERS = 3;         // one-shot serves up to 4 ranks (the default uses it up to 3)
         constexpr int G = CH < 4 ? CH : 4;// chunks polled together (more would not fit the register file)
 #pragma unroll
         for (int i0 = 0; i0 < CH; i0 += G) {
@@ -693,7 +693,8 @@ int rg_b200_comm_destroy(rg_comm *c) {
 // every rank must take the same variant: it depends on the group size and on RG_B200_AR_ALGO (1 one-shot, 2 two-shot) only
 static bool comm_two_shot(const rg_comm *c) {
     static const int algo_env = std::getenv("RG_B200_AR_ALGO") ? atoi(std::getenv("RG_B200_AR_ALGO")) : 0;
-    return c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world > 4));
+    // measured on 4 GPUs, 256 KiB per rank: one-shot 14.7 us, two-shot 12.4 us (tensor-parallel step 15.20 vs 14.93 ms)
+    return c->world > 1 && (algo_env == 2 || (algo_env != 1 && c->world >= 4));
 }
 
 // x == nullptr: receive only (this rank's input already lies in its slots)

@@ -12,6 +12,10 @@ int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const
 bool gemm_tc_swiglu_small_shape(const rg_linear_params *p);
 size_t gemm_tc_swiglu_small_workspace(const rg_linear_params *p);
 int gemm_tc_swiglu_small(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st);
+// QKV split + RoPE + cache append on 5..64 tokens, same orientation (a 128-row tile = one head of head_dim 128)
+bool gemm_tc_qkv_rope_small_shape(const rg_linear_params *p);
+size_t gemm_tc_qkv_rope_small_workspace(const rg_linear_params *p);
+int gemm_tc_qkv_rope_small(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st);
 int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st);
 size_t gemm_tc_workspace(const rg_mat_mul_params *p);// split-K partials + arrival counters (zero before first use)
 // The product of up to 64 tokens whose 16-bit result goes, paired with the flag of the communicator's call in flight, into this

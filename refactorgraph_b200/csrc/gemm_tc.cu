@@ -319,6 +319,67 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             }
             asm volatile("bar.sync 2, 128;" ::: "memory");
         };
+        // QKV split + rotation + cache append with the weights on the A side: a tile of 128 rows is one head (head_dim 128), tile
+        // rows i and i + 64 are a rotation pair.  The upper half hands its values to the lower half, which rotates the pair with
+        // the token's angle and stores both results: into the q buffer, or into the K / V cache row of the token's position
+        // (checked against the layout; a bad position or block id skips the store and raises the index error).
+        auto rope_rows = [&](const float *v, auto width, uint32_t mt, uint32_t c_first) {
+            constexpr int W = decltype(width)::value;
+            const uint32_t trow = warp * 32 + lane, nkv = a.kv.n_kv_heads;
+            if (trow >= 64) {
+#pragma unroll
+                for (int j = 0; j < W; ++j) s_up[trow - 64][j] = v[j];
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (trow < 64 && mt < a.nq + 2 * nkv) {
+                const uint32_t gh = mt;
+                const bool is_q = gh < a.nq, rotate = gh < a.nq + nkv;
+                const uint32_t kvh = is_q ? 0u : (rotate ? gh - a.nq : gh - a.nq - nkv);
+                const float inv_freq = exp2f(-a.log2_theta * (2.0f * static_cast<float>(trow) / 128.0f));
+#pragma unroll 1
+                for (int j = 0; j < W; ++j) {
+                    const uint32_t tok = c_first + j;
+                    if (tok >= a.n) break;
+                    float lo = a.alpha * v[j], hi = a.alpha * s_up[trow][j];
+                    const int64_t p = a.pos[tok];
+                    if (rotate) {
+                        float sn, cs;
+                        sincosf(static_cast<float>(p) * inv_freq, &sn, &cs);
+                        const float r0 = lo * cs - hi * sn, r1 = hi * cs + lo * sn;
+                        lo = r0, hi = r1;
+                    }
+                    T *dst;
+                    if (is_q) {
+                        dst = static_cast<T *>(a.q_out) + (static_cast<uint64_t>(tok) * a.nq + gh) * 128u;
+                    } else {
+                        if (!kv_pos_ok(p, a.kv, a.table != nullptr)) {
+                            s_tc_index_error = 1;
+                            continue;
+                        }
+                        const uint32_t seq = a.tokens_per_seq > 1 ? tok / a.tokens_per_seq : tok;
+                        uint64_t cache_row;
+                        uint32_t head_pitch;
+                        if (a.table) {
+                            const uint32_t page = a.kv.page_size;
+                            const int32_t blk = a.table[static_cast<uint64_t>(seq) * a.kv.max_blocks_per_seq + static_cast<uint32_t>(p) / page];
+                            if (!kv_block_ok(blk, a.kv)) {
+                                s_tc_index_error = 1;
+                                continue;
+                            }
+                            cache_row = (static_cast<uint64_t>(blk) * nkv * page + static_cast<uint32_t>(p) % page) * 128u;
+                            head_pitch = page * 128u;
+                        } else {
+                            cache_row = (static_cast<uint64_t>(seq) * nkv * a.kv.max_seq + static_cast<uint64_t>(p)) * 128u;
+                            head_pitch = a.kv.max_seq * 128u;
+                        }
+                        dst = static_cast<T *>(rotate ? a.kc : a.vc) + cache_row + static_cast<uint64_t>(kvh) * head_pitch;
+                    }
+                    dst[trow] = Num<T>::from_f(lo);
+                    dst[trow + 64] = Num<T>::from_f(hi);
+                }
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+        };
         uint32_t local = 0;
         TcWalk walk;
         walk.init(a, tiles, kblocks);
@@ -375,6 +436,20 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                             for (int c = 0; c < BN / 4; ++c) acc[4 * c] += v[c].x, acc[4 * c + 1] += v[c].y, acc[4 * c + 2] += v[c].z, acc[4 * c + 3] += v[c].w;
                         }
                         swiglu_rows(acc, std::integral_constant<int, BN>{}, mt, n0);
+                    } else if (a.rope) {
+                        float acc[BN];
+#pragma unroll
+                        for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+#pragma unroll 2
+                        for (uint32_t sidx = 0; sidx < sg.ncontrib; ++sidx) {
+                            const float4 *src = reinterpret_cast<const float4 *>(base + static_cast<size_t>(sidx) * (TC_BM * BN));
+                            float4 v[BN / 4];
+#pragma unroll
+                            for (int c = 0; c < BN / 4; ++c) v[c] = __ldcg(src + c);
+#pragma unroll
+                            for (int c = 0; c < BN / 4; ++c) acc[4 * c] += v[c].x, acc[4 * c + 1] += v[c].y, acc[4 * c + 2] += v[c].z, acc[4 * c + 3] += v[c].w;
+                        }
+                        rope_rows(acc, std::integral_constant<int, BN>{}, mt, n0);
                     } else if (PUSH) {
                         float acc[BN];
 #pragma unroll
@@ -444,7 +519,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
                     continue;
                 }
-                if (a.swiglu) {
+                if (a.swiglu || a.rope) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 32) {
                         uint32_t r[32];
@@ -453,7 +528,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                        swiglu_rows(v, std::integral_constant<int, 32>{}, mt, n0 + c0);
+                        if (a.swiglu) swiglu_rows(v, std::integral_constant<int, 32>{}, mt, n0 + c0);
+                        else
+                            rope_rows(v, std::integral_constant<int, 32>{}, mt, n0 + c0);
                     }
                     tc_fence_before();
                     __syncwarp();
@@ -897,6 +974,43 @@ int gemm_tc_push(const rg_mat_mul_params *p, void *ws, const void *const *in, co
     if (!make_map(&ma, in[1], is_bf16, p->n, p->k, p->k, TC_BM) || !make_map(&mb, in[0], is_bf16, p->m, p->k, p->k, pl.bn)) return RG_ERR_CUDA;
     if (pl.bn == 32) return is_bf16 ? tc_launch<__nv_bfloat16, 32, 8, true>(ma, mb, a, st) : tc_launch<__half, 32, 8, true>(ma, mb, a, st);
     return is_bf16 ? tc_launch<__nv_bfloat16, 64, 8, true>(ma, mb, a, st) : tc_launch<__half, 64, 8, true>(ma, mb, a, st);
+}
+
+// The same for the QKV projection with its split / rotation / cache-append epilogue on 5..64 tokens (a 128-row tile = one head).
+static rg_mat_mul_params qkv_small_as_mat_mul(const rg_linear_params *p) { return swiglu_small_as_mat_mul(p); }
+bool gemm_tc_qkv_rope_small_shape(const rg_linear_params *p) {
+    const uint32_t nq = p->n_heads, nkv = p->kv.n_kv_heads;
+    return (p->dtype == RG_FP16 || p->dtype == RG_BF16) && p->epilogue == 3 && p->prologue == 0 && p->m > 4 && p->m <= 64 && p->kv.head_dim == 128 &&
+           nq > 0 && nkv > 0 && p->n == (nq + 2 * nkv) * 128u && p->k % 8 == 0 && p->k >= 64 && p->theta > 0.f && encode_fn() != nullptr;
+}
+size_t gemm_tc_qkv_rope_small_workspace(const rg_linear_params *p) {
+    const rg_mat_mul_params mp = qkv_small_as_mat_mul(p);
+    return gemm_tc_workspace(&mp);
+}
+int gemm_tc_qkv_rope_small(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st) {
+    if (!gemm_tc_qkv_rope_small_shape(p)) return RG_ERR_SHAPE;
+    if (!in[0] || !in[1] || !in[4] || !out[0] || !out[1] || !out[2]) return RG_ERR_NULL;
+    if (in[5] && p->kv.page_size == 0) return RG_ERR_SHAPE;
+    if (!aligned16(in[0]) || !aligned16(in[1])) return RG_ERR_ALIGN;
+    const rg_mat_mul_params mp = qkv_small_as_mat_mul(p);
+    const TcPlan pl = tc_plan(&mp);
+    if (!pl.swap) return RG_ERR_SHAPE;
+    if (pl.splits > 1 && !ws) return RG_ERR_NULL;
+    const int is_bf16 = p->dtype == RG_BF16;
+    TcArgs a = {};
+    a.alpha = 1.f, a.beta = 0.f, a.is_bf16 = is_bf16, a.k = p->k;
+    a.m = p->n, a.n = p->m;// kernel rows = output features (a tile = a head), kernel columns = tokens
+    a.splits = pl.splits, a.streamk = pl.streamk_grid;
+    a.counter = static_cast<unsigned *>(ws);
+    a.partial = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + pl.counter_bytes);
+    a.early = 1;
+    a.rope = 1, a.nq = p->n_heads, a.tokens_per_seq = p->tokens_per_seq, a.log2_theta = log2f(p->theta);
+    a.pos = static_cast<const int64_t *>(in[4]), a.table = static_cast<const int32_t *>(in[5]);
+    a.q_out = out[0], a.kc = out[1], a.vc = out[2], a.kv = p->kv;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, in[1], is_bf16, p->n, p->k, p->k, TC_BM) || !make_map(&mb, in[0], is_bf16, p->m, p->k, p->k, pl.bn)) return RG_ERR_CUDA;
+    if (pl.bn == 32) return is_bf16 ? tc_launch<__nv_bfloat16, 32, 8>(ma, mb, a, st) : tc_launch<__half, 32, 8>(ma, mb, a, st);
+    return is_bf16 ? tc_launch<__nv_bfloat16, 64, 8>(ma, mb, a, st) : tc_launch<__half, 64, 8>(ma, mb, a, st);
 }
 
 int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const *out, cudaStream_t st) {

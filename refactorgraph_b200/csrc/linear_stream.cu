@@ -415,18 +415,25 @@ static bool linear_is_tc_swiglu_small(const rg_linear_params *p) {
     const bool skinny_wins = p->m <= 16 && p->n <= 2560 && p->k >= 4096 && linear_skinny_shape(p->dtype, p->m, p->n, p->k);
     return !skinny_wins;
 }
+static bool linear_is_tc_qkv_small(const rg_linear_params *p) {
+    if (!gemm_tc_qkv_rope_small_shape(p)) return false;
+    const bool skinny_wins = p->m <= 16 && p->n <= 2560 && p->k >= 4096 && linear_skinny_shape(p->dtype, p->m, p->n, p->k);
+    return !skinny_wins;
+}
 static bool linear_is_skinny(const rg_linear_params *p) {
     return p->m > 4 && p->m <= 32 && p->prologue == 0 && linear_skinny_shape(p->dtype, p->m, p->n, p->k);
 }
 size_t rg_b200_linear_workspace(const rg_linear_params *p) {
     if (!p) return 0;
     if (linear_is_tc_swiglu_small(p)) return gemm_tc_swiglu_small_workspace(p);
+    if (linear_is_tc_qkv_small(p)) return gemm_tc_qkv_rope_small_workspace(p);
     if (!linear_is_skinny(p)) return 0;
     return linear_skinny_workspace(p->dtype, p->m, p->n, p->k, p->epilogue, &p->kv, p->n_heads);
 }
 int rg_b200_linear(const rg_linear_params *p, void *ws, const void *const *in, void *const *out, void *stream) {
     if (!p || !in || !out) return RG_ERR_NULL;
     if (linear_is_tc_swiglu_small(p)) return gemm_tc_swiglu_small(p, ws, in, out, static_cast<cudaStream_t>(stream));
+    if (linear_is_tc_qkv_small(p)) return gemm_tc_qkv_rope_small(p, ws, in, out, static_cast<cudaStream_t>(stream));
     if (linear_is_skinny(p)) {
         SkinnyCall c = {};
         c.dtype = p->dtype, c.m = p->m, c.n = p->n, c.k = p->k, c.epilogue = p->epilogue;

@@ -143,10 +143,25 @@ namespace refactor::computation {
                 if (c == NONE) return false;
                 auto &next = g.nodes[c];
                 if (x.shape[0] <= 64) {
-                    // 5..64 tokens: only the SiLU gate has a tensor-core epilogue (weights on the M side, gate rows in 64s)
-                    if (envOff("RG_B200_FUSE_GATE_SMALL")) return false;
-                    if (!as<Swiglu>(c) || w.shape[0] % 128 != 0 || x.shape[1] % 8 != 0 || x.shape[1] < 64) return false;
-                    node.op = linear(0, 2, 1e-5f);
+                    // 5..64 tokens (weights on the M side of the instruction): the SiLU gate (gate rows in 64s) and the QKV split +
+                    // rotation + append (a 128-row tile = one head) have tensor-core epilogues
+                    if (x.shape[1] % 8 != 0 || x.shape[1] < 64) return false;
+                    auto qs = as<QkvRopeAppend>(c);
+                    if (as<Swiglu>(c) && w.shape[0] % 128 == 0 && !envOff("RG_B200_FUSE_GATE_SMALL")) {
+                        node.op = linear(0, 2, 1e-5f);
+                    } else if (qs && next.inputs[0] == y && qs->headDim == 128 && w.shape[0] == (qs->nHeads + 2 * qs->nKVHeads) * 128 &&
+                               !envOff("RG_B200_FUSE_ROPE_SMALL")) {
+                        auto const &kc = tensor(next.inputs[next.inputs.size() - 2]);
+                        Attributes a;
+                        a["n_heads"] = static_cast<int64_t>(qs->nHeads), a["n_kv_heads"] = static_cast<int64_t>(qs->nKVHeads);
+                        a["head_dim"] = static_cast<int64_t>(qs->headDim), a["theta"] = static_cast<double>(qs->theta);
+                        a["page_size"] = static_cast<int64_t>(qs->pageSize), a["tokens_per_seq"] = static_cast<int64_t>(qs->tokensPerSeq);
+                        a["max_seq"] = static_cast<int64_t>(qs->pageSize ? 0 : kc.shape[2]);
+                        node.op = linear(0, 3, 1e-5f, a);
+                        node.inputs.insert(node.inputs.end(), next.inputs.begin() + 1, next.inputs.end());
+                    } else {
+                        return false;
+                    }
                 } else if (as<Swiglu>(c) && w.shape[0] % 256 == 0) {
                     node.op = linear(0, 2, 1e-5f);
                 } else if (auto qa = as<QkvRopeAppend>(c); qa && next.inputs[0] == y && qa->headDim == 128) {

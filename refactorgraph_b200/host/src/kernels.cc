@@ -537,7 +537,9 @@ namespace refactor::kernel {
             const bool skinny = x.shape[0] <= 32 && prologue == 0 && x.shape[1] % 128 == 0;
             // 5..64 tokens, SiLU gate: the tensor-core GEMM with the weights on the instruction's M side (gate rows in 64s)
             const bool gateSmall = x.shape[0] <= 64 && prologue == 0 && epilogue == 2 && w.shape[0] % 128 == 0 && x.shape[1] % 8 == 0 && x.shape[1] >= 64;
-            if (!skinny && !gateSmall && !(x.shape[0] > 64 && prologue == 0 && (qkv || gate))) return ans;
+            // ... and the QKV split + RoPE + cache append (a 128-row tile of the weights = one head)
+            const bool qkvSmall = x.shape[0] <= 64 && prologue == 0 && qkv && x.shape[1] % 8 == 0 && x.shape[1] >= 64;
+            if (!skinny && !gateSmall && !qkvSmall && !(x.shape[0] > 64 && prologue == 0 && (qkv || gate))) return ans;
         }
         rg_linear_params p{};
         p.tokens_per_seq = static_cast<uint32_t>(tokensPerSeq);

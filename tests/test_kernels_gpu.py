@@ -416,6 +416,46 @@ def test_linear_qkv_rope_append_many_tokens(dtype, paged, nq, nkv, seqs, S):
 
 
 @pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("paged", [False, True])
+@pytest.mark.parametrize("nq,nkv,m,k", [(32, 4, 16, 8192), (8, 8, 32, 512), (3, 1, 33, 1024), (24, 8, 64, 4096), (2, 2, 5, 64)])
+def test_linear_qkv_rope_append_few_tokens_on_tensor_cores(dtype, paged, nq, nkv, m, k):
+    """5..64 tokens, one token per sequence (a decode step): the weights sit on the M side of the tcgen05 instruction, a 128-row
+    tile is one head, the k range is split over CTAs; the upper half of a tile hands its sums to the lower half, which rotates
+    the pair and stores q / K / V where they belong."""
+    rng = np.random.default_rng(nq * 7 + nkv + m + k)
+    D = 128
+    n = (nq + 2 * nkv) * D
+    x = rnd16(rng.standard_normal((m, k)).astype(np.float32), dtype)
+    w = rnd16((0.03 * rng.standard_normal((n, k))).astype(np.float32), dtype)
+    pos = rng.integers(0, 100, (m,)).astype(np.int64)
+    q_want, k_want, v_want = onp.linear_fused(x, w, epilogue=3, n_heads=nq, n_kv=nkv, head_dim=D, positions=pos)
+    if paged:
+        page, max_blocks = 16, 8
+        n_blocks = m * max_blocks
+        table = rng.permutation(n_blocks).reshape(m, max_blocks).astype(np.int32)
+        kc = torch.zeros(n_blocks, nkv, page, D, dtype=dtype, device="cuda")
+        vc = torch.zeros_like(kc)
+        kv = ops.kv_layout(nkv, D, 0, page, max_blocks, n_blocks=n_blocks)
+        q = ops.linear(ops.dev(x, dtype), ops.dev(w, dtype), epilogue=3, n_heads=nq, kv=kv, positions=ops.dev(pos), table=ops.dev(table),
+                       k_cache=kc, v_cache=vc)
+        k_got = torch.stack([kc[table[i, pos[i] // page], :, pos[i] % page] for i in range(m)])
+        v_got = torch.stack([vc[table[i, pos[i] // page], :, pos[i] % page] for i in range(m)])
+    else:
+        max_seq = 128
+        kc = torch.zeros(m, nkv, max_seq, D, dtype=dtype, device="cuda")
+        vc = torch.zeros_like(kc)
+        kv = ops.kv_layout(nkv, D, max_seq)
+        q = ops.linear(ops.dev(x, dtype), ops.dev(w, dtype), epilogue=3, n_heads=nq, kv=kv, positions=ops.dev(pos), k_cache=kc, v_cache=vc)
+        k_got = torch.stack([kc[i, :, pos[i]] for i in range(m)])
+        v_got = torch.stack([vc[i, :, pos[i]] for i in range(m)])
+    close_half(q.reshape(m, nq, D), q_want)
+    close_half(k_got, k_want)
+    close_half(v_got, v_want)
+    assert int((kc != 0).sum()) <= m * nkv * D and int((vc != 0).sum()) <= m * nkv * D   # nothing else was touched
+    assert capi.load().rg_b200_error_state() == 0
+
+
+@pytest.mark.parametrize("dtype", HALF)
 @pytest.mark.parametrize("m,f,k", [(200, 256, 512), (65, 384, 64), (300, 128, 1024)])
 def test_linear_silu_gate_many_tokens(dtype, m, f, k):
     """More than 64 tokens: silu(gate) * up computed in the epilogue of the tcgen05 GEMM (a B tile pairs 128 gate rows
