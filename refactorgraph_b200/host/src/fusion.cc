@@ -150,7 +150,7 @@ namespace refactor::computation {
                     if (as<Swiglu>(c) && w.shape[0] % 128 == 0 && !envOff("RG_B200_FUSE_GATE_SMALL")) {
                         node.op = linear(0, 2, 1e-5f);
                     } else if (qs && next.inputs[0] == y && qs->headDim == 128 && w.shape[0] == (qs->nHeads + 2 * qs->nKVHeads) * 128 &&
-                               !envOff("RG_B200_FUSE_ROPE_SMALL")) {
+                               envOn("RG_B200_FUSE_ROPE_SMALL")) {// off by default: measured slower than the product + rotation kernel
                         auto const &kc = tensor(next.inputs[next.inputs.size() - 2]);
                         Attributes a;
                         a["n_heads"] = static_cast<int64_t>(qs->nHeads), a["n_kv_heads"] = static_cast<int64_t>(qs->nKVHeads);

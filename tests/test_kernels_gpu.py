@@ -417,11 +417,12 @@ def test_linear_qkv_rope_append_many_tokens(dtype, paged, nq, nkv, seqs, S):
 
 @pytest.mark.parametrize("dtype", HALF)
 @pytest.mark.parametrize("paged", [False, True])
-@pytest.mark.parametrize("nq,nkv,m,k", [(32, 4, 16, 8192), (8, 8, 32, 512), (3, 1, 33, 1024), (24, 8, 64, 4096), (2, 2, 5, 64)])
+@pytest.mark.parametrize("nq,nkv,m,k", [(32, 4, 16, 8200), (8, 8, 32, 520), (3, 1, 33, 1024), (24, 8, 64, 4096), (2, 2, 5, 64), (8, 8, 32, 512)])
 def test_linear_qkv_rope_append_few_tokens_on_tensor_cores(dtype, paged, nq, nkv, m, k):
-    """5..64 tokens, one token per sequence (a decode step): the weights sit on the M side of the tcgen05 instruction, a 128-row
-    tile is one head, the k range is split over CTAs; the upper half of a tile hands its sums to the lower half, which rotates
-    the pair and stores q / K / V where they belong."""
+    """5..64 tokens, one token per sequence (a decode step).  More than 32 tokens, or a k that is not a multiple of 128, take the
+    tcgen05 form: the weights sit on the M side of the instruction, a 128-row tile is one head, the k range is split over CTAs;
+    the upper half of a tile hands its sums to the lower half, which rotates the pair and stores q / K / V where they belong.
+    (The last case runs on the streaming skinny kernel: same contract.)"""
     rng = np.random.default_rng(nq * 7 + nkv + m + k)
     D = 128
     n = (nq + 2 * nkv) * D
