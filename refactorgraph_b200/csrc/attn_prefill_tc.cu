@@ -18,18 +18,21 @@
 //                        exact in fp32 and far inside the 16-bit range — so most tiles skip the rescaling altogether.
 // Keeping O in registers instead of in tensor memory avoids a read-modify-write of the accumulator whenever the maximum
 // changes; the price is one tcgen05.ld of the tile per key tile.
-// Measured on [4, 32, 2048, 128] bf16: 237.5 us = 579 TFLOP/s (the warp-level mma.sync kernel: 565 us = 243 TFLOP/s).  The steps:
+// Measured on [4, 32, 2048, 128] bf16: 208.4 us = 660 TFLOP/s (the warp-level mma.sync kernel: 565 us = 243 TFLOP/s).  The steps:
 // one row per thread (four softmax warps) 306 TFLOP/s on one sequence, two threads per row 392 (499 on four sequences); P and
 // O_tile double-buffered, so that tile j's second product runs under tile j + 1's exponentials (the accumulators take O_tile
 // two tiles late, times whatever rescaling happened in between): 523; persistent CTAs, one per SM, that fetch the next item's
 // Q / K / V under the current item's tail and set tensor memory and barriers up once: 563; items dealt back and forth over the
-// CTAs instead of round-robin (the heaviest CTA carries 119 key tiles instead of 125, the mean is 117.6): 579.  Keeping a
+// CTAs instead of round-robin (the heaviest CTA carries 119 key tiles instead of 125, the mean is 117.6): 579; the output staged
+// through shared memory and written two whole rows per instruction instead of 32 half rows: 660.  Keeping a
 // thread's 64 scores in registers between the maximum pass and the exponential pass (one tcgen05.ld round instead of two) spills
 // at the 168 registers a 320-thread CTA gets and measured 532.  A head-major item order (all query tiles of a head in flight
 // together, so that K / V come from L2: ncu shows 3.2 x the algorithmic bytes in DRAM traffic, 41 % of DRAM peak) measured 568:
 // the loads are not what the kernel waits for.  Cycle counters in a softmax warp, per key tile, before the
 // double buffering: ~1480 in the exponential pass (the special-function unit's 16 results per clock bound it at 1024), ~330
 // reading the scores for the maximum, ~200 in the pair exchange, ~190 adding O_tile, ~800 waiting for the tensor core.
+// Taking a quarter or half of the exponentials from a cubic on the FMA pipe instead of the special-function unit measured 556
+// and 539 (against 574 the same day): the pass is not bound by that unit alone.
 // Every wait is bounded; on expiry the kernel records an error word, releases its tensor memory and leaves.
 #include "tcgen05.cuh"
 #include <cstdlib>
@@ -411,18 +414,32 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
         // the next item's first tile writes its maxima into the same slot: both threads must have read the sums first; the two
         // warps also agree here on whether to go on
         const bool stop = at_pair_sync_or(1u + quarter, !ok || *failed != 0);
-        if (ok && qrow < a.S) {
+        if (stop) break;
+        // The output goes through shared memory: a thread owns half a row, so stores straight from its registers would touch 32
+        // lines per instruction (measured: ~2900 cycles per item, 9 % of the kernel).  Each thread writes its 128 bytes into its line
+        // of a P buffer (both are free: the item's last product has been read), swizzled like P; then the two warps of the lane
+        // quarter write the quarter's 32 rows, two whole rows per instruction.
+        {
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            T *dst = static_cast<T *>(a.o) + w.n * a.o_sn + w.h * a.o_sh + static_cast<int64_t>(qrow) * a.o_st + col0;
+            uint8_t *stage = sP + (t & 1u) * AT_TILE_BYTES;
+            uint8_t *line = stage + half * (AT_TILE_BYTES / 2) + row * 128u;
 #pragma unroll
             for (int d = 0; d < 64; d += 8) {
                 uint4 v;
                 v.x = at_pack2<T>(acc[d] * inv, acc[d + 1] * inv), v.y = at_pack2<T>(acc[d + 2] * inv, acc[d + 3] * inv);
                 v.z = at_pack2<T>(acc[d + 4] * inv, acc[d + 5] * inv), v.w = at_pack2<T>(acc[d + 6] * inv, acc[d + 7] * inv);
-                *reinterpret_cast<uint4 *>(dst + d) = v;
+                *reinterpret_cast<uint4 *>(line + (((d >> 3) ^ (row & 7u)) << 4)) = v;
             }
+            asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
+            T *base = static_cast<T *>(a.o) + w.n * a.o_sn + w.h * a.o_sh;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t idx = i * 64u + half * 32u + lane, r = quarter * 32u + (idx >> 4), ch = idx & 15u;
+                const uint4 v = *reinterpret_cast<const uint4 *>(stage + (ch >> 3) * (AT_TILE_BYTES / 2) + r * 128u + (((ch & 7u) ^ (r & 7u)) << 4));
+                if (q0 + r < a.S) *reinterpret_cast<uint4 *>(base + static_cast<int64_t>(q0 + r) * a.o_st + ch * 8u) = v;
+            }
+            // the next write into this buffer (the next item's first probabilities) comes after a barrier of the same two warps
         }
-        if (stop) break;
         }// items
     }
     tc_fence_before();
