@@ -203,6 +203,8 @@ def workload_name(w):
         return "Llama-7B-shaped fp16 batch-32 decode, paged KV (16-token blocks), lengths uniform[512,4096], top-k 50 sampling"
     if w == "70b-tp":
         return "70B-shaped GQA fp16 batch-16 decode at KV 4096, tensor-parallel (column/row-sharded weights, all-reduce after O and down)"
+    if w == "7b-prefill":
+        return "Llama-7B-shaped bf16 prefill of 4 sequences x 2048 tokens (causal attention, KV cache written, first token by top-1)"
     return "Llama-7B-shaped fp16 batch-1 greedy decode, KV cache prefilled to 2048 tokens, one token per step"
 
 

@@ -32,7 +32,13 @@
 // double buffering: ~1480 in the exponential pass (the special-function unit's 16 results per clock bound it at 1024), ~330
 // reading the scores for the maximum, ~200 in the pair exchange, ~190 adding O_tile, ~800 waiting for the tensor core.
 // Taking a quarter or half of the exponentials from a cubic on the FMA pipe instead of the special-function unit measured 556
-// and 539 (against 574 the same day): the pass is not bound by that unit alone.
+// and 539 (against 574 the same day): the pass is not bound by that unit alone.  Packed fp32 instructions (fma / add .f32x2) and
+// the three-input maximum in the softmax warps, a sixth fewer instructions: 647 against 646; the causal mask compiled out of the
+// tiles that need none: no change (the compiler had done it); both halves of a tile requested from tensor memory before one wait in
+// the maximum pass: 618 against 650.  What the counters show (ncu, two sequences): issue slots 51 % busy, the special-function
+// pipe 33 % over the kernel but ~75 % inside the exponential pass, where all eight softmax warps arrive together because one
+// barrier releases each tile's scores; spreading that pass out in time needs two query tiles per CTA on alternating phases, with
+// O kept in tensor memory to make room in the register file.
 // Every wait is bounded; on expiry the kernel records an error word, releases its tensor memory and leaves.
 #include "tcgen05.cuh"
 #include <cstdlib>
