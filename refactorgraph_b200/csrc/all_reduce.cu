@@ -10,7 +10,9 @@
 // results).  There is no fence, no separate flag and no barrier on the path: the latency is one NVLink store flight.
 // Parity s&1 is not rewritten before call s+2, which no rank starts before it has finished call s+1, whose data it sends
 // only after it has read everything of call s.  Measured for 256 KiB per rank: a pull design (remote flag polls and remote
-// loads) 26 / 49 us on 2 / 8 GPUs; push with a system fence and one flag per CTA 20 / 26 us.
+// loads) 26 / 49 us on 2 / 8 GPUs; push with a system fence and one flag per CTA 20 / 26 us; the sum formed inside NVSwitch
+// (multimem.ld_reduce + multimem.st on a multicast mapping, two flag barriers) 30 us on 2 GPUs, where this push takes 8.9: six
+// NVLink flights in a row instead of one.  Two-shot on 8 GPUs: 15.5 us.
 // No TMA and no multicast instructions touch peer memory.
 #include "gemm_dispatch.cuh"
 #include "ar_slots.cuh"
