@@ -288,5 +288,19 @@ inline cudaError_t launch_pdl(void (*kern)(K...), dim3 grid, dim3 block, size_t 
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, std::forward<A>(args)...);
 }
+// The same for a kernel whose CTAs form clusters of `cluster_x` consecutive CTAs (grid.x a multiple of it)
+template<class... K, class... A>
+inline cudaError_t launch_pdl_cluster(void (*kern)(K...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, unsigned cluster_x, A &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<A>(args)...);
+}
 
 }// namespace rg

@@ -102,11 +102,12 @@ struct TcSeg {
 struct TcWalk {
     uint32_t streamk, splits, kblocks, items, item, G;
     uint64_t U, u, u1;
-    __device__ __forceinline__ void init(const TcArgs &a, uint32_t tiles, uint32_t kblocks_) {
-        streamk = a.streamk, splits = a.splits, kblocks = kblocks_, G = gridDim.x;
-        items = tiles * a.splits, item = blockIdx.x;
+    // unit = what walks the tiles: a CTA, or a pair of CTAs (pair mode: unit index and count are halved)
+    __device__ __forceinline__ void init(const TcArgs &a, uint32_t tiles, uint32_t kblocks_, uint32_t unit = blockIdx.x, uint32_t units = gridDim.x) {
+        streamk = a.streamk, splits = a.splits, kblocks = kblocks_, G = units;
+        items = tiles * a.splits, item = unit;
         U = static_cast<uint64_t>(tiles) * kblocks_;
-        u = U * blockIdx.x / G, u1 = U * (blockIdx.x + 1) / G;
+        u = U * unit / G, u1 = U * (unit + 1) / G;
     }
     // CTA that owns unit x: the largest c with floor(U c / G) <= x
     __device__ __forceinline__ uint32_t owner(uint64_t x) const { return static_cast<uint32_t>(((x + 1) * G + U - 1) / U - 1); }
@@ -137,10 +138,18 @@ struct TcWalk {
 
 // Persistent: CTA c computes tiles c, c + gridDim.x, ...  The accumulator is double-buffered in tensor memory (2 x BN
 // columns), so the epilogue of one tile (tcgen05.ld, conversion, stores) overlaps the MMA main loop of the next.
-template<class T, int BN, int STAGES, bool PUSH = false>// PUSH: the epilogue that stores into the all-reduce slots is compiled in
+// PAIR: two CTAs (a cluster of two on neighbouring SMs) compute one 256 x BN tile with tcgen05 ... cta_group::2: each CTA loads its
+// 128 rows of A and HALF of the B tile, the even CTA issues the products for both, each CTA's tensor memory receives its 128 rows of
+// the accumulator and its epilogue warps store them.  Per SM and k-block that is 32 KiB from L2 instead of 48 for the same 128 x 256
+// outputs: the single-CTA kernel is bound by requests to L2 (ncu: 68 % of request cycles, tensor pipe 80 %; an extra L2 prefetch
+// per box made it 22 % slower).  No load is multicast.
+template<class T, int BN, int STAGES, bool PUSH = false, bool PAIR = false>// PUSH: the epilogue that stores into the all-reduce slots is compiled in
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                               const __grid_constant__ CUtensorMap tmap_b, const TcArgs a) {
-    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = (PAIR ? BN / 2 : BN) * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t ROWS = PAIR ? 2 * TC_BM : TC_BM;// rows of a tile
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;// 0 = the CTA that issues the products
+    const uint32_t unit = PAIR ? blockIdx.x >> 1 : blockIdx.x, units = PAIR ? gridDim.x >> 1 : gridDim.x;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // the swizzled tiles need 1024-byte alignment
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -152,7 +161,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     int *failed = reinterpret_cast<int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t m_tiles = (a.m + TC_BM - 1) / TC_BM, n_tiles = (a.n + BN - 1) / BN, tiles = m_tiles * n_tiles;
+    const uint32_t m_tiles = (a.m + ROWS - 1) / ROWS, n_tiles = (a.n + BN - 1) / BN, tiles = m_tiles * n_tiles;
     const uint32_t kblocks = (a.k + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -162,17 +171,23 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);// one arrival per epilogue warp
+            mbar_init(&acc_empty[b], PAIR ? 8 : 4);// one arrival per epilogue warp (pair mode: of both CTAs, on the even CTA's barrier)
         }
         *failed = 0;
         fence_mbar_init();
     }
     if (warp == 5) {
-        tmem_alloc(tmem_slot, 2 * BN);
-        tmem_relinquish();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(tmem_slot, 2 * BN);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 2 * BN);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync();// the partner's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // Programmatic dependent launch: everything up to here, and the first stages of a weight operand, overlap the previous
@@ -202,9 +217,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 }
             };
             TcWalk walk;
-            walk.init(a, tiles, kblocks);
+            walk.init(a, tiles, kblocks, unit, units);
             TcSeg sg;
-            if (a.early) {
+            if (!PAIR && a.early) {
                 // weight tiles of this CTA's first segment go in flight before the wait; their partner tiles follow after it
                 TcWalk peek = walk;
                 if (peek.next(sg)) {
@@ -238,6 +253,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                         good = false;
                         break;
                     }
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the even CTA's barrier, which its producer arms for the two of them
+                        const uint32_t bar = cluster_map(&full[s], 0);
+                        if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * STAGE_BYTES);
+                        tma_load_2d_pair(st, &tmap_a, kb * TC_BK, (mt * 2 + rank) * TC_BM, bar);
+                        const uint32_t brow = a.swiglu ? (rank ? a.swiglu + nt * 128 : nt * 128) : nt * BN + rank * (BN / 2);
+                        tma_load_2d_pair(st + A_BYTES, &tmap_b, kb * TC_BK, brow, bar);
+                        continue;
+                    }
                     mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
                     load_a(st, kb, mt, &full[s]);
                     load_b(st + A_BYTES, kb, nt, &full[s]);
@@ -245,12 +269,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             }
         }
     } else if (warp == 5) {
-        if (lane == 0) {
-            const uint32_t idesc = instr_desc(a.is_bf16, TC_BM, BN);
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = instr_desc(a.is_bf16, ROWS, BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
             TcWalk walk;
-            walk.init(a, tiles, kblocks);
+            walk.init(a, tiles, kblocks, unit, units);
             TcSeg sg;
             for (; ok && walk.next(sg); ++local) {
                 const uint32_t buf = local & 1u, kb0 = sg.kb0, kb1 = sg.kb1;
@@ -272,11 +296,19 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 #pragma unroll
                     for (int kk = 0; kk < TC_BK / 16; ++kk) {
                         const uint64_t ad = smem_desc_sw128(a_addr + kk * 32), bd = smem_desc_sw128(b_addr + kk * 32);
-                        tc_mma_f16(d_tmem, ad, bd, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+                        if constexpr (PAIR) tc_mma_f16_pair(d_tmem, ad, bd, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+                        else
+                            tc_mma_f16(d_tmem, ad, bd, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
                     }
-                    tc_commit(&empty[s]);// frees the stage once these MMAs have read it
+                    // frees the stage once these MMAs have read it (pair mode: in both CTAs)
+                    if constexpr (PAIR) tc_commit_pair(&empty[s], 3);
+                    else
+                        tc_commit(&empty[s]);
                 }
-                tc_commit(&acc_full[buf]);// this tile's accumulator is complete when it arrives
+                // this tile's accumulator is complete when it arrives
+                if constexpr (PAIR) tc_commit_pair(&acc_full[buf], 3);
+                else
+                    tc_commit(&acc_full[buf]);
             }
         }
     } else {
@@ -382,13 +414,19 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         };
         uint32_t local = 0;
         TcWalk walk;
-        walk.init(a, tiles, kblocks);
+        walk.init(a, tiles, kblocks, unit, units);
         TcSeg sg;
+        // hands an accumulator buffer back to the thread that issues the products (pair mode: in the even CTA)
+        auto release_acc = [&](uint32_t buf) {
+            if constexpr (PAIR) mbar_arrive_cluster(cluster_map(&acc_empty[buf], 0));
+            else
+                mbar_arrive(&acc_empty[buf]);
+        };
         for (; walk.next(sg); ++local) {
             uint32_t mt, nt;
             const uint32_t tile = sg.tile, ks = sg.ord;
             tile_coords(tile, m_tiles, n_tiles, mt, nt);
-            const uint32_t buf = local & 1u, m0 = mt * TC_BM, n0 = nt * BN;
+            const uint32_t buf = local & 1u, m0 = PAIR ? (mt * 2 + rank) * TC_BM : mt * TC_BM, n0 = nt * BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1u)) {
                 *failed = 3;
                 break;
@@ -409,7 +447,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (lane == 0) release_acc(buf);
                 // the barrier orders the 128 threads' stores before thread 0's release-increment (cumulative at gpu scope)
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (threadIdx.x == 0) {
@@ -516,7 +554,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) release_acc(buf);
                     continue;
                 }
                 if (a.swiglu || a.rope) {
@@ -534,7 +572,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) release_acc(buf);
                     continue;
                 }
             }
@@ -567,7 +605,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) release_acc(buf);
                     continue;
                 }
             }
@@ -647,7 +685,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) release_acc(buf);
                     continue;
                 }
             }
@@ -694,14 +732,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             // hand the accumulator buffer back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) release_acc(buf);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync();// the partner has read its accumulators and received every arrival meant for it
     if (warp == 5) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * BN);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+        else
+            tmem_dealloc(tmem_base, 2 * BN);
     }
     if (threadIdx.x == 0 && *failed) atomicExch(&s_tc_error, *failed);
 }
@@ -842,6 +883,26 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs 
     return launch_status();
 }
 
+// Pair mode: clusters of two CTAs, one 256 x BN tile per pair (B's tensor map has boxes of BN / 2 rows).  RG_B200_GEMM_PAIR=0 keeps
+// the single-CTA kernel.
+static bool tc_pair_enabled() {
+    static const bool on = !(std::getenv("RG_B200_GEMM_PAIR") && std::getenv("RG_B200_GEMM_PAIR")[0] == '0');
+    return on;
+}
+template<class T>
+static int tc_launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
+    constexpr int BN = 256, STAGES = 6;
+    constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + (BN / 2) * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    auto kern = gemm_tc_kernel<T, BN, STAGES, false, true>;
+    RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    const uint32_t items = ((a.n + BN - 1) / BN) * ((a.m + 2 * TC_BM - 1) / (2 * TC_BM));
+    const uint32_t pairs = static_cast<uint32_t>(sm_count()) / 2;
+    const uint32_t grid = 2 * (items < pairs ? items : pairs);
+    RG_CHECK_CUDA(launch_pdl_cluster(kern, dim3(grid), dim3(TC_THREADS), smem, st, 2u, ma, mb, a));
+    count_launch();
+    return launch_status();
+}
+
 int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *const *out, cudaStream_t st) {
     const int is_bf16 = p->dtype == RG_BF16;
     const size_t es = 2;
@@ -867,6 +928,12 @@ int gemm_tc(const rg_mat_mul_params *p, void *ws, const void *const *in, void *c
             a.early = (p->flags & RG_MM_B_STATIC) ? 2u : 0u;
             a.Y = Y, a.y_row_stride = p->n, a.y_col_stride = 1;
             a.C = C, a.c_row_stride = p->bias_row_stride, a.c_col_stride = p->bias_col_stride;
+            if (bn == 256 && pl.splits == 1 && !pl.streamk_grid && p->m >= 512 && tc_pair_enabled()) {
+                if (!make_map(&ma, A, is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, B, is_bf16, p->n, p->k, p->k, 128)) return RG_ERR_CUDA;
+                const int rc = is_bf16 ? tc_launch_pair<__nv_bfloat16>(ma, mb, a, st) : tc_launch_pair<__half>(ma, mb, a, st);
+                if (rc != RG_OK) return rc;
+                continue;
+            }
             if (!make_map(&ma, A, is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, B, is_bf16, p->n, p->k, p->k, bn)) return RG_ERR_CUDA;
         } else {
             bn = p->m <= 32 ? 32 : 64;

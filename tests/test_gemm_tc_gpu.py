@@ -41,6 +41,26 @@ def test_against_numpy_oracle(dtype, m, n, k):
 
 
 @pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("m,n,k", [(512, 256, 64), (1024, 768, 512), (600, 300, 200), (513, 1000, 4096), (2050, 256, 1032)])
+def test_pairs_of_ctas(dtype, m, n, k):
+    """512 rows and 256 columns or more: two CTAs share a 256 x 256 tile (tcgen05 ... cta_group::2), ragged edges included;
+    with a residual, alpha and beta; the second call must give the same bits."""
+    rng = np.random.default_rng(m * 7 + n + k)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
+    b = torch.from_numpy((0.05 * rng.standard_normal((n, k))).astype(np.float32)).to(dtype)
+    c = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(dtype)
+    y = ops.mat_mul(a.cuda(), b.cuda(), trans_b=True, force=3)
+    assert _ok()
+    want = onp.mat_mul(a.float().numpy(), b.float().numpy(), trans_b=True)
+    np.testing.assert_allclose(y.float().cpu().numpy(), want, atol=2e-2, rtol=1e-2)
+    y2 = ops.mat_mul(a.cuda(), b.cuda(), c.cuda(), trans_b=True, alpha=0.5, beta=2.0, force=3)
+    assert _ok()
+    want2 = onp.mat_mul(a.float().numpy(), b.float().numpy(), c.float().numpy(), trans_b=True, alpha=0.5, beta=2.0)
+    np.testing.assert_allclose(y2.float().cpu().numpy(), want2, atol=4e-2, rtol=1e-2)
+    assert torch.equal(y, ops.mat_mul(a.cuda(), b.cuda(), trans_b=True, force=3))
+
+
+@pytest.mark.parametrize("dtype", HALF)
 def test_alpha_beta_bias_and_batch(dtype):
     rng = np.random.default_rng(7)
     a = torch.from_numpy(rng.standard_normal((3, 130, 128)).astype(np.float32)).to(dtype)
