@@ -973,7 +973,9 @@ int gemm_tc_qkv_rope(const rg_linear_params *p, const void *const *in, void *con
     a.pos = static_cast<const int64_t *>(in[4]), a.table = static_cast<const int32_t *>(in[5]);
     a.q_out = out[0], a.kc = out[1], a.vc = out[2], a.kv = p->kv;
     CUtensorMap ma, mb;
-    if (!make_map(&ma, in[0], is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, in[1], is_bf16, p->n, p->k, p->k, 256)) return RG_ERR_CUDA;
+    const bool pair = p->m >= 512 && tc_pair_enabled();// a pair of CTAs per 256-token tile: each loads half of the B tile
+    if (!make_map(&ma, in[0], is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, in[1], is_bf16, p->n, p->k, p->k, pair ? 128 : 256)) return RG_ERR_CUDA;
+    if (pair) return is_bf16 ? tc_launch_pair<__nv_bfloat16>(ma, mb, a, st) : tc_launch_pair<__half>(ma, mb, a, st);
     return is_bf16 ? tc_launch<__nv_bfloat16, 256, 4>(ma, mb, a, st) : tc_launch<__half, 256, 4>(ma, mb, a, st);
 }
 
@@ -1095,6 +1097,8 @@ int gemm_tc_swiglu(const rg_linear_params *p, const void *const *in, void *const
     a.Y = out[0], a.y_row_stride = f, a.y_col_stride = 1;
     CUtensorMap ma, mb;
     if (!make_map(&ma, in[0], is_bf16, p->m, p->k, p->k, TC_BM) || !make_map(&mb, in[1], is_bf16, p->n, p->k, p->k, 128)) return RG_ERR_CUDA;
+    // pair mode: the even CTA of a pair loads the tile's gate rows, the odd one its up rows
+    if (p->m >= 512 && tc_pair_enabled()) return is_bf16 ? tc_launch_pair<__nv_bfloat16>(ma, mb, a, st) : tc_launch_pair<__half>(ma, mb, a, st);
     return is_bf16 ? tc_launch<__nv_bfloat16, 256, 4>(ma, mb, a, st) : tc_launch<__half, 256, 4>(ma, mb, a, st);
 }
 

@@ -375,7 +375,7 @@ def test_linear_qkv_rope_append(dtype, paged, nq, nkv, m):
 
 @pytest.mark.parametrize("dtype", HALF)
 @pytest.mark.parametrize("paged", [False, True])
-@pytest.mark.parametrize("nq,nkv,seqs,S", [(4, 2, 2, 96), (3, 1, 1, 130), (2, 2, 3, 70)])
+@pytest.mark.parametrize("nq,nkv,seqs,S", [(4, 2, 2, 96), (3, 1, 1, 130), (2, 2, 3, 70), (3, 1, 2, 300), (4, 4, 1, 513)])  # 512 tokens and more: CTA pairs
 def test_linear_qkv_rope_append_many_tokens(dtype, paged, nq, nkv, seqs, S):
     """More than 64 tokens (prefill): the same operator runs on the tcgen05 GEMM and splits, rotates and appends in its
     epilogue.  Token t belongs to sequence t // S; an odd head count leaves the last 256-column tile half empty."""
@@ -389,7 +389,7 @@ def test_linear_qkv_rope_append_many_tokens(dtype, paged, nq, nkv, seqs, S):
     q_want, k_want, v_want = onp.linear_fused(x, w, epilogue=3, n_heads=nq, n_kv=nkv, head_dim=D, positions=pos)
     seq_of = np.arange(m) // S
     if paged:
-        page, max_blocks = 16, 16
+        page, max_blocks = 16, max(16, (S + 40 + 15) // 16)
         n_blocks = seqs * max_blocks
         table = rng.permutation(n_blocks).reshape(seqs, max_blocks).astype(np.int32)
         kc = torch.zeros(n_blocks, nkv, page, D, dtype=dtype, device="cuda")
@@ -400,7 +400,7 @@ def test_linear_qkv_rope_append_many_tokens(dtype, paged, nq, nkv, seqs, S):
         k_got = torch.stack([kc[table[seq_of[i], pos[i] // page], :, pos[i] % page] for i in range(m)])
         v_got = torch.stack([vc[table[seq_of[i], pos[i] // page], :, pos[i] % page] for i in range(m)])
     else:
-        max_seq = 256
+        max_seq = max(256, S + 40)
         kc = torch.zeros(seqs, nkv, max_seq, D, dtype=dtype, device="cuda")
         vc = torch.zeros_like(kc)
         kv = ops.kv_layout(nkv, D, max_seq)
@@ -457,7 +457,7 @@ def test_linear_qkv_rope_append_few_tokens_on_tensor_cores(dtype, paged, nq, nkv
 
 
 @pytest.mark.parametrize("dtype", HALF)
-@pytest.mark.parametrize("m,f,k", [(200, 256, 512), (65, 384, 64), (300, 128, 1024)])
+@pytest.mark.parametrize("m,f,k", [(200, 256, 512), (65, 384, 64), (300, 128, 1024), (512, 256, 256), (700, 384, 1024)])  # 512 tokens and more: CTA pairs
 def test_linear_silu_gate_many_tokens(dtype, m, f, k):
     """More than 64 tokens: silu(gate) * up computed in the epilogue of the tcgen05 GEMM (a B tile pairs 128 gate rows
     with their 128 up rows)."""
