@@ -14,6 +14,7 @@
 // The accumulator is double-buffered in tensor memory (2 x BN columns, acc_full[] / acc_empty[] mbarriers), so a tile's
 // epilogue overlaps the next tile's main loop.  Warp 5 also allocates and frees the TMEM columns.  Every mbarrier wait is bounded; on expiry the CTA records
 // an error word, still frees its tensor memory and exits.
+// Products of 512 rows and more run on CTA pairs (template flag PAIR, tcgen05 ... cta_group::2): see the comment above the kernel.
 #include "gemm_dispatch.cuh"
 #include "tcgen05.cuh"
 #include "ar_slots.cuh"
@@ -42,6 +43,7 @@ struct TcArgs {
     uint32_t streamk;  // != 0: CTA c owns the contiguous run [U c / G, U (c+1) / G) of the U = tiles * kblocks (tile, k-block) units
     float *partial;    // [tiles][splits][128][BN] fp32, used when splits > 1
     unsigned *counter; // [tiles] arrival counters, zero before the first call and left at zero
+    uint32_t group_m;  // row tiles per group of the tile order
     uint32_t early;    // operand that no earlier kernel of the stream writes (a weight): 1 = A, 2 = B, 0 = neither
     // QKV epilogue (rope != 0): columns are [q heads | k heads | v heads] of head_dim 128, rows are tokens; q is rotated into
     // q_out[token, nq * 128], k rotated and v copied into the caches at pos[token] of sequence token / tokens_per_seq
@@ -84,10 +86,10 @@ __device__ __forceinline__ void tc_push_value(const TcArgs &a, uint32_t flag, un
 // Tile order: groups of TC_GROUP_M row tiles are walked column by column, so the CTAs running at the same time share
 // a few A row-panels and B column-panels in L2 instead of streaming all of B once per row tile.
 constexpr uint32_t TC_GROUP_M = 16;
-__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t m_tiles, uint32_t n_tiles, uint32_t &mt, uint32_t &nt) {
-    const uint32_t per_group = TC_GROUP_M * n_tiles;
-    const uint32_t grp = t / per_group, first = grp * TC_GROUP_M;
-    const uint32_t rows = m_tiles - first < TC_GROUP_M ? m_tiles - first : TC_GROUP_M;
+__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t m_tiles, uint32_t n_tiles, uint32_t &mt, uint32_t &nt, uint32_t group_m = TC_GROUP_M) {
+    const uint32_t per_group = group_m * n_tiles;
+    const uint32_t grp = t / per_group, first = grp * group_m;
+    const uint32_t rows = m_tiles - first < group_m ? m_tiles - first : group_m;
     const uint32_t r = t - grp * per_group;
     mt = first + r % rows;
     nt = r / rows;
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 TcWalk peek = walk;
                 if (peek.next(sg)) {
                     uint32_t mt, nt;
-                    tile_coords(sg.tile, m_tiles, n_tiles, mt, nt);
+                    tile_coords(sg.tile, m_tiles, n_tiles, mt, nt, a.group_m);
                     for (uint32_t kb = sg.kb0; kb < sg.kb1 && pre < STAGES; ++kb, ++pre) {
                         mbar_arrive_expect_tx(&full[pre], STAGE_BYTES);
                         uint8_t *st = smem + pre * STAGE_BYTES;
@@ -238,7 +240,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             bool good = true;
             while (good && walk.next(sg)) {
                 uint32_t mt, nt;
-                tile_coords(sg.tile, m_tiles, n_tiles, mt, nt);
+                tile_coords(sg.tile, m_tiles, n_tiles, mt, nt, a.group_m);
                 for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     uint8_t *st = smem + s * STAGE_BYTES;
@@ -425,7 +427,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         for (; walk.next(sg); ++local) {
             uint32_t mt, nt;
             const uint32_t tile = sg.tile, ks = sg.ord;
-            tile_coords(tile, m_tiles, n_tiles, mt, nt);
+            tile_coords(tile, m_tiles, n_tiles, mt, nt, a.group_m);
             const uint32_t buf = local & 1u, m0 = PAIR ? (mt * 2 + rank) * TC_BM : mt * TC_BM, n0 = nt * BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1u)) {
                 *failed = 3;
@@ -869,7 +871,9 @@ size_t gemm_tc_workspace(const rg_mat_mul_params *p) {
 // left is the fill and drain of the memory pipeline around the dependency on the previous kernel (~10 us per launch): the
 // TMA-only stream has no such dependency, so its launches overlap.
 template<class T, int BN, int STAGES, bool PUSH = false>
-static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
+static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a_in, cudaStream_t st) {
+    TcArgs a = a_in;
+    a.group_m = TC_GROUP_M;
     constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<T, BN, STAGES, PUSH>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -890,8 +894,10 @@ static bool tc_pair_enabled() {
     return on;
 }
 template<class T>
-static int tc_launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a, cudaStream_t st) {
+static int tc_launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &a_in, cudaStream_t st) {
     constexpr int BN = 256, STAGES = 6;
+    TcArgs a = a_in;
+    a.group_m = TC_GROUP_M;// of 256-row tiles; measured on 8192 x 12288 x 4096: 4 / 8 / 16 / 32 row tiles per group 577 / 557 / 550 / 605 us
     constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + (BN / 2) * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<T, BN, STAGES, false, true>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
