@@ -902,7 +902,25 @@ static int tc_launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const Tc
     auto kern = gemm_tc_kernel<T, BN, STAGES, false, true>;
     RG_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const uint32_t items = ((a.n + BN - 1) / BN) * ((a.m + 2 * TC_BM - 1) / (2 * TC_BM));
-    const uint32_t pairs = static_cast<uint32_t>(sm_count()) / 2;
+    // as many pairs as the device can hold at once (asked once per device; half the SM count where the question fails)
+    static int resident[64] = {};
+    int dev = 0;
+    RG_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && resident[dev] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(sm_count()) & ~1u), cfg.blockDim = dim3(TC_THREADS), cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = sm_count() / 2;
+        }
+        resident[dev] = n;
+    }
+    const uint32_t pairs = static_cast<uint32_t>(dev >= 0 && dev < 64 ? resident[dev] : sm_count() / 2);
     const uint32_t grid = 2 * (items < pairs ? items : pairs);
     RG_CHECK_CUDA(launch_pdl_cluster(kern, dim3(grid), dim3(TC_THREADS), smem, st, 2u, ma, mb, a));
     count_launch();
