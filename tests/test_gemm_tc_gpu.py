@@ -61,6 +61,19 @@ def test_pairs_of_ctas(dtype, m, n, k):
 
 
 @pytest.mark.parametrize("dtype", HALF)
+def test_pairs_of_ctas_bias_vector_and_batch(dtype):
+    """The pair kernel behind the batched call with a broadcast bias row (element-wise loads of C)."""
+    rng = np.random.default_rng(11)
+    a = torch.from_numpy(rng.standard_normal((2, 520, 128)).astype(np.float32)).to(dtype)
+    b = torch.from_numpy((0.1 * rng.standard_normal((2, 264, 128))).astype(np.float32)).to(dtype)
+    c = torch.from_numpy(rng.standard_normal((264,)).astype(np.float32)).to(dtype)
+    y = ops.mat_mul(a.cuda(), b.cuda(), c.cuda(), trans_b=True, alpha=0.5, beta=2.0, force=3)
+    assert _ok()
+    want = onp.mat_mul(a.float().numpy(), b.float().numpy(), c.float().numpy(), trans_b=True, alpha=0.5, beta=2.0)
+    np.testing.assert_allclose(y.float().cpu().numpy(), want, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", HALF)
 def test_alpha_beta_bias_and_batch(dtype):
     rng = np.random.default_rng(7)
     a = torch.from_numpy(rng.standard_normal((3, 130, 128)).astype(np.float32)).to(dtype)
