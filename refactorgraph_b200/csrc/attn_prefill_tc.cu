@@ -457,6 +457,365 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
     if (threadIdx.x == 0 && *failed) atomicExch(&s_attn_tc_error, *failed);
 }
 
+// ---- Two query tiles per CTA ---------------------------------------------------------------------------------------------------
+// With the softmax warps of the kernel above doing nothing at all, a launch still takes 176 of its 215 us: what bounds it is the
+// stream of K / V tiles (every 128 query rows pull all the keys below their diagonal through L2: 1.14 GB per launch on
+// [4, 32, 2048, 128], 3.2 x the algorithmic bytes from HBM), not the softmax.  Here a CTA owns 256 query rows of one (sequence, head):
+// two groups of eight softmax warps (group g = rows 128 g .. 128 g + 127, two threads per row) share every K / V tile, which halves
+// that stream, and take turns on the tensor core: S_g = Q_g K^T into the group's 128 score columns of tensor memory, online softmax
+// as above, P written 16-bit OVER the scores the writer has read (two keys per 32-bit column), O_g += P V with the A operand taken
+// from tensor memory (P never crosses shared memory) and O_g accumulated in tensor memory (columns 256 + 128 g ..), rescaled in
+// place only when the group's reference maximum moves.  Per group the chain is serial (S, softmax, P V, next S: the next scores
+// overwrite P), the two groups overlap each other.  No exchange between the groups; each thread finishes its own half row.
+constexpr int AT2_SW = 16, AT2_THREADS = (AT2_SW + 2) * 32;
+constexpr uint32_t AT2_STAGE_BYTES = 16384;// per group: 128 rows x 64 d columns of 16-bit output
+
+struct At2Item {
+    uint32_t q0, h, n, kvh, ntiles[2], nt;// key tiles group 0 / 1 walk (group 1's rows lie 128 further down); nt = the larger
+};
+__device__ __forceinline__ At2Item at2_item(const AttnTcArgs &a, uint32_t qp_tiles, uint32_t i) {
+    const uint32_t hn = a.n_heads * a.batch, qp = qp_tiles - 1 - i / hn, r = i % hn;
+    At2Item it;
+    it.q0 = qp * 2 * AT_BM, it.h = r % a.n_heads, it.n = r / a.n_heads;
+    it.kvh = it.h / (a.n_heads / a.n_kv);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const uint32_t first = it.q0 + g * AT_BM;// a group whose rows all lie behind the sequence has nothing to do
+        const uint32_t last_key = first + AT_BM < a.kv_len ? first + AT_BM : a.kv_len;
+        it.ntiles[g] = first < a.S ? (last_key + AT_BN - 1) / AT_BN : 0u;
+    }
+    it.nt = it.ntiles[0] > it.ntiles[1] ? it.ntiles[0] : it.ntiles[1];
+    return it;
+}
+// OR over the 256 threads of a group (barrier 10 + g)
+__device__ __forceinline__ bool at2_group_sync_or(uint32_t g, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 q, %2, 0;\n"
+        "bar.red.or.pred p, %1, 256, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r)
+        : "r"(10u + g), "r"(pred ? 1u : 0u)
+        : "memory");
+    return r != 0;
+}
+
+template<class T>
+__global__ void __launch_bounds__(AT2_THREADS, 1) attn_prefill_q2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                                                        const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t *sQ = smem;                          // 2 x 32 KiB: group 0's and group 1's query rows
+    uint8_t *sK = sQ + 2 * AT_TILE_BYTES;        // 2 x 32 KiB
+    uint8_t *sV = sK + 2 * AT_TILE_BYTES;        // 2 x 32 KiB
+    uint8_t *sO = sV + 2 * AT_TILE_BYTES;        // 2 x 16 KiB: output staging of group 0 / 1
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sO + 2 * AT2_STAGE_BYTES);
+    uint64_t *q_full = bars, *q_empty = bars + 1, *k_full = bars + 2, *k_empty = bars + 4, *v_full = bars + 6, *v_empty = bars + 8;
+    uint64_t *s_full = bars + 10, *p_full = bars + 12, *o_full = bars + 14, *o_free = bars + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
+    volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *xch = reinterpret_cast<float *>(bars + 19);// [2 groups][2 halves][128 rows]: half-row maxima of the tile in flight, then the sums
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicExch(&s_attn_tc_error, 5);
+        return;
+    }
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t qp_tiles = (a.S + 2 * AT_BM - 1) / (2 * AT_BM);
+    const uint32_t n_items = qp_tiles * a.n_heads * a.batch;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1), mbar_init(q_empty, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1), mbar_init(&p_full[s], AT2_SW / 2);
+            mbar_init(&o_full[s], 1), mbar_init(&o_free[s], AT2_SW / 2);
+        }
+        *failed = 0;
+        fence_mbar_init();
+    }
+    if (warp == AT2_SW + 1) {
+        tmem_alloc(tmem_slot, 512);// S (and P) of group 0 / 1, O of group 0 / 1
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == AT2_SW) {
+        if (lane == 0) {
+            uint32_t t = 0, done = 0;// t: key tiles over all items of this CTA (stage t & 1, phase (t >> 1) & 1)
+            for (uint32_t band = 0; band * gridDim.x < n_items && !*failed; ++band) {
+                const uint32_t i = at_item_of(band, n_items);
+                if (i >= n_items) continue;
+                const At2Item w = at2_item(a, qp_tiles, i);
+                if (w.nt == 0) continue;
+                if (done && !mbar_wait(q_empty, (done - 1) & 1u)) {// the previous item's last S products have read Q
+                    *failed = 1;
+                    break;
+                }
+                mbar_arrive_expect_tx(q_full, 2 * AT_TILE_BYTES);
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    tma_load_4d(sQ + g * AT_TILE_BYTES, &map_q, 0, w.q0 + g * AT_BM, w.h, w.n, q_full);
+                    tma_load_4d(sQ + g * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_q, 64, w.q0 + g * AT_BM, w.h, w.n, q_full);
+                }
+                for (uint32_t j = 0; j < w.nt; ++j, ++t) {
+                    const uint32_t s = t & 1u, ph = (t >> 1) & 1u;
+                    if (!mbar_wait(&k_empty[s], ph ^ 1u)) {
+                        *failed = 1;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&k_full[s], AT_TILE_BYTES);
+                    tma_load_4d(sK + s * AT_TILE_BYTES, &map_k, 0, j * AT_BN, w.kvh, w.n, &k_full[s]);
+                    tma_load_4d(sK + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_k, 64, j * AT_BN, w.kvh, w.n, &k_full[s]);
+                    if (!mbar_wait(&v_empty[s], ph ^ 1u)) {
+                        *failed = 1;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&v_full[s], AT_TILE_BYTES);
+                    tma_load_4d(sV + s * AT_TILE_BYTES, &map_v, 0, j * AT_BN, w.kvh, w.n, &v_full[s]);
+                    tma_load_4d(sV + s * AT_TILE_BYTES + AT_TILE_BYTES / 2, &map_v, 64, j * AT_BN, w.kvh, w.n, &v_full[s]);
+                }
+                ++done;
+            }
+        }
+    } else if (warp == AT2_SW + 1) {
+        if (lane == 0) {
+            const uint32_t idesc_s = instr_desc(a.is_bf16, AT_BM, AT_BN);
+            const uint32_t idesc_o = instr_desc(a.is_bf16, AT_BM, AT_D) | (1u << 16);// B (= V) is MN-major
+            bool ok = true;
+            uint32_t t = 0, done = 0;
+            uint32_t u[2] = {0, 0}; // tiles group 0 / 1 has been given so far: phases of s_full, p_full and o_full follow them
+            uint32_t ig[2] = {0, 0};// items in which group 0 / 1 had tiles: phases of o_free
+            // S_g = Q_g K^T of the key tile in stage s; the group's score columns are free: it has read them (p_full) and its P V, which
+            // took P from them, was issued before
+            auto issue_s = [&](uint32_t g, uint32_t s) {
+                const uint32_t q_addr = smem_u32(sQ + g * AT_TILE_BYTES), k_addr = smem_u32(sK + s * AT_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = (kk >> 2) * (AT_TILE_BYTES / 2) + (kk & 3) * 32;
+                    tc_mma_f16(tmem_base + g * AT_BN, smem_desc_sw128(q_addr + off), smem_desc_sw128(k_addr + off), idesc_s, kk ? 1u : 0u);
+                }
+                tc_commit(&s_full[g]);
+            };
+            for (uint32_t band = 0; ok && band * gridDim.x < n_items; ++band) {
+                const uint32_t i = at_item_of(band, n_items);
+                if (i >= n_items) continue;
+                const At2Item w = at2_item(a, qp_tiles, i);
+                if (w.nt == 0) continue;
+                ok = mbar_wait(q_full, done & 1u) && mbar_wait(&k_full[t & 1u], (t >> 1) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                for (uint32_t g = 0; g < 2; ++g)
+                    if (w.ntiles[g]) issue_s(g, t & 1u);
+                tc_commit(&k_empty[t & 1u]);
+                if (w.nt == 1) tc_commit(q_empty);// the item's last S products: Q may be replaced once they have run
+                for (uint32_t j = 0; ok && j < w.nt; ++j, ++t) {
+                    const uint32_t s = t & 1u, ph = (t >> 1) & 1u;
+                    const bool next = j + 1 < w.nt;
+                    if (!mbar_wait(&v_full[s], ph) || (next && !mbar_wait(&k_full[s ^ 1u], ((t + 1) >> 1) & 1u))) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t v_addr = smem_u32(sV + s * AT_TILE_BYTES);
+                    // group by group: its P V of this tile, then its scores of the next one, so that one group's softmax runs under the
+                    // other group's products
+                    for (uint32_t g = 0; ok && g < 2; ++g) {
+                        if (j < w.ntiles[g]) {
+                            // O_g (+)= P V once the group has written P (and rescaled O where it moved its maximum); the item's first
+                            // tile overwrites O_g, which the group must have read out for its previous item
+                            if (!mbar_wait(&p_full[g], u[g] & 1u) || (j == 0 && ig[g] && !mbar_wait(&o_free[g], (ig[g] - 1) & 1u))) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk) {
+                                // A = P from tensor memory: keys 16 kk .. 16 kk + 15 of every row are 8 columns of 32 bits; keys 0-63 lie
+                                // in columns 0-31 of the group's scores, keys 64-127 in columns 64-95 (each over scores its writer has read)
+                                const uint64_t bd = smem_desc_sw128_ex(v_addr + kk * 2048, a.v_lbo, a.v_sbo);
+                                tc_mma_f16_ts(tmem_base + (2 + g) * AT_BN, tmem_base + g * AT_BN + (kk >> 2) * 64 + (kk & 3) * 8, bd, idesc_o,
+                                              (kk || j) ? 1u : 0u);
+                            }
+                            tc_commit(&o_full[g]);
+                            ++u[g];
+                            if (j == 0) ++ig[g];
+                        }
+                        if (next && j + 1 < w.ntiles[g]) issue_s(g, s ^ 1u);
+                    }
+                    if (!ok) break;
+                    tc_commit(&v_empty[s]);
+                    if (next) {
+                        tc_commit(&k_empty[s ^ 1u]);
+                        if (j + 2 == w.nt) tc_commit(q_empty);
+                    }
+                }
+                ++done;
+            }
+            if (!ok) *failed = 2;
+        }
+    } else {
+        // ---- softmax warps: group g = warp / 8 owns query rows 128 g .. 128 g + 127 of the item; two threads per row: lane quarter =
+        // warp % 4, column half = (warp / 4) % 2 (64 key columns of the scores, 64 d columns of O) ----
+        const uint32_t g = warp >> 3, quarter = warp & 3u, half = (warp >> 2) & 1u, row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32u) << 16, col0 = half * 64u;
+        const uint32_t s_addr = tmem_base + g * AT_BN + lane_addr + col0, o_addr = tmem_base + (2 + g) * AT_BN + lane_addr + col0;
+        const uint32_t pair_bar = 1u + g * 4u + quarter;// the 64 threads that own these 32 rows
+        const float c = a.scale_log2e, thr = 8.0f / c;
+        float *xr = xch + g * 256;// [2 halves][128 rows]
+        uint8_t *stage = sO + g * AT2_STAGE_BYTES;
+        bool ok = true;
+        uint32_t u = 0;// key tiles this group has worked on, over all items
+        for (uint32_t band = 0; band * gridDim.x < n_items; ++band) {
+            const uint32_t item = at_item_of(band, n_items);
+            if (item >= n_items) continue;
+            const At2Item w = at2_item(a, qp_tiles, item);
+            const uint32_t ntiles = w.ntiles[g];
+            if (ntiles == 0) continue;
+            const uint32_t q0 = w.q0 + g * AT_BM, qrow = q0 + row;
+            float m_used = -INFINITY, l_run = 0.f;
+            bool stop = false;
+            const uint32_t lim = qrow + 1 < a.kv_len ? qrow + 1 : a.kv_len;// first key this row may NOT see
+            const uint32_t warp_lim = q0 + quarter * 32 + 1 < a.kv_len ? q0 + quarter * 32 + 1 : a.kv_len;// smallest lim in the warp
+            for (uint32_t j = 0; j < ntiles; ++j, ++u) {
+                const uint32_t key0 = j * AT_BN + col0;
+                if (ok && !at_warp_wait(&s_full[g], u & 1u)) ok = false, *failed = 3;
+                tc_fence_after();
+                const bool masked = key0 + 64 > warp_lim;// warp-uniform: only the diagonal tile and the sequence's last one
+                // pass 1: maximum of this thread's 64 scores, then of the row
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(s_addr + c0, r);
+                    tmem_ld_wait();
+                    if (masked) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, key0 + c0 + e < lim ? __uint_as_float(r[e]) : -INFINITY);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
+                    }
+                }
+                // The partner read this slot for the previous tile before it arrived on p_full, and these scores exist only because
+                // that arrival let the tensor core go on: one slot is enough.
+                xr[half * 128 + row] = mx;
+                if (at_pair_sync_or(pair_bar, *failed != 0)) {// the two warps of these rows, leaving together
+                    stop = true;
+                    break;
+                }
+                mx = fmaxf(mx, xr[(half ^ 1u) * 128 + row]);
+                // Move the reference maximum only when some row of the warp needs it (both warps of a row see the same maxima).  O is
+                // rescaled where it lies, every thread its 64 columns: the group's previous P V has run (these scores were issued
+                // behind it).
+                if (__any_sync(0xffffffffu, mx > m_used + thr)) {
+                    const float m_new = fmaxf(m_used, mx);
+                    const float alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * c);
+                    if (j) {
+#pragma unroll 1
+                        for (int c0 = 0; c0 < 64; c0 += 32) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(o_addr + c0, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+                            tmem_st_32x32(o_addr + c0, r);
+                        }
+                    }
+                    l_run *= alpha;
+                    m_used = m_new;
+                }
+                // pass 2: p = 2^((s - m) * scale) as 16-bit, two keys per 32-bit column, over the first 32 columns of this thread's scores
+                const float mneg = (m_used == -INFINITY) ? 0.f : -m_used * c;
+                float lsum = 0.f;
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(s_addr + c0, r);
+                    tmem_ld_wait();
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        float p0, p1;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(r[e]), c, mneg)));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(r[e + 1]), c, mneg)));
+                        if (masked) {
+                            if (key0 + c0 + e >= lim) p0 = 0.f;
+                            if (key0 + c0 + e + 1 >= lim) p1 = 0.f;
+                        }
+                        lsum += p0 + p1;
+                        packed[e / 2] = at_pack2<T>(p0, p1);
+                    }
+                    // columns [c0 / 2, c0 / 2 + 16) of this thread's 64: all inside what it has read so far
+                    tmem_st_32x16(s_addr + c0 / 2, packed);
+                }
+                l_run += lsum;
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[g]);
+            }
+            // the group's last product of the item
+            if (!stop && ok && !at_warp_wait(&o_full[g], (u - 1) & 1u)) ok = false, *failed = 3;
+            // the row's denominator is the sum of its two threads' partial sums; the group agrees on whether to go on
+            xr[half * 128 + row] = l_run;
+            if (at2_group_sync_or(g, stop || !ok || *failed != 0)) break;
+            const float l_tot = l_run + xr[(half ^ 1u) * 128 + row];
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            // Output: half by half (d columns 0-63, then 64-127) through the group's staging buffer, whole 128-byte half rows per store.
+            // Each thread owns 64 d columns of its row = one 128-byte line of the round its half takes part in.
+            tc_fence_after();
+            T *base = static_cast<T *>(a.o) + w.n * a.o_sn + w.h * a.o_sh;
+            const uint32_t tid_g = (warp & 7u) * 32 + lane;
+#pragma unroll 1
+            for (uint32_t round = 0; round < 2; ++round) {
+                if (half == round) {
+#pragma unroll
+                    for (int c0 = 0; c0 < 64; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(o_addr + c0, r);
+                        tmem_ld_wait();
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int e = 0; e < 32; e += 2) packed[e / 2] = at_pack2<T>(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t chunk = (c0 >> 3) + q;
+                            *reinterpret_cast<uint4 *>(stage + row * 128u + ((chunk ^ (row & 7u)) << 4)) =
+                                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                        }
+                    }
+                    tc_fence_before();
+                }
+                asm volatile("bar.sync %0, 256;" ::"r"(10u + g) : "memory");
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t idx = i * 256u + tid_g, r = idx >> 3, ch = idx & 7u;
+                    const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * 128u + ((ch ^ (r & 7u)) << 4));
+                    if (q0 + r < a.S) *reinterpret_cast<uint4 *>(base + static_cast<int64_t>(q0 + r) * a.o_st + round * 64 + ch * 8u) = v;
+                }
+                asm volatile("bar.sync %0, 256;" ::"r"(10u + g) : "memory");
+            }
+            // O_g has been read out (the barriers above order every thread's loads before this): the next item may overwrite it
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free[g]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == AT2_SW + 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *failed) atomicExch(&s_attn_tc_error, *failed);
+}
+
 int attn_tc_error_word(bool clear) { return error_symbol(s_attn_tc_error, clear); }
 
 // (64 columns of d, tokens, heads, sequences) with the caller's element strides; box = 64 x 128 tokens, 128-byte swizzle
@@ -509,11 +868,29 @@ int attn_prefill_tc_launch(const rg_attn_prefill_params *p, const void *const *i
     a.v_lbo = lbo, a.v_sbo = sbo;
     const size_t smem = 7 * AT_TILE_BYTES + 20 * 8 + 2 * 256 * 4;
     a.q_tiles = (p->seq_len + AT_BM - 1) / AT_BM, a.batch = p->batch;
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    // the kernel with two query tiles per CTA (171.7 us = 801 TFLOP/s on [4, 32, 2048, 128] bf16 against 215 us = 639 for the kernel
+    // with one, same box); RG_B200_ATTN_Q2=0 keeps the latter
+    static const bool q2 = !(std::getenv("RG_B200_ATTN_Q2") && std::getenv("RG_B200_ATTN_Q2")[0] == '0');
+    if (q2) {
+        const size_t smem2 = 6 * AT_TILE_BYTES + 2 * AT2_STAGE_BYTES + 20 * 8 + 2048;
+        const uint64_t items2 = static_cast<uint64_t>((p->seq_len + 2 * AT_BM - 1) / (2 * AT_BM)) * p->n_heads * p->batch;
+        if (items2 > 0xffffffffull) return RG_ERR_SHAPE;
+        dim3 grid2(static_cast<unsigned>(items2 < sms ? items2 : sms));
+        if (is_bf16) {
+            RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_q2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+            RG_CHECK_CUDA(launch_pdl(attn_prefill_q2_kernel<__nv_bfloat16>, grid2, dim3(AT2_THREADS), smem2, st, mq, mk, mv, a));
+        } else {
+            RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_q2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+            RG_CHECK_CUDA(launch_pdl(attn_prefill_q2_kernel<__half>, grid2, dim3(AT2_THREADS), smem2, st, mq, mk, mv, a));
+        }
+        count_launch();
+        return RG_OK;
+    }
     // persistent CTAs, one per SM (the shared memory of a CTA fills the SM): the next item's Q, K and V are fetched while the
     // softmax warps finish the current one, and tensor memory and barriers are set up once
     const uint64_t items = static_cast<uint64_t>(a.q_tiles) * p->n_heads * p->batch;
     if (items > 0xffffffffull) return RG_ERR_SHAPE;
-    const uint32_t sms = static_cast<uint32_t>(sm_count());
     dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
     if (is_bf16) {
         RG_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
