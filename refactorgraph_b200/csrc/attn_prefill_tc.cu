@@ -1,4 +1,6 @@
 // Causal flash attention for prefill on the fifth-generation tensor cores (head_dim 128, fp16 / bf16).
+// Two kernels: attn_prefill_q2_kernel (further down; two query tiles per CTA, the default) and attn_prefill_tc_kernel (one query tile
+// per CTA, RG_B200_ATTN_Q2=0), described first because the second builds on what was measured on it.
 // Semantics: src/08-01llm/README.md:29-63 (causal multi-head self-attention, query head h uses KV head h / (heads / kv_heads),
 // scores scaled by 1/sqrt(head_dim), softmax and accumulation in fp32).
 //
