@@ -469,6 +469,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_prefill_tc_kernel(const __
 // from tensor memory (P never crosses shared memory) and O_g accumulated in tensor memory (columns 256 + 128 g ..), rescaled in
 // place only when the group's reference maximum moves.  Per group the chain is serial (S, softmax, P V, next S: the next scores
 // overwrite P), the two groups overlap each other.  No exchange between the groups; each thread finishes its own half row.
+// Measured on [4, 32, 2048, 128] bf16: 166-172 us = 801-828 TFLOP/s.  With parts of the softmax left out (results wrong, timing only): no
+// exponentials 173 us, no maximum pass 164, no exponential pass 139, no softmax at all 135.5: the products and the K / V stream are
+// still four fifths of the time.  Per key tile a CTA moves 256 KiB through shared memory (Q and K for two S products, V for two P V
+// products, the TMA writes of K and V) = 2048 cycles of its 128 bytes per clock, as long as the four products take at peak rate.
 constexpr int AT2_SW = 16, AT2_THREADS = (AT2_SW + 2) * 32;
 constexpr uint32_t AT2_STAGE_BYTES = 16384;// per group: 128 rows x 64 d columns of 16-bit output
 
