@@ -878,7 +878,7 @@ int attn_prefill_tc_launch(const rg_attn_prefill_params *p, const void *const *i
     // the kernel with two query tiles per CTA (171.7 us = 801 TFLOP/s on [4, 32, 2048, 128] bf16 against 215 us = 639 for the kernel
     // with one, same box); RG_B200_ATTN_Q2=0 keeps the latter
     static const bool q2 = !(std::getenv("RG_B200_ATTN_Q2") && std::getenv("RG_B200_ATTN_Q2")[0] == '0');
-    if (q2) {
+    if (q2 && kv_len > 0) {// (no keys at all: the other kernel writes the zero rows)
         const size_t smem2 = 6 * AT_TILE_BYTES + 2 * AT2_STAGE_BYTES + 20 * 8 + 2048;
         const uint64_t items2 = static_cast<uint64_t>((p->seq_len + 2 * AT_BM - 1) / (2 * AT_BM)) * p->n_heads * p->batch;
         if (items2 > 0xffffffffull) return RG_ERR_SHAPE;
