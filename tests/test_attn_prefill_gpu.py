@@ -76,3 +76,33 @@ def test_prefill_size_against_fp32_formula():
     want = torch.einsum("nhij,nhjd->nhid", torch.softmax(s, dim=-1), v.float())
     torch.testing.assert_close(o.float(), want, atol=2e-2, rtol=1e-2)
     assert torch.equal(o[:, :, 0], v[:, :, 0])
+
+
+def test_one_query_tile_kernel_in_a_child_process():
+    """RG_B200_ATTN_Q2=0 selects the kernel with one query tile per CTA (read once per process, hence the child): the same
+    ragged grouped-query case against the oracle, and bit-for-bit the same output twice."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+sys.path.insert(0, sys.argv[2])
+from oracle import oracle_np as onp
+import _ops as ops
+rng = np.random.default_rng(3)
+N, nH, nKV, S, D = 2, 8, 2, 300, 128
+r = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float32)).to(torch.bfloat16).float().numpy()
+q, k, v = r(N, nH, S, D), r(N, nKV, S, D), r(N, nKV, S, D)
+o = ops.attention(ops.dev(q, torch.bfloat16), ops.dev(k, torch.bfloat16), ops.dev(v, torch.bfloat16))
+o2 = ops.attention(ops.dev(q, torch.bfloat16), ops.dev(k, torch.bfloat16), ops.dev(v, torch.bfloat16))
+want, _, _ = onp.attention(q, k, v)
+np.testing.assert_allclose(o.float().cpu().numpy(), want, atol=2e-2, rtol=1e-2)
+assert torch.equal(o, o2)
+print("child ok")
+"""
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, RG_B200_ATTN_Q2="0")
+    r = subprocess.run([sys.executable, "-c", code, os.path.dirname(here), here], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=600)
+    assert r.returncode == 0 and "child ok" in r.stdout, r.stdout[-2000:]
