@@ -372,6 +372,43 @@ def time_linear_kernel(ex, index, cfg, torch, stream, reps=3):
             "avg_launch_us": 1000.0 * ms / len(calls), "gbs": bytes_total / (ms * 1e-3) / 1e9}
 
 
+def time_paged_attention(cfg, lens_h, torch, stream, launches=20):
+    """The attention launch of the paged batch workload alone (the kernel with the largest share of that step): the workload's
+    own sequence lengths, 16-token pages in a shuffled block table, two cache pairs in rotation (each larger than L2)."""
+    from refactorgraph_b200 import capi
+    B, nH, D, page = cfg.batch, cfg.heads, cfg.head_dim, 16
+    MS = 4096 + 128
+    max_blocks = MS // page
+    n_blocks = B * max_blocks
+    dev = "cuda"
+    table = torch.from_numpy(np.random.default_rng(1).permutation(n_blocks).reshape(B, max_blocks).astype(np.int32)).to(dev)
+    q = torch.randn(B, nH, D, device=dev).to(torch.float16)
+    caches = [(torch.randn(n_blocks, cfg.kv_heads, page, D, device=dev).to(torch.float16),
+               torch.randn(n_blocks, cfg.kv_heads, page, D, device=dev).to(torch.float16)) for _ in range(2)]
+    lens = torch.from_numpy(np.asarray(lens_h, dtype=np.int64)).to(dev)
+    o = torch.empty_like(q)
+    p = capi.AttnDecodeParams(capi.FP16, B, nH, MS, capi.KvLayout(cfg.kv_heads, D, MS, page, max_blocks))
+    wsb = torch.zeros(capi.workspace("attn_decode", p), dtype=torch.uint8, device=dev)
+    bytes_per = 2 * cfg.kv_heads * int(np.asarray(lens_h).sum()) * D * 2
+    sid = stream.cuda_stream
+
+    def launch(i):
+        kc, vc = caches[i % 2]
+        capi.call("attn_decode", p, [q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), table.data_ptr()], [o.data_ptr()],
+                  ws=wsb.data_ptr(), stream=sid)
+    for i in range(3):
+        launch(i)
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(launches):
+        launch(i)
+    e1.record(stream)
+    stream.synchronize()
+    ms = e0.elapsed_time(e1) / launches
+    return {"launches": launches, "avg_launch_us": 1000.0 * ms, "bytes_per_launch": bytes_per, "gbs": bytes_per / (ms * 1e-3) / 1e9}
+
+
 def run_decode_step_timeline():
     """Per-phase timeline of the single-kernel decode step at the 7B shape (KV 2048), read back from the kernel's own
     %globaltimer stamps (rg_b200_decode_step_timeline)."""
@@ -1043,6 +1080,7 @@ def measure_decode(args, torch, dist, lib, rank, world, local, workload, steps, 
     lin = None
     if rank == 0:
         lin = time_linear_kernel(ex, index, cfg, torch, stream) if workload in ("7b", "tiny", "7b-4l") else time_skinny_gemm(ex, index, cfg, torch, stream)
+        att = time_paged_attention(cfg, state["lens0"], torch, stream) if workload == "7b-b32" else None
     comm_ok = comm.status() == capi.OK if comm is not None else True
     err_state = lib.rg_b200_error_state()
     del ex
@@ -1078,6 +1116,12 @@ def measure_decode(args, torch, dist, lib, rank, world, local, workload, steps, 
     elif workload == "7b":
         ratio = ncu_traffic_ratio("linear_gate_up")
         roof["traffic"] = ratio * roof["algorithmic_bytes_per_launch"] if ratio else None
+    elif workload == "7b-b32" and att is not None:
+        # attention over the paged cache has the largest share of this step (54 % in the ncu launch list); the products come second
+        roof = {"bound": "hbm", "achieved": att["gbs"], "peak": peak, "unit": "GB/s", "frac": att["gbs"] / peak, "traffic": None,
+                "kernel": "attn_decode_mma_kernel (flash-decoding over the paged cache)", "peak_source": peak_kind + " HBM copy bandwidth",
+                "avg_launch_us": att["avg_launch_us"], "launches_timed": att["launches"], "algorithmic_bytes_per_launch": att["bytes_per_launch"],
+                "second_kernel": roof}
     line = {
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
